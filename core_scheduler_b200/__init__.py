@@ -1,0 +1,53 @@
+"""core_scheduler_b200: a B200-native training framework with the capabilities of CoreScheduler.
+
+The runtime (future-tensor handles, the three-stream task scheduler, ops, modules, optimizers,
+collectives, data loaders, checkpoints, GPT-2) is C++/CUDA in ``csrc/``; this package loads the
+in-tree build and exposes it. ``core_scheduler_b200._C`` is the pybind11 module; the
+sub-packages add configuration presets and process launch helpers only.
+"""
+from __future__ import annotations
+
+import os as _os
+
+import torch as _torch  # noqa: F401  (libtorch must be loaded before the extension)
+
+from . import build as _build
+
+if not _build.is_built():
+    if _os.environ.get("CS_NO_AUTOBUILD") == "1":
+        raise ImportError("core_scheduler_b200 native library is not built; run `python -m core_scheduler_b200.build`")
+    _build.build()
+
+import pyarrow as _pyarrow  # noqa: F401,E402  (provides libarrow/libparquet for checkpoints and datasets)
+
+from . import _C  # noqa: E402
+from ._C import (  # noqa: E402,F401
+    AdamW,
+    AllReduceBucket,
+    DynamicScheduler,
+    Error,
+    GPT2,
+    GPT2Config,
+    GradientSync,
+    Tensor,
+    autocast,
+    from_torch,
+    manual_seed,
+    to_torch,
+)
+
+__all__ = [
+    "_C",
+    "AdamW",
+    "AllReduceBucket",
+    "DynamicScheduler",
+    "Error",
+    "GPT2",
+    "GPT2Config",
+    "GradientSync",
+    "Tensor",
+    "autocast",
+    "from_torch",
+    "manual_seed",
+    "to_torch",
+]

@@ -1,0 +1,175 @@
+"""In-tree build of the native runtime.
+
+Produces, next to this file:
+  lib/libcs_b200.so   C++ framework + sm_100a kernels (what C++ programs link against)
+  _C.<abi>.so         pybind11 bindings over the same library
+
+CUDA sources are compiled by nvcc for sm_100a only (-gencode arch=compute_100a,code=sm_100a);
+they include no torch headers, so they build in seconds. C++ sources are compiled by g++
+against the libtorch headers of the running interpreter. A ninja file is generated and run,
+so rebuilds are incremental.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+CSRC = HERE / "csrc"
+BUILD = HERE / "build"
+LIBDIR = HERE / "lib"
+
+CPP_SOURCES = [
+    "src/core.cpp",
+    "src/compute_ops.cpp",
+    "src/attention_utils.cpp",
+    "src/optimizer.cpp",
+    "src/module.cpp",
+    "src/modules.cpp",
+    "src/parquet_io.cpp",
+    "src/communication.cpp",
+    "src/comm_nccl.cpp",
+    "src/symmetric.cpp",
+    "src/data.cpp",
+    "src/models_gpt2.cpp",
+]
+CUDA_SOURCES = [
+    "kernels/elementwise.cu",
+    "kernels/gemm_tcgen05.cu",
+]
+BINDING_SOURCES = ["python/bindings.cpp"]
+
+
+def _optional_sources():
+    extra_cpp, extra_cu = [], []
+    for name in ("src/parallel.cpp",):
+        if (CSRC / name).exists():
+            extra_cpp.append(name)
+    for name in ("kernels/attention_tcgen05.cu", "kernels/collectives.cu", "kernels/no_alloc.cu"):
+        if (CSRC / name).exists():
+            extra_cu.append(name)
+    return extra_cpp, extra_cu
+
+
+def _paths():
+    import torch
+    import pyarrow
+
+    torch_dir = Path(torch.__file__).resolve().parent
+    site = torch_dir.parent
+    nccl_inc = site / "nvidia" / "nccl" / "include"
+    cuda_home = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+    return {
+        "torch_inc": [torch_dir / "include", torch_dir / "include" / "torch" / "csrc" / "api" / "include"],
+        "torch_lib": torch_dir / "lib",
+        "arrow_inc": Path(pyarrow.get_include()),
+        "arrow_lib": Path(pyarrow.get_library_dirs()[0]),
+        "nccl_inc": nccl_inc if nccl_inc.exists() else Path("/usr/include"),
+        "cuda_home": cuda_home,
+        "py_inc": Path(sysconfig.get_paths()["include"]),
+        "pybind_flags": [
+            f'-DPYBIND11_COMPILER_TYPE=\\"{getattr(torch._C, "_PYBIND11_COMPILER_TYPE", "_gcc")}\\"',
+            f'-DPYBIND11_STDLIB=\\"{getattr(torch._C, "_PYBIND11_STDLIB", "_libstdcpp")}\\"',
+            f'-DPYBIND11_BUILD_ABI=\\"{getattr(torch._C, "_PYBIND11_BUILD_ABI", "_cxxabi1018")}\\"',
+        ],
+        "cxx11_abi": int(torch._C._GLIBCXX_USE_CXX11_ABI),
+    }
+
+
+def ext_suffix() -> str:
+    return sysconfig.get_config_var("EXT_SUFFIX")
+
+
+def generate_ninja() -> Path:
+    p = _paths()
+    BUILD.mkdir(exist_ok=True)
+    LIBDIR.mkdir(exist_ok=True)
+    extra_cpp, extra_cu = _optional_sources()
+    inc = [CSRC / "include", CSRC, CSRC / "src"] + p["torch_inc"] + [p["cuda_home"] / "include"]
+    cxxflags = [
+        "-std=c++20", "-O2", "-fPIC", "-Wall", "-Wno-unused-function", "-Wno-interference-size",
+        "-Wno-sign-compare", "-Wno-unused-local-typedefs", "-Wno-deprecated-declarations",
+        f"-D_GLIBCXX_USE_CXX11_ABI={p['cxx11_abi']}", "-DUSE_C10D_NCCL", "-DUSE_DISTRIBUTED", "-DUSE_RPC", "-DUSE_CUDA",
+    ] + [f"-I{i}" for i in inc]
+    nvccflags = [
+        "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
+        "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", f"-I{CSRC}", f"-I{CSRC / 'kernels'}",
+    ]
+    lines = [
+        "ninja_required_version = 1.5",
+        f"cxx = {os.environ.get('CS_CXX', 'g++')}",
+        f"nvcc = {p['cuda_home'] / 'bin' / 'nvcc'}",
+        f"cxxflags = {' '.join(cxxflags)}",
+        f"nvccflags = {' '.join(nvccflags)}",
+        "rule cxx",
+        "  command = $cxx -MMD -MF $out.d $cxxflags $extra -c $in -o $out",
+        "  depfile = $out.d",
+        "  deps = gcc",
+        "rule nvcc",
+        "  command = $nvcc $nvccflags -MD -MF $out.d -c $in -o $out",
+        "  depfile = $out.d",
+        "  deps = gcc",
+        "rule link",
+        "  command = $cxx -shared $in -o $out $ldflags",
+    ]
+    objs = []
+    for src in CPP_SOURCES + extra_cpp:
+        obj = BUILD / (src.replace("/", "_") + ".o")
+        extra = ""
+        if src.endswith("parquet_io.cpp"):
+            extra = f"-I{p['arrow_inc']}"
+        if src.endswith("comm_nccl.cpp"):
+            extra = f"-I{p['nccl_inc']}"
+        lines += [f"build {obj}: cxx {CSRC / src}", f"  extra = {extra}"]
+        objs.append(obj)
+    for src in CUDA_SOURCES + extra_cu:
+        obj = BUILD / (src.replace("/", "_") + ".o")
+        lines += [f"build {obj}: nvcc {CSRC / src}"]
+        objs.append(obj)
+    cuda_lib = p["cuda_home"] / "lib64"
+    lib_ld = [
+        f"-L{p['torch_lib']}", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",
+        f"-L{p['arrow_lib']}", "-l:libarrow.so.2400", "-l:libparquet.so.2400",
+        f"-L{cuda_lib}", "-lcudart", "-ldl", "-lpthread",
+        f"-Wl,-rpath,{p['torch_lib']}", f"-Wl,-rpath,{p['arrow_lib']}", f"-Wl,-rpath,{cuda_lib}",
+        "-Wl,--no-as-needed",
+    ]
+    libcs = LIBDIR / "libcs_b200.so"
+    lines += [f"build {libcs}: link {' '.join(map(str, objs))}", f"  ldflags = {' '.join(lib_ld)}"]
+    bobjs = []
+    for src in BINDING_SOURCES:
+        obj = BUILD / (src.replace("/", "_") + ".o")
+        lines += [f"build {obj}: cxx {CSRC / src}", f"  extra = -I{p['py_inc']} {' '.join(p['pybind_flags'])} -DTORCH_EXTENSION_NAME=_C -DTORCH_API_INCLUDE_EXTENSION_H"]
+        bobjs.append(obj)
+    ext = HERE / f"_C{ext_suffix()}"
+    ext_ld = [
+        f"-L{LIBDIR}", "-lcs_b200", f"-L{p['torch_lib']}", "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10",
+        "-Wl,-rpath,'$$ORIGIN/lib'", f"-Wl,-rpath,{p['torch_lib']}",
+    ]
+    lines += [f"build {ext}: link {' '.join(map(str, bobjs))} | {libcs}", f"  ldflags = {' '.join(ext_ld)}"]
+    lines += [f"default {ext}"]
+    ninja_file = BUILD / "build.ninja"
+    ninja_file.write_text("\n".join(lines) + "\n")
+    return ninja_file
+
+
+def build(verbose: bool = False) -> None:
+    ninja_file = generate_ninja()
+    cmd = [sys.executable, "-m", "ninja", "-f", str(ninja_file)]
+    if verbose:
+        cmd.append("-v")
+    jobs = os.environ.get("CS_BUILD_JOBS")
+    if jobs:
+        cmd += ["-j", jobs]
+    subprocess.run(cmd, check=True, cwd=str(BUILD))
+
+
+def is_built() -> bool:
+    return (HERE / f"_C{ext_suffix()}").exists() and (LIBDIR / "libcs_b200.so").exists()
+
+
+if __name__ == "__main__":
+    build(verbose="-v" in sys.argv)

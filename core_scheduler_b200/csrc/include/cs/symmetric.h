@@ -1,0 +1,69 @@
+// Peer-mapped ("symmetric") device memory for the ranks of one NVSwitch domain, a caching
+// sub-allocator on top of it, and the collectives / fused paths that run as this library's
+// own kernels over peer pointers.
+//
+// The reference declares an NVLink peer-to-peer backend (BackendType::kNVP2P,
+// include/communication/communication.h:51 of the reference project) without implementing it;
+// this is that backend. Every rank allocates one arena with cudaMalloc, exports it with CUDA
+// IPC through the communicator's store and maps every peer's arena, so a kernel on rank r can
+// load/store rank p's buffer at the same offset. Waits on peer flags are bounded: a kernel that
+// gives up records a status word that the host turns into cs::Error.
+#pragma once
+#include "cs/communication.h"
+
+namespace cs::communication {
+struct SymmetricBlock {
+  int64_t offset{0};  // bytes from the arena base, identical on every rank
+  int64_t bytes{0};
+};
+
+struct CS_API SymmetricContext {
+  int rank{0};
+  int size{1};
+  int device{0};
+  int64_t arena_bytes{0};
+  std::vector<char *> bases;       // bases[p]: rank p's arena as mapped into this process
+  std::vector<uint32_t *> flags;   // flags[p]: rank p's signal pad (kFlagWords words)
+  char **device_bases{nullptr};    // the same pointers in device memory (for kernels)
+  uint32_t **device_flags{nullptr};
+  void *status{nullptr};           // kernels::DeviceStatus in device memory
+  uint32_t epoch{0};               // monotonically increasing barrier/flag generation
+  static constexpr int kFlagWords = 4096;
+
+  // Caching sub-allocator. Blocks are handed out in the same order on every rank, so equal
+  // call sequences yield equal offsets (the symmetric-address property kernels rely on).
+  SymmetricBlock allocate(int64_t bytes);
+  void release(const SymmetricBlock &block);
+  [[nodiscard]] int64_t bytes_in_use() const { return in_use_; }
+  [[nodiscard]] int64_t cached_blocks() const { return static_cast<int64_t>(free_.size()); }
+  // A tensor view over a block of this rank's arena (storage is not owned by the tensor).
+  [[nodiscard]] at::Tensor tensor(const SymmetricBlock &block, at::IntArrayRef sizes, at::ScalarType dtype) const;
+  // True when [ptr, ptr+bytes) lies inside this rank's arena; *offset receives the position.
+  bool locate(const void *ptr, int64_t bytes, int64_t *offset) const;
+  ~SymmetricContext();
+
+ private:
+  friend std::shared_ptr<SymmetricContext> create_symmetric_context(const Comm &, int64_t);
+  int64_t bump_{0};
+  int64_t in_use_{0};
+  std::vector<SymmetricBlock> free_;
+  bool owns_{false};
+};
+
+// Collective: every rank of `comm` must call it with the same size. Attaches the context to
+// the communicator (comm.impl()->symmetric).
+CS_API std::shared_ptr<SymmetricContext> create_symmetric_context(const Comm &comm, int64_t arena_bytes);
+
+// The collectives below run on the current stream; they return false when the tensors are
+// not eligible (the caller then uses the library path).
+CS_API bool symmetric_all_reduce(SymmetricContext &ctx, const std::vector<at::Tensor> &tensors, Operation op);
+CS_API bool symmetric_all_gather(SymmetricContext &ctx, const std::vector<std::vector<at::Tensor>> &recv,
+                                 const std::vector<at::Tensor> &send);
+CS_API bool symmetric_reduce_scatter(SymmetricContext &ctx, const std::vector<at::Tensor> &recv,
+                                     const std::vector<std::vector<at::Tensor>> &send, Operation op);
+CS_API bool symmetric_all_to_all(SymmetricContext &ctx, const std::vector<at::Tensor> &recv,
+                                 const std::vector<at::Tensor> &send);
+// Reads (and clears) the device status word; raises cs::Error when a kernel reported a
+// timed-out wait.
+CS_API void check_device_status(SymmetricContext &ctx, const char *where);
+}  // namespace cs::communication

@@ -1,0 +1,117 @@
+"""Scheduler semantics: stream classes, ordering across streams, re-join of side tasks, errors."""
+import pytest
+import torch
+
+import core_scheduler_b200 as cs
+
+C = cs._C
+
+
+def test_cpu_scheduler_runs_tasks_inline_and_tags_outputs(cpu_scheduler):
+    s = cpu_scheduler
+    out = cs.Tensor()
+    seen = []
+    s.submit_python("t0", 1, [out], [], lambda: (seen.append(1), out.set_raw(torch.ones(3)))[0])
+    assert seen == [1]
+    assert out.stream_class() == 1
+    assert s.submitted()[1] == 1
+
+
+def test_task_failure_carries_task_name(cpu_scheduler):
+    def boom():
+        raise ValueError("bad thing")
+
+    with pytest.raises(RuntimeError) as e:
+        cpu_scheduler.submit_python("my_failing_task", 0, [], [], boom)
+    assert "my_failing_task" in str(e.value)
+
+
+def test_autocast_guard_sets_and_restores(cpu_scheduler):
+    s = cpu_scheduler
+    assert not s.autocast_enabled()
+    with cs.autocast(s, torch.bfloat16):
+        assert s.autocast_enabled()
+    assert not s.autocast_enabled()
+    assert s.submitted()[3] == 2  # two config tasks
+
+
+def test_to_torch_returns_detached_clone(cpu_scheduler):
+    x = torch.arange(6.0)
+    t = cs.from_torch(x)
+    y = cs.to_torch(cpu_scheduler, t)
+    y += 1
+    assert torch.equal(x, torch.arange(6.0))
+
+
+@pytest.mark.gpu
+def test_cross_stream_read_after_write_is_ordered(gpu_scheduler):
+    """A slow writer on the assist stream must be visible to a main-stream reader."""
+    s = gpu_scheduler
+    n = 1 << 24
+    src = torch.zeros(n, device="cuda")
+    out = cs.Tensor()
+    res = cs.Tensor()
+
+    def writer():
+        t = src
+        for _ in range(50):  # long chain of kernels on the assist stream
+            t = t + 1
+        out.set_raw(t)
+
+    def reader():
+        res.set_raw(out.raw().sum())
+
+    s.submit_python("writer", 1, [out], [], writer)
+    s.submit_python("reader", 0, [res], [out], reader)
+    val = cs.to_torch(s, res).item()
+    assert val == 50 * n
+
+
+@pytest.mark.gpu
+def test_write_after_read_across_streams_is_ordered(gpu_scheduler):
+    """A main-stream writer must wait for a side-stream reader of the same tensor."""
+    s = gpu_scheduler
+    n = 1 << 24
+    buf = cs.from_torch(torch.ones(n, device="cuda"))
+    res = cs.Tensor()
+
+    def slow_reader():
+        t = buf.raw()
+        acc = torch.zeros((), device="cuda")
+        for _ in range(40):
+            acc = acc + t.sum()
+        res.set_raw(acc)
+
+    def overwriter():
+        buf.raw().zero_()
+
+    s.submit_python("slow_reader", 2, [res], [buf], slow_reader)
+    s.submit_python("overwriter", 0, [buf], [], overwriter)
+    assert cs.to_torch(s, res).item() == 40 * n
+
+
+@pytest.mark.gpu
+def test_side_tasks_rejoin_and_events_are_pooled(gpu_scheduler):
+    s = gpu_scheduler
+    x = cs.from_torch(torch.ones(1024, device="cuda"))
+    for i in range(20):
+        o = cs.Tensor()
+        s.submit_python("side", 1 + (i % 2), [o], [x], lambda o=o: o.set_raw(x.raw() * 2))
+        m = cs.Tensor()
+        s.submit_python("main", 0, [m], [o], lambda m=m, o=o: m.set_raw(o.raw() + 1))
+    s.synchronize()
+    assert cs.to_torch(s, m).eq(3).all()
+    del o, m
+    assert C.event_pool_size() > 0
+
+
+@pytest.mark.gpu
+def test_profiling_reports_task_times(gpu_scheduler):
+    s = gpu_scheduler
+    s.set_profiling(True)
+    x = cs.from_torch(torch.ones(1 << 20, device="cuda"))
+    o = cs.Tensor()
+    s.submit_python("timed_task", 0, [o], [x], lambda: o.set_raw(x.raw() * 3))
+    t = s.drain_timings()
+    s.set_profiling(False)
+    assert any(r.name == "timed_task" and r.device_ms >= 0 for r in t)
