@@ -1,0 +1,230 @@
+"""Headline benchmark: GPT-2 training tokens/sec (device-timed, max over ranks) on N GPUs of one node.
+
+  python bench.py --gpus 1 --steps 10 --warmup 3
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+      bench.py --gpus N --steps K --warmup W
+
+Prints ONE JSON line from rank 0. `value` is the whole-job tokens/sec with inputs already on the
+device; `e2e` repeats the measurement through the public data-loading path (pinned host buffers ->
+H2D copy every step, loss read back to the host every step).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "GPT-2 train tokens/sec, device-timed max over ranks"
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=10)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--model", default="124M")
+    p.add_argument("--micro-batch", type=int, default=16)
+    p.add_argument("--seq-len", type=int, default=1024)
+    p.add_argument("--mode", default="dp", choices=["dp", "zero", "tp"])
+    p.add_argument("--backend", default="fused", choices=["fused", "library"])
+    p.add_argument("--bucket-mb", type=float, default=25.0)
+    p.add_argument("--no-e2e", action="store_true")
+    return p.parse_args()
+
+
+def reference_arm(args):
+    # The reference is a CMake C++ project without setup.py/pyproject.toml, so the prescribed
+    # `pip install --target baseline/_ref /root/reference` stops with "not installable".
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "reference is a CMake C++ library (no setup.py/pyproject.toml): pip install "
+                                     "--target baseline/_ref fails; it also needs MPI/hwloc/cxxopts which the image lacks"}))
+    return 0
+
+
+class Trainer:
+    """One optimizer step of GPT-2 through the framework's public API."""
+
+    def __init__(self, args, cs, comm, rank, world, local_rank):
+        from core_scheduler_b200.models import gpt2_config
+
+        self.cs, self.C = cs, cs._C
+        self.comm, self.rank, self.world = comm, rank, world
+        self.s = cs.DynamicScheduler(local_rank, device="cuda")
+        self.C.set_backend(args.backend)
+        cs.manual_seed(1234)  # same weights on every rank
+        self.cfg = gpt2_config(args.model, dtype=torch.float32)
+        self.model = cs.GPT2(self.s, self.cfg)
+        self.flat = self.C.flatten_parameters(self.s, self.model, lp_dtype=torch.bfloat16)
+        self.opt = cs.AdamW(self.s, self.model, lr=3e-4, beta1=0.9, beta2=0.95, weight_decay=0.1, flat=self.flat)
+        self.bucket = None
+        self.sync = None
+        if world > 1:
+            self.bucket = cs.AllReduceBucket(int(args.bucket_mb * (1 << 20)), "sum")
+            self.sync = cs.GradientSync(comm, self.bucket, True)
+            self.opt.set_grad_scale(1.0 / world)  # the average is folded into the optimizer kernel
+        self.s.synchronize()
+
+    def step(self, ids, labels):
+        s, m = self.s, self.model
+        with self.cs.autocast(s, torch.bfloat16):
+            loss = m.forward_loss(s, ids, labels)
+        m.backward_loss(s, self.sync)
+        if self.bucket is not None:
+            self.bucket.sync(s, self.comm)
+        self.opt.step(s)
+        self.opt.zero_grad(s)
+        return loss
+
+
+def max_over_ranks(value: float, world: int) -> float:
+    if world <= 1:
+        return value
+    import torch.distributed as dist
+
+    t = torch.tensor([value], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(world: int):
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if not torch.cuda.is_available():
+        print(json.dumps({"metric": METRIC, "error": "no CUDA device visible"}))
+        return 1
+    import core_scheduler_b200 as cs
+    from core_scheduler_b200.parallel import init_distributed
+    from core_scheduler_b200.utils.clocks import ClockSampler
+
+    comm, rank, world, local_rank = init_distributed("cuda")
+    torch.cuda.set_device(local_rank)
+    C = cs._C
+    trainer = Trainer(args, cs, comm, rank, world, local_rank)
+    B, T = args.micro_batch, args.seq_len
+    vocab = trainer.cfg.vocab_size
+
+    # ---- device-resident inputs for the kernel-level number (a few distinct batches) -------------
+    gen = torch.Generator(device="cuda").manual_seed(1000 + rank)
+    batches = []
+    for _ in range(4):
+        ids = torch.randint(0, vocab, (B, T + 1), generator=gen, device="cuda")
+        batches.append((cs.from_torch(ids[:, :-1].contiguous()), cs.from_torch(ids[:, 1:].contiguous())))
+
+    for i in range(args.warmup):
+        loss = trainer.step(*batches[i % len(batches)])
+    trainer.s.synchronize()
+    barrier(world)
+
+    sampler = ClockSampler(local_rank).start() if rank == 0 else None
+    launches_before = C.kernel_launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    main_stream = torch.cuda.ExternalStream(trainer.s.raw_stream(0))
+    start.record(main_stream)
+    for i in range(args.steps):
+        loss = trainer.step(*batches[i % len(batches)])
+    trainer.s.synchronize()  # every stream drained (optimizer runs on the assist stream)
+    stop.record(main_stream)
+    torch.cuda.synchronize()
+    launches = C.kernel_launch_count() - launches_before
+    device_ms = start.elapsed_time(stop)
+    barrier(world)
+    clocks = sampler.stop() if sampler else None
+    device_ms = max_over_ranks(device_ms, world)
+    final_loss = float(cs.to_torch(trainer.s, loss).item())
+
+    tokens_per_step = B * T * world
+    ms_per_step = device_ms / args.steps
+    value = tokens_per_step / (ms_per_step / 1e3)
+
+    # ---- end to end: pinned host staging + H2D every step, loss read back every step ----------------
+    e2e = None
+    if not args.no_e2e:
+        loader = C.SyntheticDataLoader(B, T, vocab, seed=77 + rank)
+        for _ in range(2):
+            d = loader.load(trainer.s)
+            float(cs.to_torch(trainer.s, trainer.step(d["input_ids"], d["labels"])).item())
+        trainer.s.synchronize()
+        barrier(world)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            d = loader.load(trainer.s)
+            loss = trainer.step(d["input_ids"], d["labels"])
+            float(cs.to_torch(trainer.s, loss).item())
+        trainer.s.synchronize()
+        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1e3
+        e2e_ms = max_over_ranks(e2e_ms, world)
+        e2e = {
+            "value": tokens_per_step / (e2e_ms / args.steps / 1e3),
+            "unit": "tokens/s",
+            "ms_per_step": e2e_ms / args.steps,
+            "h2d_bytes_per_step": loader.bytes_per_batch(),
+            "d2h_bytes_per_step": 4,
+        }
+
+    if rank == 0:
+        weights_gb = trainer.cfg.parameter_count() * (4 + 2 + 2) / 1e9
+        out = {
+            "metric": METRIC,
+            "value": value,
+            "unit": "tokens/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": ms_per_step,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic uniform token ids, random-init weights N(0,0.02)",
+            "impl": "ours",
+            "config": {
+                "model": f"GPT-2 {args.model} ({trainer.cfg.parameter_count() / 1e6:.1f}M params, untied lm_head)",
+                "global_batch": B * world,
+                "micro_batch_per_gpu": B,
+                "seq_len": T,
+                "parallelism": f"{args.mode}{world}",
+                "precision": "bf16 compute, fp32 master weights + AdamW moments",
+                "backend": args.backend,
+                "bucket_mb": args.bucket_mb,
+                "l2": f"per-step working set (~{weights_gb:.1f} GB weights/optimizer + activations) exceeds the 126 MB L2; no flush needed",
+            },
+            "final_loss": final_loss,
+            "mfu_vs_measured_sustained": None,
+            "clocks": clocks,
+            "e2e": e2e,
+            "gpu_launches": int(launches),
+        }
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+            flops = trainer.cfg.train_flops_per_token(T) * value / world
+            out["mfu_vs_measured_sustained"] = flops / (peaks["bf16_tflops_sustained"] * 1e12)
+        except Exception:
+            pass
+        print(json.dumps(out))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -96,7 +96,7 @@ def generate_ninja() -> Path:
     ] + [f"-I{i}" for i in inc]
     nvccflags = [
         "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
-        "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", f"-I{CSRC}", f"-I{CSRC / 'kernels'}",
+        "-Xcompiler", "-fPIC", f"-I{CSRC}", f"-I{CSRC / 'kernels'}",
     ]
     lines = [
         "ninja_required_version = 1.5",

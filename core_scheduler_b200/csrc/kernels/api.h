@@ -9,6 +9,12 @@
 namespace cs::kernels {
 using stream_t = void *;  // cudaStream_t
 
+// Number of kernels of this library launched by this process so far (all streams).
+int64_t launch_count();
+void count_launch(int n);
+// Adds n to the launch counter and returns cudaGetLastError() as int.
+int finish_launch(int n = 1);
+
 // ---- optimizer -------------------------------------------------------------------------
 struct AdamWArgs {
   void *param;          // master values, dtype given by param_dtype

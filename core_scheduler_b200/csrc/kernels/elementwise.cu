@@ -9,9 +9,20 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include "api.h"
 
 namespace cs::kernels {
+namespace {
+std::atomic<int64_t> g_launches{0};
+}
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+int64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
+int finish_launch(int n) {
+  count_launch(n);
+  return static_cast<int>(cudaGetLastError());
+}
 namespace {
 constexpr int kSmCount = 148;
 
@@ -168,7 +179,7 @@ int launch_adamw(cudaStream_t s, const AdamWArgs &a) {
         a.lr, a.beta1, a.beta2, a.eps, a.weight_decay, a.inv_bias_correction1, a.inv_bias_correction2, a.grad_scale,
         a.clip_coef);
   }
-  return static_cast<int>(cudaGetLastError());
+  return finish_launch();
 }
 }  // namespace
 
@@ -264,7 +275,7 @@ int gelu_forward(stream_t stream, const void *x, void *y, int64_t n) {
   if (n8) gelu_fwd_kernel<<<grid_for(n8, 256), 256, 0, s>>>(static_cast<const Bf16x8 *>(x), static_cast<Bf16x8 *>(y), n8);
   if (n % 8)
     tail_kernel<<<1, 8, 0, s>>>(static_cast<const __nv_bfloat16 *>(x), nullptr, static_cast<__nv_bfloat16 *>(y), n8 * 8, n, 0);
-  return static_cast<int>(cudaGetLastError());
+  return finish_launch();
 }
 int gelu_backward(stream_t stream, const void *dy, const void *x, void *dx, int64_t n) {
   auto s = static_cast<cudaStream_t>(stream);
@@ -275,7 +286,7 @@ int gelu_backward(stream_t stream, const void *dy, const void *x, void *dx, int6
   if (n % 8)
     tail_kernel<<<1, 8, 0, s>>>(static_cast<const __nv_bfloat16 *>(dy), static_cast<const __nv_bfloat16 *>(x),
                                 static_cast<__nv_bfloat16 *>(dx), n8 * 8, n, 1);
-  return static_cast<int>(cudaGetLastError());
+  return finish_launch();
 }
 int add_bf16(stream_t stream, const void *a, const void *b, void *out, int64_t n) {
   auto s = static_cast<cudaStream_t>(stream);
@@ -286,11 +297,11 @@ int add_bf16(stream_t stream, const void *a, const void *b, void *out, int64_t n
   if (n % 8)
     tail_kernel<<<1, 8, 0, s>>>(static_cast<const __nv_bfloat16 *>(a), static_cast<const __nv_bfloat16 *>(b),
                                 static_cast<__nv_bfloat16 *>(out), n8 * 8, n, 2);
-  return static_cast<int>(cudaGetLastError());
+  return finish_launch();
 }
 int cast_fp32_to_bf16(stream_t stream, const float *src, void *dst, int64_t n) {
   if (n) cast_kernel<<<grid_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(src, static_cast<__nv_bfloat16 *>(dst), n);
-  return static_cast<int>(cudaGetLastError());
+  return finish_launch();
 }
 int transpose_cast_to_bf16(stream_t stream, const void *src, int src_dtype, void *dst_t, int64_t rows, int64_t cols) {
   auto s = static_cast<cudaStream_t>(stream);
@@ -302,7 +313,7 @@ int transpose_cast_to_bf16(stream_t stream, const void *src, int src_dtype, void
                                                          static_cast<__nv_bfloat16 *>(dst_t), rows, cols);
   else
     return static_cast<int>(cudaErrorInvalidValue);
-  return static_cast<int>(cudaGetLastError());
+  return finish_launch();
 }
 
 // --------------------------------------------------------------------------- LayerNorm ----
@@ -483,7 +494,7 @@ int launch_ln_fwd(cudaStream_t s, const void *x, const void *gamma, const void *
   const int grid = static_cast<int>(blocks > kSmCount * 16 ? kSmCount * 16 : blocks);
   ln_fwd_kernel<CHUNKS><<<grid, kLnWarps * 32, 0, s>>>(static_cast<const __nv_bfloat16 *>(x), gamma, beta, pdt,
                                                        static_cast<__nv_bfloat16 *>(y), mean, rstd, rows, d, eps);
-  return static_cast<int>(cudaGetLastError());
+  return finish_launch();
 }
 template <int CHUNKS>
 int launch_ln_bwd(cudaStream_t s, const void *dy, const void *x, const void *gamma, int pdt, const float *mean,
@@ -495,7 +506,7 @@ int launch_ln_bwd(cudaStream_t s, const void *dy, const void *x, const void *gam
   ln_bwd_kernel<CHUNKS><<<parts, kLnWarps * 32, smem, s>>>(
       static_cast<const __nv_bfloat16 *>(dy), static_cast<const __nv_bfloat16 *>(x), gamma, pdt, mean, rstd,
       static_cast<const __nv_bfloat16 *>(dres), static_cast<__nv_bfloat16 *>(dx), scratch, rows, d);
-  return static_cast<int>(cudaGetLastError());
+  return finish_launch();
 }
 }  // namespace
 
@@ -536,7 +547,7 @@ int layernorm_backward(stream_t stream, const void *dy, const void *x, const voi
   if (code != 0) return code;
   dim3 grid(static_cast<unsigned>((d + 31) / 32), 2);
   ln_bwd_reduce_kernel<<<grid, dim3(32, 8), 0, s>>>(scratch, parts, di, dgamma, dbeta, accumulate);
-  return static_cast<int>(cudaGetLastError());
+  return finish_launch(1);
 }
 
 // --------------------------------------------------------------------------- embedding ----
@@ -614,7 +625,7 @@ int embedding_forward(stream_t stream, const int64_t *idx, const void *wte, cons
   if (d % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
   embedding_fwd_kernel<<<grid_for(rows * (d / 8), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       idx, wte, wpe, table_dtype, static_cast<__nv_bfloat16 *>(out), rows, seq_len, static_cast<int>(d), vocab);
-  return static_cast<int>(cudaGetLastError());
+  return finish_launch();
 }
 
 int embedding_backward(stream_t stream, const int64_t *idx, const void *dy, float *dwte, float *dwpe, int accumulate_wpe,
@@ -629,7 +640,7 @@ int embedding_backward(stream_t stream, const int64_t *idx, const void *dy, floa
     embedding_bwd_wpe_kernel<<<grid_for(seq_len * (d / 8), 256), 256, 0, s>>>(static_cast<const __nv_bfloat16 *>(dy), dwpe,
                                                                              accumulate_wpe, rows / seq_len, seq_len,
                                                                              static_cast<int>(d));
-  return static_cast<int>(cudaGetLastError());
+  return finish_launch((dwte ? 1 : 0) + (dwpe ? 1 : 0));
 }
 
 // ----------------------------------------------------------------------- cross entropy ----
@@ -728,7 +739,7 @@ int cross_entropy_finalize(stream_t stream, const float *stats, int64_t n_tiles,
   ce_finalize_kernel<<<static_cast<unsigned>(blocks), threads, 0, s>>>(stats, n_tiles, static_cast<const __nv_bfloat16 *>(logits),
                                                                      ld, target, lse, loss, count, rows, ignore_index);
   ce_mean_kernel<<<1, 1, 0, s>>>(loss, count);
-  return static_cast<int>(cudaGetLastError());
+  return finish_launch(2);
 }
 
 int cross_entropy_backward_inplace(stream_t stream, void *logits, int64_t ld, const float *lse, const int64_t *target,
@@ -737,7 +748,7 @@ int cross_entropy_backward_inplace(stream_t stream, void *logits, int64_t ld, co
   if (n % 8 != 0 || ld % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
   ce_backward_kernel<<<grid_for(rows * (n / 8), 256, 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16 *>(logits), ld, lse, target, count, grad_scale, rows, n, n_valid, ignore_index);
-  return static_cast<int>(cudaGetLastError());
+  return finish_launch();
 }
 
 // ----------------------------------------------------------------------- gradient norm ----
@@ -781,11 +792,11 @@ int sum_squares(stream_t stream, const void *x, int dtype, int64_t n, float *sum
   if (dtype == 0) sumsq_kernel<float><<<grid_for(n, 256, 4), 256, 0, s>>>(static_cast<const float *>(x), n, sumsq);
   else if (dtype == 1) sumsq_kernel<__nv_bfloat16><<<grid_for(n, 256, 4), 256, 0, s>>>(static_cast<const __nv_bfloat16 *>(x), n, sumsq);
   else return static_cast<int>(cudaErrorInvalidValue);
-  return static_cast<int>(cudaGetLastError());
+  return finish_launch();
 }
 int clip_coefficient(stream_t stream, const float *sumsq, float max_norm, float *coef, float *norm_out) {
   clip_coef_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(sumsq, max_norm, coef, norm_out);
-  return static_cast<int>(cudaGetLastError());
+  return finish_launch();
 }
 int scale_by_device_scalar(stream_t stream, void *x, int dtype, int64_t n, const float *coef) {
   auto s = static_cast<cudaStream_t>(stream);
@@ -793,6 +804,6 @@ int scale_by_device_scalar(stream_t stream, void *x, int dtype, int64_t n, const
   if (dtype == 0) scale_kernel<float><<<grid_for(n, 256, 4), 256, 0, s>>>(static_cast<float *>(x), n, coef);
   else if (dtype == 1) scale_kernel<__nv_bfloat16><<<grid_for(n, 256, 4), 256, 0, s>>>(static_cast<__nv_bfloat16 *>(x), n, coef);
   else return static_cast<int>(cudaErrorInvalidValue);
-  return static_cast<int>(cudaGetLastError());
+  return finish_launch();
 }
 }  // namespace cs::kernels

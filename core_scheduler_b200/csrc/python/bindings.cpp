@@ -72,6 +72,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("from_torch", &Tensor::wrap);
   m.def("manual_seed", &cs::manual_seed);
   m.def("event_pool_size", &Event::pooled);
+  m.def("kernel_launch_count", &cs::kernels::launch_count);
 
   py::class_<TaskTiming>(m, "TaskTiming")
       .def_readonly("name", &TaskTiming::name)
