@@ -89,7 +89,7 @@ struct GemmArgs {
   void *d2;          // second output (kEpiGeluDual)
   const void *aux;   // residual / pre-activation, same shape & leading dim as d
   const void *bias;  // bf16 [N] or nullptr
-  float *stats;      // kEpiCrossEntropy: [M, n_tiles, 2] (max, sum-exp) partials
+  float *stats;      // kEpiCrossEntropy: [M, gemm_ce_stat_tiles(N), 2] (max, sum-exp) partials
   int64_t m, n, k;
   int64_t lda, ldb, ldd;
   int layout;
@@ -98,7 +98,12 @@ struct GemmArgs {
 };
 // Returns 0 on success, -1 when the shape/alignment is not supported (caller falls back).
 int gemm_bf16(stream_t stream, const GemmArgs &args);
-int gemm_tile_n();  // N extent of one output tile (stats partial granularity)
+// Number of (max, sum-exp) partials per row that kEpiCrossEntropy writes for N columns.
+int64_t gemm_ce_stat_tiles(int64_t n);
+// Copies / clears the status word of the GEMM kernel (synchronises the device).
+struct DeviceStatus;
+int gemm_status(DeviceStatus *out);
+int gemm_status_reset();
 
 // ---- fused cross-entropy helpers -----------------------------------------------------------
 // Reduces the per-tile partials to lse[row], computes loss_row = lse - logit[target] and the

@@ -1,5 +1,649 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05) with fp32 accumulators in tensor
+// memory (TMEM), operands staged in shared memory by TMA, and fused epilogues.
+//
+//   D[M,N] = A * B^T     kTN: A [M,K] and B [N,K] row-major (K contiguous)   forward / dgrad
+//                        kNT: A [K,M] and B [K,N] row-major (M/N contiguous) weight gradient
+//
+// Structure (one persistent CTA per SM, 320 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor tiles -> 4-stage shared-memory ring
+//   warp 1      allocates TMEM and issues tcgen05.mma (one elected lane); 128x256 fp32
+//               accumulators, two of them (512 TMEM columns) so the epilogue of tile i overlaps
+//               the main loop of tile i+1
+//   warps 2-9   epilogue: tcgen05.ld the accumulator (each warp owns a 32-row lane quadrant
+//               and a 128-column half), apply the fused op, store to global memory
+// Shared-memory tiles use the 128-byte swizzle; the K-major operands of kTN are described to
+// the MMA with SBO = 1024 B (8 rows x 128 B), the MN-major operands of kNT with LBO = 8192 B
+// (next 64-element block) and SBO = 1024 B (next 8 k-rows).
+// Every mbarrier wait is bounded: a wait that runs out raises an abort flag, the CTA drains,
+// frees its TMEM and returns; the host sees DeviceStatus.code != 0.
+//
+// What it replaces in the reference project: the cuBLAS calls behind at::linear / at::matmul in
+// src/compute/linear.cpp:178-207,245,286-296 and the cuDNN-frontend fused graphs of
+// src/compute/gelu_linear_cudnn.cpp:123-311 (GELU+matmul, matmul+GELU', GELU+wgrad), plus the
+// log_softmax pass of src/compute/cross_entropy.cpp:57-63 (folded into the classifier epilogue).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
 #include "api.h"
+
 namespace cs::kernels {
-int gemm_bf16(stream_t, const GemmArgs &) { return -1; }
-int gemm_tile_n() { return 256; }
+namespace {
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = 64 + EPI_WARPS * 32;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr long long kWaitBudgetCycles = 4000000000LL;  // ~2 s at 2 GHz
+
+struct KParams {
+  void *d;
+  void *d2;
+  const void *aux;
+  const void *bias;
+  float *stats;
+  long long m, n, k, ldd, n_valid;
+  int layout, epilogue;
+  int m_tiles, n_tiles, splits, kb_total, kb_per_split;
+  int atomic_out;     // fp32 output accumulated with red.global.add (split-K or accumulate mode)
+  unsigned lbo_mn, sbo_mn, kstep_mn;  // MN-major descriptor parameters (bytes)
+  DeviceStatus *status;
+};
+
+__device__ DeviceStatus g_gemm_status;
+
+// ------------------------------------------------------------------------- PTX helpers ----
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the budget ran out or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitBudgetCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (tcgen05): start address, leading/stride byte offsets in
+// 16-byte units, descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((addr & 0x3FFFF) >> 4);
+  desc |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+  desc |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+  desc |= static_cast<uint64_t>(1) << 46;  // version
+  desc |= static_cast<uint64_t>(2) << 61;  // SWIZZLE_128B
+  return desc;
+}
+
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
+__device__ __forceinline__ float gelu_grad_f(float x) {
+  const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752440f));
+  const float pdf = 0.39894228040143267794f * __expf(-0.5f * x * x);
+  return cdf + x * pdf;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&t);
+}
+__device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
+  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&u));
+}
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+struct TileCoord {
+  int m0, n0, kb_begin, kb_end, n_tile;
+};
+__device__ __forceinline__ TileCoord tile_coord(const KParams &p, int tile) {
+  const int mn = p.m_tiles * p.n_tiles;
+  const int split = tile / mn;
+  const int rem = tile - split * mn;
+  const int n_tile = rem / p.m_tiles;
+  const int m_tile = rem - n_tile * p.m_tiles;
+  TileCoord c;
+  c.m0 = m_tile * BM;
+  c.n0 = n_tile * BN;
+  c.n_tile = n_tile;
+  c.kb_begin = split * p.kb_per_split;
+  c.kb_end = min(p.kb_total, c.kb_begin + p.kb_per_split);
+  return c;
+}
+
+// ------------------------------------------------------------------------------ kernel ----
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: the 128-byte swizzle pattern is a function of the absolute address.
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_aligned + STAGES * STAGE_BYTES);
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  // barrier slots: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars + 2 * STAGES + 4);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * STAGES + 5);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_tiles = p.m_tiles * p.n_tiles * p.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tmem_full_bar(b), 1);
+      mbar_init(tmem_empty_bar(b), EPI_WARPS);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t *>(tmem_slot))),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer ----
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const TileCoord c = tile_coord(p, tile);
+        for (int kb = c.kb_begin; kb < c.kb_end; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
+          const uint32_t b_dst = a_dst + A_BYTES;
+          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+          if (p.layout == kTN) {
+            tma_load_2d(a_dst, &map_a, full_bar(stage), kb * BK, c.m0);
+            tma_load_2d(b_dst, &map_b, full_bar(stage), kb * BK, c.n0);
+          } else {
+            // MN-major: 64-element (128-byte) wide boxes of 64 k-rows, 8 KB each
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &map_a, full_bar(stage), c.m0 + j * 64, kb * BK);
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &map_b, full_bar(stage), c.n0 + j * 64, kb * BK);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // Abort path: give loads that are still in flight a bounded chance to land before the
+        // shared memory goes away.
+        for (int s = 0; s < STAGES; ++s) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(full_bar(s), 0) && !mbar_try_wait(full_bar(s), 1) && clock64() - t0 < 2000000LL) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------------- MMA issuer ----
+    if (lane == 0) {
+      const uint32_t a_major = p.layout == kNT ? 1u : 0u;
+      const uint32_t idesc = (1u << 4) /*fp32 accum*/ | (1u << 7) /*A bf16*/ | (1u << 10) /*B bf16*/ | (a_major << 15) |
+                             (a_major << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                             (static_cast<uint32_t>(BM >> 4) << 24);
+      const uint32_t lbo = p.layout == kNT ? p.lbo_mn : 16u;
+      const uint32_t sbo = p.layout == kNT ? p.sbo_mn : 1024u;
+      const uint32_t kstep = p.layout == kNT ? p.kstep_mn : static_cast<uint32_t>(UMMA_K * 2);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const TileCoord c = tile_coord(p, tile);
+        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag)) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = c.kb_begin; kb < c.kb_end; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t a_src = smem_base + stage * STAGE_BYTES;
+          const uint32_t b_src = a_src + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = make_smem_desc(a_src + k * kstep, lbo, sbo);
+            const uint64_t db = make_smem_desc(b_src + k * kstep, lbo, sbo);
+            tcgen05_mma(d_tmem, da, db, idesc, (kb > c.kb_begin || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit(empty_bar(stage));  // frees the stage once these MMAs retired
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tcgen05_commit(tmem_full_bar(acc));
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------------- epilogue ----
+    const int q = warp & 3;                 // TMEM lane quadrant this warp may access
+    const int half = (warp - 2) >> 2;       // which 128 columns of the tile
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const TileCoord c = tile_coord(p, tile);
+      if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag)) break;
+      tcgen05_fence_after();
+      const long long row = c.m0 + q * 32 + lane;
+      const bool row_ok = row < p.m;
+      float run_max = -INFINITY, run_sum = 0.f;
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        const int col0 = half * 128 + ch * 32;
+        uint32_t v[32];
+        tcgen05_ld_32x32b_x32(tmem_base + acc * BN + col0 + (static_cast<uint32_t>(q * 32) << 16), v);
+        tcgen05_wait_ld();
+        const long long gcol = c.n0 + col0;
+        if (!row_ok || gcol >= p.n) continue;
+        float f[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+        if (p.epilogue == kEpiStoreF32 || p.epilogue == kEpiAccumF32) {
+          float *dst = static_cast<float *>(p.d) + row * p.ldd + gcol;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            if (gcol + g * 4 + 4 > p.n) break;
+            if (p.atomic_out) {
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + g * 4), "f"(f[4 * g]),
+                           "f"(f[4 * g + 1]), "f"(f[4 * g + 2]), "f"(f[4 * g + 3])
+                           : "memory");
+            } else {
+              float4 o = make_float4(f[4 * g], f[4 * g + 1], f[4 * g + 2], f[4 * g + 3]);
+              if (p.epilogue == kEpiAccumF32) {
+                const float4 old = *reinterpret_cast<const float4 *>(dst + g * 4);
+                o.x += old.x;
+                o.y += old.y;
+                o.z += old.z;
+                o.w += old.w;
+              }
+              *reinterpret_cast<float4 *>(dst + g * 4) = o;
+            }
+          }
+          continue;
+        }
+        if (p.bias) {
+          const uint4 *bp = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.bias) + gcol);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (gcol + g * 8 + 8 > p.n) break;
+            const uint4 b = __ldg(bp + g);
+            const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 t = unpack_bf16(w[i]);
+              f[g * 8 + 2 * i] += t.x;
+              f[g * 8 + 2 * i + 1] += t.y;
+            }
+          }
+        }
+        __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(p.d) + row * p.ldd + gcol;
+        if (p.epilogue == kEpiResidualBf16 || p.epilogue == kEpiDGelu) {
+          const uint4 *ap = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.aux) + row * p.ldd + gcol);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (gcol + g * 8 + 8 > p.n) break;
+            const uint4 a = *(ap + g);
+            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 t = unpack_bf16(w[i]);
+              if (p.epilogue == kEpiResidualBf16) {
+                f[g * 8 + 2 * i] += t.x;
+                f[g * 8 + 2 * i + 1] += t.y;
+              } else {
+                f[g * 8 + 2 * i] *= gelu_grad_f(t.x);
+                f[g * 8 + 2 * i + 1] *= gelu_grad_f(t.y);
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (gcol + g * 8 + 8 > p.n) break;
+          uint4 o;
+          o.x = pack_bf16(f[g * 8 + 0], f[g * 8 + 1]);
+          o.y = pack_bf16(f[g * 8 + 2], f[g * 8 + 3]);
+          o.z = pack_bf16(f[g * 8 + 4], f[g * 8 + 5]);
+          o.w = pack_bf16(f[g * 8 + 6], f[g * 8 + 7]);
+          *reinterpret_cast<uint4 *>(dst + g * 8) = o;
+        }
+        if (p.epilogue == kEpiGeluDual) {
+          __nv_bfloat16 *dst2 = static_cast<__nv_bfloat16 *>(p.d2) + row * p.ldd + gcol;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (gcol + g * 8 + 8 > p.n) break;
+            uint4 o;
+            // GELU of the value as stored (bf16-rounded), so that backward sees the same input
+            o.x = pack_bf16(gelu_f(bf16_round(f[g * 8 + 0])), gelu_f(bf16_round(f[g * 8 + 1])));
+            o.y = pack_bf16(gelu_f(bf16_round(f[g * 8 + 2])), gelu_f(bf16_round(f[g * 8 + 3])));
+            o.z = pack_bf16(gelu_f(bf16_round(f[g * 8 + 4])), gelu_f(bf16_round(f[g * 8 + 5])));
+            o.w = pack_bf16(gelu_f(bf16_round(f[g * 8 + 6])), gelu_f(bf16_round(f[g * 8 + 7])));
+            *reinterpret_cast<uint4 *>(dst2 + g * 8) = o;
+          }
+        }
+        if (p.epilogue == kEpiCrossEntropy) {
+          // running (max, sum-exp) over the valid columns, on the bf16-rounded logits
+          float cmax = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            f[i] = bf16_round(f[i]);
+            if (gcol + i < p.n_valid) cmax = fmaxf(cmax, f[i]);
+          }
+          if (cmax > -INFINITY) {
+            const float new_max = fmaxf(run_max, cmax);
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (gcol + i < p.n_valid) s += __expf(f[i] - new_max);
+            run_sum = run_sum * __expf(run_max - new_max) + s;
+            run_max = new_max;
+          }
+        }
+      }
+      if (p.epilogue == kEpiCrossEntropy && row_ok) {
+        float *st = p.stats + (row * (2LL * p.n_tiles) + 2LL * c.n_tile + half) * 2;
+        st[0] = run_max;
+        st[1] = run_sum;
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------------- teardown ----
+  tcgen05_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) {
+    p.status->code = 1;
+    p.status->kernel_id = 1;
+    p.status->block = blockIdx.x;
+    p.status->detail = p.layout;
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host: tensor maps ----
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      return static_cast<EncodeFn>(nullptr);
+    }
+    return reinterpret_cast<EncodeFn>(ptr);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void *ptr;
+  uint64_t inner, outer, stride_bytes;
+  uint32_t box_inner, box_outer;
+  bool operator==(const MapKey &o) const {
+    return ptr == o.ptr && inner == o.inner && outer == o.outer && stride_bytes == o.stride_bytes &&
+           box_inner == o.box_inner && box_outer == o.box_outer;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey &k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    auto mix = [&h](uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ULL + (h << 6) + (h >> 2); };
+    mix(k.inner);
+    mix(k.outer);
+    mix(k.stride_bytes);
+    mix((static_cast<uint64_t>(k.box_inner) << 32) | k.box_outer);
+    return h;
+  }
+};
+
+// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row stride in
+// elements; box = box_inner x box_outer with the 128-byte swizzle (box_inner == 64).
+bool get_tensor_map(const void *ptr, uint64_t inner, uint64_t outer, uint64_t stride_elems, uint32_t box_inner,
+                    uint32_t box_outer, CUtensorMap *out) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{ptr, inner, outer, stride_elems * 2, box_inner, box_outer};
+  std::lock_guard<std::mutex> lock{mu};
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return true;
+  }
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {stride_elems * 2};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  CUtensorMap map;
+  const CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, elem_strides,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, map);
+  *out = map;
+  return true;
+}
+
+unsigned env_unsigned(const char *name, unsigned fallback) {
+  const char *v = std::getenv(name);
+  return v ? static_cast<unsigned>(std::strtoul(v, nullptr, 0)) : fallback;
+}
+}  // namespace
+
+int64_t gemm_ce_stat_tiles(int64_t n) { return 2 * ((n + BN - 1) / BN); }  // one (max, sum) pair per 128-column half tile
+
+int gemm_status(DeviceStatus *out) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out, g_gemm_status, sizeof(DeviceStatus)));
+}
+int gemm_status_reset() {
+  DeviceStatus zero{};
+  return static_cast<int>(cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(DeviceStatus)));
+}
+
+int gemm_bf16(stream_t stream, const GemmArgs &a) {
+  auto s = static_cast<cudaStream_t>(stream);
+  if (a.m <= 0 || a.n <= 0 || a.k <= 0) return -1;
+  if (a.n % 8 != 0 || a.ldd % 8 != 0 || a.lda % 8 != 0 || a.ldb % 8 != 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(a.a) | reinterpret_cast<uintptr_t>(a.b) | reinterpret_cast<uintptr_t>(a.d)) & 15) return -1;
+  if (a.aux && (reinterpret_cast<uintptr_t>(a.aux) & 15)) return -1;
+  if (a.d2 && (reinterpret_cast<uintptr_t>(a.d2) & 15)) return -1;
+  if (a.bias && (reinterpret_cast<uintptr_t>(a.bias) & 15)) return -1;
+  const bool f32_out = a.epilogue == kEpiStoreF32 || a.epilogue == kEpiAccumF32;
+  if (a.layout == kTN && a.k % 8 != 0) return -1;
+  if (a.layout == kNT && (a.m % 8 != 0)) return -1;
+  if (f32_out && a.n % 4 != 0) return -1;
+  if (a.m > 0x7fffffffLL || a.n > 0x7fffffffLL || a.k > 0x7fffffffLL) return -1;
+  static const bool disabled = std::getenv("CS_DISABLE_TCGEN05_GEMM") != nullptr;
+  if (disabled) return -1;
+
+  CUtensorMap map_a, map_b;
+  if (a.layout == kTN) {
+    if (!get_tensor_map(a.a, a.k, a.m, a.lda, BK, BM, &map_a)) return -1;
+    if (!get_tensor_map(a.b, a.k, a.n, a.ldb, BK, BN, &map_b)) return -1;
+  } else {
+    if (!get_tensor_map(a.a, a.m, a.k, a.lda, 64, BK, &map_a)) return -1;
+    if (!get_tensor_map(a.b, a.n, a.k, a.ldb, 64, BK, &map_b)) return -1;
+  }
+
+  KParams p{};
+  p.d = a.d;
+  p.d2 = a.d2;
+  p.aux = a.aux;
+  p.bias = a.bias;
+  p.stats = a.stats;
+  p.m = a.m;
+  p.n = a.n;
+  p.k = a.k;
+  p.ldd = a.ldd;
+  p.n_valid = a.n_valid > 0 ? a.n_valid : a.n;
+  p.layout = a.layout;
+  p.epilogue = a.epilogue;
+  p.m_tiles = static_cast<int>((a.m + BM - 1) / BM);
+  p.n_tiles = static_cast<int>((a.n + BN - 1) / BN);
+  p.kb_total = static_cast<int>((a.k + BK - 1) / BK);
+  p.splits = 1;
+  static const int sm_count = [] {
+    int dev = 0, n = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n;
+  }();
+  if (f32_out) {
+    // Weight gradients have few output tiles and a long reduction: split K so that every SM
+    // has work; partial sums meet in the fp32 output through vector atomics.
+    const int mn = p.m_tiles * p.n_tiles;
+    int want = (2 * sm_count + mn - 1) / mn;
+    const int max_splits = p.kb_total / 4 > 0 ? p.kb_total / 4 : 1;
+    if (want > max_splits) want = max_splits;
+    if (want < 1) want = 1;
+    p.splits = want;
+  }
+  p.kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
+  p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+  p.atomic_out = 0;
+  if (f32_out && p.splits > 1) {
+    p.atomic_out = 1;
+    if (a.epilogue == kEpiStoreF32) {
+      // every split adds into a zeroed output
+      const cudaError_t e = cudaMemset2DAsync(a.d, static_cast<size_t>(a.ldd) * 4, 0, static_cast<size_t>(a.n) * 4,
+                                              static_cast<size_t>(a.m), s);
+      if (e != cudaSuccess) return static_cast<int>(e);
+    }
+  }
+  p.lbo_mn = env_unsigned("CS_GEMM_MN_LBO", 8192);
+  p.sbo_mn = env_unsigned("CS_GEMM_MN_SBO", 1024);
+  p.kstep_mn = env_unsigned("CS_GEMM_MN_KSTEP", 2048);
+  static DeviceStatus *status_ptr = [] {
+    void *ptr = nullptr;
+    cudaGetSymbolAddress(&ptr, g_gemm_status);
+    return static_cast<DeviceStatus *>(ptr);
+  }();
+  p.status = status_ptr;
+
+  static const bool attr_set = [] {
+    return cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) == cudaSuccess;
+  }();
+  if (!attr_set) return -1;
+  const int total_tiles = p.m_tiles * p.n_tiles * p.splits;
+  const int grid = total_tiles < sm_count ? total_tiles : sm_count;
+  gemm_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(map_a, map_b, p);
+  return finish_launch(1);
+}
 }  // namespace cs::kernels

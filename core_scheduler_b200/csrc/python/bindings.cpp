@@ -4,6 +4,7 @@
 #include <torch/csrc/distributed/c10d/Backend.hpp>
 #include <torch/csrc/distributed/c10d/ProcessGroup.hpp>
 #include <torch/extension.h>
+#include <c10/cuda/CUDAStream.h>
 
 #include "cs/communication.h"
 #include "cs/compute.h"
@@ -73,6 +74,41 @@ PYBIND11_MODULE(_C, m) {
   m.def("manual_seed", &cs::manual_seed);
   m.def("event_pool_size", &Event::pooled);
   m.def("kernel_launch_count", &cs::kernels::launch_count);
+  m.def("gemm_status", [] {
+    cs::kernels::DeviceStatus st{};
+    cs::kernels::gemm_status(&st);
+    return std::vector<int>{st.code, st.kernel_id, st.block, st.detail};
+  });
+  m.def("gemm_status_reset", [] { cs::kernels::gemm_status_reset(); });
+  // Raw access to the tcgen05 GEMM for kernel tests and microbenchmarks (current torch stream).
+  m.def("gemm_bf16",
+        [](const at::Tensor &a, const at::Tensor &b, at::Tensor d, int layout, int epilogue, py::object aux, py::object bias,
+           py::object d2, py::object stats, int64_t n_valid) {
+          cs::kernels::GemmArgs g{};
+          g.a = a.data_ptr();
+          g.b = b.data_ptr();
+          g.d = d.data_ptr();
+          at::Tensor aux_t, bias_t, d2_t, stats_t;
+          if (!aux.is_none()) { aux_t = py::cast<at::Tensor>(aux); g.aux = aux_t.data_ptr(); }
+          if (!bias.is_none()) { bias_t = py::cast<at::Tensor>(bias); g.bias = bias_t.data_ptr(); }
+          if (!d2.is_none()) { d2_t = py::cast<at::Tensor>(d2); g.d2 = d2_t.data_ptr(); }
+          if (!stats.is_none()) { stats_t = py::cast<at::Tensor>(stats); g.stats = stats_t.data_ptr<float>(); }
+          g.layout = layout;
+          g.epilogue = epilogue;
+          if (layout == cs::kernels::kTN) {
+            g.m = a.size(0); g.k = a.size(1); g.n = b.size(0);
+            g.lda = a.stride(0); g.ldb = b.stride(0);
+          } else {
+            g.k = a.size(0); g.m = a.size(1); g.n = b.size(1);
+            g.lda = a.stride(0); g.ldb = b.stride(0);
+          }
+          g.ldd = d.stride(0);
+          g.n_valid = n_valid;
+          return cs::kernels::gemm_bf16(c10::cuda::getCurrentCUDAStream().stream(), g);
+        },
+        py::arg("a"), py::arg("b"), py::arg("d"), py::arg("layout") = 0, py::arg("epilogue") = 0, py::arg("aux") = py::none(),
+        py::arg("bias") = py::none(), py::arg("d2") = py::none(), py::arg("stats") = py::none(), py::arg("n_valid") = -1);
+  m.def("gemm_ce_stat_tiles", &cs::kernels::gemm_ce_stat_tiles);
 
   py::class_<TaskTiming>(m, "TaskTiming")
       .def_readonly("name", &TaskTiming::name)

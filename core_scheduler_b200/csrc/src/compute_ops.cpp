@@ -539,10 +539,10 @@ std::shared_ptr<LayerNorm::State> LayerNorm::init(const Scheduler &scheduler, co
 }
 
 namespace {
-bool ln_fused_ok(const at::Tensor &x, const at::Tensor &w, size_t norm_dims) {
+bool ln_fused_ok(const at::Tensor &x, const at::Tensor &w, size_t norm_dims, int64_t max_d = 8192) {
   if (!(x.is_cuda() && x.scalar_type() == at::kBFloat16 && fused_enabled() && norm_dims == 1)) return false;
   const int64_t d = x.size(-1);
-  return d % 8 == 0 && d <= 8192 && dtype_code(w.scalar_type()) >= 0 && dtype_code(w.scalar_type()) <= 1;
+  return d % 8 == 0 && d <= max_d && dtype_code(w.scalar_type()) >= 0 && dtype_code(w.scalar_type()) <= 1;
 }
 }  // namespace
 
@@ -629,7 +629,7 @@ Tensor layer_norm_backward_task(const Scheduler &scheduler, const std::shared_pt
            const at::Tensor x = x_h.impl()->tensor.contiguous();
            const at::Tensor &wt = w.impl()->tensor;
            const at::ScalarType store = wt.scalar_type();
-           if (plan.want_input && plan.want_params && ln_fused_ok(x, wt, args.normalized_shape.size()) &&
+           if (plan.want_input && plan.want_params && ln_fused_ok(x, wt, args.normalized_shape.size(), 2048) &&
                dy.scalar_type() == at::kBFloat16 && store == at::kFloat && args.bias) {
              const int64_t d = x.size(-1), rows = x.numel() / d;
              auto &sw = *gw.impl();
@@ -686,7 +686,7 @@ bool ln_single_pass(const Scheduler &scheduler, const std::shared_ptr<LayerNorm:
                     const ReadOnlyTensor &grad_output) {
   const auto &x = state->backward.input.impl()->tensor;
   return scheduler.device().is_cuda() && x.defined() &&
-         ln_fused_ok(x, state->forward.weight.impl()->tensor, state->args.normalized_shape.size()) &&
+         ln_fused_ok(x, state->forward.weight.impl()->tensor, state->args.normalized_shape.size(), 2048) &&
          grad_output.impl()->tensor.scalar_type() == at::kBFloat16 &&
          state->forward.weight.impl()->tensor.scalar_type() == at::kFloat && state->args.bias;
 }
@@ -1060,8 +1060,7 @@ Tensor LinearCrossEntropy::forward(const Scheduler &scheduler, const std::shared
            const int64_t rows = x2.size(0), V = wc.size(0);
            const int64_t n_valid = valid > 0 ? valid : V;
            if (x2.is_cuda() && dt == at::kBFloat16 && fused_enabled() && tgt.scalar_type() == at::kLong) {
-             const int64_t tile_n = kernels::gemm_tile_n();
-             const int64_t n_tiles = (V + tile_n - 1) / tile_n;
+             const int64_t n_tiles = kernels::gemm_ce_stat_tiles(V);
              at::Tensor lg = at::empty({rows, V}, x2.options());
              at::Tensor stats = at::empty({rows, n_tiles, 2}, x2.options().dtype(at::kFloat));
              kernels::GemmArgs g{};
