@@ -1,0 +1,118 @@
+"""Kernel microbenchmarks with CUDA-event timing (after warm-up, L2 flushed between iterations).
+
+  python -m core_scheduler_b200.utils.microbench gemm        # tcgen05 GEMM vs torch.matmul (cuBLAS)
+  python -m core_scheduler_b200.utils.microbench elementwise # LayerNorm / GELU / AdamW bandwidth
+
+Prints one line per case: achieved TFLOP/s or GB/s and the fraction of the measured peak
+(MEASURED_PEAKS.json at the repository root when present, else the fallback 1.59 PFLOP/s, 6.65 TB/s).
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+
+import torch
+
+import core_scheduler_b200 as cs
+
+C = cs._C
+BF = torch.bfloat16
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks():
+    try:
+        p = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        return p["bf16_tflops"], p["hbm_gbs"], "measured"
+    except Exception:
+        return 1590.0, 6650.0, "fallback"
+
+
+_flush = None
+
+
+def flush_l2():
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _flush.zero_()
+
+
+def time_ms(fn, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        flush_l2()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def bench_gemm():
+    tflops_peak, _, tag = peaks()
+    shapes = [  # (name, layout, M, N, K) in GEMM terms; GPT-2 124M at 16x1024 tokens
+        ("c_attn fwd", 0, 16384, 2304, 768), ("c_proj fwd", 0, 16384, 768, 768), ("fc1 fwd", 0, 16384, 3072, 768),
+        ("fc2 fwd", 0, 16384, 768, 3072), ("lm_head fwd", 0, 16384, 50304, 768), ("lm_head dgrad", 0, 16384, 768, 50304),
+        ("fc1 wgrad", 1, 3072, 768, 16384), ("c_attn wgrad", 1, 2304, 768, 16384), ("c_proj wgrad", 1, 768, 768, 16384),
+        ("lm_head wgrad", 1, 50304, 768, 16384), ("square 8192", 0, 8192, 8192, 8192),
+    ]
+    for name, layout, M, N, K in shapes:
+        if layout == 0:
+            a = torch.randn(M, K, device="cuda").to(BF)
+            b = torch.randn(N, K, device="cuda").to(BF)
+            d = torch.empty(M, N, device="cuda", dtype=BF)
+            ours = lambda: C.gemm_bf16(a, b, d, 0, 0)
+            lib = lambda: torch.matmul(a, b.t(), out=d)
+        else:
+            a = torch.randn(K, M, device="cuda").to(BF)
+            b = torch.randn(K, N, device="cuda").to(BF)
+            d = torch.empty(M, N, device="cuda")
+            d16 = torch.empty(M, N, device="cuda", dtype=BF)
+            ours = lambda: C.gemm_bf16(a, b, d, 1, 4)
+            lib = lambda: torch.matmul(a.t(), b, out=d16)
+        flops = 2.0 * M * N * K
+        t_ours, t_lib = time_ms(ours), time_ms(lib)
+        print(f"gemm {name:14s} M={M:6d} N={N:6d} K={K:6d}  ours {t_ours:8.4f} ms {flops / t_ours / 1e9:8.1f} TFLOP/s "
+              f"({flops / t_ours / 1e9 / tflops_peak:.2f} of {tag})   cuBLAS {t_lib:8.4f} ms {flops / t_lib / 1e9:8.1f} TFLOP/s")
+
+
+def bench_elementwise():
+    _, gbs_peak, tag = peaks()
+    s = cs.DynamicScheduler(0, device="cuda")
+    rows, d = 16384, 768
+    x = torch.randn(rows, d, device="cuda").to(BF)
+    ln = C.layer_norm_init(s, [d])
+    tx = cs.from_torch(x)
+
+    def ln_fwd():
+        with cs.autocast(s, BF):
+            C.layer_norm_forward(s, ln, tx)
+
+    t = time_ms(ln_fwd)
+    print(f"layernorm fwd [{rows},{d}] {t:.4f} ms {2 * x.numel() * 2 / t / 1e6:.0f} GB/s ({2 * x.numel() * 2 / t / 1e6 / gbs_peak:.2f} of {tag})")
+    g = C.gelu_init(s)
+    y = torch.randn(rows, 4 * d, device="cuda").to(BF)
+    ty = cs.from_torch(y)
+    t = time_ms(lambda: C.gelu_forward(s, g, ty))
+    print(f"gelu fwd [{rows},{4 * d}] {t:.4f} ms {2 * y.numel() * 2 / t / 1e6:.0f} GB/s ({2 * y.numel() * 2 / t / 1e6 / gbs_peak:.2f} of {tag})")
+    n = 163_000_000
+    w = cs.from_torch(torch.randn(n, device="cuda"))
+    C.working_copy(s, w, BF)
+    st = C.adamw_init(s, w)
+    gr = cs.from_torch(torch.randn(n, device="cuda"))
+    t = time_ms(lambda: C.adamw_step(s, st, w, gr))
+    bytes_moved = n * (4 * 4 + 3 * 4 + 2)
+    print(f"adamw fp32 master + bf16 copy n={n} {t:.4f} ms {bytes_moved / t / 1e6:.0f} GB/s ({bytes_moved / t / 1e6 / gbs_peak:.2f} of {tag})")
+
+
+if __name__ == "__main__":
+    what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    {"gemm": bench_gemm, "elementwise": bench_elementwise}[what]()
