@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <mutex>
 
 #include "api.h"
 
@@ -807,3 +808,61 @@ int scale_by_device_scalar(stream_t stream, void *x, int dtype, int64_t n, const
   return finish_launch();
 }
 }  // namespace cs::kernels
+
+// ------------------------------------------------------------- allocation-free entry ----
+// LayerNorm backward for callers that cannot allocate (see no_alloc.h). Same kernels as
+// layernorm_backward() above; the partial dgamma/dbeta rows go to a file-scope device array.
+#include "no_alloc.h"
+
+namespace {
+static __device__ __align__(256) float g_noalloc_ln_scratch[CS_NOALLOC_LN_PARTS * 2 * CS_NOALLOC_LN_MAX_D];
+
+constexpr int kNoAllocMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+float *g_noalloc_scratch_ptr[kNoAllocMaxDevices] = {};
+
+// In host code `g_noalloc_ln_scratch` is only a handle for the runtime; the address a kernel
+// can use has to be asked for, once per device, with that device current.
+int noalloc_scratch(float **out) {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (device < 0 || device >= kNoAllocMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
+  std::lock_guard<std::mutex> lock{g_noalloc_mutex};
+  if (!g_noalloc_scratch_ptr[device]) {
+    float *ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_noalloc_ln_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_noalloc_scratch_ptr[device] = ptr;
+  }
+  *out = g_noalloc_scratch_ptr[device];
+  return 0;
+}
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) int cs_layernorm_backward_noalloc(
+    const void *dy, const void *x, const float *gamma, const float *mean, const float *rstd, const void *grad_residual,
+    void *dx, float *dgamma, float *dbeta, int accumulate, int64_t rows, int64_t d, void *stream) {
+  using namespace cs::kernels;
+  if (!dy || !x || !gamma || !mean || !rstd || !dx || !dgamma || !dbeta || rows < 0) return -2;
+  if (d <= 0 || d % 8 != 0 || d > CS_NOALLOC_LN_MAX_D) return -1;
+  if (rows == 0) return 0;
+  float *scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc != 0) return rc;
+  auto s = static_cast<cudaStream_t>(stream);
+  const int chunks = static_cast<int>((d / 8 + 31) / 32);
+  const int di = static_cast<int>(d);
+  const int64_t blocks = (rows + kLnWarps - 1) / kLnWarps;
+  const int parts = static_cast<int>(blocks > CS_NOALLOC_LN_PARTS ? CS_NOALLOC_LN_PARTS : blocks);
+  int code;
+  if (chunks <= 2) code = launch_ln_bwd<2>(s, dy, x, gamma, 0, mean, rstd, grad_residual, dx, scratch, rows, di, parts);
+  else if (chunks <= 3) code = launch_ln_bwd<3>(s, dy, x, gamma, 0, mean, rstd, grad_residual, dx, scratch, rows, di, parts);
+  else if (chunks <= 4) code = launch_ln_bwd<4>(s, dy, x, gamma, 0, mean, rstd, grad_residual, dx, scratch, rows, di, parts);
+  else if (chunks <= 5) code = launch_ln_bwd<5>(s, dy, x, gamma, 0, mean, rstd, grad_residual, dx, scratch, rows, di, parts);
+  else code = launch_ln_bwd<8>(s, dy, x, gamma, 0, mean, rstd, grad_residual, dx, scratch, rows, di, parts);
+  if (code != 0) return code;
+  dim3 grid(static_cast<unsigned>((d + 31) / 32), 2);
+  ln_bwd_reduce_kernel<<<grid, dim3(32, 8), 0, s>>>(scratch, parts, di, dgamma, dbeta, accumulate);
+  return finish_launch(1);
+}
