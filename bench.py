@@ -36,6 +36,8 @@ def parse_args():
     p.add_argument("--mode", default="dp", choices=["dp", "zero", "tp"])
     p.add_argument("--backend", default="fused", choices=["fused", "library"])
     p.add_argument("--bucket-mb", type=float, default=25.0)
+    p.add_argument("--comm", default="nvp2p", choices=["nvp2p", "nccl"],
+                   help="gradient collectives: this library's peer-memory kernels, or NCCL")
     p.add_argument("--no-e2e", action="store_true")
     return p.parse_args()
 
@@ -62,10 +64,24 @@ class Trainer:
         cs.manual_seed(1234)  # same weights on every rank
         self.cfg = gpt2_config(args.model, dtype=torch.float32)
         self.model = cs.GPT2(self.s, self.cfg)
-        self.flat = self.C.flatten_parameters(self.s, self.model, lp_dtype=torch.bfloat16)
-        self.opt = cs.AdamW(self.s, self.model, lr=3e-4, beta1=0.9, beta2=0.95, weight_decay=0.1, flat=self.flat)
         self.bucket = None
         self.sync = None
+        self.zero = args.mode == "zero" and world > 1
+        if world > 1 and (args.comm == "nvp2p" or self.zero):
+            import torch.distributed as dist
+
+            pg = dist.distributed_c10d._get_default_group()
+            self.comm = comm = self.C.comm_from_process_group(pg.group_name, "cuda", True)
+            arena = self.cfg.parameter_count() * 6 + (256 << 20)  # fp32 grads + bf16 copies + staging
+            self.symm = self.C.create_symmetric_context(comm, int(arena))
+            self.flat = self.C.flatten_symmetric(self.s, self.model, comm)
+        else:
+            self.flat = self.C.flatten_parameters(self.s, self.model, lp_dtype=torch.bfloat16)
+        if self.zero:
+            self.opt = self.C.ZeroAdamW(self.s, self.model, self.flat, comm, lr=3e-4, beta1=0.9, beta2=0.95, weight_decay=0.1)
+            self.s.synchronize()
+            return
+        self.opt = cs.AdamW(self.s, self.model, lr=3e-4, beta1=0.9, beta2=0.95, weight_decay=0.1, flat=self.flat)
         if world > 1:
             self.bucket = cs.AllReduceBucket(int(args.bucket_mb * (1 << 20)), "sum")
             self.sync = cs.GradientSync(comm, self.bucket, True)
@@ -204,6 +220,7 @@ def main():
                 "precision": "bf16 compute, fp32 master weights + AdamW moments",
                 "backend": args.backend,
                 "bucket_mb": args.bucket_mb,
+                "collectives": (args.comm if world > 1 else "none"),
                 "l2": f"per-step working set (~{weights_gb:.1f} GB weights/optimizer + activations) exceeds the 126 MB L2; no flush needed",
             },
             "final_loss": final_loss,

@@ -39,6 +39,7 @@ CPP_SOURCES = [
 CUDA_SOURCES = [
     "kernels/elementwise.cu",
     "kernels/gemm_tcgen05.cu",
+    "kernels/collectives.cu",
 ]
 BINDING_SOURCES = ["python/bindings.cpp"]
 
@@ -48,7 +49,7 @@ def _optional_sources():
     for name in ("src/parallel.cpp",):
         if (CSRC / name).exists():
             extra_cpp.append(name)
-    for name in ("kernels/attention_tcgen05.cu", "kernels/collectives.cu", "kernels/no_alloc.cu"):
+    for name in ("kernels/attention_tcgen05.cu",):
         if (CSRC / name).exists():
             extra_cu.append(name)
     return extra_cpp, extra_cu

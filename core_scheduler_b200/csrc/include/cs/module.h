@@ -199,6 +199,9 @@ struct CS_API FlatParameters {
 
 struct FlattenOptions {
   FlattenOptions() {}
+  // When set, gradient and low-precision arenas are taken from this allocator (used to place
+  // them in peer-mapped symmetric memory): (bytes) -> 1-D uint8 tensor of that many bytes.
+  CS_ARG(std::function<at::Tensor(int64_t)>, arena_allocator) = {};
   CS_ARG(optional<at::ScalarType>, lp_dtype) = {};  // e.g. kBFloat16 for mixed precision
   CS_ARG(bool, transposed_copies) = true;
   CS_ARG(int64_t, pad_total_to) = 1;                // pad arena length (e.g. world size * 128 for sharding)

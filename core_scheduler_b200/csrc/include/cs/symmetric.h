@@ -24,8 +24,6 @@ struct CS_API SymmetricContext {
   int64_t arena_bytes{0};
   std::vector<char *> bases;       // bases[p]: rank p's arena as mapped into this process
   std::vector<uint32_t *> flags;   // flags[p]: rank p's signal pad (kFlagWords words)
-  char **device_bases{nullptr};    // the same pointers in device memory (for kernels)
-  uint32_t **device_flags{nullptr};
   void *status{nullptr};           // kernels::DeviceStatus in device memory
   uint32_t epoch{0};               // monotonically increasing barrier/flag generation
   static constexpr int kFlagWords = 4096;
@@ -40,6 +38,11 @@ struct CS_API SymmetricContext {
   [[nodiscard]] at::Tensor tensor(const SymmetricBlock &block, at::IntArrayRef sizes, at::ScalarType dtype) const;
   // True when [ptr, ptr+bytes) lies inside this rank's arena; *offset receives the position.
   bool locate(const void *ptr, int64_t bytes, int64_t *offset) const;
+  // Device-side barrier of all ranks on the current stream (bounded wait).
+  void barrier();
+  // Reusable staging block of at least `bytes` (same offset on every rank when every rank asks
+  // for the same sizes in the same order).
+  SymmetricBlock staging(int64_t bytes);
   ~SymmetricContext();
 
  private:
@@ -47,7 +50,9 @@ struct CS_API SymmetricContext {
   int64_t bump_{0};
   int64_t in_use_{0};
   std::vector<SymmetricBlock> free_;
+  SymmetricBlock staging_{};
   bool owns_{false};
+  std::vector<void *> opened_;  // IPC mappings to close
 };
 
 // Collective: every rank of `comm` must call it with the same size. Attaches the context to
@@ -56,7 +61,8 @@ CS_API std::shared_ptr<SymmetricContext> create_symmetric_context(const Comm &co
 
 // The collectives below run on the current stream; they return false when the tensors are
 // not eligible (the caller then uses the library path).
-CS_API bool symmetric_all_reduce(SymmetricContext &ctx, const std::vector<at::Tensor> &tensors, Operation op);
+// `ranges` are contiguous 1-D views (adjacent arena slots already merged by the caller).
+CS_API bool symmetric_all_reduce(SymmetricContext &ctx, const std::vector<at::Tensor> &ranges, Operation op);
 CS_API bool symmetric_all_gather(SymmetricContext &ctx, const std::vector<std::vector<at::Tensor>> &recv,
                                  const std::vector<at::Tensor> &send);
 CS_API bool symmetric_reduce_scatter(SymmetricContext &ctx, const std::vector<at::Tensor> &recv,

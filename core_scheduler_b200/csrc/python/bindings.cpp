@@ -2,6 +2,7 @@
 // no behaviour of its own to these calls: tests, the benchmark and the examples drive the same
 // C++ objects a C++ program would.
 #include <torch/csrc/distributed/c10d/Backend.hpp>
+#include <torch/csrc/distributed/c10d/GroupRegistry.hpp>
 #include <torch/csrc/distributed/c10d/ProcessGroup.hpp>
 #include <torch/extension.h>
 #include <c10/cuda/CUDAStream.h>
@@ -13,7 +14,9 @@
 #include "cs/models.h"
 #include "cs/modules.h"
 #include "cs/optimizer.h"
+#include "cs/parallel.h"
 #include "cs/symmetric.h"
+#include "kernels/collectives.h"
 #include "kernels/api.h"
 
 namespace py = pybind11;
@@ -33,8 +36,10 @@ py::dict tensor_dict(const Dict &d) {
   return out;
 }
 
-communication::Comm comm_from_process_group(const c10::intrusive_ptr<c10d::ProcessGroup> &pg, const std::string &device,
-                                            bool nvp2p) {
+// The group is looked up by name in libtorch's process-group registry (torch.distributed registers
+// every group it creates), which avoids sharing pybind11 type registrations with torch._C.
+communication::Comm comm_from_process_group(const std::string &group_name, const std::string &device, bool nvp2p) {
+  auto pg = c10d::resolve_process_group(group_name);
   const bool cuda = device == "cuda";
   auto backend = pg->getBackend(cuda ? c10::DeviceType::CUDA : c10::DeviceType::CPU);
   auto type = cuda ? (nvp2p ? communication::kNVP2P : communication::kNCCL) : communication::kGLOO;
@@ -511,7 +516,7 @@ PYBIND11_MODULE(_C, m) {
       .def("get_size", &Comm::get_size)
       .def("inject_failure_after", [](const Comm &c, int64_t n) { c.impl()->fail_after = n; })
       .def("has_symmetric", [](const Comm &c) { return c.impl()->symmetric != nullptr; });
-  m.def("comm_from_process_group", &comm_from_process_group, py::arg("process_group"), py::arg("device") = "cuda",
+  m.def("comm_from_process_group", &comm_from_process_group, py::arg("group_name"), py::arg("device") = "cuda",
         py::arg("nvp2p") = false);
   m.def("get_comm_world", [](const std::string &backend) {
     return communication::get_comm_world(backend == "nvp2p" ? communication::kNVP2P : communication::kNCCL);
@@ -538,6 +543,48 @@ PYBIND11_MODULE(_C, m) {
       .def(py::init<const Comm &, int64_t>())
       .def("beat", &communication::Heartbeat::beat)
       .def("stale_ranks", &communication::Heartbeat::stale_ranks);
+
+  // ---- symmetric memory / parallel strategies -------------------------------------------------
+  using communication::SymmetricContext;
+  py::class_<SymmetricContext, std::shared_ptr<SymmetricContext>>(m, "SymmetricContext")
+      .def_readonly("rank", &SymmetricContext::rank)
+      .def_readonly("size", &SymmetricContext::size)
+      .def_readonly("arena_bytes", &SymmetricContext::arena_bytes)
+      .def("bytes_in_use", &SymmetricContext::bytes_in_use)
+      .def("cached_blocks", &SymmetricContext::cached_blocks)
+      .def("empty", [](SymmetricContext &c, std::vector<int64_t> sizes, at::ScalarType dt) {
+        int64_t numel = 1;
+        for (auto v : sizes) numel *= v;
+        const auto block = c.allocate(numel * static_cast<int64_t>(c10::elementSize(dt)));
+        return py::make_tuple(c.tensor(block, sizes, dt), block.offset, block.bytes);
+      })
+      .def("release", [](SymmetricContext &c, int64_t offset, int64_t bytes) {
+        c.release(communication::SymmetricBlock{offset, bytes});
+      })
+      .def("check_status", [](SymmetricContext &c) { communication::check_device_status(c, "python"); });
+  m.def("create_symmetric_context", &communication::create_symmetric_context, py::arg("comm"), py::arg("arena_bytes"));
+  m.def("symmetric_barrier", [](const Scheduler &s, const Comm &c) {
+    cs::submit(s, "cs::communication::barrier", Task::Impl::kComm, Task::Impl::kNccl, {}, {},
+               [c](const FnTask &) { c.impl()->symmetric->barrier(); });
+  });
+  m.def("set_peer_wait_budget", &cs::kernels::set_peer_wait_budget);
+  m.def("flatten_symmetric", [](const Scheduler &s, const module::Module &mod, const Comm &c) {
+    return parallel::flatten_symmetric(s, mod, c);
+  });
+  py::class_<parallel::ZeroAdamWImpl, module::OptimizerModule, std::shared_ptr<parallel::ZeroAdamWImpl>>(m, "ZeroAdamW")
+      .def(py::init([](const Scheduler &s, const std::shared_ptr<module::Module> &mod,
+                       std::shared_ptr<module::FlatParameters> flat, const Comm &c, double lr, double beta1, double beta2,
+                       double eps, double wd) {
+             optimizer::AdamW::Options o;
+             o.lr(lr).beta1(beta1).beta2(beta2).eps(eps).weight_decay(wd);
+             return std::make_shared<parallel::ZeroAdamWImpl>(s, *mod, flat, c, o);
+           }),
+           py::keep_alive<1, 3>(), py::arg("scheduler"), py::arg("module"), py::arg("flat"), py::arg("comm"),
+           py::arg("lr") = 1e-3, py::arg("beta1") = 0.9, py::arg("beta2") = 0.999, py::arg("eps") = 1e-8,
+           py::arg("weight_decay") = 1e-2)
+      .def("gather_master", &parallel::ZeroAdamWImpl::gather_master)
+      .def("shard_begin", &parallel::ZeroAdamWImpl::shard_begin)
+      .def("shard_count", &parallel::ZeroAdamWImpl::shard_count);
 
   // ---- data ---------------------------------------------------------------------------------------
   py::class_<data::LlmDataset>(m, "LlmDataset")

@@ -164,8 +164,8 @@ void AllReduce::run_inplace(const Scheduler &scheduler, const Comm &comm, const 
              raw.push_back(t.impl()->tensor);
            }
            if (impl.size <= 1 || !impl.backend) return;
-           if (impl.type == kNVP2P && impl.symmetric && symmetric_all_reduce(*impl.symmetric, raw, operation)) return;
            std::vector<at::Tensor> ranges = merge_adjacent(raw);
+           if (impl.type == kNVP2P && impl.symmetric && symmetric_all_reduce(*impl.symmetric, ranges, operation)) return;
            const bool avg = backend_has_avg(impl);
            c10d::AllreduceOptions opts;
            opts.reduceOp = reduce_op(operation, avg);

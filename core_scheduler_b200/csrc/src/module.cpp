@@ -149,13 +149,21 @@ std::shared_ptr<FlatParameters> flatten_parameters(const Scheduler &scheduler, c
   for (auto &g : grad_handles) outs.push_back(g);
   submit(scheduler, "cs::module::flatten_parameters", Task::Impl::kMain, Task::Impl::kCompute, outs, {},
          [flat, param_handles, grad_handles, dtype, want_lp, lp_dtype = options.lp_dtype().value_or(at::kBFloat16),
-          transposed = options.transposed_copies(), device = scheduler.device()](const FnTask &) {
+          transposed = options.transposed_copies(), device = scheduler.device(),
+          alloc = options.arena_allocator()](const FnTask &) {
            auto opts = at::TensorOptions().device(device).dtype(dtype);
+           auto arena = [&](at::ScalarType dt) {
+             if (!alloc) return at::zeros({flat->total}, opts.dtype(dt));
+             at::Tensor raw = alloc(flat->total * static_cast<int64_t>(c10::elementSize(dt)));
+             at::Tensor typed = raw.view(dt);
+             typed.zero_();
+             return typed;
+           };
            at::Tensor P = at::zeros({flat->total}, opts);
-           at::Tensor G = at::zeros({flat->total}, opts);
+           at::Tensor G = arena(dtype);
            at::Tensor L, LT;
            if (want_lp) {
-             L = at::zeros({flat->total}, opts.dtype(lp_dtype));
+             L = arena(lp_dtype);
              if (transposed) LT = at::zeros({flat->total}, opts.dtype(lp_dtype));
            }
            for (size_t i = 0; i < flat->slots.size(); ++i) {

@@ -1,16 +1,333 @@
 // Symmetric memory context and peer-memory collectives (host side). See cs/symmetric.h.
 #include "cs/symmetric.h"
 
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <chrono>
+#include <thread>
+
+#include "kernels/collectives.h"
+
 namespace cs::communication {
-SymmetricContext::~SymmetricContext() = default;
-SymmetricBlock SymmetricContext::allocate(int64_t) { return {}; }
-void SymmetricContext::release(const SymmetricBlock &) {}
-at::Tensor SymmetricContext::tensor(const SymmetricBlock &, at::IntArrayRef, at::ScalarType) const { return {}; }
-bool SymmetricContext::locate(const void *, int64_t, int64_t *) const { return false; }
-std::shared_ptr<SymmetricContext> create_symmetric_context(const Comm &, int64_t) { return nullptr; }
-bool symmetric_all_reduce(SymmetricContext &, const std::vector<at::Tensor> &, Operation) { return false; }
-bool symmetric_all_gather(SymmetricContext &, const std::vector<std::vector<at::Tensor>> &, const std::vector<at::Tensor> &) { return false; }
-bool symmetric_reduce_scatter(SymmetricContext &, const std::vector<at::Tensor> &, const std::vector<std::vector<at::Tensor>> &, Operation) { return false; }
-bool symmetric_all_to_all(SymmetricContext &, const std::vector<at::Tensor> &, const std::vector<at::Tensor> &) { return false; }
-void check_device_status(SymmetricContext &, const char *) {}
+namespace {
+constexpr int64_t kAlign = 256;
+int64_t round_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+void *cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+void check(int code, const char *what) {
+  CS_ASSERT_TRUE(code == 0, "`", what, "` failed: ", cuda_error_string(code));
+}
+
+kernels::PeerTable table_of(const SymmetricContext &ctx) {
+  kernels::PeerTable t{};
+  for (int p = 0; p < ctx.size; ++p) {
+    t.base[p] = ctx.bases[p];
+    t.flags[p] = ctx.flags[p];
+  }
+  t.rank = ctx.rank;
+  t.size = ctx.size;
+  return t;
+}
+
+std::vector<uint8_t> to_bytes(const cudaIpcMemHandle_t &h) {
+  const auto *p = reinterpret_cast<const uint8_t *>(&h);
+  return std::vector<uint8_t>(p, p + sizeof(h));
+}
+cudaIpcMemHandle_t from_bytes(const std::vector<uint8_t> &b) {
+  cudaIpcMemHandle_t h;
+  CS_ASSERT_TRUE(b.size() == sizeof(h), "malformed IPC handle in the store");
+  std::memcpy(&h, b.data(), sizeof(h));
+  return h;
+}
+
+int dtype_code(at::ScalarType t) { return t == at::kFloat ? 0 : (t == at::kBFloat16 ? 1 : -1); }
+}  // namespace
+
+SymmetricContext::~SymmetricContext() {
+  if (!owns_) return;
+  // Mappings of peers first, then our own memory. Errors at teardown are ignored on purpose.
+  for (void *p : opened_) cudaIpcCloseMemHandle(p);
+  if (!bases.empty() && bases[rank]) cudaFree(bases[rank]);
+  if (!flags.empty() && flags[rank]) cudaFree(flags[rank]);
+  if (status) cudaFree(status);
+  (void)cudaGetLastError();
+}
+
+SymmetricBlock SymmetricContext::allocate(int64_t bytes) {
+  bytes = round_up(std::max<int64_t>(bytes, 1), kAlign);
+  // best fit among cached blocks
+  int best = -1;
+  for (size_t i = 0; i < free_.size(); ++i)
+    if (free_[i].bytes >= bytes && (best < 0 || free_[i].bytes < free_[best].bytes)) best = static_cast<int>(i);
+  if (best >= 0 && free_[best].bytes <= 2 * bytes) {
+    SymmetricBlock b = free_[best];
+    free_.erase(free_.begin() + best);
+    in_use_ += b.bytes;
+    return b;
+  }
+  CS_ASSERT_TRUE(bump_ + bytes <= arena_bytes, "symmetric arena exhausted: ", bump_, " + ", bytes, " > ", arena_bytes);
+  SymmetricBlock b{bump_, bytes};
+  bump_ += bytes;
+  in_use_ += bytes;
+  return b;
+}
+
+void SymmetricContext::release(const SymmetricBlock &block) {
+  if (block.bytes <= 0) return;
+  in_use_ -= block.bytes;
+  free_.push_back(block);
+}
+
+SymmetricBlock SymmetricContext::staging(int64_t bytes) {
+  if (staging_.bytes >= bytes) return staging_;
+  if (staging_.bytes > 0) release(staging_);
+  staging_ = allocate(std::max<int64_t>(bytes, 32 << 20));
+  return staging_;
+}
+
+at::Tensor SymmetricContext::tensor(const SymmetricBlock &block, at::IntArrayRef sizes, at::ScalarType dtype) const {
+  int64_t numel = 1;
+  for (auto s : sizes) numel *= s;
+  CS_ASSERT_TRUE(numel * static_cast<int64_t>(c10::elementSize(dtype)) <= block.bytes, "tensor does not fit its symmetric block");
+  return at::from_blob(bases[rank] + block.offset, sizes, [](void *) {},
+                       at::TensorOptions().dtype(dtype).device(at::kCUDA, static_cast<c10::DeviceIndex>(device)));
+}
+
+bool SymmetricContext::locate(const void *ptr, int64_t bytes, int64_t *offset) const {
+  const char *p = static_cast<const char *>(ptr);
+  const char *lo = bases[rank];
+  if (p < lo || p + bytes > lo + arena_bytes) return false;
+  *offset = p - lo;
+  return true;
+}
+
+void SymmetricContext::barrier() {
+  ++epoch;
+  check(kernels::symm_barrier(cur_stream(), table_of(*this), 0, epoch, static_cast<kernels::DeviceStatus *>(status)),
+        "symm_barrier");
+}
+
+std::shared_ptr<SymmetricContext> create_symmetric_context(const Comm &comm, int64_t arena_bytes) {
+  auto &impl = *comm.impl();
+  CS_ASSERT_TRUE(impl.size <= kernels::kMaxPeers, "symmetric memory supports up to ", kernels::kMaxPeers, " ranks");
+  auto ctx = std::make_shared<SymmetricContext>();
+  ctx->rank = static_cast<int>(impl.rank);
+  ctx->size = static_cast<int>(impl.size);
+  int device = 0;
+  CS_CHECK_CUDART(cudaGetDevice(&device));
+  ctx->device = device;
+  ctx->arena_bytes = round_up(arena_bytes, kAlign);
+  ctx->bases.assign(ctx->size, nullptr);
+  ctx->flags.assign(ctx->size, nullptr);
+  ctx->owns_ = true;
+  void *base = nullptr, *pad = nullptr;
+  CS_CHECK_CUDART(cudaMalloc(&base, ctx->arena_bytes));
+  CS_CHECK_CUDART(cudaMalloc(&pad, SymmetricContext::kFlagWords * sizeof(uint32_t)));
+  CS_CHECK_CUDART(cudaMalloc(&ctx->status, sizeof(kernels::DeviceStatus)));
+  CS_CHECK_CUDART(cudaMemset(pad, 0, SymmetricContext::kFlagWords * sizeof(uint32_t)));
+  CS_CHECK_CUDART(cudaMemset(ctx->status, 0, sizeof(kernels::DeviceStatus)));
+  CS_CHECK_CUDART(cudaDeviceSynchronize());
+  ctx->bases[ctx->rank] = static_cast<char *>(base);
+  ctx->flags[ctx->rank] = static_cast<uint32_t *>(pad);
+  if (ctx->size > 1) {
+    CS_ASSERT_TRUE(impl.store != nullptr, "symmetric memory needs the communicator's store to exchange IPC handles");
+    static int generation = 0;
+    const std::string prefix = str_cat("cs/symm/", generation++, "/");
+    cudaIpcMemHandle_t h_base, h_pad;
+    CS_CHECK_CUDART(cudaIpcGetMemHandle(&h_base, base));
+    CS_CHECK_CUDART(cudaIpcGetMemHandle(&h_pad, pad));
+    impl.store->set(str_cat(prefix, "arena/", ctx->rank), to_bytes(h_base));
+    impl.store->set(str_cat(prefix, "flags/", ctx->rank), to_bytes(h_pad));
+    for (int p = 0; p < ctx->size; ++p) {
+      if (p == ctx->rank) continue;
+      auto hb = from_bytes(impl.store->get(str_cat(prefix, "arena/", p)));
+      auto hp = from_bytes(impl.store->get(str_cat(prefix, "flags/", p)));
+      void *pb = nullptr, *pp = nullptr;
+      CS_CHECK_CUDART(cudaIpcOpenMemHandle(&pb, hb, cudaIpcMemLazyEnablePeerAccess));
+      CS_CHECK_CUDART(cudaIpcOpenMemHandle(&pp, hp, cudaIpcMemLazyEnablePeerAccess));
+      ctx->bases[p] = static_cast<char *>(pb);
+      ctx->flags[p] = static_cast<uint32_t *>(pp);
+      ctx->opened_.push_back(pb);
+      ctx->opened_.push_back(pp);
+    }
+    // host rendezvous: nobody proceeds (and possibly frees) before everyone mapped everything
+    impl.store->add(str_cat(prefix, "mapped"), 1);
+    const auto t0 = std::chrono::steady_clock::now();
+    while (impl.store->add(str_cat(prefix, "mapped"), 0) < ctx->size) {
+      CS_ASSERT_TRUE(std::chrono::steady_clock::now() - t0 < std::chrono::seconds(120),
+                     "timed out waiting for all ranks to map the symmetric arena");
+      std::this_thread::sleep_for(std::chrono::milliseconds(2));
+    }
+  }
+  impl.symmetric = ctx;
+  return ctx;
+}
+
+void check_device_status(SymmetricContext &ctx, const char *where) {
+  kernels::DeviceStatus st{};
+  CS_CHECK_CUDART(cudaMemcpy(&st, ctx.status, sizeof(st), cudaMemcpyDeviceToHost));
+  if (st.code == 0) return;
+  CS_CHECK_CUDART(cudaMemset(ctx.status, 0, sizeof(st)));
+  fail(__FILE__, __LINE__,
+       str_cat("device-side wait timed out in ", where, ": code=", st.code, " kernel=", st.kernel_id, " peer/block=", st.block,
+               " detail=", st.detail, " (rank ", ctx.rank, ")"));
+}
+
+// ------------------------------------------------------------------------ collectives ----
+bool symmetric_all_reduce(SymmetricContext &ctx, const std::vector<at::Tensor> &ranges, Operation op) {
+  for (auto &r : ranges)
+    if (!r.is_cuda() || !r.is_contiguous() || dtype_code(r.scalar_type()) < 0 || r.nbytes() % 16 != 0 ||
+        (reinterpret_cast<uintptr_t>(r.data_ptr()) & 15))
+      return false;
+  const float scale = op == kAVG ? 1.0f / static_cast<float>(ctx.size) : 1.0f;
+  const auto table = table_of(ctx);
+  for (auto &r : ranges) {
+    int64_t offset = 0;
+    const int dt = dtype_code(r.scalar_type());
+    if (ctx.locate(r.data_ptr(), static_cast<int64_t>(r.nbytes()), &offset)) {
+      ctx.barrier();  // every rank's contribution is complete
+      check(kernels::symm_all_reduce_inplace(cur_stream(), table, offset, r.numel(), dt, scale), "symm_all_reduce_inplace");
+      ctx.barrier();  // every slice has been written everywhere
+    } else {
+      // Not in the arena: stage the contribution, reduce straight into the destination.
+      const SymmetricBlock st = ctx.staging(static_cast<int64_t>(r.nbytes()));
+      CS_CHECK_CUDART(cudaMemcpyAsync(ctx.bases[ctx.rank] + st.offset, r.data_ptr(), r.nbytes(), cudaMemcpyDeviceToDevice,
+                                      static_cast<cudaStream_t>(cur_stream())));
+      ctx.barrier();
+      check(kernels::symm_all_reduce_oneshot(cur_stream(), table, st.offset, r.data_ptr(), r.numel(), dt, scale),
+            "symm_all_reduce_oneshot");
+      ctx.barrier();  // staging may be overwritten by the next call only after everyone read it
+    }
+  }
+  return true;
+}
+
+bool symmetric_all_gather(SymmetricContext &ctx, const std::vector<std::vector<at::Tensor>> &recv,
+                          const std::vector<at::Tensor> &send) {
+  for (size_t i = 0; i < send.size(); ++i) {
+    if (!send[i].is_cuda() || !send[i].is_contiguous() || send[i].nbytes() % 16 != 0) return false;
+    for (auto &r : recv[i])
+      if (!r.is_contiguous() || r.nbytes() != send[i].nbytes() || (reinterpret_cast<uintptr_t>(r.data_ptr()) & 15)) return false;
+  }
+  const auto table = table_of(ctx);
+  auto stream = static_cast<cudaStream_t>(cur_stream());
+  for (size_t i = 0; i < send.size(); ++i) {
+    const int64_t bytes = static_cast<int64_t>(send[i].nbytes());
+    int64_t offset = 0;
+    if (!ctx.locate(send[i].data_ptr(), bytes, &offset)) {
+      const SymmetricBlock st = ctx.staging(bytes);
+      offset = st.offset;
+      CS_CHECK_CUDART(cudaMemcpyAsync(ctx.bases[ctx.rank] + offset, send[i].data_ptr(), bytes, cudaMemcpyDeviceToDevice, stream));
+    }
+    ctx.barrier();
+    kernels::PullCopyArgs a{};
+    for (int p = 0; p < ctx.size; ++p) {
+      a.src_offset[p] = offset;
+      a.dst[p] = static_cast<char *>(recv[i][p].data_ptr());
+    }
+    a.rows = 1;
+    a.row_bytes = bytes;
+    a.src_stride = bytes;
+    a.dst_stride = bytes;
+    check(kernels::symm_pull_copy(cur_stream(), table, a), "symm_pull_copy");
+    ctx.barrier();
+  }
+  return true;
+}
+
+bool symmetric_reduce_scatter(SymmetricContext &ctx, const std::vector<at::Tensor> &recv,
+                              const std::vector<std::vector<at::Tensor>> &send, Operation op) {
+  for (size_t i = 0; i < recv.size(); ++i) {
+    if (!recv[i].is_cuda() || !recv[i].is_contiguous() || dtype_code(recv[i].scalar_type()) < 0 || recv[i].nbytes() % 16 != 0 ||
+        (reinterpret_cast<uintptr_t>(recv[i].data_ptr()) & 15))
+      return false;
+    for (auto &s : send[i])
+      if (!s.is_contiguous() || s.nbytes() != recv[i].nbytes() || s.scalar_type() != recv[i].scalar_type()) return false;
+  }
+  const float scale = op == kAVG ? 1.0f / static_cast<float>(ctx.size) : 1.0f;
+  const auto table = table_of(ctx);
+  auto stream = static_cast<cudaStream_t>(cur_stream());
+  for (size_t i = 0; i < recv.size(); ++i) {
+    const int64_t chunk = static_cast<int64_t>(recv[i].nbytes());
+    // Contiguous send chunks already in the arena are read in place; otherwise stage them.
+    int64_t first = 0;
+    bool in_place = ctx.locate(send[i][0].data_ptr(), chunk * ctx.size, &first);
+    for (int p = 1; in_place && p < ctx.size; ++p)
+      in_place = static_cast<const char *>(send[i][p].data_ptr()) == static_cast<const char *>(send[i][0].data_ptr()) + p * chunk;
+    int64_t offset = first;
+    if (!in_place) {
+      const SymmetricBlock st = ctx.staging(chunk * ctx.size);
+      offset = st.offset;
+      for (int p = 0; p < ctx.size; ++p)
+        CS_CHECK_CUDART(cudaMemcpyAsync(ctx.bases[ctx.rank] + offset + p * chunk, send[i][p].data_ptr(), chunk,
+                                        cudaMemcpyDeviceToDevice, stream));
+    }
+    ctx.barrier();
+    check(kernels::symm_pull_reduce(cur_stream(), table, offset + ctx.rank * chunk, recv[i].data_ptr(), recv[i].numel(),
+                                    dtype_code(recv[i].scalar_type()), scale),
+          "symm_pull_reduce");
+    ctx.barrier();
+  }
+  return true;
+}
+
+bool symmetric_all_to_all(SymmetricContext &ctx, const std::vector<at::Tensor> &recv, const std::vector<at::Tensor> &send) {
+  // Chunks may be 2-D row-strided views (pack/unpack fused into the transfer) as long as every
+  // chunk has the same [rows, row_bytes] and, when read in place, the same row stride.
+  auto rows_of = [](const at::Tensor &t) { return t.dim() == 2 ? t.size(0) : 1; };
+  auto row_bytes_of = [](const at::Tensor &t) {
+    return static_cast<int64_t>((t.dim() == 2 ? t.size(1) : t.numel()) * t.element_size());
+  };
+  auto row_stride_of = [&](const at::Tensor &t) {
+    return t.dim() == 2 ? static_cast<int64_t>(t.stride(0) * t.element_size()) : row_bytes_of(t);
+  };
+  auto row_major = [](const at::Tensor &t) { return t.dim() == 2 ? t.stride(1) == 1 : t.is_contiguous(); };
+  const int64_t rows = rows_of(send[0]), row_bytes = row_bytes_of(send[0]);
+  for (int p = 0; p < ctx.size; ++p) {
+    if (!send[p].is_cuda() || !row_major(send[p]) || !row_major(recv[p])) return false;
+    if (rows_of(send[p]) != rows || rows_of(recv[p]) != rows || row_bytes_of(send[p]) != row_bytes || row_bytes_of(recv[p]) != row_bytes)
+      return false;
+    if (row_bytes % 16 != 0 || row_stride_of(send[p]) % 16 != 0 || row_stride_of(recv[p]) % 16 != 0) return false;
+    if (row_stride_of(recv[p]) != row_stride_of(recv[0])) return false;
+    if ((reinterpret_cast<uintptr_t>(recv[p].data_ptr()) | reinterpret_cast<uintptr_t>(send[p].data_ptr())) & 15) return false;
+  }
+  const auto table = table_of(ctx);
+  auto stream = static_cast<cudaStream_t>(cur_stream());
+  // Source of the chunk this rank wants from peer p = peer p's send[rank]; it must sit at an
+  // offset that is the same on every rank, so either all send chunks are equally strided views
+  // of one arena block, or they are packed into the staging block.
+  std::vector<int64_t> send_offsets(ctx.size);
+  bool in_place = true;
+  const int64_t src_stride = row_stride_of(send[0]);
+  for (int p = 0; p < ctx.size && in_place; ++p) {
+    in_place = row_stride_of(send[p]) == src_stride &&
+               ctx.locate(send[p].data_ptr(), (rows - 1) * src_stride + row_bytes, &send_offsets[p]);
+  }
+  kernels::PullCopyArgs a{};
+  a.rows = rows;
+  a.row_bytes = row_bytes;
+  a.dst_stride = row_stride_of(recv[0]);
+  if (in_place) {
+    // every rank laid its chunks out identically, so peer p's chunk for us is at our own offset of send[rank]
+    a.src_stride = src_stride;
+    for (int p = 0; p < ctx.size; ++p) a.src_offset[p] = send_offsets[ctx.rank];
+  } else {
+    const int64_t chunk = rows * row_bytes;
+    const SymmetricBlock st = ctx.staging(chunk * ctx.size);
+    for (int p = 0; p < ctx.size; ++p)
+      CS_CHECK_CUDART(cudaMemcpy2DAsync(ctx.bases[ctx.rank] + st.offset + p * chunk, row_bytes, send[p].data_ptr(),
+                                        row_stride_of(send[p]), row_bytes, rows, cudaMemcpyDeviceToDevice, stream));
+    a.src_stride = row_bytes;
+    for (int p = 0; p < ctx.size; ++p) a.src_offset[p] = st.offset + ctx.rank * chunk;
+  }
+  for (int p = 0; p < ctx.size; ++p) a.dst[p] = static_cast<char *>(recv[p].data_ptr());
+  ctx.barrier();
+  check(kernels::symm_pull_copy(cur_stream(), table, a), "symm_pull_copy");
+  ctx.barrier();
+  return true;
+}
 }  // namespace cs::communication

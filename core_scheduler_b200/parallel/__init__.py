@@ -30,5 +30,5 @@ def init_distributed(device: str = "cuda", timeout_s: float = 600.0):
         else:
             dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=timeout_s))
     pg = dist.distributed_c10d._get_default_group()
-    comm = _C.comm_from_process_group(pg, device)
+    comm = _C.comm_from_process_group(pg.group_name, device)
     return comm, rank, world, local_rank

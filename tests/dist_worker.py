@@ -1,0 +1,273 @@
+"""Multi-rank test body. Launched by tests/test_distributed*.py through torch.distributed.run:
+
+    python -m torch.distributed.run --standalone ... tests/dist_worker.py <device> <case>
+
+Every case asserts on every rank and prints `OK <case>` from rank 0 when all ranks passed.
+"""
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import core_scheduler_b200 as cs  # noqa: E402
+from core_scheduler_b200.parallel import init_distributed  # noqa: E402
+
+C = cs._C
+T = cs.from_torch
+
+
+def seeded(seed, *shape, dtype=torch.float32, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g).to(dtype).to(device)
+
+
+def make_comm(device, nvp2p=False, arena_mb=256):
+    comm, rank, world, local_rank = init_distributed(device)
+    if device == "cuda" and nvp2p:
+        pg = dist.distributed_c10d._get_default_group()
+        comm = C.comm_from_process_group(pg.group_name, "cuda", True)
+        C.create_symmetric_context(comm, arena_mb << 20)
+    s = cs.DynamicScheduler(local_rank if device == "cuda" else 0, device=device)
+    return comm, rank, world, s
+
+
+def case_all_reduce(device, nvp2p):
+    comm, rank, world, s = make_comm(device, nvp2p)
+    for dtype in (torch.float32, torch.bfloat16) if device == "cuda" else (torch.float32, torch.float64):
+        # every tensor of a multi-tensor call gets the reduced value, the last one included
+        xs = [seeded(100 * rank + i, 128 * (i + 1), dtype=dtype, device=device) for i in range(3)]
+        expect = [sum(seeded(100 * r + i, 128 * (i + 1), dtype=dtype, device=device).double() for r in range(world)) for i in range(3)]
+        hs = [T(x.clone()) for x in xs]
+        C.all_reduce(s, comm, hs, "sum")
+        for h, e in zip(hs, expect):
+            got = cs.to_torch(s, h).double()
+            assert torch.allclose(got, e, rtol=2e-2 if dtype == torch.bfloat16 else 1e-6, atol=1e-1 if dtype == torch.bfloat16 else 1e-6), (rank, dtype)
+        h = T(xs[0].clone())
+        C.all_reduce(s, comm, [h], "avg")
+        assert torch.allclose(cs.to_torch(s, h).double(), expect[0] / world, rtol=2e-2, atol=1e-1 if dtype == torch.bfloat16 else 1e-6)
+    # large message (8 MiB) on GPUs
+    if device == "cuda":
+        big = seeded(rank, 1 << 21, device=device)
+        e = sum(seeded(r, 1 << 21, device=device) for r in range(world))
+        h = T(big.clone())
+        C.all_reduce(s, comm, [h], "sum")
+        assert torch.allclose(cs.to_torch(s, h), e, atol=1e-4)
+
+
+def case_bucket(device, nvp2p):
+    comm, rank, world, s = make_comm(device, nvp2p)
+    bucket = cs.AllReduceBucket(1024 * 4, "sum")  # 1024 fp32 elements
+    xs = [T(torch.full((400,), float(rank + 1 + i), device=device)) for i in range(5)]
+    for x in xs:
+        bucket.push_back(s, comm, x)
+    assert bucket.launches() == 1  # 3 x 400 elements crossed the threshold once; two tensors still queued
+    bucket.sync(s, comm)           # the partial last bucket must be flushed in the same step
+    assert bucket.launches() == 2
+    total_rank = sum(range(1, world + 1))
+    for i, x in enumerate(xs):
+        assert torch.allclose(cs.to_torch(s, x), torch.full((400,), float(total_rank + world * i), device=device)), (rank, i)
+
+
+def case_all_gather(device, nvp2p):
+    comm, rank, world, s = make_comm(device, nvp2p)
+    send = T(seeded(rank + 1, 128, device=device))
+    recv = [T(torch.zeros(128, device=device)) for _ in range(world)]
+    C.all_gather(s, comm, [recv], [send])
+    for r in range(world):
+        assert torch.allclose(cs.to_torch(s, recv[r]), seeded(r + 1, 128, device=device)), (rank, r)
+
+
+def case_reduce_scatter(device, nvp2p):
+    comm, rank, world, s = make_comm(device, nvp2p)
+    send = [T(seeded(10 * rank + p, 128, device=device)) for p in range(world)]
+    recv = T(torch.zeros(128, device=device))
+    C.reduce_scatter(s, comm, [recv], [send], "sum")
+    expect = sum(seeded(10 * r + rank, 128, device=device) for r in range(world))
+    assert torch.allclose(cs.to_torch(s, recv), expect, atol=1e-5), rank
+
+
+def case_all_to_all(device, nvp2p):
+    comm, rank, world, s = make_comm(device, nvp2p)
+    send = [T(seeded(10 * rank + p, 128, device=device)) for p in range(world)]
+    recv = [T(torch.zeros(128, device=device)) for _ in range(world)]
+    C.all_to_all(s, comm, recv, send)
+    for p in range(world):
+        assert torch.allclose(cs.to_torch(s, recv[p]), seeded(10 * p + rank, 128, device=device)), (rank, p)
+    if device == "cuda" and nvp2p:
+        # pack/unpack fused: strided [rows, cols] column blocks of one symmetric buffer go straight
+        # into strided column blocks of the destination
+        ctx_rows, cols = 64, 32
+        symm = comm_symmetric_tensor(comm, [ctx_rows, cols * world], torch.float32)
+        symm.copy_(seeded(500 + rank, ctx_rows, cols * world, device=device))
+        dst = torch.zeros(ctx_rows, cols * world, device=device)
+        send2 = [T(symm[:, p * cols:(p + 1) * cols]) for p in range(world)]
+        recv2 = [T(dst[:, p * cols:(p + 1) * cols]) for p in range(world)]
+        C.all_to_all(s, comm, recv2, send2)
+        s.synchronize()
+        for p in range(world):
+            src = seeded(500 + p, ctx_rows, cols * world, device=device)[:, rank * cols:(rank + 1) * cols]
+            assert torch.allclose(dst[:, p * cols:(p + 1) * cols], src), (rank, p)
+
+
+_symm_keep = []
+
+
+def comm_symmetric_tensor(comm, sizes, dtype):
+    ctx = C.create_symmetric_context(comm, 64 << 20)
+    t, off, nbytes = ctx.empty(sizes, dtype)
+    _symm_keep.append(ctx)
+    return t
+
+
+def tiny_model(s, seed=0):
+    cs.manual_seed(seed)
+    cfg = cs.GPT2Config(n_layer=2, n_head=2, n_embd=64, block_size=32, vocab_size=128, padded_vocab_size=128)
+    return cfg, cs.GPT2(s, cfg)
+
+
+def case_dp_training(device, nvp2p):
+    """Two-rank data-parallel steps equal single-process steps on the concatenated batch."""
+    comm, rank, world, s = make_comm(device, nvp2p)
+    _, model = tiny_model(s)
+    _, ref = tiny_model(s)
+    amp = device == "cuda"
+    if amp:
+        flat = C.flatten_symmetric(s, model, comm) if nvp2p else C.flatten_parameters(s, model, lp_dtype=torch.bfloat16)
+        rflat = C.flatten_parameters(s, ref, lp_dtype=torch.bfloat16)
+    else:
+        flat, rflat = C.flatten_parameters(s, model), C.flatten_parameters(s, ref)
+    opt = cs.AdamW(s, model, lr=1e-2, weight_decay=0.1, flat=flat)
+    ropt = cs.AdamW(s, ref, lr=1e-2, weight_decay=0.1, flat=rflat)
+    opt.set_grad_scale(1.0 / world)
+    ropt.set_grad_scale(1.0 / world)
+    bucket = cs.AllReduceBucket(64 * 1024, "sum")
+    sync = cs.GradientSync(comm, bucket, True)
+    g = torch.Generator().manual_seed(7)
+    for step in range(3):
+        ids = torch.randint(0, 128, (world, 2, 33), generator=g).to(device)
+        mine = ids[rank]
+        def run(m, x):
+            if amp:
+                with cs.autocast(s, torch.bfloat16):
+                    return m.forward_loss(s, T(x[:, :-1].contiguous()), T(x[:, 1:].contiguous()))
+            return m.forward_loss(s, T(x[:, :-1].contiguous()), T(x[:, 1:].contiguous()))
+        run(model, mine)
+        model.backward_loss(s, sync)
+        bucket.sync(s, comm)
+        opt.step(s)
+        opt.zero_grad(s)
+        for r in range(world):  # reference: accumulate every rank's micro-batch locally
+            run(ref, ids[r])
+            ref.backward_loss(s)
+        ropt.step(s)
+        ropt.zero_grad(s)
+    s.synchronize()
+    pa, pb = model.named_parameters(), ref.named_parameters()
+    tol = 3e-3 if amp else 1e-5
+    for k in pa:
+        assert torch.allclose(pa[k].raw(), pb[k].raw(), atol=tol), (rank, k, (pa[k].raw() - pb[k].raw()).abs().max().item())
+    assert bucket.launches() >= 3
+
+
+def case_zero_training(device, nvp2p):
+    """ZeRO (fused reduce-scatter + AdamW + all-gather) equals replicated data-parallel AdamW."""
+    comm, rank, world, s = make_comm(device, True)
+    _, model = tiny_model(s)
+    _, ref = tiny_model(s)
+    flat = C.flatten_symmetric(s, model, comm)
+    rflat = C.flatten_parameters(s, ref, lp_dtype=torch.bfloat16)
+    opt = C.ZeroAdamW(s, model, flat, comm, lr=1e-2, weight_decay=0.1)
+    ropt = cs.AdamW(s, ref, lr=1e-2, weight_decay=0.1, flat=rflat)
+    ropt.set_grad_scale(1.0 / world)
+    g = torch.Generator().manual_seed(11)
+    for step in range(3):
+        ids = torch.randint(0, 128, (world, 2, 33), generator=g).to(device)
+        with cs.autocast(s, torch.bfloat16):
+            model.forward_loss(s, T(ids[rank][:, :-1].contiguous()), T(ids[rank][:, 1:].contiguous()))
+        model.backward_loss(s)
+        opt.step(s)
+        opt.zero_grad(s)
+        for r in range(world):
+            with cs.autocast(s, torch.bfloat16):
+                ref.forward_loss(s, T(ids[r][:, :-1].contiguous()), T(ids[r][:, 1:].contiguous()))
+            ref.backward_loss(s)
+        ropt.step(s)
+        ropt.zero_grad(s)
+    opt.gather_master(s)
+    s.synchronize()
+    pa, pb = model.named_parameters(), ref.named_parameters()
+    for k in pa:
+        assert torch.allclose(pa[k].raw(), pb[k].raw(), atol=3e-3), (rank, k, (pa[k].raw() - pb[k].raw()).abs().max().item())
+        assert torch.allclose(pa[k].lp().float(), pb[k].lp().float(), atol=2e-2), (rank, k)
+
+
+def case_failure_injection(device, nvp2p):
+    """A collective that fails on one rank surfaces as an error there; the others see the rank stop beating."""
+    comm, rank, world, s = make_comm(device, False)
+    hb = C.Heartbeat(comm, 500)
+    hb.beat(0)
+    dist.barrier()
+    assert hb.stale_ranks() == []
+    x = T(torch.ones(8, device=device))
+    C.all_reduce(s, comm, [x], "sum")  # healthy step
+    failed = False
+    if rank == world - 1:
+        comm.inject_failure_after(0)
+        try:
+            C.all_reduce(s, comm, [x], "sum")
+        except RuntimeError as e:
+            failed = "injected communication failure" in str(e)
+        assert failed
+        # this rank stops between steps (nothing in flight) and never beats again
+    else:
+        deadline = time.time() + 10
+        stale = []
+        while time.time() < deadline:
+            hb.beat(1)
+            stale = hb.stale_ranks()
+            if stale:
+                break
+            time.sleep(0.1)
+        assert stale == [world - 1], (rank, stale)
+    dist.barrier()
+
+
+def case_timeout_status(device, nvp2p):
+    """A peer flag that nothing sets: the barrier kernel gives up within its budget and reports it."""
+    comm, rank, world, s = make_comm(device, True)
+    ctx = C.create_symmetric_context(comm, 1 << 20)
+    C.set_peer_wait_budget(2_000_000)  # about a millisecond
+    if rank == 0:
+        C.symmetric_barrier(s, comm)   # nobody else joins this barrier
+        s.synchronize()
+        try:
+            ctx.check_status()
+            raised = False
+        except RuntimeError as e:
+            raised = "timed out" in str(e)
+        assert raised
+        ctx.check_status()  # cleared, context still usable
+        y = torch.ones(4, device="cuda") * 2
+        assert y.sum().item() == 8
+    dist.barrier()
+    C.set_peer_wait_budget(4_000_000_000)
+
+
+CASES = {k[len("case_"):]: v for k, v in globals().items() if k.startswith("case_")}
+
+if __name__ == "__main__":
+    device, case = sys.argv[1], sys.argv[2]
+    nvp2p = len(sys.argv) > 3 and sys.argv[3] == "nvp2p"
+    CASES[case](device, nvp2p)
+    if dist.is_initialized():
+        dist.barrier()
+        if dist.get_rank() == 0:
+            print(f"OK {case}")
+        dist.destroy_process_group()
+    else:
+        print(f"OK {case}")
