@@ -39,6 +39,7 @@ def parse_args():
     p.add_argument("--comm", default="nvp2p", choices=["nvp2p", "nccl"],
                    help="gradient collectives: this library's peer-memory kernels, or NCCL")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--profile", action="store_true", help="print per-task device time of one step (not a bench value)")
     return p.parse_args()
 
 
@@ -147,6 +148,21 @@ def main():
         loss = trainer.step(*batches[i % len(batches)])
     trainer.s.synchronize()
     barrier(world)
+    if args.profile:
+        trainer.s.set_profiling(True)
+        trainer.step(*batches[0])
+        rows = trainer.s.drain_timings()
+        trainer.s.set_profiling(False)
+        if rank == 0:
+            agg = {}
+            for r in rows:
+                a = agg.setdefault((r.name, r.stream_class), [0, 0.0])
+                a[0] += 1
+                a[1] += r.device_ms
+            total = sum(v[1] for v in agg.values())
+            print(f"per-task device time of one step (sum over streams {total:.3f} ms; tasks overlap across streams)", file=sys.stderr)
+            for (name, cls), (n, ms) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
+                print(f"  {ms:8.3f} ms  x{n:4d}  stream{cls}  {name}", file=sys.stderr)
 
     sampler = ClockSampler(local_rank).start() if rank == 0 else None
     launches_before = C.kernel_launch_count()

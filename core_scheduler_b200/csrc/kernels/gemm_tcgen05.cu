@@ -179,6 +179,133 @@ __device__ __forceinline__ TileCoord tile_coord(const KParams &p, int tile) {
   return c;
 }
 
+// One warp's share of a finished accumulator tile: lane quadrant q (rows m0 + 32q .. +32) and
+// column half `half` (128 of the 256 columns). tmem_acc is the TMEM address of the tile.
+__device__ __forceinline__ void epilogue_tile(const KParams &p, int m0, int n0, int n_tile, uint32_t tmem_acc, int q,
+                                              int half, int lane) {
+  const long long row = m0 + q * 32 + lane;
+  const bool row_ok = row < p.m;
+  float run_max = -INFINITY, run_sum = 0.f;
+#pragma unroll 1
+  for (int ch = 0; ch < 4; ++ch) {
+    const int col0 = half * 128 + ch * 32;
+    uint32_t v[32];
+    tcgen05_ld_32x32b_x32(tmem_acc + col0 + (static_cast<uint32_t>(q * 32) << 16), v);
+    tcgen05_wait_ld();
+    const long long gcol = n0 + col0;
+    if (!row_ok || gcol >= p.n) continue;
+    float f[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+    if (p.epilogue == kEpiStoreF32 || p.epilogue == kEpiAccumF32) {
+      float *dst = static_cast<float *>(p.d) + row * p.ldd + gcol;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        if (gcol + g * 4 + 4 > p.n) break;
+        if (p.atomic_out) {
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + g * 4), "f"(f[4 * g]),
+                       "f"(f[4 * g + 1]), "f"(f[4 * g + 2]), "f"(f[4 * g + 3])
+                       : "memory");
+        } else {
+          float4 o = make_float4(f[4 * g], f[4 * g + 1], f[4 * g + 2], f[4 * g + 3]);
+          if (p.epilogue == kEpiAccumF32) {
+            const float4 old = *reinterpret_cast<const float4 *>(dst + g * 4);
+            o.x += old.x;
+            o.y += old.y;
+            o.z += old.z;
+            o.w += old.w;
+          }
+          *reinterpret_cast<float4 *>(dst + g * 4) = o;
+        }
+      }
+      continue;
+    }
+    if (p.bias) {
+      const uint4 *bp = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.bias) + gcol);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (gcol + g * 8 + 8 > p.n) break;
+        const uint4 b = __ldg(bp + g);
+        const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 t = unpack_bf16(w[i]);
+          f[g * 8 + 2 * i] += t.x;
+          f[g * 8 + 2 * i + 1] += t.y;
+        }
+      }
+    }
+    __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(p.d) + row * p.ldd + gcol;
+    if (p.epilogue == kEpiResidualBf16 || p.epilogue == kEpiDGelu) {
+      const uint4 *ap = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.aux) + row * p.ldd + gcol);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (gcol + g * 8 + 8 > p.n) break;
+        const uint4 a = *(ap + g);
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 t = unpack_bf16(w[i]);
+          if (p.epilogue == kEpiResidualBf16) {
+            f[g * 8 + 2 * i] += t.x;
+            f[g * 8 + 2 * i + 1] += t.y;
+          } else {
+            f[g * 8 + 2 * i] *= gelu_grad_f(t.x);
+            f[g * 8 + 2 * i + 1] *= gelu_grad_f(t.y);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (gcol + g * 8 + 8 > p.n) break;
+      uint4 o;
+      o.x = pack_bf16(f[g * 8 + 0], f[g * 8 + 1]);
+      o.y = pack_bf16(f[g * 8 + 2], f[g * 8 + 3]);
+      o.z = pack_bf16(f[g * 8 + 4], f[g * 8 + 5]);
+      o.w = pack_bf16(f[g * 8 + 6], f[g * 8 + 7]);
+      *reinterpret_cast<uint4 *>(dst + g * 8) = o;
+    }
+    if (p.epilogue == kEpiGeluDual) {
+      __nv_bfloat16 *dst2 = static_cast<__nv_bfloat16 *>(p.d2) + row * p.ldd + gcol;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (gcol + g * 8 + 8 > p.n) break;
+        uint4 o;
+        // GELU of the value as stored (bf16-rounded), so that backward sees the same input
+        o.x = pack_bf16(gelu_f(bf16_round(f[g * 8 + 0])), gelu_f(bf16_round(f[g * 8 + 1])));
+        o.y = pack_bf16(gelu_f(bf16_round(f[g * 8 + 2])), gelu_f(bf16_round(f[g * 8 + 3])));
+        o.z = pack_bf16(gelu_f(bf16_round(f[g * 8 + 4])), gelu_f(bf16_round(f[g * 8 + 5])));
+        o.w = pack_bf16(gelu_f(bf16_round(f[g * 8 + 6])), gelu_f(bf16_round(f[g * 8 + 7])));
+        *reinterpret_cast<uint4 *>(dst2 + g * 8) = o;
+      }
+    }
+    if (p.epilogue == kEpiCrossEntropy) {
+      // running (max, sum-exp) over the valid columns, on the bf16-rounded logits
+      float cmax = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        f[i] = bf16_round(f[i]);
+        if (gcol + i < p.n_valid) cmax = fmaxf(cmax, f[i]);
+      }
+      if (cmax > -INFINITY) {
+        const float new_max = fmaxf(run_max, cmax);
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (gcol + i < p.n_valid) s += __expf(f[i] - new_max);
+        run_sum = run_sum * __expf(run_max - new_max) + s;
+        run_max = new_max;
+      }
+    }
+  }
+  if (p.epilogue == kEpiCrossEntropy && row_ok) {
+    float *st = p.stats + (row * (2LL * p.n_tiles) + 2LL * n_tile + half) * 2;
+    st[0] = run_max;
+    st[1] = run_sum;
+  }
+}
+
 // ------------------------------------------------------------------------------ kernel ----
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KParams p) {
@@ -325,127 +452,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const TileCoord c = tile_coord(p, tile);
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag)) break;
       tcgen05_fence_after();
-      const long long row = c.m0 + q * 32 + lane;
-      const bool row_ok = row < p.m;
-      float run_max = -INFINITY, run_sum = 0.f;
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        const int col0 = half * 128 + ch * 32;
-        uint32_t v[32];
-        tcgen05_ld_32x32b_x32(tmem_base + acc * BN + col0 + (static_cast<uint32_t>(q * 32) << 16), v);
-        tcgen05_wait_ld();
-        const long long gcol = c.n0 + col0;
-        if (!row_ok || gcol >= p.n) continue;
-        float f[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
-        if (p.epilogue == kEpiStoreF32 || p.epilogue == kEpiAccumF32) {
-          float *dst = static_cast<float *>(p.d) + row * p.ldd + gcol;
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            if (gcol + g * 4 + 4 > p.n) break;
-            if (p.atomic_out) {
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + g * 4), "f"(f[4 * g]),
-                           "f"(f[4 * g + 1]), "f"(f[4 * g + 2]), "f"(f[4 * g + 3])
-                           : "memory");
-            } else {
-              float4 o = make_float4(f[4 * g], f[4 * g + 1], f[4 * g + 2], f[4 * g + 3]);
-              if (p.epilogue == kEpiAccumF32) {
-                const float4 old = *reinterpret_cast<const float4 *>(dst + g * 4);
-                o.x += old.x;
-                o.y += old.y;
-                o.z += old.z;
-                o.w += old.w;
-              }
-              *reinterpret_cast<float4 *>(dst + g * 4) = o;
-            }
-          }
-          continue;
-        }
-        if (p.bias) {
-          const uint4 *bp = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.bias) + gcol);
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (gcol + g * 8 + 8 > p.n) break;
-            const uint4 b = __ldg(bp + g);
-            const uint32_t w[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 t = unpack_bf16(w[i]);
-              f[g * 8 + 2 * i] += t.x;
-              f[g * 8 + 2 * i + 1] += t.y;
-            }
-          }
-        }
-        __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(p.d) + row * p.ldd + gcol;
-        if (p.epilogue == kEpiResidualBf16 || p.epilogue == kEpiDGelu) {
-          const uint4 *ap = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.aux) + row * p.ldd + gcol);
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (gcol + g * 8 + 8 > p.n) break;
-            const uint4 a = *(ap + g);
-            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 t = unpack_bf16(w[i]);
-              if (p.epilogue == kEpiResidualBf16) {
-                f[g * 8 + 2 * i] += t.x;
-                f[g * 8 + 2 * i + 1] += t.y;
-              } else {
-                f[g * 8 + 2 * i] *= gelu_grad_f(t.x);
-                f[g * 8 + 2 * i + 1] *= gelu_grad_f(t.y);
-              }
-            }
-          }
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          if (gcol + g * 8 + 8 > p.n) break;
-          uint4 o;
-          o.x = pack_bf16(f[g * 8 + 0], f[g * 8 + 1]);
-          o.y = pack_bf16(f[g * 8 + 2], f[g * 8 + 3]);
-          o.z = pack_bf16(f[g * 8 + 4], f[g * 8 + 5]);
-          o.w = pack_bf16(f[g * 8 + 6], f[g * 8 + 7]);
-          *reinterpret_cast<uint4 *>(dst + g * 8) = o;
-        }
-        if (p.epilogue == kEpiGeluDual) {
-          __nv_bfloat16 *dst2 = static_cast<__nv_bfloat16 *>(p.d2) + row * p.ldd + gcol;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (gcol + g * 8 + 8 > p.n) break;
-            uint4 o;
-            // GELU of the value as stored (bf16-rounded), so that backward sees the same input
-            o.x = pack_bf16(gelu_f(bf16_round(f[g * 8 + 0])), gelu_f(bf16_round(f[g * 8 + 1])));
-            o.y = pack_bf16(gelu_f(bf16_round(f[g * 8 + 2])), gelu_f(bf16_round(f[g * 8 + 3])));
-            o.z = pack_bf16(gelu_f(bf16_round(f[g * 8 + 4])), gelu_f(bf16_round(f[g * 8 + 5])));
-            o.w = pack_bf16(gelu_f(bf16_round(f[g * 8 + 6])), gelu_f(bf16_round(f[g * 8 + 7])));
-            *reinterpret_cast<uint4 *>(dst2 + g * 8) = o;
-          }
-        }
-        if (p.epilogue == kEpiCrossEntropy) {
-          // running (max, sum-exp) over the valid columns, on the bf16-rounded logits
-          float cmax = -INFINITY;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            f[i] = bf16_round(f[i]);
-            if (gcol + i < p.n_valid) cmax = fmaxf(cmax, f[i]);
-          }
-          if (cmax > -INFINITY) {
-            const float new_max = fmaxf(run_max, cmax);
-            float s = 0.f;
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (gcol + i < p.n_valid) s += __expf(f[i] - new_max);
-            run_sum = run_sum * __expf(run_max - new_max) + s;
-            run_max = new_max;
-          }
-        }
-      }
-      if (p.epilogue == kEpiCrossEntropy && row_ok) {
-        float *st = p.stats + (row * (2LL * p.n_tiles) + 2LL * c.n_tile + half) * 2;
-        st[0] = run_max;
-        st[1] = run_sum;
-      }
+      epilogue_tile(p, c.m0, c.n0, c.n_tile, tmem_base + acc * BN, q, half, lane);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
@@ -468,6 +475,246 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   if (warp == 1) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+
+// ===================================================================================
+// 2-CTA variant: a thread-block cluster of two CTAs on neighbouring SMs computes one 256x256
+// tile with tcgen05.mma.cta_group::2. CTA r of the pair loads rows [128r, 128r+128) of the A
+// tile and rows [128r, 128r+128) of the B tile (plain TMA loads, no multicast), so every CTA
+// moves 32 KB per 256x256x64 block instead of 48 KB per 128x256x64 block: one third less
+// L2-to-shared-memory traffic per FLOP, which is what bounds the 1-CTA kernel.
+// The leader CTA (cluster rank 0) issues the MMAs for the pair; barriers:
+//   full[s]       in the leader: the leader's producer arrives with the byte count of both
+//                 CTAs, both CTAs' TMA loads complete on it
+//   empty[s]      in each CTA: tcgen05.commit multicasts the arrival to both
+//   tmem_full[b]  in each CTA (multicast commit); tmem_empty[b] in the leader, counted by the
+//                 epilogue warps of both CTAs
+// ===================================================================================
+constexpr int STAGES2 = 6;
+constexpr int B2_BYTES = 128 * BK * 2;               // this CTA's half of the B tile
+constexpr int STAGE2_BYTES = A_BYTES + B2_BYTES;     // 32 KB
+constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 256;
+constexpr int BM2 = 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(cta));
+  return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(mask)
+               : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ TileCoord tile_coord2(const KParams &p, int tile) {
+  const int mn = p.m_tiles * p.n_tiles;
+  const int split = tile / mn;
+  const int rem = tile - split * mn;
+  const int n_tile = rem / p.m_tiles;
+  const int m_tile = rem - n_tile * p.m_tiles;
+  TileCoord c;
+  c.m0 = m_tile * BM2;
+  c.n0 = n_tile * BN;
+  c.n_tile = n_tile;
+  c.kb_begin = split * p.kb_per_split;
+  c.kb_end = min(p.kb_total, c.kb_begin + p.kb_per_split);
+  return c;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_aligned + STAGES2 * STAGE2_BYTES);
+  const uint32_t bar_base = smem_base + STAGES2 * STAGE2_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES2 + s); };
+  auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES2 + b); };
+  auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES2 + 2 + b); };
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars + 2 * STAGES2 + 4);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * STAGES2 + 5);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();
+  const bool leader = cta == 0;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int total_tiles = p.m_tiles * p.n_tiles * p.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tmem_full_bar(b), 1);
+      mbar_init(tmem_empty_bar(b), 2 * EPI_WARPS);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t *>(tmem_slot))),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anyone signals across the pair
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------- TMA producer (one per CTA) ----
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
+        const TileCoord c = tile_coord2(p, tile);
+        const int m0 = c.m0 + static_cast<int>(cta) * 128;   // this CTA's rows of A / D
+        const int nb0 = c.n0 + static_cast<int>(cta) * 128;  // this CTA's rows of the B tile
+        for (int kb = c.kb_begin; kb < c.kb_end; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + stage * STAGE2_BYTES;
+          const uint32_t b_dst = a_dst + A_BYTES;
+          const uint32_t full_leader = mapa_shared(full_bar(stage), 0);
+          if (leader) mbar_expect_tx(full_bar(stage), 2 * STAGE2_BYTES);
+          if (p.layout == kTN) {
+            tma_load_2d_pair(a_dst, &map_a, full_leader, kb * BK, m0);
+            tma_load_2d_pair(b_dst, &map_b, full_leader, kb * BK, nb0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) tma_load_2d_pair(a_dst + j * 8192, &map_a, full_leader, m0 + j * 64, kb * BK);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) tma_load_2d_pair(b_dst + j * 8192, &map_b, full_leader, nb0 + j * 64, kb * BK);
+          }
+          if (++stage == STAGES2) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer (leader CTA only) ----
+    if (lane == 0 && leader) {
+      const uint32_t major = p.layout == kNT ? 1u : 0u;
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (major << 15) | (major << 16) |
+                             (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM2 >> 4) << 24);
+      const uint32_t lbo = p.layout == kNT ? p.lbo_mn : 16u;
+      const uint32_t sbo = p.layout == kNT ? p.sbo_mn : 1024u;
+      const uint32_t kstep = p.layout == kNT ? p.kstep_mn : static_cast<uint32_t>(UMMA_K * 2);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
+        const TileCoord c = tile_coord2(p, tile);
+        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag)) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = c.kb_begin; kb < c.kb_end; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t a_src = smem_base + stage * STAGE2_BYTES;
+          const uint32_t b_src = a_src + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = make_smem_desc(a_src + k * kstep, lbo, sbo);
+            const uint64_t db = make_smem_desc(b_src + k * kstep, lbo, sbo);
+            tcgen05_mma_pair(d_tmem, da, db, idesc, (kb > c.kb_begin || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit_pair(empty_bar(stage));
+          if (++stage == STAGES2) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tcgen05_commit_pair(tmem_full_bar(acc));
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------- epilogue (each CTA) ----
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = pair; tile < total_tiles; tile += num_pairs) {
+      const TileCoord c = tile_coord2(p, tile);
+      if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag)) break;
+      tcgen05_fence_after();
+      epilogue_tile(p, c.m0 + static_cast<int>(cta) * 128, c.n0, c.n_tile, tmem_base + acc * BN, q, half, lane);
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(tmem_empty_bar(acc), 0));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------------- teardown ----
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer may still be signalling our barriers or reading our shared memory
+  if (threadIdx.x == 0 && *abort_flag) {
+    p.status->code = 1;
+    p.status->kernel_id = 2;
+    p.status->block = blockIdx.x;
+    p.status->detail = p.layout;
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -573,10 +820,14 @@ int gemm_bf16(stream_t stream, const GemmArgs &a) {
   static const bool disabled = std::getenv("CS_DISABLE_TCGEN05_GEMM") != nullptr;
   if (disabled) return -1;
 
+  static const bool one_cta_only = std::getenv("CS_GEMM_1CTA") != nullptr;
+  const bool pair_kernel = !one_cta_only && a.m > 128;  // a single 128-row tile gains nothing from pairing
+  const int tile_m = pair_kernel ? BM2 : BM;
+  const uint32_t b_box_rows = pair_kernel ? 128u : static_cast<uint32_t>(BN);
   CUtensorMap map_a, map_b;
   if (a.layout == kTN) {
     if (!get_tensor_map(a.a, a.k, a.m, a.lda, BK, BM, &map_a)) return -1;
-    if (!get_tensor_map(a.b, a.k, a.n, a.ldb, BK, BN, &map_b)) return -1;
+    if (!get_tensor_map(a.b, a.k, a.n, a.ldb, BK, b_box_rows, &map_b)) return -1;
   } else {
     if (!get_tensor_map(a.a, a.m, a.k, a.lda, 64, BK, &map_a)) return -1;
     if (!get_tensor_map(a.b, a.n, a.k, a.ldb, 64, BK, &map_b)) return -1;
@@ -595,7 +846,7 @@ int gemm_bf16(stream_t stream, const GemmArgs &a) {
   p.n_valid = a.n_valid > 0 ? a.n_valid : a.n;
   p.layout = a.layout;
   p.epilogue = a.epilogue;
-  p.m_tiles = static_cast<int>((a.m + BM - 1) / BM);
+  p.m_tiles = static_cast<int>((a.m + tile_m - 1) / tile_m);
   p.n_tiles = static_cast<int>((a.n + BN - 1) / BN);
   p.kb_total = static_cast<int>((a.k + BK - 1) / BK);
   p.splits = 1;
@@ -609,7 +860,8 @@ int gemm_bf16(stream_t stream, const GemmArgs &a) {
     // Weight gradients have few output tiles and a long reduction: split K so that every SM
     // has work; partial sums meet in the fp32 output through vector atomics.
     const int mn = p.m_tiles * p.n_tiles;
-    int want = (2 * sm_count + mn - 1) / mn;
+    const int workers = pair_kernel ? sm_count / 2 : sm_count;
+    int want = (2 * workers + mn - 1) / mn;
     const int max_splits = p.kb_total / 4 > 0 ? p.kb_total / 4 : 1;
     if (want > max_splits) want = max_splits;
     if (want < 1) want = 1;
@@ -638,10 +890,30 @@ int gemm_bf16(stream_t stream, const GemmArgs &a) {
   p.status = status_ptr;
 
   static const bool attr_set = [] {
-    return cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) == cudaSuccess;
+    return cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) == cudaSuccess &&
+           cudaFuncSetAttribute(gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES) == cudaSuccess;
   }();
   if (!attr_set) return -1;
   const int total_tiles = p.m_tiles * p.n_tiles * p.splits;
+  if (pair_kernel) {
+    const int pairs = sm_count / 2;
+    const int grid = 2 * (total_tiles < pairs ? total_tiles : pairs);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM2_BYTES;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm2_kernel, map_a, map_b, p);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    return finish_launch(1);
+  }
   const int grid = total_tiles < sm_count ? total_tiles : sm_count;
   gemm_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(map_a, map_b, p);
   return finish_launch(1);

@@ -6,7 +6,9 @@
 #include <ATen/cuda/CUDAContext.h>
 
 #include <cmath>
+#include <cstdlib>
 #include <limits>
+#include <string>
 
 #include "cs/compute.h"
 #include "op_common.h"
@@ -66,6 +68,17 @@ bool library_flash_ok(const at::Tensor &q) {
          q.size(-1) <= 256;
 }
 
+// Library engine for half/bf16 CUDA attention: "cudnn" (fused flash attention of cuDNN, the
+// counterpart of the reference's ScaledDotProductCuDnn) or "flash" (the flash-attention kernels
+// bundled with libtorch, the counterpart of ScaledDotProductFlashAttention).
+bool use_cudnn_engine() {
+  static const bool cudnn = [] {
+    const char *e = std::getenv("CS_ATTENTION_ENGINE");
+    return e == nullptr || std::string(e) != "flash";
+  }();
+  return cudnn;
+}
+
 double resolve_scale(const optional<double> &scale, int64_t head_dim) {
   return scale.has_value() ? *scale : 1.0 / std::sqrt(static_cast<double>(head_dim));
 }
@@ -80,6 +93,19 @@ at::Tensor attention_forward_body(const at::Tensor &q4, const at::Tensor &k4, co
                                   ScaledDotProductAttention::State::Backward *bw_meta, const Saved &saved) {
   const at::Tensor q = q4.transpose(1, 2), k = k4.transpose(1, 2), v = v4.transpose(1, 2);  // [B,H,T,D]
   const double scale = resolve_scale(args.scale, q.size(-1));
+  if (library_flash_ok(q) && use_cudnn_engine() && q.size(-1) <= 128) {
+    auto r = at::_scaled_dot_product_cudnn_attention(q, k, v, std::nullopt, true, args.dropout_p, args.is_causal,
+                                                     args.return_debug_mask, scale);
+    saved.out.impl()->tensor = std::get<0>(r);
+    saved.lse.impl()->tensor = std::get<1>(r);
+    saved.cum_q.impl()->tensor = std::get<2>(r);
+    saved.cum_k.impl()->tensor = std::get<3>(r);
+    bw_meta->max_q = std::get<4>(r).expect_int();
+    bw_meta->max_k = std::get<5>(r).expect_int();
+    saved.seed.impl()->tensor = std::get<6>(r);
+    saved.offset.impl()->tensor = std::get<7>(r);
+    return std::get<0>(r).transpose(1, 2);
+  }
   if (library_flash_ok(q)) {
     auto r = at::_scaled_dot_product_flash_attention(q, k, v, args.dropout_p, args.is_causal, args.return_debug_mask,
                                                      scale);
@@ -109,6 +135,13 @@ std::array<at::Tensor, 3> attention_backward_body(const at::Tensor &dout4, const
   const double scale = resolve_scale(args.scale, q.size(-1));
   const at::Tensor &out = bw.out.impl()->tensor;
   const at::Tensor &lse = bw.logsumexp.impl()->tensor;
+  if (library_flash_ok(q) && use_cudnn_engine() && q.size(-1) <= 128) {
+    auto r = at::_scaled_dot_product_cudnn_attention_backward(
+        dout.to(q.scalar_type()).contiguous(), q, k, v, out, lse, bw.philox_seed.impl()->tensor, bw.philox_offset.impl()->tensor,
+        at::Tensor{}, bw.cum_seq_q.impl()->tensor, bw.cum_seq_k.impl()->tensor, bw.max_q, bw.max_k, args.dropout_p,
+        args.is_causal, scale);
+    return {std::get<0>(r).transpose(1, 2), std::get<1>(r).transpose(1, 2), std::get<2>(r).transpose(1, 2)};
+  }
   if (library_flash_ok(q)) {
     auto r = at::_scaled_dot_product_flash_attention_backward(
         dout.to(q.scalar_type()), q, k, v, out, lse, bw.cum_seq_q.impl()->tensor, bw.cum_seq_k.impl()->tensor,

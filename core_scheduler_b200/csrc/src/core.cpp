@@ -277,6 +277,9 @@ struct CudaImpl final : Scheduler::Impl {
     streams_.push_back(c10::cuda::getStreamFromPool(-2, dev));
     const char *p = std::getenv("CS_PROFILE");
     profiling_ = p && p[0] == '1';
+    // Experiment switch: run assist-class tasks on the main stream (no compute/compute overlap).
+    const char *a = std::getenv("CS_ASSIST_ON_MAIN");
+    if (a && a[0] == '1') streams_[Task::Impl::kAssist] = streams_[Task::Impl::kMain];
   }
 
   ~CudaImpl() override {

@@ -236,6 +236,17 @@ void AdamWImpl::step(const Scheduler &scheduler) {
     if (flat_->lp.defined()) {
       pimpl.lp = flat_->lp.impl()->tensor;
     }
+    // Gradients are written through the per-parameter views (by backward on the assist stream and
+    // by collectives on the comm stream); joining them here orders the update after all of them.
+    {
+      std::vector<ReadOnlyTensor> writers(flat_->grad_handles.begin(), flat_->grad_handles.end());
+      submit(scheduler, "cs::module::AdamW::join_gradients", Task::Impl::kAssist, Task::Impl::kCompute, {flat_->grads},
+             writers, [handles = flat_->grad_handles](const FnTask &) {
+               // a slot nobody wrote this step must not contribute stale values
+               for (auto &h : handles)
+                 if (h.impl()->fresh && h.impl()->tensor.defined()) h.impl()->tensor.zero_();
+             });
+    }
     OptAdamW::step(scheduler, flat_state_, flat_->params, flat_->grads);
     for (auto &s : states_) std::dynamic_pointer_cast<OptAdamW::State>(s.second)->options.t = flat_state_->options.t;
     auto named = m->named_parameters();

@@ -60,6 +60,14 @@ void ZeroAdamWImpl::step(const Scheduler &scheduler) {
   auto named = m->named_parameters();
   std::vector<Tensor> touched;
   for (auto &slot : flat_->slots) touched.push_back(named[slot.key]);
+  {
+    std::vector<ReadOnlyTensor> writers(flat_->grad_handles.begin(), flat_->grad_handles.end());
+    submit(scheduler, "cs::parallel::ZeroAdamW::join_gradients", Task::Impl::kComm, Task::Impl::kCompute, {flat_->grads}, writers,
+           [handles = flat_->grad_handles](const FnTask &) {
+             for (auto &h : handles)
+               if (h.impl()->fresh && h.impl()->tensor.defined()) h.impl()->tensor.zero_();
+           });
+  }
   std::vector<Tensor> outs{flat_->params, flat_->lp, state_->tensors.m, state_->tensors.v};
   outs.insert(outs.end(), touched.begin(), touched.end());
   submit(scheduler, "cs::parallel::ZeroAdamW::step", Task::Impl::kComm, Task::Impl::kNccl, outs, {flat_->grads},

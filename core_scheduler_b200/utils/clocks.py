@@ -17,7 +17,7 @@ _REASONS = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_pow
 class ClockSampler:
     """Polls `nvidia-smi --query-gpu` (never sets anything) every `period_ms` for one GPU index."""
 
-    def __init__(self, gpu_index: int = 0, period_ms: int = 200):
+    def __init__(self, gpu_index: int = 0, period_ms: int = 50):
         self.gpu_index = gpu_index
         self.period_ms = period_ms
         self.samples: list[dict] = []

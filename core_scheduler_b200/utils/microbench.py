@@ -39,17 +39,20 @@ def flush_l2():
     _flush.zero_()
 
 
-def time_ms(fn, iters=10, warmup=3):
+def time_ms(fn, iters=10, warmup=3, stream=None):
+    """Median CUDA-event time of fn() on `stream` (the launching stream; default: torch's current)."""
+    stream = stream or torch.cuda.current_stream()
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     times = []
     for _ in range(iters):
         flush_l2()
+        torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
+        a.record(stream)
         fn()
-        b.record()
+        b.record(stream)
         torch.cuda.synchronize()
         times.append(a.elapsed_time(b))
     times.sort()
@@ -87,6 +90,8 @@ def bench_gemm():
 def bench_elementwise():
     _, gbs_peak, tag = peaks()
     s = cs.DynamicScheduler(0, device="cuda")
+    main = torch.cuda.ExternalStream(s.raw_stream(0))
+    assist = torch.cuda.ExternalStream(s.raw_stream(1))
     rows, d = 16384, 768
     x = torch.randn(rows, d, device="cuda").to(BF)
     ln = C.layer_norm_init(s, [d])
@@ -96,23 +101,45 @@ def bench_elementwise():
         with cs.autocast(s, BF):
             C.layer_norm_forward(s, ln, tx)
 
-    t = time_ms(ln_fwd)
+    t = time_ms(ln_fwd, stream=main)
     print(f"layernorm fwd [{rows},{d}] {t:.4f} ms {2 * x.numel() * 2 / t / 1e6:.0f} GB/s ({2 * x.numel() * 2 / t / 1e6 / gbs_peak:.2f} of {tag})")
+    dy = cs.from_torch(torch.randn(rows, d, device="cuda").to(BF))
+
+    def ln_bwd():
+        with cs.autocast(s, BF):
+            C.layer_norm_forward(s, ln, tx)
+        C.layer_norm_backward(s, ln, dy, dy)
+
+    t_both = time_ms(ln_bwd, stream=main)
+    print(f"layernorm fwd+bwd(+residual) [{rows},{d}] {t_both:.4f} ms -> bwd alone {t_both - t:.4f} ms "
+          f"{4 * x.numel() * 2 / (t_both - t) / 1e6:.0f} GB/s ({4 * x.numel() * 2 / (t_both - t) / 1e6 / gbs_peak:.2f} of {tag})")
     g = C.gelu_init(s)
     y = torch.randn(rows, 4 * d, device="cuda").to(BF)
     ty = cs.from_torch(y)
-    t = time_ms(lambda: C.gelu_forward(s, g, ty))
+    t = time_ms(lambda: C.gelu_forward(s, g, ty), stream=main)
     print(f"gelu fwd [{rows},{4 * d}] {t:.4f} ms {2 * y.numel() * 2 / t / 1e6:.0f} GB/s ({2 * y.numel() * 2 / t / 1e6 / gbs_peak:.2f} of {tag})")
     n = 163_000_000
     w = cs.from_torch(torch.randn(n, device="cuda"))
     C.working_copy(s, w, BF)
     st = C.adamw_init(s, w)
     gr = cs.from_torch(torch.randn(n, device="cuda"))
-    t = time_ms(lambda: C.adamw_step(s, st, w, gr))
+    t = time_ms(lambda: C.adamw_step(s, st, w, gr), stream=assist)
     bytes_moved = n * (4 * 4 + 3 * 4 + 2)
     print(f"adamw fp32 master + bf16 copy n={n} {t:.4f} ms {bytes_moved / t / 1e6:.0f} GB/s ({bytes_moved / t / 1e6 / gbs_peak:.2f} of {tag})")
 
 
+def gemm_one():
+    """One GPT-2 shape, a handful of launches: the workload for an ncu capture."""
+    M, N, K = 16384, 3072, 768
+    a = torch.randn(M, K, device="cuda").to(BF)
+    b = torch.randn(N, K, device="cuda").to(BF)
+    d = torch.empty(M, N, device="cuda", dtype=BF)
+    for _ in range(5):
+        C.gemm_bf16(a, b, d, 0, 0)
+    torch.cuda.synchronize()
+    print("gemm_one done")
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    {"gemm": bench_gemm, "elementwise": bench_elementwise}[what]()
+    {"gemm": bench_gemm, "elementwise": bench_elementwise, "gemm_one": gemm_one}[what]()

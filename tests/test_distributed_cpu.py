@@ -16,7 +16,10 @@ def run_case(case, nproc=2, device="cpu", extra=(), timeout=240, env_extra=None)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1", "--nnodes=1",
            f"--nproc-per-node={nproc}", os.path.join(HERE, "dist_worker.py"), device, case, *extra]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
-    assert proc.returncode == 0 and f"OK {case}" in proc.stdout, proc.stdout[-3000:] + proc.stderr[-3000:]
+    if proc.returncode != 0 or f"OK {case}" not in proc.stdout:
+        lines = [l for l in (proc.stdout + proc.stderr).splitlines()
+                 if any(k in l for k in ("Error", "error", "assert", "Assert", "Traceback", "File \"/"))]
+        raise AssertionError("\n".join(lines[-40:]))
 
 
 @pytest.mark.parametrize("case", ["all_reduce", "bucket", "all_gather", "reduce_scatter", "all_to_all", "dp_training",
