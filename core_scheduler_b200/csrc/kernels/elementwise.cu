@@ -321,7 +321,7 @@ int transpose_cast_to_bf16(stream_t stream, const void *src, int src_dtype, void
 namespace {
 constexpr int kLnWarps = 4;       // rows per CTA iteration
 constexpr int kLnMaxChunks = 8;   // register-resident path: d <= 8 * 256 = 2048
-constexpr int kLnBwdCtas = kSmCount * 4;
+constexpr int kLnBwdCtas = kSmCount * 3;
 
 // One warp per row. Lane l owns the 8-element chunks l, l+32, ... of the row.
 template <int CHUNKS>
@@ -383,47 +383,87 @@ __global__ void __launch_bounds__(kLnWarps * 32) ln_fwd_kernel(const __nv_bfloat
   }
 }
 
-// Backward: one warp per row, grid-stride over rows; each lane keeps dgamma/dbeta partials for
-// its chunks in registers, warps of a CTA combine through shared memory and the CTA writes one
-// partial row to scratch; ln_bwd_reduce_kernel sums the partial rows.
+// Backward: one warp per row, grid-stride over rows, with the next row's operands (packed bf16,
+// still in their 128-bit load registers) fetched while the current row is reduced, so that
+// global loads stay in flight during the shuffles. Each lane keeps dgamma/dbeta partials for
+// its chunks in registers; gamma sits in shared memory. At the end the warps of a CTA combine
+// through shared memory and the CTA writes one partial row to scratch; ln_bwd_reduce_kernel
+// sums the partial rows.
+template <int CHUNKS>
+struct LnRowRegs {
+  Bf16x8 x[CHUNKS], dy[CHUNKS], res[CHUNKS];
+  float mu, rs;
+};
+
+template <int CHUNKS>
+__device__ __forceinline__ void ln_load_row(LnRowRegs<CHUNKS> &r, const __nv_bfloat16 *x, const __nv_bfloat16 *dy,
+                                            const __nv_bfloat16 *dres, const float *mean, const float *rstd, int64_t row,
+                                            int d, int nchunks, int lane) {
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int chunk = lane + 32 * c;
+    if (chunk < nchunks) {
+      r.x[c] = *reinterpret_cast<const Bf16x8 *>(x + row * d + chunk * 8);
+      r.dy[c] = *reinterpret_cast<const Bf16x8 *>(dy + row * d + chunk * 8);
+      if (dres) r.res[c] = *reinterpret_cast<const Bf16x8 *>(dres + row * d + chunk * 8);
+    }
+  }
+  r.mu = mean[row];
+  r.rs = rstd[row];
+}
+
 template <int CHUNKS>
 __global__ void __launch_bounds__(kLnWarps * 32) ln_bwd_kernel(
     const __nv_bfloat16 *__restrict__ dy, const __nv_bfloat16 *__restrict__ x, const void *__restrict__ gamma, int pdt,
     const float *__restrict__ mean, const float *__restrict__ rstd, const __nv_bfloat16 *__restrict__ dres,
     __nv_bfloat16 *__restrict__ dx, float *__restrict__ scratch, int64_t rows, int d) {
-  extern __shared__ float smem[];  // [kLnWarps][2][d]
+  extern __shared__ float smem[];  // [d] gamma, then [kLnWarps][2][d] partials
+  float *gamma_s = smem;
+  float *partial_s = smem + d;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nchunks = d / 8;
-  float dg[CHUNKS][8], db[CHUNKS][8], g[CHUNKS][8];
+  for (int i = threadIdx.x; i < nchunks; i += blockDim.x) {
+    float g[8];
+    load8(gamma, i * 8, pdt, g);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) gamma_s[i * 8 + k] = g[k];
+  }
+  __syncthreads();
+  float dg[CHUNKS][8], db[CHUNKS][8];
 #pragma unroll
   for (int c = 0; c < CHUNKS; ++c) {
-    const int chunk = lane + 32 * c;
-    if (chunk < nchunks) load8(gamma, chunk * 8, pdt, g[c]);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       dg[c][k] = 0.f;
       db[c][k] = 0.f;
     }
   }
-  for (int64_t row = static_cast<int64_t>(blockIdx.x) * kLnWarps + warp; row < rows;
-       row += static_cast<int64_t>(gridDim.x) * kLnWarps) {
-    const float mu = mean[row], rs = rstd[row];
-    float xh[CHUNKS][8], gy[CHUNKS][8];
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kLnWarps;
+  int64_t row = static_cast<int64_t>(blockIdx.x) * kLnWarps + warp;
+  LnRowRegs<CHUNKS> cur, nxt;
+  if (row < rows) ln_load_row<CHUNKS>(cur, x, dy, dres, mean, rstd, row, d, nchunks, lane);
+  while (row < rows) {
+    const int64_t next = row + stride;
+    if (next < rows) ln_load_row<CHUNKS>(nxt, x, dy, dres, mean, rstd, next, d, nchunks, lane);
+    const float mu = cur.mu, rs = cur.rs;
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
       const int chunk = lane + 32 * c;
       if (chunk < nchunks) {
         float xv[8], dyv[8];
-        unpack(*reinterpret_cast<const Bf16x8 *>(x + row * d + chunk * 8), xv);
-        unpack(*reinterpret_cast<const Bf16x8 *>(dy + row * d + chunk * 8), dyv);
+        unpack(cur.x[c], xv);
+        unpack(cur.dy[c], dyv);
+        const float4 g0 = *reinterpret_cast<const float4 *>(gamma_s + chunk * 8);
+        const float4 g1 = *reinterpret_cast<const float4 *>(gamma_s + chunk * 8 + 4);
+        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          xh[c][k] = (xv[k] - mu) * rs;
-          gy[c][k] = dyv[k] * g[c][k];
-          s1 += gy[c][k] * xh[c][k];
-          s2 += gy[c][k];
-          dg[c][k] += dyv[k] * xh[c][k];
+          const float xh = (xv[k] - mu) * rs;
+          const float gy = dyv[k] * g[k];
+          s1 += gy * xh;
+          s2 += gy;
+          dg[c][k] += dyv[k] * xh;
           db[c][k] += dyv[k];
         }
       }
@@ -433,20 +473,27 @@ __global__ void __launch_bounds__(kLnWarps * 32) ln_bwd_kernel(
     for (int c = 0; c < CHUNKS; ++c) {
       const int chunk = lane + 32 * c;
       if (chunk < nchunks) {
-        float o[8];
+        float xv[8], dyv[8], o[8];
+        unpack(cur.x[c], xv);
+        unpack(cur.dy[c], dyv);
+        const float4 g0 = *reinterpret_cast<const float4 *>(gamma_s + chunk * 8);
+        const float4 g1 = *reinterpret_cast<const float4 *>(gamma_s + chunk * 8 + 4);
+        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
 #pragma unroll
-        for (int k = 0; k < 8; ++k) o[k] = rs * (gy[c][k] - c2 - xh[c][k] * c1);
+        for (int k = 0; k < 8; ++k) o[k] = rs * (dyv[k] * g[k] - c2 - (xv[k] - mu) * rs * c1);
         if (dres) {
           float r[8];
-          unpack(*reinterpret_cast<const Bf16x8 *>(dres + row * d + chunk * 8), r);
+          unpack(cur.res[c], r);
 #pragma unroll
           for (int k = 0; k < 8; ++k) o[k] += r[k];
         }
         *reinterpret_cast<Bf16x8 *>(dx + row * d + chunk * 8) = pack(o);
       }
     }
+    cur = nxt;
+    row = next;
   }
-  float *my = smem + warp * 2 * d;
+  float *my = partial_s + warp * 2 * d;
 #pragma unroll
   for (int c = 0; c < CHUNKS; ++c) {
     const int chunk = lane + 32 * c;
@@ -462,27 +509,27 @@ __global__ void __launch_bounds__(kLnWarps * 32) ln_bwd_kernel(
   for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) {
     float acc = 0.f;
 #pragma unroll
-    for (int w = 0; w < kLnWarps; ++w) acc += smem[w * 2 * d + i];
+    for (int w = 0; w < kLnWarps; ++w) acc += partial_s[w * 2 * d + i];
     scratch[static_cast<int64_t>(blockIdx.x) * 2 * d + i] = acc;
   }
 }
 
-__global__ void __launch_bounds__(256) ln_bwd_reduce_kernel(const float *__restrict__ scratch, int parts, int d,
-                                                            float *__restrict__ dgamma, float *__restrict__ dbeta,
-                                                            int accumulate) {
-  // blockDim = (32, 8): 32 columns per CTA, 8 row-groups summed through shared memory
-  __shared__ float red[8][33];
+__global__ void __launch_bounds__(1024) ln_bwd_reduce_kernel(const float *__restrict__ scratch, int parts, int d,
+                                                             float *__restrict__ dgamma, float *__restrict__ dbeta,
+                                                             int accumulate) {
+  // blockDim = (32, 32): 32 columns per CTA, 32 row-groups summed through shared memory
+  __shared__ float red[32][33];
   const int col = blockIdx.x * 32 + threadIdx.x;
   const int which = blockIdx.y;  // 0 = dgamma, 1 = dbeta
   float acc = 0.f;
   if (col < d)
-    for (int p = threadIdx.y; p < parts; p += 8) acc += scratch[static_cast<int64_t>(p) * 2 * d + which * d + col];
+    for (int p = threadIdx.y; p < parts; p += 32) acc += scratch[static_cast<int64_t>(p) * 2 * d + which * d + col];
   red[threadIdx.y][threadIdx.x] = acc;
   __syncthreads();
   if (threadIdx.y == 0 && col < d) {
     float t = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) t += red[i][threadIdx.x];
+    for (int i = 0; i < 32; ++i) t += red[i][threadIdx.x];
     float *out = which == 0 ? dgamma : dbeta;
     out[col] = accumulate ? out[col] + t : t;
   }
@@ -500,7 +547,7 @@ int launch_ln_fwd(cudaStream_t s, const void *x, const void *gamma, const void *
 template <int CHUNKS>
 int launch_ln_bwd(cudaStream_t s, const void *dy, const void *x, const void *gamma, int pdt, const float *mean,
                   const float *rstd, const void *dres, void *dx, float *scratch, int64_t rows, int d, int parts) {
-  const size_t smem = static_cast<size_t>(kLnWarps) * 2 * d * sizeof(float);
+  const size_t smem = (static_cast<size_t>(kLnWarps) * 2 * d + d) * sizeof(float);
   if (smem > 48 * 1024) {
     cudaFuncSetAttribute(ln_bwd_kernel<CHUNKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   }
@@ -547,7 +594,7 @@ int layernorm_backward(stream_t stream, const void *dy, const void *x, const voi
   else return static_cast<int>(cudaErrorInvalidValue);  // wider rows use the library path
   if (code != 0) return code;
   dim3 grid(static_cast<unsigned>((d + 31) / 32), 2);
-  ln_bwd_reduce_kernel<<<grid, dim3(32, 8), 0, s>>>(scratch, parts, di, dgamma, dbeta, accumulate);
+  ln_bwd_reduce_kernel<<<grid, dim3(32, 32), 0, s>>>(scratch, parts, di, dgamma, dbeta, accumulate);
   return finish_launch(1);
 }
 
@@ -863,6 +910,6 @@ extern "C" __attribute__((visibility("default"))) int cs_layernorm_backward_noal
   else code = launch_ln_bwd<8>(s, dy, x, gamma, 0, mean, rstd, grad_residual, dx, scratch, rows, di, parts);
   if (code != 0) return code;
   dim3 grid(static_cast<unsigned>((d + 31) / 32), 2);
-  ln_bwd_reduce_kernel<<<grid, dim3(32, 8), 0, s>>>(scratch, parts, di, dgamma, dbeta, accumulate);
+  ln_bwd_reduce_kernel<<<grid, dim3(32, 32), 0, s>>>(scratch, parts, di, dgamma, dbeta, accumulate);
   return finish_launch(1);
 }

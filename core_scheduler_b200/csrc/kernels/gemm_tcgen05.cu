@@ -479,6 +479,191 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 }
 
 
+
+// ----------------------------------------------------- epilogue through shared memory + TMA ----
+// The accumulator rows a thread reads from TMEM are 64-byte pieces of different output rows;
+// storing them directly makes every store instruction touch 32 half-filled sectors. Instead each
+// epilogue warp stages 32 rows x 128 bytes in shared memory (128-byte swizzle, conflict-free
+// for 16-byte accesses) and one lane issues a TMA store (or, for fp32 gradients, a TMA
+// reduce-add) of that box: full 128-byte lines, bounds clipped by the tensor map.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+constexpr int EPI_BUF_BYTES = 4096;  // 32 rows x 128 bytes
+constexpr int EPI_STAGING_BYTES = EPI_WARPS * 2 * EPI_BUF_BYTES;
+
+struct EpilogueStaging {
+  uint32_t buf[2];  // shared-memory addresses of this warp's two staging boxes
+  int next;         // which one the next fill uses
+};
+
+// Claims a staging box: the TMA operation that last read it (two fills ago) must have finished
+// reading shared memory.
+__device__ __forceinline__ uint32_t staging_acquire(EpilogueStaging &st, int lane, bool drain_all = false) {
+  if (lane == 0) {
+    if (drain_all)
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    else
+      bulk_wait_read_1();
+  }
+  __syncwarp();
+  const uint32_t b = st.buf[st.next];
+  st.next ^= 1;
+  return b;
+}
+// 16-byte piece `piece` (0..7) of row `lane` inside a swizzled 32 x 128-byte box.
+__device__ __forceinline__ uint32_t staging_addr(uint32_t box, int lane, int piece) {
+  return box + lane * 128 + ((piece ^ (lane & 7)) << 4);
+}
+// Makes the box visible to the async proxy and lets lane 0 issue the store / reduce.
+__device__ __forceinline__ void staging_release(const CUtensorMap *map, uint32_t box, int c0, int c1, bool in_range, bool reduce,
+                                                int lane) {
+  fence_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    if (in_range) {
+      if (reduce)
+        tma_reduce_add_2d(map, box, c0, c1);
+      else
+        tma_store_2d(map, box, c0, c1);
+    }
+    bulk_commit();  // an empty group keeps the acquire/commit pairing uniform
+  }
+}
+
+__device__ __forceinline__ void epilogue_tile_tma(const KParams &p, const CUtensorMap *map_d, const CUtensorMap *map_d2, int m0,
+                                                  int n0, int n_tile, uint32_t tmem_acc, int q, int half, int lane,
+                                                  EpilogueStaging &st) {
+  const int row0 = m0 + q * 32;
+  const long long row = row0 + lane;
+  const bool row_ok = row < p.m;
+  const bool rows_in_range = row0 < p.m;
+  float run_max = -INFINITY, run_sum = 0.f;
+  const bool f32_out = p.epilogue == kEpiStoreF32 || p.epilogue == kEpiAccumF32;
+  const bool reduce = f32_out && (p.atomic_out || p.epilogue == kEpiAccumF32);
+  uint32_t box = 0, box2 = 0;
+#pragma unroll 1
+  for (int ch = 0; ch < 4; ++ch) {
+    const int col0 = half * 128 + ch * 32;
+    uint32_t v[32];
+    tcgen05_ld_32x32b_x32(tmem_acc + col0 + (static_cast<uint32_t>(q * 32) << 16), v);
+    tcgen05_wait_ld();
+    const long long gcol = n0 + col0;
+    const bool cols_in_range = gcol < p.n;
+    float f[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+    if (f32_out) {
+      // one box per 32 fp32 columns
+      box = staging_acquire(st, lane);
+#pragma unroll
+      for (int g = 0; g < 8; ++g)
+        st_shared_v4(staging_addr(box, lane, g), v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+      staging_release(map_d, box, static_cast<int>(gcol), row0, rows_in_range && cols_in_range, reduce, lane);
+      continue;
+    }
+    if (p.bias && cols_in_range) {
+      const uint4 *bp = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.bias) + gcol);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (gcol + g * 8 + 8 > p.n) break;
+        const uint4 b = __ldg(bp + g);
+        const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 t = unpack_bf16(w[i]);
+          f[g * 8 + 2 * i] += t.x;
+          f[g * 8 + 2 * i + 1] += t.y;
+        }
+      }
+    }
+    if ((p.epilogue == kEpiResidualBf16 || p.epilogue == kEpiDGelu) && row_ok && cols_in_range) {
+      const uint4 *ap = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.aux) + row * p.ldd + gcol);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (gcol + g * 8 + 8 > p.n) break;
+        const uint4 a = *(ap + g);
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 t = unpack_bf16(w[i]);
+          if (p.epilogue == kEpiResidualBf16) {
+            f[g * 8 + 2 * i] += t.x;
+            f[g * 8 + 2 * i + 1] += t.y;
+          } else {
+            f[g * 8 + 2 * i] *= gelu_grad_f(t.x);
+            f[g * 8 + 2 * i + 1] *= gelu_grad_f(t.y);
+          }
+        }
+      }
+    }
+    // two 32-column chunks share one 64-column (128-byte) box
+    const int sub = ch & 1;
+    if (sub == 0) {
+      // the dual-output epilogue fills both boxes at once, so both previous stores must be done
+      box = staging_acquire(st, lane, p.epilogue == kEpiGeluDual);
+      if (p.epilogue == kEpiGeluDual) box2 = staging_acquire(st, lane, true);
+    }
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      st_shared_v4(staging_addr(box, lane, sub * 4 + g), pack_bf16(f[g * 8 + 0], f[g * 8 + 1]), pack_bf16(f[g * 8 + 2], f[g * 8 + 3]),
+                   pack_bf16(f[g * 8 + 4], f[g * 8 + 5]), pack_bf16(f[g * 8 + 6], f[g * 8 + 7]));
+    if (p.epilogue == kEpiGeluDual) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+        st_shared_v4(staging_addr(box2, lane, sub * 4 + g),
+                     pack_bf16(gelu_f(bf16_round(f[g * 8 + 0])), gelu_f(bf16_round(f[g * 8 + 1]))),
+                     pack_bf16(gelu_f(bf16_round(f[g * 8 + 2])), gelu_f(bf16_round(f[g * 8 + 3]))),
+                     pack_bf16(gelu_f(bf16_round(f[g * 8 + 4])), gelu_f(bf16_round(f[g * 8 + 5]))),
+                     pack_bf16(gelu_f(bf16_round(f[g * 8 + 6])), gelu_f(bf16_round(f[g * 8 + 7]))));
+    }
+    if (p.epilogue == kEpiCrossEntropy && row_ok && cols_in_range) {
+      float cmax = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        f[i] = bf16_round(f[i]);
+        if (gcol + i < p.n_valid) cmax = fmaxf(cmax, f[i]);
+      }
+      if (cmax > -INFINITY) {
+        const float new_max = fmaxf(run_max, cmax);
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (gcol + i < p.n_valid) s += __expf(f[i] - new_max);
+        run_sum = run_sum * __expf(run_max - new_max) + s;
+        run_max = new_max;
+      }
+    }
+    if (sub == 1) {
+      const int c0 = n0 + half * 128 + (ch - 1) * 32;
+      const bool in_range = rows_in_range && c0 < p.n;
+      staging_release(map_d, box, c0, row0, in_range, false, lane);
+      if (p.epilogue == kEpiGeluDual) staging_release(map_d2, box2, c0, row0, in_range, false, lane);
+    }
+  }
+  if (p.epilogue == kEpiCrossEntropy && row_ok) {
+    float *stp = p.stats + (row * (2LL * p.n_tiles) + 2LL * n_tile + half) * 2;
+    stp[0] = run_max;
+    stp[1] = run_sum;
+  }
+}
+
 // ===================================================================================
 // 2-CTA variant: a thread-block cluster of two CTAs on neighbouring SMs computes one 256x256
 // tile with tcgen05.mma.cta_group::2. CTA r of the pair loads rows [128r, 128r+128) of the A
@@ -492,10 +677,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 //   tmem_full[b]  in each CTA (multicast commit); tmem_empty[b] in the leader, counted by the
 //                 epilogue warps of both CTAs
 // ===================================================================================
-constexpr int STAGES2 = 6;
+constexpr int STAGES2 = 5;
 constexpr int B2_BYTES = 128 * BK * 2;               // this CTA's half of the B tile
 constexpr int STAGE2_BYTES = A_BYTES + B2_BYTES;     // 32 KB
-constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 256;
+constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + EPI_STAGING_BYTES + 1024 + 256;
 constexpr int BM2 = 256;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -552,12 +737,14 @@ __device__ __forceinline__ TileCoord tile_coord2(const KParams &p, int tile) {
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
-gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KParams p) {
+gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+             const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_d2, const KParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_aligned + STAGES2 * STAGE2_BYTES);
-  const uint32_t bar_base = smem_base + STAGES2 * STAGE2_BYTES;
+  const uint32_t staging_base = smem_base + STAGES2 * STAGE2_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_aligned + STAGES2 * STAGE2_BYTES + EPI_STAGING_BYTES);
+  const uint32_t bar_base = staging_base + EPI_STAGING_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES2 + s); };
   auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES2 + b); };
@@ -687,11 +874,16 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     const int half = (warp - 2) >> 2;
     int acc = 0;
     uint32_t acc_phase = 0;
+    EpilogueStaging st;
+    st.buf[0] = staging_base + (warp - 2) * 2 * EPI_BUF_BYTES;
+    st.buf[1] = st.buf[0] + EPI_BUF_BYTES;
+    st.next = 0;
     for (int tile = pair; tile < total_tiles; tile += num_pairs) {
       const TileCoord c = tile_coord2(p, tile);
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag)) break;
       tcgen05_fence_after();
-      epilogue_tile(p, c.m0 + static_cast<int>(cta) * 128, c.n0, c.n_tile, tmem_base + acc * BN, q, half, lane);
+      epilogue_tile_tma(p, &map_d, &map_d2, c.m0 + static_cast<int>(cta) * 128, c.n0, c.n_tile, tmem_base + acc * BN, q, half,
+                        lane, st);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(tmem_empty_bar(acc), 0));
@@ -700,6 +892,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         acc_phase ^= 1u;
       }
     }
+    if (lane == 0) bulk_wait_all();  // this warp's stores have left shared memory and are complete
   }
 
   // ------------------------------------------------------------------------- teardown ----
@@ -741,9 +934,10 @@ struct MapKey {
   const void *ptr;
   uint64_t inner, outer, stride_bytes;
   uint32_t box_inner, box_outer;
+  int elem_bytes;
   bool operator==(const MapKey &o) const {
     return ptr == o.ptr && inner == o.inner && outer == o.outer && stride_bytes == o.stride_bytes &&
-           box_inner == o.box_inner && box_outer == o.box_outer;
+           box_inner == o.box_inner && box_outer == o.box_outer && elem_bytes == o.elem_bytes;
   }
 };
 struct MapKeyHash {
@@ -761,10 +955,10 @@ struct MapKeyHash {
 // 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row stride in
 // elements; box = box_inner x box_outer with the 128-byte swizzle (box_inner == 64).
 bool get_tensor_map(const void *ptr, uint64_t inner, uint64_t outer, uint64_t stride_elems, uint32_t box_inner,
-                    uint32_t box_outer, CUtensorMap *out) {
+                    uint32_t box_outer, CUtensorMap *out, int elem_bytes = 2) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  const MapKey key{ptr, inner, outer, stride_elems * 2, box_inner, box_outer};
+  const MapKey key{ptr, inner, outer, stride_elems * elem_bytes, box_inner, box_outer, elem_bytes};
   std::lock_guard<std::mutex> lock{mu};
   auto it = cache.find(key);
   if (it != cache.end()) {
@@ -774,11 +968,11 @@ bool get_tensor_map(const void *ptr, uint64_t inner, uint64_t outer, uint64_t st
   EncodeFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {inner, outer};
-  const cuuint64_t strides[1] = {stride_elems * 2};
+  const cuuint64_t strides[1] = {stride_elems * elem_bytes};
   const cuuint32_t box[2] = {box_inner, box_outer};
   const cuuint32_t elem_strides[2] = {1, 1};
   CUtensorMap map;
-  const CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, elem_strides,
+  const CUresult r = fn(&map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, elem_strides,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
@@ -832,6 +1026,17 @@ int gemm_bf16(stream_t stream, const GemmArgs &a) {
     if (!get_tensor_map(a.a, a.m, a.k, a.lda, 64, BK, &map_a)) return -1;
     if (!get_tensor_map(a.b, a.n, a.k, a.ldb, 64, BK, &map_b)) return -1;
   }
+  CUtensorMap map_d{}, map_d2{};
+  if (pair_kernel) {
+    // output boxes of the TMA-store epilogue: 32 rows x 128 bytes
+    if (f32_out) {
+      if (!get_tensor_map(a.d, a.n, a.m, a.ldd, 32, 32, &map_d, 4)) return -1;
+    } else {
+      if (!get_tensor_map(a.d, a.n, a.m, a.ldd, 64, 32, &map_d)) return -1;
+    }
+    map_d2 = map_d;
+    if (a.d2 && !get_tensor_map(a.d2, a.n, a.m, a.ldd, 64, 32, &map_d2)) return -1;
+  }
 
   KParams p{};
   p.d = a.d;
@@ -861,11 +1066,22 @@ int gemm_bf16(stream_t stream, const GemmArgs &a) {
     // has work; partial sums meet in the fp32 output through vector atomics.
     const int mn = p.m_tiles * p.n_tiles;
     const int workers = pair_kernel ? sm_count / 2 : sm_count;
-    int want = (2 * workers + mn - 1) / mn;
-    const int max_splits = p.kb_total / 4 > 0 ? p.kb_total / 4 : 1;
-    if (want > max_splits) want = max_splits;
-    if (want < 1) want = 1;
-    p.splits = want;
+    // Pick the split count whose tile total fills whole waves of `workers` best, keeping at
+    // least 8 k-blocks per split; ties go to fewer splits (fewer reduce-adds).
+    const int max_splits = p.kb_total / 8 > 0 ? p.kb_total / 8 : 1;
+    int best = 1;
+    double best_eff = 0.0;
+    for (int sp = 1; sp <= max_splits && sp <= 64; ++sp) {
+      const int tiles = mn * sp;
+      const int waves = (tiles + workers - 1) / workers;
+      const double eff = static_cast<double>(tiles) / (static_cast<double>(waves) * workers);
+      if (eff > best_eff + 0.02) {
+        best_eff = eff;
+        best = sp;
+      }
+      if (tiles >= 4 * workers) break;
+    }
+    p.splits = best;
   }
   p.kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
   p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
@@ -910,7 +1126,7 @@ int gemm_bf16(stream_t stream, const GemmArgs &a) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm2_kernel, map_a, map_b, p);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm2_kernel, map_a, map_b, map_d, map_d2, p);
     if (e != cudaSuccess) return static_cast<int>(e);
     return finish_launch(1);
   }
