@@ -168,9 +168,33 @@ def build(verbose: bool = False) -> None:
     subprocess.run(cmd, check=True, cwd=str(BUILD))
 
 
+def build_examples() -> list[str]:
+    """Compiles the C++ programs under examples/ against libcs_b200.so into examples/bin/."""
+    build()
+    p = _paths()
+    root = HERE.parent / "examples"
+    out_dir = root / "bin"
+    out_dir.mkdir(exist_ok=True)
+    inc = [CSRC / "include", CSRC] + p["torch_inc"] + [p["cuda_home"] / "include"]
+    built = []
+    for src in sorted(root.glob("*.cpp")):
+        exe = out_dir / src.stem
+        cmd = [os.environ.get("CS_CXX", "g++"), "-std=c++20", "-O2", "-Wno-interference-size",
+               f"-D_GLIBCXX_USE_CXX11_ABI={p['cxx11_abi']}", "-DUSE_C10D_NCCL", "-DUSE_DISTRIBUTED"]
+        cmd += [f"-I{i}" for i in inc] + [str(src), "-o", str(exe), f"-L{LIBDIR}", "-lcs_b200", f"-L{p['torch_lib']}",
+                "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda", f"-L{p['cuda_home'] / 'lib64'}", "-lcudart",
+                f"-Wl,-rpath,{LIBDIR}", f"-Wl,-rpath,{p['torch_lib']}", f"-Wl,-rpath,{p['arrow_lib']}", "-Wl,--no-as-needed"]
+        subprocess.run(cmd, check=True)
+        built.append(str(exe))
+    return built
+
+
 def is_built() -> bool:
     return (HERE / f"_C{ext_suffix()}").exists() and (LIBDIR / "libcs_b200.so").exists()
 
 
 if __name__ == "__main__":
-    build(verbose="-v" in sys.argv)
+    if "examples" in sys.argv:
+        print("\n".join(build_examples()))
+    else:
+        build(verbose="-v" in sys.argv)

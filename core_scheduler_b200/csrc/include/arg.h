@@ -1,0 +1,4 @@
+// Source compatibility: programs written against the original include layout find the same
+// declarations here.
+#pragma once
+#include "cs/core.h"
