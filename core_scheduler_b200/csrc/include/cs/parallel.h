@@ -46,4 +46,60 @@ struct CS_API ZeroAdamWImpl : module::OptimizerModule {
   int64_t shard_begin_{0}, shard_count_{0};
 };
 CS_MODULE(ZeroAdamW);
+
+// ---------------------------------------------------------------------------------------
+// Tensor parallelism with sequence-parallel activations (Megatron style)
+// ---------------------------------------------------------------------------------------
+// The B*T token rows are split evenly over the ranks between blocks ("sequence-parallel"
+// region: LayerNorm, residual stream, embedding, classifier + loss all work on M/tp rows).
+// Entering a column-parallel Linear (c_attn, fc1; output features split over ranks, attention
+// heads split over ranks) the rows are all-gathered; leaving a row-parallel Linear (c_proj,
+// fc2; input features split) the partial outputs are reduce-scattered back to row shards and
+// the residual is added. Backward mirrors this (all-gather <-> reduce-scatter). Parameters of
+// the sharded Linears are rank-local; LayerNorm, embedding and classifier parameters are
+// replicated and their gradients are summed over the ranks through the all-reduce bucket.
+// n_head must be divisible by the number of ranks, and so must B*T.
+struct CS_API TPBlockImpl : module::Module {
+  TPBlockImpl(const Scheduler &scheduler, const models::GPT2Config &config, const communication::Comm &comm);
+  Tensor forward(const Scheduler &scheduler, const ReadOnlyTensor &x_shard, int64_t batch, int64_t seq);
+  Tensor backward(const Scheduler &scheduler, const ReadOnlyTensor &grad_shard, const models::GradientSync &sync);
+  module::LayerNorm ln1{nullptr}, ln2{nullptr};
+  module::Linear c_attn{nullptr}, c_proj{nullptr}, fc1{nullptr};
+  module::GeluLinear fc2{nullptr};
+  std::shared_ptr<compute::ScaledDotProductAttention::State> attn_state;
+  communication::Comm comm;
+  int64_t local_heads{0};
+};
+CS_MODULE(TPBlock);
+
+struct CS_API TPGPT2Impl : module::Module {
+  TPGPT2Impl(const Scheduler &scheduler, const models::GPT2Config &config, const communication::Comm &comm);
+  // input_ids, labels: the FULL [B, T] batch on every rank (each rank embeds and scores only its
+  // own row shard). Returns this rank's mean loss over its rows; average over ranks for the
+  // global loss.
+  Tensor forward_loss(const Scheduler &scheduler, const ReadOnlyTensor &input_ids, const ReadOnlyTensor &labels);
+  void backward_loss(const Scheduler &scheduler, const models::GradientSync &sync);
+  [[nodiscard]] const models::GPT2Config &config() const { return config_; }
+  // Names of the parameters that are replicated on every rank (gradients need the all-reduce).
+  [[nodiscard]] std::vector<std::string> replicated_parameters() const;
+
+  module::Embedding wte{nullptr}, wpe{nullptr};
+  std::vector<TPBlock> h;
+  module::LayerNorm lnf{nullptr};
+  module::Linear lm_head{nullptr};
+
+ private:
+  models::GPT2Config config_;
+  communication::Comm comm_;
+  std::shared_ptr<compute::LinearCrossEntropy::State> lce_state_;
+  int64_t batch_{0}, seq_{0};
+};
+CS_MODULE(TPGPT2);
+
+// Row-shard collectives used by the TP model (comm-stream tasks):
+// gathers [M/tp, d] row shards into [M, d];
+CS_API Tensor all_gather_rows(const Scheduler &scheduler, const communication::Comm &comm, const ReadOnlyTensor &shard);
+// sums [M, d] partials over ranks and keeps this rank's [M/tp, d] rows (+ residual when given).
+CS_API Tensor reduce_scatter_rows(const Scheduler &scheduler, const communication::Comm &comm, const ReadOnlyTensor &full,
+                                  const ReadOnlyTensor *residual = nullptr);
 }  // namespace cs::parallel

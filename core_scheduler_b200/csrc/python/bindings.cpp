@@ -586,6 +586,18 @@ PYBIND11_MODULE(_C, m) {
       .def("shard_begin", &parallel::ZeroAdamWImpl::shard_begin)
       .def("shard_count", &parallel::ZeroAdamWImpl::shard_count);
 
+  py::class_<parallel::TPGPT2Impl, module::Module, std::shared_ptr<parallel::TPGPT2Impl>>(m, "TPGPT2")
+      .def(py::init<const Scheduler &, const models::GPT2Config &, const Comm &>())
+      .def("forward_loss", &parallel::TPGPT2Impl::forward_loss)
+      .def("backward_loss", [](parallel::TPGPT2Impl &g, const Scheduler &s, py::object sync) {
+        g.backward_loss(s, sync.is_none() ? models::GradientSync{} : py::cast<models::GradientSync>(sync));
+      }, py::arg("scheduler"), py::arg("sync") = py::none())
+      .def("replicated_parameters", &parallel::TPGPT2Impl::replicated_parameters);
+  m.def("all_gather_rows", &parallel::all_gather_rows);
+  m.def("reduce_scatter_rows", [](const Scheduler &s, const Comm &c, const ReadOnlyTensor &full) {
+    return parallel::reduce_scatter_rows(s, c, full, nullptr);
+  });
+
   // ---- data ---------------------------------------------------------------------------------------
   py::class_<data::LlmDataset>(m, "LlmDataset")
       .def(py::init<const std::string &>())

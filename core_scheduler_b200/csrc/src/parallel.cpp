@@ -154,4 +154,213 @@ void ZeroAdamWImpl::gather_master(const Scheduler &scheduler) {
          });
   communication::AllGather::run(scheduler, comm_, {recv}, {send});
 }
+
+// ======================================================================================
+// Tensor parallel GPT-2
+// ======================================================================================
+Tensor all_gather_rows(const Scheduler &scheduler, const communication::Comm &comm, const ReadOnlyTensor &shard) {
+  const int64_t world = comm.get_size();
+  if (world <= 1) {
+    Tensor same;
+    submit(scheduler, "cs::parallel::all_gather_rows", Task::Impl::kMain, Task::Impl::kCompute, {same}, {shard},
+           [same, shard](const FnTask &) { same.impl()->tensor = shard.impl()->tensor; });
+    return same;
+  }
+  Tensor full;
+  std::vector<Tensor> parts(static_cast<size_t>(world));
+  std::vector<Tensor> outs{full};
+  outs.insert(outs.end(), parts.begin(), parts.end());
+  submit(scheduler, "cs::parallel::all_gather_rows::allocate", Task::Impl::kMain, Task::Impl::kCompute, outs, {shard},
+         [full, parts, shard, world](const FnTask &) {
+           const at::Tensor &s = shard.impl()->tensor;
+           auto sizes = s.sizes().vec();
+           const int64_t rows = sizes[0];
+           sizes[0] = rows * world;
+           full.impl()->tensor = at::empty(sizes, s.options());
+           for (int64_t r = 0; r < world; ++r) parts[r].impl()->tensor = full.impl()->tensor.narrow(0, r * rows, rows);
+         });
+  communication::AllGather::run(scheduler, comm, {parts}, {shard});
+  // The gather wrote through the row views; tie the result handle to the comm-stream work.
+  Tensor joined;
+  std::vector<ReadOnlyTensor> deps(parts.begin(), parts.end());
+  deps.push_back(full);
+  submit(scheduler, "cs::parallel::all_gather_rows::join", Task::Impl::kComm, Task::Impl::kCompute, {joined}, deps,
+         [joined, full](const FnTask &) { joined.impl()->tensor = full.impl()->tensor; });
+  return joined;
+}
+
+Tensor reduce_scatter_rows(const Scheduler &scheduler, const communication::Comm &comm, const ReadOnlyTensor &full,
+                           const ReadOnlyTensor *residual) {
+  const int64_t world = comm.get_size();
+  const int64_t rank = comm.get_rank();
+  Tensor out;
+  if (world <= 1) {
+    std::vector<ReadOnlyTensor> ins{full};
+    std::optional<ReadOnlyTensor> res;
+    if (residual) {
+      res = *residual;
+      ins.push_back(*residual);
+    }
+    submit(scheduler, "cs::parallel::reduce_scatter_rows", Task::Impl::kMain, Task::Impl::kCompute, {out}, ins,
+           [out, full, res](const FnTask &) {
+             out.impl()->tensor = res ? full.impl()->tensor + res->impl()->tensor : full.impl()->tensor;
+           });
+    return out;
+  }
+  std::vector<Tensor> parts(static_cast<size_t>(world));
+  Tensor recv;
+  std::vector<Tensor> outs{recv};
+  outs.insert(outs.end(), parts.begin(), parts.end());
+  submit(scheduler, "cs::parallel::reduce_scatter_rows::views", Task::Impl::kMain, Task::Impl::kCompute, outs, {full},
+         [recv, parts, full, world](const FnTask &) {
+           const at::Tensor &f = full.impl()->tensor;
+           CS_ASSERT_TRUE(f.size(0) % world == 0, "row count ", f.size(0), " does not split over ", world, " ranks");
+           const int64_t rows = f.size(0) / world;
+           for (int64_t r = 0; r < world; ++r) parts[r].impl()->tensor = f.narrow(0, r * rows, rows);
+           auto sizes = f.sizes().vec();
+           sizes[0] = rows;
+           recv.impl()->tensor = at::empty(sizes, f.options());
+         });
+  std::vector<ReadOnlyTensor> send(parts.begin(), parts.end());
+  communication::ReduceScatter::run(scheduler, comm, {recv}, {send}, communication::kSUM);
+  (void)rank;
+  if (!residual) return recv;
+  return compute::Utils::add(scheduler, recv, *residual);
+}
+
+namespace {
+compute::Linear::Options tp_linear(const Scheduler &scheduler, const models::GPT2Config &c, int64_t in, int64_t out) {
+  return compute::Linear::Options{in, out}.bias(false).device(c.device().value_or(scheduler.device())).dtype(c.dtype());
+}
+}  // namespace
+
+TPBlockImpl::TPBlockImpl(const Scheduler &scheduler, const models::GPT2Config &config, const communication::Comm &comm_)
+    : comm{comm_} {
+  const int64_t tp = comm.get_size();
+  const int64_t d = config.n_embd();
+  CS_ASSERT_TRUE(config.n_head() % tp == 0, "n_head (", config.n_head(), ") must be divisible by the tensor-parallel size ", tp);
+  local_heads = config.n_head() / tp;
+  auto ln_opts = compute::LayerNorm::Options{d}.device(config.device().value_or(scheduler.device())).dtype(config.dtype());
+  ln1 = register_module("ln1", module::LayerNorm{scheduler, ln_opts});
+  c_attn = register_module("c_attn", module::Linear{scheduler, tp_linear(scheduler, config, d, 3 * d / tp)});
+  c_proj = register_module("c_proj", module::Linear{scheduler, tp_linear(scheduler, config, d / tp, d)});
+  ln2 = register_module("ln2", module::LayerNorm{scheduler, ln_opts});
+  fc1 = register_module("fc1", module::Linear{scheduler, tp_linear(scheduler, config, d, 4 * d / tp).gelu_epilogue(true)});
+  fc2 = register_module("fc2", module::GeluLinear{scheduler, tp_linear(scheduler, config, 4 * d / tp, d)});
+  attn_state = compute::ScaledDotProductAttention::init(scheduler, compute::ScaledDotProductAttention::Options{}.is_causal(true));
+  for (auto *w : {&c_attn->state()->forward.weight, &c_proj->state()->forward.weight, &fc1->state()->forward.weight})
+    compute::Utils::normal_(scheduler, *w, 0, config.init_std());
+  compute::Utils::normal_(scheduler, fc2->state()->forward.weight, 0, config.init_std());
+}
+
+Tensor TPBlockImpl::forward(const Scheduler &scheduler, const ReadOnlyTensor &x_shard, int64_t batch, int64_t seq) {
+  using compute::Utils;
+  const int64_t d_local = c_proj->state()->forward.weight.size(1);
+  Tensor a = ln1->forward(scheduler, x_shard);                 // [M/tp, d]
+  Tensor a_full = all_gather_rows(scheduler, comm, a);          // [M, d]
+  Tensor qkv = c_attn->forward(scheduler, a_full);              // [M, 3 d/tp]
+  Tensor qkv3 = Utils::view(scheduler, qkv, {batch, seq, 3 * d_local});
+  Tensor ctx = compute::ScaledDotProductAttention::forward_packed(scheduler, attn_state, qkv3, local_heads);
+  Tensor ctx2 = Utils::view(scheduler, ctx, {batch * seq, d_local});
+  Tensor y = c_proj->forward(scheduler, ctx2);                   // partial [M, d]
+  Tensor x1 = reduce_scatter_rows(scheduler, comm, y, &x_shard); // [M/tp, d] + residual
+  Tensor b = ln2->forward(scheduler, x1);
+  Tensor b_full = all_gather_rows(scheduler, comm, b);
+  Tensor pre = fc1->forward(scheduler, b_full);                  // [M, 4d/tp], carries GELU
+  Tensor z = fc2->forward(scheduler, pre);                       // partial [M, d]
+  return reduce_scatter_rows(scheduler, comm, z, &x1);
+}
+
+Tensor TPBlockImpl::backward(const Scheduler &scheduler, const ReadOnlyTensor &grad_shard, const models::GradientSync &sync) {
+  using compute::Utils;
+  // MLP: reduce-scatter backward = all-gather of the incoming row shard
+  Tensor dz = all_gather_rows(scheduler, comm, grad_shard);      // [M, d]
+  Tensor d_pre = fc2->backward_input(scheduler, dz);
+  fc2->backward_parameter(scheduler, dz);
+  Tensor d_b_full = fc1->backward_input(scheduler, d_pre);       // partial [M, d]
+  fc1->backward_parameter(scheduler, d_pre);
+  Tensor d_b = reduce_scatter_rows(scheduler, comm, d_b_full);   // all-gather backward
+  Tensor d_x1 = ln2->backward(scheduler, d_b, grad_shard);       // + residual branch
+  sync.push(scheduler, ln2->state()->forward.grad_weight);
+  sync.push(scheduler, ln2->state()->forward.grad_bias);
+  // attention
+  Tensor dy = all_gather_rows(scheduler, comm, d_x1);
+  Tensor d_ctx = c_proj->backward_input(scheduler, dy);          // [M, d/tp]
+  c_proj->backward_parameter(scheduler, dy);
+  Tensor d_qkv = compute::ScaledDotProductAttention::backward_packed(scheduler, attn_state, d_ctx);
+  const int64_t three_d_local = c_attn->state()->forward.weight.size(0);
+  Tensor d_qkv2 = Utils::view(scheduler, d_qkv, {-1, three_d_local});
+  Tensor d_a_full = c_attn->backward_input(scheduler, d_qkv2);   // partial [M, d]
+  c_attn->backward_parameter(scheduler, d_qkv2);
+  Tensor d_a = reduce_scatter_rows(scheduler, comm, d_a_full);
+  Tensor d_x = ln1->backward(scheduler, d_a, d_x1);
+  sync.push(scheduler, ln1->state()->forward.grad_weight);
+  sync.push(scheduler, ln1->state()->forward.grad_bias);
+  return d_x;
+}
+
+TPGPT2Impl::TPGPT2Impl(const Scheduler &scheduler, const models::GPT2Config &config, const communication::Comm &comm)
+    : config_{config}, comm_{comm} {
+  const auto dev = config.device().value_or(scheduler.device());
+  const int64_t d = config.n_embd();
+  wte = register_module("wte", module::Embedding{scheduler, compute::Embedding::Options{config.padded_vocab_size(), d}.device(dev).dtype(config.dtype())});
+  wpe = register_module("wpe", module::Embedding{scheduler, compute::Embedding::Options{config.block_size(), d}.device(dev).dtype(config.dtype())});
+  compute::Utils::normal_(scheduler, wte->state()->forward.weight, 0, config.init_std());
+  compute::Utils::normal_(scheduler, wpe->state()->forward.weight, 0, config.init_std());
+  for (int64_t l = 0; l < config.n_layer(); ++l) h.push_back(register_module(std::to_string(l), TPBlock{scheduler, config, comm}));
+  lnf = register_module("lnf", module::LayerNorm{scheduler, compute::LayerNorm::Options{d}.device(dev).dtype(config.dtype())});
+  lm_head = register_module("lm_head", module::Linear{scheduler, compute::Linear::Options{d, config.padded_vocab_size()}.bias(false).device(dev).dtype(config.dtype())});
+  compute::Utils::normal_(scheduler, lm_head->state()->forward.weight, 0, config.init_std());
+  lce_state_ = compute::LinearCrossEntropy::init(scheduler, lm_head->state(), config.vocab_size(), -100);
+}
+
+std::vector<std::string> TPGPT2Impl::replicated_parameters() const {
+  std::vector<std::string> out{"wte.weight", "wpe.weight", "lnf.weight", "lnf.bias", "lm_head.weight"};
+  for (size_t l = 0; l < h.size(); ++l)
+    for (const char *k : {".ln1.weight", ".ln1.bias", ".ln2.weight", ".ln2.bias"}) out.push_back(std::to_string(l) + k);
+  return out;
+}
+
+Tensor TPGPT2Impl::forward_loss(const Scheduler &scheduler, const ReadOnlyTensor &input_ids, const ReadOnlyTensor &labels) {
+  using compute::Utils;
+  CS_ASSERT_TRUE(input_ids.defined() && input_ids.sizes().size() == 2, "input_ids must be a materialised [B,T] tensor");
+  batch_ = input_ids.size(0);
+  seq_ = input_ids.size(1);
+  const int64_t tp = comm_.get_size(), rank = comm_.get_rank();
+  const int64_t rows = batch_ * seq_;
+  CS_ASSERT_TRUE(rows % tp == 0, "B*T (", rows, ") must be divisible by the tensor-parallel size ", tp);
+  CS_ASSERT_TRUE(seq_ % (rows / tp) == 0 || (rows / tp) % seq_ == 0, "row shards must align with sequence boundaries");
+  const int64_t shard = rows / tp;
+  // Token and position embedding of this rank's rows only. Rows are b*T + t, so the shard is a
+  // contiguous range of the flattened batch; positions repeat with period T.
+  Tensor ids_shard, lab_shard;
+  submit(scheduler, "cs::parallel::TPGPT2::shard_tokens", Task::Impl::kMain, Task::Impl::kCompute, {ids_shard, lab_shard},
+         {input_ids, labels}, [=, T = seq_](const FnTask &) {
+           // keep a [rows_in_shard / T', T'] shape so that positions line up: T' = min(T, shard)
+           const int64_t cols = std::min<int64_t>(T, shard);
+           ids_shard.impl()->tensor = input_ids.impl()->tensor.reshape({-1}).narrow(0, rank * shard, shard).reshape({shard / cols, cols});
+           lab_shard.impl()->tensor = labels.impl()->tensor.reshape({-1}).narrow(0, rank * shard, shard).contiguous();
+         });
+  CS_ASSERT_TRUE(shard % seq_ == 0, "each rank must own whole sequences (B divisible by the tensor-parallel size)");
+  Tensor x = compute::Embedding::forward_token_position(scheduler, wte->state(), wpe->state(), ids_shard);  // [B/tp, T, d]
+  x = Utils::view(scheduler, x, {shard, config_.n_embd()});
+  for (auto &block : h) x = block->forward(scheduler, x, batch_, seq_);
+  x = lnf->forward(scheduler, x);
+  return compute::LinearCrossEntropy::forward(scheduler, lce_state_, x, lab_shard);
+}
+
+void TPGPT2Impl::backward_loss(const Scheduler &scheduler, const models::GradientSync &sync) {
+  using compute::Utils;
+  Tensor grad = compute::LinearCrossEntropy::backward(scheduler, lce_state_);
+  sync.push(scheduler, lm_head->state()->forward.grad_weight);
+  grad = lnf->backward(scheduler, grad);
+  sync.push(scheduler, lnf->state()->forward.grad_weight);
+  sync.push(scheduler, lnf->state()->forward.grad_bias);
+  for (auto it = h.rbegin(); it != h.rend(); ++it) grad = (*it)->backward(scheduler, grad, sync);
+  const int64_t shard = batch_ * seq_ / comm_.get_size();
+  grad = Utils::view(scheduler, grad, {shard / seq_, seq_, config_.n_embd()});
+  compute::Embedding::backward_token_position(scheduler, wte->state(), wpe->state(), grad);
+  sync.push(scheduler, wpe->state()->forward.grad_weight);
+  sync.push(scheduler, wte->state()->forward.grad_weight);
+}
 }  // namespace cs::parallel

@@ -206,6 +206,86 @@ def case_zero_training(device, nvp2p):
         assert torch.allclose(pa[k].lp().float(), pb[k].lp().float(), atol=2e-2), (rank, k)
 
 
+def shard_full_into_tp(full, tp_model, rank, world, cfg):
+    """Copies the matching slices of a full GPT-2's parameters into this rank's TP model."""
+    H, d = cfg.n_head, cfg.n_embd
+    D = d // H
+    Hl = H // world
+    fp, tpp = full.named_parameters(), tp_model.named_parameters()
+    for k, dst in tpp.items():
+        src = fp[k.replace(".c_attn", ".attn.c_attn").replace(".c_proj", ".attn.c_proj").replace(".fc1", ".mlp.fc1").replace(".fc2", ".mlp.fc2")].raw()
+        if k.endswith("c_attn.weight"):
+            src = src.view(3, H, D, d)[:, rank * Hl:(rank + 1) * Hl].reshape(3 * Hl * D, d)
+        elif k.endswith("c_proj.weight"):
+            src = src[:, rank * d // world:(rank + 1) * d // world]
+        elif k.endswith("fc1.weight"):
+            src = src[rank * 4 * d // world:(rank + 1) * 4 * d // world]
+        elif k.endswith("fc2.weight"):
+            src = src[:, rank * 4 * d // world:(rank + 1) * 4 * d // world]
+        dst.raw().copy_(src)
+
+
+def full_grad_slice(name, g, rank, world, cfg):
+    H, d = cfg.n_head, cfg.n_embd
+    D, Hl = d // H, H // world
+    if name.endswith("c_attn.weight"):
+        return g.view(3, H, D, d)[:, rank * Hl:(rank + 1) * Hl].reshape(3 * Hl * D, d)
+    if name.endswith("c_proj.weight"):
+        return g[:, rank * d // world:(rank + 1) * d // world]
+    if name.endswith("fc1.weight"):
+        return g[rank * 4 * d // world:(rank + 1) * 4 * d // world]
+    if name.endswith("fc2.weight"):
+        return g[:, rank * 4 * d // world:(rank + 1) * 4 * d // world]
+    return g
+
+
+def case_tp_training(device, nvp2p):
+    """Tensor-parallel GPT-2 (sequence-parallel activations) reproduces the single-device loss and gradients."""
+    comm, rank, world, s = make_comm(device, nvp2p)
+    amp = device == "cuda"
+    dtype = torch.float32 if amp else torch.float64
+    cs.manual_seed(3)
+    cfg = cs.GPT2Config(n_layer=2, n_head=4, n_embd=64, block_size=32, vocab_size=128, padded_vocab_size=128, dtype=dtype)
+    full = cs.GPT2(s, cfg)
+    tp = C.TPGPT2(s, cfg, comm)
+    s.synchronize()
+    shard_full_into_tp(full, tp, rank, world, cfg)
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, 128, (2 * world, 33), generator=g).to(device)
+    x, y = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+    bucket = cs.AllReduceBucket(1 << 16, "sum")
+    sync = cs.GradientSync(comm, bucket, True)
+
+    def run(m, *extra):
+        if amp:
+            with cs.autocast(s, torch.bfloat16):
+                return m.forward_loss(s, T(x), T(y))
+        return m.forward_loss(s, T(x), T(y))
+
+    loss_tp = run(tp)
+    tp.backward_loss(s, sync)
+    bucket.sync(s, comm)
+    loss_full = run(full)
+    full.backward_loss(s)
+    s.synchronize()
+    lt = cs.to_torch(s, loss_tp).double().to("cpu")
+    gathered = [torch.zeros_like(lt) for _ in range(world)]
+    dist.all_gather(gathered, lt) if device == "cpu" else None
+    if device == "cpu":
+        assert abs(sum(gathered).item() / world - loss_full.raw().item()) < 1e-9
+    gt, gf = tp.named_gradients(), full.named_gradients()
+    tol = dict(atol=3e-2, rtol=5e-2) if amp else dict(atol=1e-9, rtol=1e-7)
+    for k, gtp in gt.items():
+        fk = k.replace(".c_attn", ".attn.c_attn").replace(".c_proj", ".attn.c_proj").replace(".fc1", ".mlp.fc1").replace(".fc2", ".mlp.fc2")
+        ref = full_grad_slice(k, gf[fk].raw(), rank, world, cfg)
+        got = gtp.raw() / world
+        if amp:
+            err = (got.float() - ref.float()).norm() / (ref.float().norm() + 1e-12)
+            assert err < 6e-2, (rank, k, err.item())
+        else:
+            assert torch.allclose(got, ref, **tol), (rank, k, (got - ref).abs().max().item())
+
+
 def case_failure_injection(device, nvp2p):
     """A collective that fails on one rank surfaces as an error there; the others see the rank stop beating."""
     comm, rank, world, s = make_comm(device, False)

@@ -20,6 +20,12 @@ def test_two_gpu_ranks(case, backend):
 
 
 @needs2
+@pytest.mark.parametrize("backend", ["nccl", "nvp2p"])
+def test_tensor_parallel_matches_single_device(backend):
+    run_case("tp_training", device="cuda", extra=(backend,), timeout=600)
+
+
+@needs2
 def test_zero_fused_step_matches_replicated_adamw():
     run_case("zero_training", device="cuda", extra=("nvp2p",), timeout=600)
 
