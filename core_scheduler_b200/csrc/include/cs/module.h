@@ -203,7 +203,7 @@ struct FlattenOptions {
   // them in peer-mapped symmetric memory): (bytes) -> 1-D uint8 tensor of that many bytes.
   CS_ARG(std::function<at::Tensor(int64_t)>, arena_allocator) = {};
   CS_ARG(optional<at::ScalarType>, lp_dtype) = {};  // e.g. kBFloat16 for mixed precision
-  CS_ARG(bool, transposed_copies) = true;
+  CS_ARG(bool, transposed_copies) = false;          // only needed by consumers that want W^T laid out K-major
   CS_ARG(int64_t, pad_total_to) = 1;                // pad arena length (e.g. world size * 128 for sharding)
 };
 

@@ -69,6 +69,7 @@ struct CS_API TPBlockImpl : module::Module {
   std::shared_ptr<compute::ScaledDotProductAttention::State> attn_state;
   communication::Comm comm;
   int64_t local_heads{0};
+  Tensor saved_ln1_out, saved_ln2_out;  // row shards kept for the backward re-gather (fused path)
 };
 CS_MODULE(TPBlock);
 
@@ -95,6 +96,20 @@ struct CS_API TPGPT2Impl : module::Module {
   int64_t batch_{0}, seq_{0};
 };
 CS_MODULE(TPGPT2);
+
+// Fused tensor-parallel paths (one tcgen05 GEMM kernel each, over peer memory):
+//   all-gather -> GEMM: y[M, out_local] = gather(x_shard)[M, in] * W^T. The kernel's TMA producer
+//     reads every row block of x directly from its owner's symmetric buffer, own block first.
+//   GEMM -> reduce-scatter: the partial product's tiles are reduce-added (fp32) by the epilogue
+//     into the accumulator of the rank that owns the rows; the owner then adds the residual and
+//     rounds to bf16.
+// They apply when the communicator has symmetric memory, tensors are bf16 on the GPU and
+// M / tp is a multiple of 256; otherwise the unfused composition is used.
+CS_API Tensor column_parallel_forward(const Scheduler &scheduler, const communication::Comm &comm,
+                                      const std::shared_ptr<compute::Linear::State> &state, const ReadOnlyTensor &x_shard);
+CS_API Tensor row_parallel_forward(const Scheduler &scheduler, const communication::Comm &comm, const ReadOnlyTensor &weight,
+                                   const ReadOnlyTensor &x, const ReadOnlyTensor *residual_shard, bool weight_is_rhs);
+CS_API int64_t fused_tp_launches();
 
 // Row-shard collectives used by the TP model (comm-stream tasks):
 // gathers [M/tp, d] row shards into [M, d];

@@ -40,10 +40,17 @@ int gelu_forward(stream_t stream, const void *x, void *y, int64_t n);
 int gelu_backward(stream_t stream, const void *dy, const void *x, void *dx, int64_t n);
 // out = a + b (bf16)
 int add_bf16(stream_t stream, const void *a, const void *b, void *out, int64_t n);
+// out(bf16) = acc(fp32) (+ residual(bf16) when given); n % 8 == 0.
+int add_f32_residual_to_bf16(stream_t stream, const float *acc, const void *residual, void *out, int64_t n);
 // dst(bf16) = src(fp32); optionally also writes the [cols, rows] transpose of a row-major
 // [rows, cols] matrix (dst_t may be nullptr).
 int cast_fp32_to_bf16(stream_t stream, const float *src, void *dst, int64_t n);
 int transpose_cast_to_bf16(stream_t stream, const void *src, int src_dtype, void *dst_t, int64_t rows, int64_t cols);
+
+// packed[b,t,i,h,:] = src_i[b,h,t,:] for i in {q,k,v}: three [B,H,T,D] bf16 tensors into one
+// [B,T,3,H,D] tensor in a single pass (D % 8 == 0).
+int pack_qkv_bhtd(stream_t stream, const void *q, const void *k, const void *v, void *packed, int64_t B, int64_t H, int64_t T,
+                  int64_t D);
 
 // LayerNorm over the last dimension d (d % 8 == 0, d <= 8192). x,y bf16; gamma/beta fp32 or
 // bf16 (param_dtype as above); mean/rstd fp32 [rows].
@@ -71,8 +78,9 @@ int embedding_backward(stream_t stream, const int64_t *idx, const void *dy, floa
 // D[M,N] = op(A) * op(B)^T with bf16 operands and fp32 accumulation in tensor memory.
 //   layout kTN : A is [M,K] row-major (K contiguous), B is [N,K] row-major.        (forward / dgrad)
 //   layout kNT : A is [K,M] row-major (M contiguous), B is [K,N] row-major.        (weight gradient)
+//   layout kTM : A is [M,K] row-major (K contiguous), B is [K,N] row-major.        (input gradient dY * W)
 // Leading dimensions are in elements and must be multiples of 8; base pointers 16-byte aligned.
-enum GemmLayout : int { kTN = 0, kNT = 1 };
+enum GemmLayout : int { kTN = 0, kNT = 1, kTM = 2 };
 enum GemmEpilogue : int {
   kEpiStoreBf16 = 0,     // D(bf16) = acc (+ bias[n])
   kEpiResidualBf16 = 1,  // D(bf16) = acc (+ bias[n]) + aux[m,n]
@@ -95,6 +103,16 @@ struct GemmArgs {
   int layout;
   int epilogue;
   int64_t n_valid;   // kEpiCrossEntropy: columns >= n_valid are excluded from the softmax
+  // Fused collectives over peer memory (tensor parallelism); peer_count > 1 enables one of:
+  //   a_peers: all-gather -> GEMM. Row block j of A ([m / peer_count, k], leading dim lda) is read
+  //            by TMA straight from a_peers[j] (a peer's symmetric memory); no gathered copy exists.
+  //   d_peers: GEMM -> reduce-scatter. Row block j of D is reduce-added (fp32) into d_peers[j]
+  //            ([m / peer_count, n], leading dim ldd) on its owner; epilogue must be kEpiAccumF32.
+  // m / peer_count must be a multiple of 256. Tiles are visited starting with this rank's block.
+  int peer_count;
+  int peer_rank;
+  const void *a_peers[8];
+  void *d_peers[8];
 };
 // Returns 0 on success, -1 when the shape/alignment is not supported (caller falls back).
 int gemm_bf16(stream_t stream, const GemmArgs &args);

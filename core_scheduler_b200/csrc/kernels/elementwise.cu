@@ -300,6 +300,32 @@ int add_bf16(stream_t stream, const void *a, const void *b, void *out, int64_t n
                                 static_cast<__nv_bfloat16 *>(out), n8 * 8, n, 2);
   return finish_launch();
 }
+namespace {
+__global__ void __launch_bounds__(256) acc_residual_kernel(const float *__restrict__ acc, const Bf16x8 *__restrict__ res,
+                                                           Bf16x8 *__restrict__ out, int64_t n8) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float f[8];
+    load8(acc, i * 8, 0, f);
+    if (res) {
+      float r[8];
+      unpack(res[i], r);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) f[k] += r[k];
+    }
+    out[i] = pack(f);
+  }
+}
+}  // namespace
+
+int add_f32_residual_to_bf16(stream_t stream, const float *acc, const void *residual, void *out, int64_t n) {
+  if (n % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
+  if (n == 0) return 0;
+  acc_residual_kernel<<<grid_for(n / 8, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      acc, static_cast<const Bf16x8 *>(residual), static_cast<Bf16x8 *>(out), n / 8);
+  return finish_launch();
+}
+
 int cast_fp32_to_bf16(stream_t stream, const float *src, void *dst, int64_t n) {
   if (n) cast_kernel<<<grid_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(src, static_cast<__nv_bfloat16 *>(dst), n);
   return finish_launch();
@@ -314,6 +340,40 @@ int transpose_cast_to_bf16(stream_t stream, const void *src, int src_dtype, void
                                                          static_cast<__nv_bfloat16 *>(dst_t), rows, cols);
   else
     return static_cast<int>(cudaErrorInvalidValue);
+  return finish_launch();
+}
+
+namespace {
+__global__ void __launch_bounds__(256) pack_qkv_kernel(const Bf16x8 *__restrict__ q, const Bf16x8 *__restrict__ k,
+                                                       const Bf16x8 *__restrict__ v, Bf16x8 *__restrict__ out, int64_t B,
+                                                       int64_t H, int64_t T, int d8) {
+  // one thread per 16-byte piece of the output, output-major so that writes are fully coalesced
+  const int64_t total = B * T * 3 * H * d8;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    int64_t r = i;
+    const int c = static_cast<int>(r % d8);
+    r /= d8;
+    const int64_t h = r % H;
+    r /= H;
+    const int which = static_cast<int>(r % 3);
+    r /= 3;
+    const int64_t t = r % T;
+    const int64_t b = r / T;
+    const Bf16x8 *src = which == 0 ? q : (which == 1 ? k : v);
+    out[i] = src[((b * H + h) * T + t) * d8 + c];
+  }
+}
+}  // namespace
+
+int pack_qkv_bhtd(stream_t stream, const void *q, const void *k, const void *v, void *packed, int64_t B, int64_t H, int64_t T,
+                  int64_t D) {
+  if (D % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
+  const int64_t total = B * T * 3 * H * (D / 8);
+  if (total == 0) return 0;
+  pack_qkv_kernel<<<grid_for(total, 256, 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const Bf16x8 *>(q), static_cast<const Bf16x8 *>(k), static_cast<const Bf16x8 *>(v),
+      static_cast<Bf16x8 *>(packed), B, H, T, static_cast<int>(D / 8));
   return finish_launch();
 }
 

@@ -1,8 +1,9 @@
 // bf16 GEMM on the 5th-generation tensor cores (tcgen05) with fp32 accumulators in tensor
 // memory (TMEM), operands staged in shared memory by TMA, and fused epilogues.
 //
-//   D[M,N] = A * B^T     kTN: A [M,K] and B [N,K] row-major (K contiguous)   forward / dgrad
+//   D[M,N] = A * B^T     kTN: A [M,K] and B [N,K] row-major (K contiguous)   forward
 //                        kNT: A [K,M] and B [K,N] row-major (M/N contiguous) weight gradient
+//                        kTM: A [M,K] row-major, B [K,N] row-major           input gradient (dY * W)
 //
 // Structure (one persistent CTA per SM, 320 threads):
 //   warp 0      TMA producer: cp.async.bulk.tensor tiles -> 4-stage shared-memory ring
@@ -60,7 +61,14 @@ struct KParams {
   int m_tiles, n_tiles, splits, kb_total, kb_per_split;
   int atomic_out;     // fp32 output accumulated with red.global.add (split-K or accumulate mode)
   unsigned lbo_mn, sbo_mn, kstep_mn;  // MN-major descriptor parameters (bytes)
+  int peer_mode;       // 0 none, 1 = A row blocks come from peers, 2 = D row blocks go to peers
+  int peer_rank, peer_count;
+  int rows_per_peer;
   DeviceStatus *status;
+};
+
+struct PeerMaps {
+  CUtensorMap m[8];
 };
 
 __device__ DeviceStatus g_gemm_status;
@@ -146,11 +154,37 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_b
   return desc;
 }
 
-__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
+// Exact-form GELU (erf) for the epilogues. erf uses the rational approximation 7.1.26 of
+// Abramowitz & Stegun (absolute error < 1.5e-7, far below bf16 resolution): one reciprocal, one
+// exponential and five FMAs. GELU'(x) needs exp(-x^2/2) as well, which is the exponential the
+// erf of x/sqrt(2) already computed, so the derivative costs two special-function ops per element
+// instead of the ~45 instructions of erff + expf: the dGELU epilogue stays hidden behind a
+// K = 768 main loop.
+struct ErfParts {
+  float erf_abs;  // erf(|x| / sqrt(2))
+  float e;        // exp(-x^2 / 2)
+};
+__device__ __forceinline__ ErfParts erf_parts(float x) {
+  const float z = fabsf(x) * 0.70710678118654752440f;
+  const float t = __frcp_rn(fmaf(0.3275911f, z, 1.0f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  poly *= t;
+  ErfParts r;
+  r.e = __expf(-z * z);
+  r.erf_abs = fmaf(-poly, r.e, 1.0f);
+  return r;
+}
+__device__ __forceinline__ float gelu_f(float x) {
+  const ErfParts p = erf_parts(x);
+  return 0.5f * x * (1.0f + copysignf(p.erf_abs, x));
+}
 __device__ __forceinline__ float gelu_grad_f(float x) {
-  const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752440f));
-  const float pdf = 0.39894228040143267794f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
+  const ErfParts p = erf_parts(x);
+  const float cdf = 0.5f * (1.0f + copysignf(p.erf_abs, x));
+  return fmaf(x * 0.39894228040143267794f, p.e, cdf);
 }
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
@@ -368,13 +402,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
           const uint32_t b_dst = a_dst + A_BYTES;
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
-          if (p.layout == kTN) {
-            tma_load_2d(a_dst, &map_a, full_bar(stage), kb * BK, c.m0);
-            tma_load_2d(b_dst, &map_b, full_bar(stage), kb * BK, c.n0);
-          } else {
-            // MN-major: 64-element (128-byte) wide boxes of 64 k-rows, 8 KB each
+          // K-major operands: one box; MN-major operands: 64-element (128-byte) wide boxes of
+          // 64 k-rows, 8 KB each
+          if (p.layout == kNT) {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &map_a, full_bar(stage), c.m0 + j * 64, kb * BK);
+          } else {
+            tma_load_2d(a_dst, &map_a, full_bar(stage), kb * BK, c.m0);
+          }
+          if (p.layout == kTN) {
+            tma_load_2d(b_dst, &map_b, full_bar(stage), kb * BK, c.n0);
+          } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &map_b, full_bar(stage), c.n0 + j * 64, kb * BK);
           }
@@ -398,12 +436,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     // -------------------------------------------------------------------- MMA issuer ----
     if (lane == 0) {
       const uint32_t a_major = p.layout == kNT ? 1u : 0u;
+      const uint32_t b_major = p.layout == kTN ? 0u : 1u;
       const uint32_t idesc = (1u << 4) /*fp32 accum*/ | (1u << 7) /*A bf16*/ | (1u << 10) /*B bf16*/ | (a_major << 15) |
-                             (a_major << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                             (b_major << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
                              (static_cast<uint32_t>(BM >> 4) << 24);
-      const uint32_t lbo = p.layout == kNT ? p.lbo_mn : 16u;
-      const uint32_t sbo = p.layout == kNT ? p.sbo_mn : 1024u;
-      const uint32_t kstep = p.layout == kNT ? p.kstep_mn : static_cast<uint32_t>(UMMA_K * 2);
+      const uint32_t lbo_a = a_major ? p.lbo_mn : 16u, lbo_b = b_major ? p.lbo_mn : 16u;
+      const uint32_t sbo_a = a_major ? p.sbo_mn : 1024u, sbo_b = b_major ? p.sbo_mn : 1024u;
+      const uint32_t kstep_a = a_major ? p.kstep_mn : static_cast<uint32_t>(UMMA_K * 2);
+      const uint32_t kstep_b = b_major ? p.kstep_mn : static_cast<uint32_t>(UMMA_K * 2);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -424,8 +464,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           const uint32_t b_src = a_src + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = make_smem_desc(a_src + k * kstep, lbo, sbo);
-            const uint64_t db = make_smem_desc(b_src + k * kstep, lbo, sbo);
+            const uint64_t da = make_smem_desc(a_src + k * kstep_a, lbo_a, sbo_a);
+            const uint64_t db = make_smem_desc(b_src + k * kstep_b, lbo_b, sbo_b);
             tcgen05_mma(d_tmem, da, db, idesc, (kb > c.kb_begin || k > 0) ? 1u : 0u);
           }
           tcgen05_commit(empty_bar(stage));  // frees the stage once these MMAs retired
@@ -549,7 +589,9 @@ __device__ __forceinline__ void staging_release(const CUtensorMap *map, uint32_t
 
 __device__ __forceinline__ void epilogue_tile_tma(const KParams &p, const CUtensorMap *map_d, const CUtensorMap *map_d2, int m0,
                                                   int n0, int n_tile, uint32_t tmem_acc, int q, int half, int lane,
-                                                  EpilogueStaging &st) {
+                                                  EpilogueStaging &st, int store_row_base) {
+  // store_row_base: first row of the destination tensor map inside the logical output (non-zero
+  // when the rows are scattered to per-owner buffers)
   const int row0 = m0 + q * 32;
   const long long row = row0 + lane;
   const bool row_ok = row < p.m;
@@ -575,7 +617,7 @@ __device__ __forceinline__ void epilogue_tile_tma(const KParams &p, const CUtens
 #pragma unroll
       for (int g = 0; g < 8; ++g)
         st_shared_v4(staging_addr(box, lane, g), v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
-      staging_release(map_d, box, static_cast<int>(gcol), row0, rows_in_range && cols_in_range, reduce, lane);
+      staging_release(map_d, box, static_cast<int>(gcol), row0 - store_row_base, rows_in_range && cols_in_range, reduce, lane);
       continue;
     }
     if (p.bias && cols_in_range) {
@@ -653,8 +695,8 @@ __device__ __forceinline__ void epilogue_tile_tma(const KParams &p, const CUtens
     if (sub == 1) {
       const int c0 = n0 + half * 128 + (ch - 1) * 32;
       const bool in_range = rows_in_range && c0 < p.n;
-      staging_release(map_d, box, c0, row0, in_range, false, lane);
-      if (p.epilogue == kEpiGeluDual) staging_release(map_d2, box2, c0, row0, in_range, false, lane);
+      staging_release(map_d, box, c0, row0 - store_row_base, in_range, false, lane);
+      if (p.epilogue == kEpiGeluDual) staging_release(map_d2, box2, c0, row0 - store_row_base, in_range, false, lane);
     }
   }
   if (p.epilogue == kEpiCrossEntropy && row_ok) {
@@ -726,7 +768,13 @@ __device__ __forceinline__ TileCoord tile_coord2(const KParams &p, int tile) {
   const int split = tile / mn;
   const int rem = tile - split * mn;
   const int n_tile = rem / p.m_tiles;
-  const int m_tile = rem - n_tile * p.m_tiles;
+  int m_tile = rem - n_tile * p.m_tiles;
+  if (p.peer_mode) {
+    // start with the rows this rank owns, then walk the peers' blocks in ring order, so that
+    // local data is consumed while remote traffic ramps up and no two ranks hammer the same peer
+    const int per_peer = p.rows_per_peer / BM2;
+    m_tile = (m_tile + p.peer_rank * per_peer) % p.m_tiles;
+  }
   TileCoord c;
   c.m0 = m_tile * BM2;
   c.n0 = n_tile * BN;
@@ -738,7 +786,8 @@ __device__ __forceinline__ TileCoord tile_coord2(const KParams &p, int tile) {
 
 __global__ void __launch_bounds__(THREADS, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-             const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_d2, const KParams p) {
+             const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_d2,
+             const __grid_constant__ PeerMaps peer_maps, const KParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -805,12 +854,19 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
           const uint32_t b_dst = a_dst + A_BYTES;
           const uint32_t full_leader = mapa_shared(full_bar(stage), 0);
           if (leader) mbar_expect_tx(full_bar(stage), 2 * STAGE2_BYTES);
-          if (p.layout == kTN) {
-            tma_load_2d_pair(a_dst, &map_a, full_leader, kb * BK, m0);
-            tma_load_2d_pair(b_dst, &map_b, full_leader, kb * BK, nb0);
-          } else {
+          if (p.layout == kNT) {
 #pragma unroll
             for (int j = 0; j < 2; ++j) tma_load_2d_pair(a_dst + j * 8192, &map_a, full_leader, m0 + j * 64, kb * BK);
+          } else if (p.peer_mode == 1) {
+            // all-gather fused into the load: this tile's rows live in their owner's memory
+            const int owner = m0 / p.rows_per_peer;
+            tma_load_2d_pair(a_dst, &peer_maps.m[owner], full_leader, kb * BK, m0 - owner * p.rows_per_peer);
+          } else {
+            tma_load_2d_pair(a_dst, &map_a, full_leader, kb * BK, m0);
+          }
+          if (p.layout == kTN) {
+            tma_load_2d_pair(b_dst, &map_b, full_leader, kb * BK, nb0);
+          } else {
 #pragma unroll
             for (int j = 0; j < 2; ++j) tma_load_2d_pair(b_dst + j * 8192, &map_b, full_leader, nb0 + j * 64, kb * BK);
           }
@@ -824,12 +880,14 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   } else if (warp == 1) {
     // ------------------------------------------------ MMA issuer (leader CTA only) ----
     if (lane == 0 && leader) {
-      const uint32_t major = p.layout == kNT ? 1u : 0u;
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (major << 15) | (major << 16) |
+      const uint32_t a_major = p.layout == kNT ? 1u : 0u;
+      const uint32_t b_major = p.layout == kTN ? 0u : 1u;
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (a_major << 15) | (b_major << 16) |
                              (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM2 >> 4) << 24);
-      const uint32_t lbo = p.layout == kNT ? p.lbo_mn : 16u;
-      const uint32_t sbo = p.layout == kNT ? p.sbo_mn : 1024u;
-      const uint32_t kstep = p.layout == kNT ? p.kstep_mn : static_cast<uint32_t>(UMMA_K * 2);
+      const uint32_t lbo_a = a_major ? p.lbo_mn : 16u, lbo_b = b_major ? p.lbo_mn : 16u;
+      const uint32_t sbo_a = a_major ? p.sbo_mn : 1024u, sbo_b = b_major ? p.sbo_mn : 1024u;
+      const uint32_t kstep_a = a_major ? p.kstep_mn : static_cast<uint32_t>(UMMA_K * 2);
+      const uint32_t kstep_b = b_major ? p.kstep_mn : static_cast<uint32_t>(UMMA_K * 2);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -850,8 +908,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
           const uint32_t b_src = a_src + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = make_smem_desc(a_src + k * kstep, lbo, sbo);
-            const uint64_t db = make_smem_desc(b_src + k * kstep, lbo, sbo);
+            const uint64_t da = make_smem_desc(a_src + k * kstep_a, lbo_a, sbo_a);
+            const uint64_t db = make_smem_desc(b_src + k * kstep_b, lbo_b, sbo_b);
             tcgen05_mma_pair(d_tmem, da, db, idesc, (kb > c.kb_begin || k > 0) ? 1u : 0u);
           }
           tcgen05_commit_pair(empty_bar(stage));
@@ -882,8 +940,15 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       const TileCoord c = tile_coord2(p, tile);
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag)) break;
       tcgen05_fence_after();
-      epilogue_tile_tma(p, &map_d, &map_d2, c.m0 + static_cast<int>(cta) * 128, c.n0, c.n_tile, tmem_base + acc * BN, q, half,
-                        lane, st);
+      const int m0_cta = c.m0 + static_cast<int>(cta) * 128;
+      if (p.peer_mode == 2) {
+        // reduce-scatter fused into the epilogue: add this tile into its owner's accumulator
+        const int owner = m0_cta / p.rows_per_peer;
+        epilogue_tile_tma(p, &peer_maps.m[owner], &map_d2, m0_cta, c.n0, c.n_tile, tmem_base + acc * BN, q, half, lane, st,
+                          owner * p.rows_per_peer);
+      } else {
+        epilogue_tile_tma(p, &map_d, &map_d2, m0_cta, c.n0, c.n_tile, tmem_base + acc * BN, q, half, lane, st, 0);
+      }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(tmem_empty_bar(acc), 0));
@@ -1003,11 +1068,13 @@ int gemm_bf16(stream_t stream, const GemmArgs &a) {
   if (a.m <= 0 || a.n <= 0 || a.k <= 0) return -1;
   if (a.n % 8 != 0 || a.ldd % 8 != 0 || a.lda % 8 != 0 || a.ldb % 8 != 0) return -1;
   if ((reinterpret_cast<uintptr_t>(a.a) | reinterpret_cast<uintptr_t>(a.b) | reinterpret_cast<uintptr_t>(a.d)) & 15) return -1;
+  if (!a.b || (!a.a && !(a.peer_count > 1 && a.a_peers[0])) || (!a.d && !(a.peer_count > 1 && a.d_peers[0]))) return -1;
   if (a.aux && (reinterpret_cast<uintptr_t>(a.aux) & 15)) return -1;
   if (a.d2 && (reinterpret_cast<uintptr_t>(a.d2) & 15)) return -1;
   if (a.bias && (reinterpret_cast<uintptr_t>(a.bias) & 15)) return -1;
   const bool f32_out = a.epilogue == kEpiStoreF32 || a.epilogue == kEpiAccumF32;
-  if (a.layout == kTN && a.k % 8 != 0) return -1;
+  if (a.layout != kNT && a.k % 8 != 0) return -1;
+  if (a.layout < 0 || a.layout > kTM) return -1;
   if (a.layout == kNT && (a.m % 8 != 0)) return -1;
   if (f32_out && a.n % 4 != 0) return -1;
   if (a.m > 0x7fffffffLL || a.n > 0x7fffffffLL || a.k > 0x7fffffffLL) return -1;
@@ -1018,18 +1085,48 @@ int gemm_bf16(stream_t stream, const GemmArgs &a) {
   const bool pair_kernel = !one_cta_only && a.m > 128;  // a single 128-row tile gains nothing from pairing
   const int tile_m = pair_kernel ? BM2 : BM;
   const uint32_t b_box_rows = pair_kernel ? 128u : static_cast<uint32_t>(BN);
+  PeerMaps peer_maps{};
+  int peer_mode = 0;
+  int rows_per_peer = 0;
+  if (a.peer_count > 1) {
+    if (!pair_kernel || a.peer_count > 8 || a.m % a.peer_count != 0) return -1;
+    rows_per_peer = static_cast<int>(a.m / a.peer_count);
+    if (rows_per_peer % BM2 != 0) return -1;
+    if (a.a_peers[0]) {
+      if (a.layout == kNT) return -1;
+      peer_mode = 1;
+      for (int j = 0; j < a.peer_count; ++j)
+        if (!a.a_peers[j] || (reinterpret_cast<uintptr_t>(a.a_peers[j]) & 15) ||
+            !get_tensor_map(a.a_peers[j], a.k, rows_per_peer, a.lda, BK, BM, &peer_maps.m[j]))
+          return -1;
+    } else if (a.d_peers[0]) {
+      if (a.epilogue != kEpiAccumF32) return -1;
+      peer_mode = 2;
+      for (int j = 0; j < a.peer_count; ++j)
+        if (!a.d_peers[j] || (reinterpret_cast<uintptr_t>(a.d_peers[j]) & 15) ||
+            !get_tensor_map(a.d_peers[j], a.n, rows_per_peer, a.ldd, 32, 32, &peer_maps.m[j], 4))
+          return -1;
+    }
+  }
   CUtensorMap map_a, map_b;
-  if (a.layout == kTN) {
+  if (peer_mode == 1) {
+    map_a = peer_maps.m[0];
+  } else if (a.layout == kNT) {
+    if (!get_tensor_map(a.a, a.m, a.k, a.lda, 64, BK, &map_a)) return -1;
+  } else {
     if (!get_tensor_map(a.a, a.k, a.m, a.lda, BK, BM, &map_a)) return -1;
+  }
+  if (a.layout == kTN) {
     if (!get_tensor_map(a.b, a.k, a.n, a.ldb, BK, b_box_rows, &map_b)) return -1;
   } else {
-    if (!get_tensor_map(a.a, a.m, a.k, a.lda, 64, BK, &map_a)) return -1;
     if (!get_tensor_map(a.b, a.n, a.k, a.ldb, 64, BK, &map_b)) return -1;
   }
   CUtensorMap map_d{}, map_d2{};
   if (pair_kernel) {
     // output boxes of the TMA-store epilogue: 32 rows x 128 bytes
-    if (f32_out) {
+    if (peer_mode == 2) {
+      map_d = peer_maps.m[0];
+    } else if (f32_out) {
       if (!get_tensor_map(a.d, a.n, a.m, a.ldd, 32, 32, &map_d, 4)) return -1;
     } else {
       if (!get_tensor_map(a.d, a.n, a.m, a.ldd, 64, 32, &map_d)) return -1;
@@ -1095,6 +1192,15 @@ int gemm_bf16(stream_t stream, const GemmArgs &a) {
       if (e != cudaSuccess) return static_cast<int>(e);
     }
   }
+  p.peer_mode = peer_mode;
+  p.peer_rank = a.peer_rank;
+  p.peer_count = a.peer_count;
+  p.rows_per_peer = rows_per_peer;
+  if (peer_mode == 2) {
+    p.splits = 1;  // the cross-rank sum already happens in the destination
+    p.kb_per_split = p.kb_total;
+    p.atomic_out = 1;
+  }
   p.lbo_mn = env_unsigned("CS_GEMM_MN_LBO", 8192);
   p.sbo_mn = env_unsigned("CS_GEMM_MN_SBO", 1024);
   p.kstep_mn = env_unsigned("CS_GEMM_MN_KSTEP", 2048);
@@ -1126,7 +1232,7 @@ int gemm_bf16(stream_t stream, const GemmArgs &a) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm2_kernel, map_a, map_b, map_d, map_d2, p);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm2_kernel, map_a, map_b, map_d, map_d2, peer_maps, p);
     if (e != cudaSuccess) return static_cast<int>(e);
     return finish_launch(1);
   }

@@ -103,8 +103,11 @@ PYBIND11_MODULE(_C, m) {
           if (layout == cs::kernels::kTN) {
             g.m = a.size(0); g.k = a.size(1); g.n = b.size(0);
             g.lda = a.stride(0); g.ldb = b.stride(0);
-          } else {
+          } else if (layout == cs::kernels::kNT) {
             g.k = a.size(0); g.m = a.size(1); g.n = b.size(1);
+            g.lda = a.stride(0); g.ldb = b.stride(0);
+          } else {
+            g.m = a.size(0); g.k = a.size(1); g.n = b.size(1);
             g.lda = a.stride(0); g.ldb = b.stride(0);
           }
           g.ldd = d.stride(0);
@@ -219,7 +222,7 @@ PYBIND11_MODULE(_C, m) {
           o.transposed_copies(transposed).pad_total_to(pad_to);
           return module::flatten_parameters(s, mod, o);
         },
-        py::arg("scheduler"), py::arg("module"), py::arg("lp_dtype") = py::none(), py::arg("transposed_copies") = true,
+        py::arg("scheduler"), py::arg("module"), py::arg("lp_dtype") = py::none(), py::arg("transposed_copies") = false,
         py::arg("pad_total_to") = 1);
 
   // ---- compute ops ---------------------------------------------------------------------------
@@ -594,6 +597,7 @@ PYBIND11_MODULE(_C, m) {
       }, py::arg("scheduler"), py::arg("sync") = py::none())
       .def("replicated_parameters", &parallel::TPGPT2Impl::replicated_parameters);
   m.def("all_gather_rows", &parallel::all_gather_rows);
+  m.def("fused_tp_launches", &parallel::fused_tp_launches);
   m.def("reduce_scatter_rows", [](const Scheduler &s, const Comm &c, const ReadOnlyTensor &full) {
     return parallel::reduce_scatter_rows(s, c, full, nullptr);
   });

@@ -137,7 +137,7 @@ std::array<at::Tensor, 3> attention_backward_body(const at::Tensor &dout4, const
   const at::Tensor &lse = bw.logsumexp.impl()->tensor;
   if (library_flash_ok(q) && use_cudnn_engine() && q.size(-1) <= 128) {
     auto r = at::_scaled_dot_product_cudnn_attention_backward(
-        dout.to(q.scalar_type()).contiguous(), q, k, v, out, lse, bw.philox_seed.impl()->tensor, bw.philox_offset.impl()->tensor,
+        dout.to(q.scalar_type()), q, k, v, out, lse, bw.philox_seed.impl()->tensor, bw.philox_offset.impl()->tensor,
         at::Tensor{}, bw.cum_seq_q.impl()->tensor, bw.cum_seq_k.impl()->tensor, bw.max_q, bw.max_k, args.dropout_p,
         args.is_causal, scale);
     return {std::get<0>(r).transpose(1, 2), std::get<1>(r).transpose(1, 2), std::get<2>(r).transpose(1, 2)};
@@ -255,9 +255,18 @@ Tensor ScaledDotProductAttention::backward_packed(const Scheduler &scheduler, co
            const at::Tensor do4 = grad_out.impl()->tensor.reshape({B, T, H, D});
            auto r = attention_backward_body(do4, x5.select(2, 0), x5.select(2, 1), x5.select(2, 2), args, bw);
            at::Tensor packed = at::empty({B, T, 3, H, D}, x.options());
-           packed.select(2, 0).copy_(r[0]);
-           packed.select(2, 1).copy_(r[1]);
-           packed.select(2, 2).copy_(r[2]);
+           // r[i] are [B,T,H,D] views of [B,H,T,D] buffers; one kernel interleaves all three
+           const at::Tensor dq = r[0].transpose(1, 2), dk = r[1].transpose(1, 2), dv = r[2].transpose(1, 2);
+           if (x.is_cuda() && x.scalar_type() == at::kBFloat16 && fused_enabled() && D % 8 == 0 && dq.is_contiguous() &&
+               dk.is_contiguous() && dv.is_contiguous()) {
+             check_kernel(kernels::pack_qkv_bhtd(current_stream(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                                 packed.data_ptr(), B, H, T, D),
+                          "pack_qkv_bhtd");
+           } else {
+             packed.select(2, 0).copy_(r[0]);
+             packed.select(2, 1).copy_(r[1]);
+             packed.select(2, 2).copy_(r[2]);
+           }
            dqkv.impl()->tensor = packed.view({B, T, 3 * H * D});
          });
   attention_release(b);

@@ -230,23 +230,23 @@ void linear_forward_body(const ReadOnlyTensor &input, const Tensor &weight, cons
 at::Tensor linear_dgrad(const at::Tensor &dy_in, const Tensor &weight, at::ScalarType dt, const at::Tensor *pre) {
   const at::Tensor dy = cast_if(dy_in, dt);
   if (dy.is_cuda() && dt == at::kBFloat16 && fused_enabled()) {
-    const at::Tensor wt = working_copy_transposed(weight, dt);  // [in, out]
+    const at::Tensor wc = working_copy(weight, dt);  // [out, in], read as the MN-major B operand
     const at::Tensor dy2 = as2d(dy);
     auto out_sizes = dy.sizes().vec();
-    out_sizes.back() = wt.size(0);
+    out_sizes.back() = wc.size(1);
     at::Tensor dx = at::empty(out_sizes, dy.options());
     at::Tensor pre2;
     kernels::GemmArgs g{};
     g.a = dy2.data_ptr();
-    g.b = wt.data_ptr();
+    g.b = wc.data_ptr();
     g.d = dx.data_ptr();
     g.m = dy2.size(0);
-    g.n = wt.size(0);
+    g.n = wc.size(1);
     g.k = dy2.size(1);
     g.lda = g.k;
-    g.ldb = g.k;
+    g.ldb = g.n;
     g.ldd = g.n;
-    g.layout = kernels::kTN;
+    g.layout = kernels::kTM;
     g.epilogue = kernels::kEpiStoreBf16;
     if (pre) {
       pre2 = cast_if(*pre, dt).contiguous();

@@ -3,7 +3,9 @@
 
 #include <c10/cuda/CUDAStream.h>
 
+#include <atomic>
 #include <cmath>
+#include <unordered_map>
 
 #include "kernels/collectives.h"
 
@@ -14,7 +16,7 @@ std::shared_ptr<module::FlatParameters> flatten_symmetric(const Scheduler &sched
                                                          const communication::Comm &comm, optional<at::ScalarType> lp_dtype) {
   auto ctx = comm.impl()->symmetric;
   module::FlattenOptions opts;
-  opts.lp_dtype(lp_dtype).transposed_copies(true).pad_total_to(comm.get_size() * 128);
+  opts.lp_dtype(lp_dtype).transposed_copies(false).pad_total_to(comm.get_size() * 128);
   if (ctx) {
     opts.arena_allocator([ctx](int64_t bytes) {
       const auto block = ctx->allocate(bytes);
@@ -228,6 +230,149 @@ Tensor reduce_scatter_rows(const Scheduler &scheduler, const communication::Comm
   return compute::Utils::add(scheduler, recv, *residual);
 }
 
+// ------------------------------------------------------------ fused TP GEMM + collective ----
+namespace {
+std::atomic<int64_t> g_fused_tp_launches{0};
+
+struct SymmetricSlots {
+  communication::SymmetricBlock block[2];
+  int next{0};
+};
+// Per-context staging buffers for the fused paths (allocated on first use, identical call
+// sequences on every rank give identical offsets).
+std::unordered_map<const communication::SymmetricContext *, SymmetricSlots> g_ag_slots, g_rs_slots;
+
+communication::SymmetricBlock next_slot(std::unordered_map<const communication::SymmetricContext *, SymmetricSlots> &table,
+                                        communication::SymmetricContext &ctx, int64_t bytes, bool alternate) {
+  auto &slots = table[&ctx];
+  const int idx = alternate ? slots.next : 0;
+  if (alternate) slots.next ^= 1;
+  if (slots.block[idx].bytes < bytes) {
+    if (slots.block[idx].bytes > 0) ctx.release(slots.block[idx]);
+    slots.block[idx] = ctx.allocate(bytes);
+  }
+  return slots.block[idx];
+}
+
+bool fused_tp_ok(const communication::Comm &comm, const at::Tensor &x, int64_t total_rows) {
+  auto ctx = comm.impl()->symmetric;
+  const int64_t tp = comm.get_size();
+  return ctx && tp > 1 && tp <= 8 && x.is_cuda() && x.scalar_type() == at::kBFloat16 &&
+         compute::get_backend() == compute::Backend::kFused && total_rows % tp == 0 && (total_rows / tp) % 256 == 0 &&
+         std::getenv("CS_TP_UNFUSED") == nullptr;
+}
+}  // namespace
+
+int64_t fused_tp_launches() { return g_fused_tp_launches.load(); }
+
+Tensor column_parallel_forward(const Scheduler &scheduler, const communication::Comm &comm,
+                               const std::shared_ptr<compute::Linear::State> &state, const ReadOnlyTensor &x_shard) {
+  const int64_t tp = comm.get_size();
+  const bool can_fuse = x_shard.defined() && fused_tp_ok(comm, x_shard.impl()->tensor, x_shard.size(0) * tp) &&
+                        scheduler.impl()->autocast_enabled && !state->args.bias;
+  if (!can_fuse) {
+    Tensor full = all_gather_rows(scheduler, comm, x_shard);
+    return compute::Linear::forward(scheduler, state, full);
+  }
+  Tensor out;
+  const bool gelu = state->args.gelu_epilogue;
+  state->backward.input = Tensor{};  // backward re-gathers the input; nothing is kept alive here
+  state->forward.weight.impl()->autocast_enabled = true;
+  state->forward.weight.impl()->autocast_dtype = at::kBFloat16;
+  submit(scheduler, "cs::parallel::column_parallel_forward(all-gather+GEMM)", Task::Impl::kMain, Task::Impl::kCompute, {out},
+         {x_shard, state->forward.weight}, [out, x_shard, w = state->forward.weight, comm, gelu, tp](const FnTask &) {
+           auto &ctx = *comm.impl()->symmetric;
+           const at::Tensor xs = x_shard.impl()->tensor.contiguous();
+           const at::Tensor wc = compute::working_copy(w, at::kBFloat16);
+           const int64_t rows = xs.size(0), k = xs.size(1), n = wc.size(0);
+           const auto slot = next_slot(g_ag_slots, ctx, rows * k * 2, true);
+           auto stream = c10::cuda::getCurrentCUDAStream().stream();
+           CS_CHECK_CUDART(cudaMemcpyAsync(ctx.bases[ctx.rank] + slot.offset, xs.data_ptr(), static_cast<size_t>(rows * k * 2),
+                                           cudaMemcpyDeviceToDevice, stream));
+           ctx.barrier();  // every rank's shard is in place (and the slot's previous readers are done)
+           at::Tensor y = at::empty({rows * tp, n}, xs.options());
+           at::Tensor y2;
+           kernels::GemmArgs g{};
+           g.b = wc.data_ptr();
+           g.d = y.data_ptr();
+           g.m = rows * tp;
+           g.n = n;
+           g.k = k;
+           g.lda = k;
+           g.ldb = k;
+           g.ldd = n;
+           g.layout = kernels::kTN;
+           g.epilogue = kernels::kEpiStoreBf16;
+           if (gelu) {
+             y2 = at::empty_like(y);
+             g.d2 = y2.data_ptr();
+             g.epilogue = kernels::kEpiGeluDual;
+           }
+           g.peer_count = static_cast<int>(tp);
+           g.peer_rank = ctx.rank;
+           for (int p = 0; p < tp; ++p) g.a_peers[p] = ctx.bases[p] + slot.offset;
+           const int code = kernels::gemm_bf16(stream, g);
+           CS_ASSERT_TRUE(code == 0, "fused all-gather+GEMM launch failed (", code, ")");
+           g_fused_tp_launches.fetch_add(1);
+           out.impl()->tensor = y;
+           out.impl()->companion = y2;
+         });
+  return out;
+}
+
+Tensor row_parallel_forward(const Scheduler &scheduler, const communication::Comm &comm, const ReadOnlyTensor &weight,
+                            const ReadOnlyTensor &x, const ReadOnlyTensor *residual_shard, bool weight_is_rhs) {
+  // weight_is_rhs == false: y = x * W^T with W [out, in_local]      (forward of c_proj / fc2)
+  // weight_is_rhs == true : y = x * W   with W [out_local, in]      (input gradient of c_attn / fc1)
+  const int64_t tp = comm.get_size();
+  Tensor out;
+  std::vector<ReadOnlyTensor> ins{x, weight};
+  std::optional<ReadOnlyTensor> res;
+  if (residual_shard) {
+    res = *residual_shard;
+    ins.push_back(*residual_shard);
+  }
+  submit(scheduler, "cs::parallel::row_parallel_forward(GEMM+reduce-scatter)", Task::Impl::kMain, Task::Impl::kCompute, {out}, ins,
+         [out, x, weight, res, comm, tp, weight_is_rhs](const FnTask &) {
+           auto &ctx = *comm.impl()->symmetric;
+           const at::Tensor xa = x.impl()->tensor.reshape({-1, x.impl()->tensor.size(-1)}).contiguous();
+           const at::Tensor wc = compute::working_copy(weight, at::kBFloat16);
+           const int64_t m = xa.size(0), k = xa.size(1);
+           const int64_t n = weight_is_rhs ? wc.size(1) : wc.size(0);
+           const int64_t rows = m / tp;
+           const auto slot = next_slot(g_rs_slots, ctx, rows * n * 4, false);
+           auto stream = c10::cuda::getCurrentCUDAStream().stream();
+           float *acc = reinterpret_cast<float *>(ctx.bases[ctx.rank] + slot.offset);
+           CS_CHECK_CUDART(cudaMemsetAsync(acc, 0, static_cast<size_t>(rows * n * 4), stream));
+           ctx.barrier();  // all accumulators are zero before anybody adds
+           kernels::GemmArgs g{};
+           g.a = xa.data_ptr();
+           g.b = wc.data_ptr();
+           g.m = m;
+           g.n = n;
+           g.k = k;
+           g.lda = k;
+           g.ldb = weight_is_rhs ? n : k;
+           g.ldd = n;
+           g.layout = weight_is_rhs ? kernels::kTM : kernels::kTN;
+           g.epilogue = kernels::kEpiAccumF32;
+           g.peer_count = static_cast<int>(tp);
+           g.peer_rank = ctx.rank;
+           for (int p = 0; p < tp; ++p) g.d_peers[p] = ctx.bases[p] + slot.offset;
+           const int code = kernels::gemm_bf16(stream, g);
+           CS_ASSERT_TRUE(code == 0, "fused GEMM+reduce-scatter launch failed (", code, ")");
+           g_fused_tp_launches.fetch_add(1);
+           ctx.barrier();  // every rank's tiles have been added into our rows
+           at::Tensor y = at::empty({rows, n}, xa.options());
+           at::Tensor r;
+           if (res) r = res->impl()->tensor.contiguous();
+           const int rc = kernels::add_f32_residual_to_bf16(stream, acc, res ? r.data_ptr() : nullptr, y.data_ptr(), rows * n);
+           CS_ASSERT_TRUE(rc == 0, "accumulator finalisation failed");
+           out.impl()->tensor = y;
+         });
+  return out;
+}
+
 namespace {
 compute::Linear::Options tp_linear(const Scheduler &scheduler, const models::GPT2Config &c, int64_t in, int64_t out) {
   return compute::Linear::Options{in, out}.bias(false).device(c.device().value_or(scheduler.device())).dtype(c.dtype());
@@ -256,19 +401,50 @@ TPBlockImpl::TPBlockImpl(const Scheduler &scheduler, const models::GPT2Config &c
 Tensor TPBlockImpl::forward(const Scheduler &scheduler, const ReadOnlyTensor &x_shard, int64_t batch, int64_t seq) {
   using compute::Utils;
   const int64_t d_local = c_proj->state()->forward.weight.size(1);
+  const bool fuse = x_shard.defined() && fused_tp_ok(comm, x_shard.impl()->tensor, batch * seq) &&
+                    scheduler.impl()->autocast_enabled;
+  saved_ln1_out = Tensor{};
+  saved_ln2_out = Tensor{};
   Tensor a = ln1->forward(scheduler, x_shard);                 // [M/tp, d]
-  Tensor a_full = all_gather_rows(scheduler, comm, a);          // [M, d]
-  Tensor qkv = c_attn->forward(scheduler, a_full);              // [M, 3 d/tp]
+  Tensor qkv;                                                   // [M, 3 d/tp]
+  if (fuse) {
+    saved_ln1_out = a;  // backward re-gathers it for the weight gradient
+    qkv = column_parallel_forward(scheduler, comm, c_attn->state(), a);
+  } else {
+    qkv = c_attn->forward(scheduler, all_gather_rows(scheduler, comm, a));
+  }
   Tensor qkv3 = Utils::view(scheduler, qkv, {batch, seq, 3 * d_local});
   Tensor ctx = compute::ScaledDotProductAttention::forward_packed(scheduler, attn_state, qkv3, local_heads);
   Tensor ctx2 = Utils::view(scheduler, ctx, {batch * seq, d_local});
-  Tensor y = c_proj->forward(scheduler, ctx2);                   // partial [M, d]
-  Tensor x1 = reduce_scatter_rows(scheduler, comm, y, &x_shard); // [M/tp, d] + residual
+  Tensor x1;                                                     // [M/tp, d] + residual
+  if (fuse) {
+    c_proj->state()->backward.input = ctx2;
+    c_proj->state()->forward.weight.impl()->autocast_enabled = true;
+    c_proj->state()->forward.weight.impl()->autocast_dtype = at::kBFloat16;
+    x1 = row_parallel_forward(scheduler, comm, c_proj->state()->forward.weight, ctx2, &x_shard, false);
+  } else {
+    x1 = reduce_scatter_rows(scheduler, comm, c_proj->forward(scheduler, ctx2), &x_shard);
+  }
   Tensor b = ln2->forward(scheduler, x1);
-  Tensor b_full = all_gather_rows(scheduler, comm, b);
-  Tensor pre = fc1->forward(scheduler, b_full);                  // [M, 4d/tp], carries GELU
-  Tensor z = fc2->forward(scheduler, pre);                       // partial [M, d]
-  return reduce_scatter_rows(scheduler, comm, z, &x1);
+  Tensor pre;                                                    // [M, 4d/tp], carries GELU
+  if (fuse) {
+    saved_ln2_out = b;
+    pre = column_parallel_forward(scheduler, comm, fc1->state(), b);
+  } else {
+    pre = fc1->forward(scheduler, all_gather_rows(scheduler, comm, b));
+  }
+  if (!fuse) return reduce_scatter_rows(scheduler, comm, fc2->forward(scheduler, pre), &x1);
+  // fused fc2: GELU(pre) is the companion emitted by the fc1 epilogue
+  Tensor act;
+  submit(scheduler, "cs::parallel::TPBlock::activation_view", Task::Impl::kMain, Task::Impl::kCompute, {act}, {pre},
+         [act, pre](const FnTask &) { act.impl()->tensor = pre.impl()->companion; });
+  auto fs = fc2->state();
+  fs->backward.input = pre;
+  fs->backward.activated = act;
+  fs->backward.input_count = 2;
+  fs->forward.weight.impl()->autocast_enabled = true;
+  fs->forward.weight.impl()->autocast_dtype = at::kBFloat16;
+  return row_parallel_forward(scheduler, comm, fs->forward.weight, act, &x1, false);
 }
 
 Tensor TPBlockImpl::backward(const Scheduler &scheduler, const ReadOnlyTensor &grad_shard, const models::GradientSync &sync) {
@@ -277,9 +453,15 @@ Tensor TPBlockImpl::backward(const Scheduler &scheduler, const ReadOnlyTensor &g
   Tensor dz = all_gather_rows(scheduler, comm, grad_shard);      // [M, d]
   Tensor d_pre = fc2->backward_input(scheduler, dz);
   fc2->backward_parameter(scheduler, dz);
-  Tensor d_b_full = fc1->backward_input(scheduler, d_pre);       // partial [M, d]
+  const bool fused_bwd = saved_ln2_out.defined();
+  Tensor d_b;                                                    // all-gather backward = reduce-scatter
+  if (fused_bwd) {
+    d_b = row_parallel_forward(scheduler, comm, fc1->state()->forward.weight, d_pre, nullptr, true);
+    fc1->state()->backward.input = all_gather_rows(scheduler, comm, saved_ln2_out);  // re-gather for the weight gradient
+  } else {
+    d_b = reduce_scatter_rows(scheduler, comm, fc1->backward_input(scheduler, d_pre));
+  }
   fc1->backward_parameter(scheduler, d_pre);
-  Tensor d_b = reduce_scatter_rows(scheduler, comm, d_b_full);   // all-gather backward
   Tensor d_x1 = ln2->backward(scheduler, d_b, grad_shard);       // + residual branch
   sync.push(scheduler, ln2->state()->forward.grad_weight);
   sync.push(scheduler, ln2->state()->forward.grad_bias);
@@ -290,9 +472,16 @@ Tensor TPBlockImpl::backward(const Scheduler &scheduler, const ReadOnlyTensor &g
   Tensor d_qkv = compute::ScaledDotProductAttention::backward_packed(scheduler, attn_state, d_ctx);
   const int64_t three_d_local = c_attn->state()->forward.weight.size(0);
   Tensor d_qkv2 = Utils::view(scheduler, d_qkv, {-1, three_d_local});
-  Tensor d_a_full = c_attn->backward_input(scheduler, d_qkv2);   // partial [M, d]
+  Tensor d_a;
+  if (fused_bwd) {
+    d_a = row_parallel_forward(scheduler, comm, c_attn->state()->forward.weight, d_qkv2, nullptr, true);
+    c_attn->state()->backward.input = all_gather_rows(scheduler, comm, saved_ln1_out);
+  } else {
+    d_a = reduce_scatter_rows(scheduler, comm, c_attn->backward_input(scheduler, d_qkv2));
+  }
   c_attn->backward_parameter(scheduler, d_qkv2);
-  Tensor d_a = reduce_scatter_rows(scheduler, comm, d_a_full);
+  saved_ln1_out = Tensor{};
+  saved_ln2_out = Tensor{};
   Tensor d_x = ln1->backward(scheduler, d_a, d_x1);
   sync.push(scheduler, ln1->state()->forward.grad_weight);
   sync.push(scheduler, ln1->state()->forward.grad_bias);

@@ -260,7 +260,12 @@ def full_grad_slice(name, g, rank, world, cfg):
     return g
 
 
-def case_tp_training(device, nvp2p):
+def case_tp_training_fused(device, nvp2p):
+    """Same check at a size where the fused all-gather+GEMM / GEMM+reduce-scatter kernels engage."""
+    case_tp_training(device, True, batch_per_rank=16, expect_fused=True)
+
+
+def case_tp_training(device, nvp2p, batch_per_rank=2, expect_fused=False):
     """Tensor-parallel GPT-2 (sequence-parallel activations) reproduces the single-device loss and gradients."""
     comm, rank, world, s = make_comm(device, nvp2p)
     amp = device == "cuda"
@@ -272,7 +277,7 @@ def case_tp_training(device, nvp2p):
     s.synchronize()
     shard_full_into_tp(full, tp, rank, world, cfg)
     g = torch.Generator().manual_seed(5)
-    ids = torch.randint(0, 128, (2 * world, 33), generator=g).to(device)
+    ids = torch.randint(0, 128, (batch_per_rank * world, 33), generator=g).to(device)
     x, y = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
     bucket = cs.AllReduceBucket(1 << 16, "sum")
     sync = cs.GradientSync(comm, bucket, True)
@@ -294,6 +299,10 @@ def case_tp_training(device, nvp2p):
     dist.all_gather(gathered, lt) if device == "cpu" else None
     if device == "cpu":
         assert abs(sum(gathered).item() / world - loss_full.raw().item()) < 1e-9
+    if expect_fused:
+        assert C.fused_tp_launches() >= 8 * 2, C.fused_tp_launches()  # 4 forward + 4 backward per block... at least
+        lf, ltp = loss_full.raw().item(), cs.to_torch(s, loss_tp).item()
+        assert abs(lf - ltp) < 0.2, (lf, ltp)
     gt, gf = tp.named_gradients(), full.named_gradients()
     tol = dict(atol=3e-2, rtol=5e-2) if amp else dict(atol=1e-9, rtol=1e-7)
     for k, gtp in gt.items():

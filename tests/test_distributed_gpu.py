@@ -26,6 +26,11 @@ def test_tensor_parallel_matches_single_device(backend):
 
 
 @needs2
+def test_tensor_parallel_fused_gemm_collectives():
+    run_case("tp_training_fused", device="cuda", extra=("nvp2p",), timeout=600)
+
+
+@needs2
 def test_zero_fused_step_matches_replicated_adamw():
     run_case("zero_training", device="cuda", extra=("nvp2p",), timeout=600)
 

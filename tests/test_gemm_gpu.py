@@ -108,3 +108,21 @@ def test_unsupported_shapes_are_declined():
     b = torch.randn(64, 60, device="cuda").to(BF)
     d = torch.empty(64, 64, device="cuda", dtype=BF)
     assert C.gemm_bf16(a, b, d, TN, STORE) == -1
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (4096, 768, 2304), (1000, 776, 264), (16384, 3072, 768), (100, 264, 136)])
+def test_tm_input_gradient_layout(M, N, K):
+    """A [M,K] row-major times B [K,N] row-major (the weight as stored): dX = dY * W."""
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda").to(BF)
+    b = torch.randn(K, N, device="cuda").mul_(0.1).to(BF)
+    d = torch.full((M, N), float("nan"), device="cuda", dtype=BF)
+    assert C.gemm_bf16(a, b, d, 2, STORE) == 0
+    ref = a.float() @ b.float()
+    assert rel(d, ref) < 4e-3
+    aux = torch.randn(M, N, device="cuda").to(BF)
+    assert C.gemm_bf16(a, b, d, 2, DGELU, aux=aux) == 0
+    x = aux.float().requires_grad_(True)
+    F.gelu(x).backward(torch.ones_like(x))
+    assert rel(d, ref * x.grad) < 5e-3
+    assert C.gemm_status()[0] == 0
