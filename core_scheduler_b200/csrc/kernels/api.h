@@ -47,10 +47,10 @@ int add_f32_residual_to_bf16(stream_t stream, const float *acc, const void *resi
 int cast_fp32_to_bf16(stream_t stream, const float *src, void *dst, int64_t n);
 int transpose_cast_to_bf16(stream_t stream, const void *src, int src_dtype, void *dst_t, int64_t rows, int64_t cols);
 
-// packed[b,t,i,h,:] = src_i[b,h,t,:] for i in {q,k,v}: three [B,H,T,D] bf16 tensors into one
-// [B,T,3,H,D] tensor in a single pass (D % 8 == 0).
-int pack_qkv_bhtd(stream_t stream, const void *q, const void *k, const void *v, void *packed, int64_t B, int64_t H, int64_t T,
-                  int64_t D);
+// Interleaves three bf16 tensors (q, k, v gradients) into one packed [B,T,3,H,D] tensor in a
+// single pass (D % 8 == 0). Sources are contiguous [B,H,T,D] (src_bthd = 0) or [B,T,H,D] (1).
+int pack_qkv(stream_t stream, const void *q, const void *k, const void *v, void *packed, int64_t B, int64_t H, int64_t T,
+             int64_t D, int src_bthd);
 
 // LayerNorm over the last dimension d (d % 8 == 0, d <= 8192). x,y bf16; gamma/beta fp32 or
 // bf16 (param_dtype as above); mean/rstd fp32 [rows].

@@ -346,7 +346,7 @@ int transpose_cast_to_bf16(stream_t stream, const void *src, int src_dtype, void
 namespace {
 __global__ void __launch_bounds__(256) pack_qkv_kernel(const Bf16x8 *__restrict__ q, const Bf16x8 *__restrict__ k,
                                                        const Bf16x8 *__restrict__ v, Bf16x8 *__restrict__ out, int64_t B,
-                                                       int64_t H, int64_t T, int d8) {
+                                                       int64_t H, int64_t T, int d8, int src_bthd) {
   // one thread per 16-byte piece of the output, output-major so that writes are fully coalesced
   const int64_t total = B * T * 3 * H * d8;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -361,19 +361,19 @@ __global__ void __launch_bounds__(256) pack_qkv_kernel(const Bf16x8 *__restrict_
     const int64_t t = r % T;
     const int64_t b = r / T;
     const Bf16x8 *src = which == 0 ? q : (which == 1 ? k : v);
-    out[i] = src[((b * H + h) * T + t) * d8 + c];
+    out[i] = src_bthd ? src[((b * T + t) * H + h) * d8 + c] : src[((b * H + h) * T + t) * d8 + c];
   }
 }
 }  // namespace
 
-int pack_qkv_bhtd(stream_t stream, const void *q, const void *k, const void *v, void *packed, int64_t B, int64_t H, int64_t T,
-                  int64_t D) {
+int pack_qkv(stream_t stream, const void *q, const void *k, const void *v, void *packed, int64_t B, int64_t H, int64_t T,
+             int64_t D, int src_bthd) {
   if (D % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
   const int64_t total = B * T * 3 * H * (D / 8);
   if (total == 0) return 0;
   pack_qkv_kernel<<<grid_for(total, 256, 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const Bf16x8 *>(q), static_cast<const Bf16x8 *>(k), static_cast<const Bf16x8 *>(v),
-      static_cast<Bf16x8 *>(packed), B, H, T, static_cast<int>(D / 8));
+      static_cast<Bf16x8 *>(packed), B, H, T, static_cast<int>(D / 8), src_bthd);
   return finish_launch();
 }
 

@@ -166,14 +166,16 @@ struct ErfParts {
 };
 __device__ __forceinline__ ErfParts erf_parts(float x) {
   const float z = fabsf(x) * 0.70710678118654752440f;
-  const float t = __frcp_rn(fmaf(0.3275911f, z, 1.0f));
+  float t;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.0f)));
   float poly = fmaf(1.061405429f, t, -1.453152027f);
   poly = fmaf(poly, t, 1.421413741f);
   poly = fmaf(poly, t, -0.284496736f);
   poly = fmaf(poly, t, 0.254829592f);
   poly *= t;
   ErfParts r;
-  r.e = __expf(-z * z);
+  // exp(-z^2) = 2^(-z^2 * log2 e)
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r.e) : "f"(z * z * -1.4426950408889634f));
   r.erf_abs = fmaf(-poly, r.e, 1.0f);
   return r;
 }
@@ -587,9 +589,28 @@ __device__ __forceinline__ void staging_release(const CUtensorMap *map, uint32_t
   }
 }
 
+// The 64 bytes of the auxiliary operand (residual / pre-activation) that belong to this thread's
+// row in one 32-column chunk. Loaded one chunk ahead of its use so that the global-memory
+// latency overlaps the TMEM read and the math of the previous chunk.
+struct AuxChunk {
+  uint4 v[4];
+};
+__device__ __forceinline__ AuxChunk load_aux_chunk(const KParams &p, long long row, bool row_ok, long long gcol) {
+  AuxChunk a;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) a.v[g] = make_uint4(0u, 0u, 0u, 0u);
+  if (row_ok && gcol < p.n) {
+    const uint4 *ap = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.aux) + row * p.ldd + gcol);
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      if (gcol + g * 8 + 8 <= p.n) a.v[g] = __ldg(ap + g);
+  }
+  return a;
+}
+
 __device__ __forceinline__ void epilogue_tile_tma(const KParams &p, const CUtensorMap *map_d, const CUtensorMap *map_d2, int m0,
                                                   int n0, int n_tile, uint32_t tmem_acc, int q, int half, int lane,
-                                                  EpilogueStaging &st, int store_row_base) {
+                                                  EpilogueStaging &st, int store_row_base, AuxChunk aux_next) {
   // store_row_base: first row of the destination tensor map inside the logical output (non-zero
   // when the rows are scattered to per-owner buffers)
   const int row0 = m0 + q * 32;
@@ -600,9 +621,12 @@ __device__ __forceinline__ void epilogue_tile_tma(const KParams &p, const CUtens
   const bool f32_out = p.epilogue == kEpiStoreF32 || p.epilogue == kEpiAccumF32;
   const bool reduce = f32_out && (p.atomic_out || p.epilogue == kEpiAccumF32);
   uint32_t box = 0, box2 = 0;
+  const bool uses_aux = p.epilogue == kEpiResidualBf16 || p.epilogue == kEpiDGelu;
 #pragma unroll 1
   for (int ch = 0; ch < 4; ++ch) {
     const int col0 = half * 128 + ch * 32;
+    const AuxChunk aux = aux_next;
+    if (uses_aux && ch < 3) aux_next = load_aux_chunk(p, row, row_ok, n0 + col0 + 32);
     uint32_t v[32];
     tcgen05_ld_32x32b_x32(tmem_acc + col0 + (static_cast<uint32_t>(q * 32) << 16), v);
     tcgen05_wait_ld();
@@ -635,12 +659,11 @@ __device__ __forceinline__ void epilogue_tile_tma(const KParams &p, const CUtens
         }
       }
     }
-    if ((p.epilogue == kEpiResidualBf16 || p.epilogue == kEpiDGelu) && row_ok && cols_in_range) {
-      const uint4 *ap = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.aux) + row * p.ldd + gcol);
+    if (uses_aux && row_ok && cols_in_range) {
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         if (gcol + g * 8 + 8 > p.n) break;
-        const uint4 a = *(ap + g);
+        const uint4 a = aux.v[g];
         const uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -669,11 +692,9 @@ __device__ __forceinline__ void epilogue_tile_tma(const KParams &p, const CUtens
     if (p.epilogue == kEpiGeluDual) {
 #pragma unroll
       for (int g = 0; g < 4; ++g)
-        st_shared_v4(staging_addr(box2, lane, sub * 4 + g),
-                     pack_bf16(gelu_f(bf16_round(f[g * 8 + 0])), gelu_f(bf16_round(f[g * 8 + 1]))),
-                     pack_bf16(gelu_f(bf16_round(f[g * 8 + 2])), gelu_f(bf16_round(f[g * 8 + 3]))),
-                     pack_bf16(gelu_f(bf16_round(f[g * 8 + 4])), gelu_f(bf16_round(f[g * 8 + 5]))),
-                     pack_bf16(gelu_f(bf16_round(f[g * 8 + 6])), gelu_f(bf16_round(f[g * 8 + 7]))));
+        st_shared_v4(staging_addr(box2, lane, sub * 4 + g), pack_bf16(gelu_f(f[g * 8 + 0]), gelu_f(f[g * 8 + 1])),
+                     pack_bf16(gelu_f(f[g * 8 + 2]), gelu_f(f[g * 8 + 3])), pack_bf16(gelu_f(f[g * 8 + 4]), gelu_f(f[g * 8 + 5])),
+                     pack_bf16(gelu_f(f[g * 8 + 6]), gelu_f(f[g * 8 + 7])));
     }
     if (p.epilogue == kEpiCrossEntropy && row_ok && cols_in_range) {
       float cmax = -INFINITY;
@@ -938,16 +959,22 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     st.next = 0;
     for (int tile = pair; tile < total_tiles; tile += num_pairs) {
       const TileCoord c = tile_coord2(p, tile);
+      const int m0_cta = c.m0 + static_cast<int>(cta) * 128;
+      // first chunk of the auxiliary operand is requested before waiting for the accumulator
+      AuxChunk aux0{};
+      if (p.epilogue == kEpiResidualBf16 || p.epilogue == kEpiDGelu) {
+        const long long r = m0_cta + q * 32 + lane;
+        aux0 = load_aux_chunk(p, r, r < p.m, c.n0 + half * 128);
+      }
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag)) break;
       tcgen05_fence_after();
-      const int m0_cta = c.m0 + static_cast<int>(cta) * 128;
       if (p.peer_mode == 2) {
         // reduce-scatter fused into the epilogue: add this tile into its owner's accumulator
         const int owner = m0_cta / p.rows_per_peer;
         epilogue_tile_tma(p, &peer_maps.m[owner], &map_d2, m0_cta, c.n0, c.n_tile, tmem_base + acc * BN, q, half, lane, st,
-                          owner * p.rows_per_peer);
+                          owner * p.rows_per_peer, aux0);
       } else {
-        epilogue_tile_tma(p, &map_d, &map_d2, m0_cta, c.n0, c.n_tile, tmem_base + acc * BN, q, half, lane, st, 0);
+        epilogue_tile_tma(p, &map_d, &map_d2, m0_cta, c.n0, c.n_tile, tmem_base + acc * BN, q, half, lane, st, 0, aux0);
       }
       tcgen05_fence_before();
       __syncwarp();

@@ -255,13 +255,15 @@ Tensor ScaledDotProductAttention::backward_packed(const Scheduler &scheduler, co
            const at::Tensor do4 = grad_out.impl()->tensor.reshape({B, T, H, D});
            auto r = attention_backward_body(do4, x5.select(2, 0), x5.select(2, 1), x5.select(2, 2), args, bw);
            at::Tensor packed = at::empty({B, T, 3, H, D}, x.options());
-           // r[i] are [B,T,H,D] views of [B,H,T,D] buffers; one kernel interleaves all three
+           // r[i] are [B,T,H,D] tensors, either contiguous or views of [B,H,T,D] buffers (depends on
+           // the library engine); one kernel interleaves all three
+           const bool bthd = r[0].is_contiguous() && r[1].is_contiguous() && r[2].is_contiguous();
            const at::Tensor dq = r[0].transpose(1, 2), dk = r[1].transpose(1, 2), dv = r[2].transpose(1, 2);
-           if (x.is_cuda() && x.scalar_type() == at::kBFloat16 && fused_enabled() && D % 8 == 0 && dq.is_contiguous() &&
-               dk.is_contiguous() && dv.is_contiguous()) {
-             check_kernel(kernels::pack_qkv_bhtd(current_stream(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                                 packed.data_ptr(), B, H, T, D),
-                          "pack_qkv_bhtd");
+           const bool bhtd = dq.is_contiguous() && dk.is_contiguous() && dv.is_contiguous();
+           if (x.is_cuda() && x.scalar_type() == at::kBFloat16 && fused_enabled() && D % 8 == 0 && (bthd || bhtd)) {
+             check_kernel(kernels::pack_qkv(current_stream(), r[0].data_ptr(), r[1].data_ptr(), r[2].data_ptr(),
+                                            packed.data_ptr(), B, H, T, D, bthd ? 1 : 0),
+                          "pack_qkv");
            } else {
              packed.select(2, 0).copy_(r[0]);
              packed.select(2, 1).copy_(r[1]);

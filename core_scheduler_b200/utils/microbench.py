@@ -129,15 +129,24 @@ def bench_elementwise():
 
 
 def gemm_one():
-    """One GPT-2 shape, a handful of launches: the workload for an ncu capture."""
+    """One GPT-2 shape (fc1), a handful of launches: the workload for an ncu capture.
+
+    Optional argument: epilogue id (0 store, 1 residual, 2 GELU dual, 3 dGELU)."""
+    epi = int(sys.argv[2]) if len(sys.argv) > 2 else 0
     M, N, K = 16384, 3072, 768
     a = torch.randn(M, K, device="cuda").to(BF)
     b = torch.randn(N, K, device="cuda").to(BF)
     d = torch.empty(M, N, device="cuda", dtype=BF)
-    for _ in range(5):
-        C.gemm_bf16(a, b, d, 0, 0)
+    aux = torch.randn(M, N, device="cuda").to(BF) if epi in (1, 3) else None
+    d2 = torch.empty_like(d) if epi == 2 else None
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(6):
+        if i == 3:
+            start.record()
+        C.gemm_bf16(a, b, d, 0, epi, aux=aux, d2=d2)
+    stop.record()
     torch.cuda.synchronize()
-    print("gemm_one done")
+    print(f"gemm_one epilogue={epi}: {start.elapsed_time(stop) / 3 * 1e3:.1f} us per launch")
 
 
 if __name__ == "__main__":
