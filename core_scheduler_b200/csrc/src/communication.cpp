@@ -4,6 +4,7 @@
 #include <torch/csrc/distributed/c10d/TCPStore.hpp>
 #include <torch/csrc/distributed/c10d/Types.hpp>
 
+#include <algorithm>
 #include <chrono>
 #include <cstdlib>
 #include <map>
@@ -87,46 +88,56 @@ void wait_work(const c10::intrusive_ptr<c10d::Work> &work) {
   if (work) work->wait();
 }
 
-// Groups tensors that sit back to back in one storage (views of a flat arena) into single
-// contiguous ranges so that a bucket needs one collective and no staging copies.
+// Groups tensors that live in one storage (views of a flat arena) into as few contiguous ranges
+// as possible so that a bucket needs one collective and no staging copies. The tensors are
+// sorted by address and their byte intervals are united (an interval that lies inside or
+// overlaps a previous one is absorbed, so nothing is ever reduced twice); intervals separated
+// by no more than the arena's alignment padding are joined, the padding being zeros on every
+// rank. Non-contiguous tensors are returned as they are.
 std::vector<at::Tensor> merge_adjacent(const std::vector<at::Tensor> &tensors) {
+  struct Piece {
+    const char *lo, *hi;
+  };
   std::vector<at::Tensor> out;
-  size_t i = 0;
-  while (i < tensors.size()) {
+  std::vector<bool> used(tensors.size(), false);
+  constexpr int64_t slack = 4096;  // arena alignment padding between slots
+  // Ranges are emitted in the order in which their arena first appears in the bucket and, inside
+  // an arena, by address: both are the same on every rank, so all ranks issue the same sequence
+  // of collectives (sorting unrelated allocations by address would not be).
+  for (size_t i = 0; i < tensors.size(); ++i) {
+    if (used[i]) continue;
     const at::Tensor &first = tensors[i];
-    if (!first.is_contiguous()) {
+    used[i] = true;
+    if (!first.is_contiguous() || first.numel() == 0) {
       out.push_back(first);
-      ++i;
       continue;
     }
-    const char *base = static_cast<const char *>(first.data_ptr());
-    const char *lo = base;
-    const char *hi = base + first.nbytes();
-    size_t j = i + 1;
-    // extend in either direction (backward visits parameters in reverse arena order)
-    while (j < tensors.size() && tensors[j].is_contiguous() && tensors[j].scalar_type() == first.scalar_type() &&
-           tensors[j].storage().is_alias_of(first.storage())) {
-      const char *p = static_cast<const char *>(tensors[j].data_ptr());
-      const char *q = p + tensors[j].nbytes();
-      const int64_t slack = 4096;  // arena alignment padding between slots
-      if (p >= hi && p - hi <= slack) {
-        hi = q;
-      } else if (q <= lo && lo - q <= slack) {
-        lo = p;
-      } else {
-        break;
+    std::vector<Piece> pieces;
+    const char *p0 = static_cast<const char *>(first.data_ptr());
+    pieces.push_back({p0, p0 + first.nbytes()});
+    for (size_t j = i + 1; j < tensors.size(); ++j) {
+      const at::Tensor &t = tensors[j];
+      if (used[j] || !t.is_contiguous() || t.numel() == 0 || t.scalar_type() != first.scalar_type() ||
+          !t.storage().is_alias_of(first.storage()))
+        continue;
+      used[j] = true;
+      const char *p = static_cast<const char *>(t.data_ptr());
+      pieces.push_back({p, p + t.nbytes()});
+    }
+    std::sort(pieces.begin(), pieces.end(), [](const Piece &a, const Piece &b) { return a.lo < b.lo; });
+    const int64_t elem = static_cast<int64_t>(first.element_size());
+    const char *storage_base = static_cast<const char *>(first.storage().data());
+    size_t k = 0;
+    while (k < pieces.size()) {
+      const char *lo = pieces[k].lo, *hi = pieces[k].hi;
+      size_t j = k + 1;
+      while (j < pieces.size() && pieces[j].lo <= hi + slack) {
+        if (pieces[j].hi > hi) hi = pieces[j].hi;
+        ++j;
       }
-      ++j;
+      out.push_back(at::as_strided(first, {(hi - lo) / elem}, {1}, (lo - storage_base) / elem));
+      k = j;
     }
-    if (j == i + 1) {
-      out.push_back(first.view({-1}));
-    } else {
-      const int64_t elems = (hi - lo) / static_cast<int64_t>(first.element_size());
-      const int64_t storage_offset =
-          (lo - static_cast<const char *>(first.storage().data())) / static_cast<int64_t>(first.element_size());
-      out.push_back(at::as_strided(first, {elems}, {1}, storage_offset));
-    }
-    i = j;
   }
   return out;
 }

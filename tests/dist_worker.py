@@ -73,6 +73,25 @@ def case_bucket(device, nvp2p):
         assert torch.allclose(cs.to_torch(s, x), torch.full((400,), float(total_rank + world * i), device=device)), (rank, i)
 
 
+def case_bucket_arena_order(device, nvp2p):
+    """Views of one arena queued in mixed address order are each reduced exactly once."""
+    comm, rank, world, s = make_comm(device, nvp2p)
+    arena = torch.zeros(4 * 128, device=device)
+    views = [arena[i * 128:i * 128 + 100] for i in range(4)]  # 28-element padding after each
+    for i, v in enumerate(views):
+        v.fill_(float(rank + 1 + i))
+    bucket = cs.AllReduceBucket(1 << 30, "sum")
+    # descending overall, with one ascending pair (like LayerNorm weight/bias pushed after a matrix)
+    for idx in (3, 1, 2, 0):
+        bucket.push_back(s, comm, T(views[idx]))
+    bucket.sync(s, comm)
+    s.synchronize()
+    base = sum(range(1, world + 1))
+    for i, v in enumerate(views):
+        assert torch.allclose(v, torch.full((100,), float(base + world * i), device=device)), (rank, i, v[:3])
+    assert bucket.launches() == 1
+
+
 def case_all_gather(device, nvp2p):
     comm, rank, world, s = make_comm(device, nvp2p)
     send = T(seeded(rank + 1, 128, device=device))
