@@ -1,6 +1,9 @@
 // Communicators and library-backed collectives. See cs/communication.h for the parity map.
 #include "cs/communication.h"
 
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAStream.h>
+#include <cuda_runtime.h>
 #include <torch/csrc/distributed/c10d/TCPStore.hpp>
 #include <torch/csrc/distributed/c10d/Types.hpp>
 
@@ -22,6 +25,21 @@ void Bucket::apply(const Scheduler &, const Comm &) const {
 
 // Defined in comm_nccl.cpp (compiled only when the NCCL process group headers are usable).
 c10::intrusive_ptr<c10d::Backend> create_nccl_backend(const c10::intrusive_ptr<c10d::Store> &store, int rank, int size);
+
+namespace {
+// The library may finish connecting its transports lazily inside the first collective; running
+// one tiny all-reduce followed by a device synchronisation here keeps that set-up out of the
+// first training step (where it was observed to let a consumer run ahead of the reduction).
+void warm_up(Comm::Impl &impl) {
+  if (impl.size <= 1 || !impl.backend || (impl.type != kNCCL && impl.type != kNVP2P)) return;
+  at::Tensor probe = at::ones({8}, at::TensorOptions().dtype(at::kFloat).device(at::kCUDA));
+  std::vector<at::Tensor> one{probe};
+  c10d::AllreduceOptions opts;
+  auto work = impl.backend->allreduce(one, opts);
+  if (work) work->wait();
+  cudaDeviceSynchronize();
+}
+}  // namespace
 
 namespace {
 int64_t env_int(const char *name, int64_t fallback) {
@@ -52,6 +70,7 @@ Comm create_from_env(BackendType type) {
   opts.waitWorkers = true;
   impl->store = c10::make_intrusive<c10d::TCPStore>(host, opts);
   impl->backend = create_nccl_backend(impl->store, static_cast<int>(impl->rank), static_cast<int>(impl->size));
+  warm_up(*impl);
   return Comm{impl};
 }
 
@@ -86,6 +105,8 @@ void wait_work(const c10::intrusive_ptr<c10d::Work> &work) {
   // NCCL: orders the current (comm) stream after the collective without blocking the host.
   // Gloo: blocks the host until the data arrived.
   if (work) work->wait();
+  static const bool host_sync = std::getenv("CS_COMM_HOST_SYNC") != nullptr;
+  if (host_sync && at::hasCUDA() && at::cuda::is_available()) cudaStreamSynchronize(c10::cuda::getCurrentCUDAStream().stream());
 }
 
 // Groups tensors that live in one storage (views of a flat arena) into as few contiguous ranges
@@ -157,6 +178,7 @@ Comm wrap_backend(c10::intrusive_ptr<c10d::Backend> backend, int64_t rank, int64
   impl->rank = rank;
   impl->size = size;
   impl->type = type;
+  warm_up(*impl);
   return Comm{impl};
 }
 
@@ -180,6 +202,7 @@ void AllReduce::run_inplace(const Scheduler &scheduler, const Comm &comm, const 
            const bool avg = backend_has_avg(impl);
            c10d::AllreduceOptions opts;
            opts.reduceOp = reduce_op(operation, avg);
+           opts.asyncOp = false;  // run on the current (comm) stream, not on a stream of the library
            for (auto &r : ranges) {
              at::Tensor buf = r.is_contiguous() ? r : r.contiguous();
              std::vector<at::Tensor> one{buf};
@@ -244,7 +267,9 @@ void AllGather::run(const Scheduler &scheduler, const Comm &comm, const std::vec
              return;
            }
            if (impl.type == kNVP2P && impl.symmetric && symmetric_all_gather(*impl.symmetric, r, s)) return;
-           wait_work(impl.backend->allgather(r, s));
+           c10d::AllgatherOptions ag_opts;
+           ag_opts.asyncOp = false;
+           wait_work(impl.backend->allgather(r, s, ag_opts));
          });
 }
 
@@ -288,6 +313,7 @@ void ReduceScatter::run(const Scheduler &scheduler, const Comm &comm, const std:
            }
            c10d::ReduceScatterOptions opts;
            opts.reduceOp = reduce_op(operation, true);
+           opts.asyncOp = false;
            wait_work(impl.backend->reduce_scatter(r, s, opts));
          });
 }
@@ -323,7 +349,9 @@ void AllToAll::run(const Scheduler &scheduler, const Comm &comm, const std::vect
              }
              return;
            }
-           wait_work(impl.backend->alltoall(r, s));
+           c10d::AllToAllOptions a2a_opts;
+           a2a_opts.asyncOp = false;
+           wait_work(impl.backend->alltoall(r, s, a2a_opts));
          });
 }
 

@@ -167,6 +167,8 @@ void Event::block() const {
 
 bool Event::query() const {
   if (!impl_->ev) return true;
+  static const bool always_pending = std::getenv("CS_EVENT_ALWAYS_BLOCK") != nullptr;
+  if (always_pending) return false;
   const cudaError_t code = cudaEventQuery(impl_->ev);
   if (code == cudaSuccess) return true;
   if (code == cudaErrorNotReady) {
