@@ -40,6 +40,7 @@ CUDA_SOURCES = [
     "kernels/elementwise.cu",
     "kernels/gemm_tcgen05.cu",
     "kernels/collectives.cu",
+    "kernels/attention_tcgen05.cu",
 ]
 BINDING_SOURCES = ["python/bindings.cpp"]
 
@@ -49,7 +50,7 @@ def _optional_sources():
     for name in ("src/parallel.cpp",):
         if (CSRC / name).exists():
             extra_cpp.append(name)
-    for name in ("kernels/attention_tcgen05.cu",):
+    for name in ():
         if (CSRC / name).exists():
             extra_cu.append(name)
     return extra_cpp, extra_cu

@@ -123,6 +123,14 @@ struct DeviceStatus;
 int gemm_status(DeviceStatus *out);
 int gemm_status_reset();
 
+// ---- tcgen05 causal attention (forward) -----------------------------------------------------------
+// qkv: packed bf16 [B, T, 3, H, D] (D == 64, T % 128 == 0); out: bf16 [B, T, H*D]; lse: fp32
+// [B, H, T] = log-sum-exp of the scaled scores. Returns -1 when the shape is not covered.
+int attention_forward_packed(stream_t stream, const void *qkv, void *out, float *lse, int64_t B, int64_t T, int64_t H, int64_t D,
+                             float scale);
+struct DeviceStatus;
+int attention_status(DeviceStatus *out);
+
 // ---- fused cross-entropy helpers -----------------------------------------------------------
 // Reduces the per-tile partials to lse[row], computes loss_row = lse - logit[target] and the
 // mean over non-ignored rows into loss[0] (fp32); count[0] receives the number of valid rows.

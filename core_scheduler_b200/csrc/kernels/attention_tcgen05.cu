@@ -1,0 +1,434 @@
+// Causal self-attention forward on tcgen05 tensor cores for head dimension 64, reading the packed
+// qkv tensor [B, T, 3, H, 64] (the c_attn output) directly and writing [B, T, H*64] plus the
+// per-row log-sum-exp.
+//
+// One CTA per (batch, head, 128-query block), 192 threads:
+//   warp 0     TMA producer: Q once, then K and V tiles (128 keys x 64) through 2-stage rings
+//   warp 1     MMA issuer: S = Q K^T (128x128x64, fp32 in TMEM, double-buffered) and
+//              O_j = P V (128x64x128; P from shared memory, V as an MN-major operand)
+//   warps 2-5  softmax: one thread per query row reads its S row from TMEM, keeps the running
+//              max / sum, writes P (bf16, 128-byte swizzled) to shared memory for the second MMA,
+//              then folds the partial O_j into fp32 registers with the usual rescaling
+// Scores never touch global memory. Every mbarrier wait is bounded (abort flag + status word).
+//
+// What it replaces in the reference project: at::_scaled_dot_product_flash_attention
+// (src/compute/sdpa_flash_attn.cpp:56-60) and the cuDNN-frontend SDPA graph
+// (src/compute/sdpa_cudnn.cpp:84-172) together with the split/view glue around them.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdlib>
+#include <mutex>
+#include <unordered_map>
+
+#include "api.h"
+
+namespace cs::kernels {
+namespace {
+constexpr int BQ = 128;      // queries per CTA
+constexpr int BKV = 128;     // keys per step
+constexpr int HD = 64;       // head dimension
+constexpr int TILE_BYTES = 128 * HD * 2;   // 16 KB: Q, K or V tile
+constexpr int P_BYTES = BQ * BKV * 2;      // 32 KB
+constexpr int KV_STAGES = 2;
+constexpr int THREADS = 192;
+constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + 2 * P_BYTES + 1024 + 256;
+constexpr int TMEM_COLS = 512;             // S: 2 x 128 columns, O_j: 2 x 64 columns
+constexpr long long kWaitBudgetCycles = 4000000000LL;
+
+__device__ DeviceStatus g_attn_status;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitBudgetCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((addr & 0x3FFFF) >> 4);
+  desc |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+  desc |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+  desc |= static_cast<uint64_t>(1) << 46;
+  desc |= static_cast<uint64_t>(2) << 61;  // 128-byte swizzle
+  return desc;
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&t);
+}
+
+struct AttnParams {
+  __nv_bfloat16 *out;   // [B, T, H*64]
+  float *lse;           // [B, H, T]
+  int B, T, H;
+  float scale_log2e;    // softmax scale * log2(e)
+  float scale;
+  DeviceStatus *status;
+};
+
+__global__ void __launch_bounds__(THREADS, 1) attention_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *aligned = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_smem = base;
+  const uint32_t k_smem = q_smem + TILE_BYTES;
+  const uint32_t v_smem = k_smem + KV_STAGES * TILE_BYTES;
+  const uint32_t p_smem = v_smem + KV_STAGES * TILE_BYTES;
+  const uint32_t bar_base = p_smem + 2 * P_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + (bar_base - base));
+  // barrier slots
+  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13, P_EMPTY = 15,
+         O_FULL = 17, O_EMPTY = 19, NUM_BARS = 21 };
+  auto bar = [&](int i) { return bar_base + 8u * i; };
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars + NUM_BARS);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + NUM_BARS + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = gridDim.x - 1 - blockIdx.x;  // longest rows first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qb * BQ;
+  const int num_kv = qb + 1;  // causal: key blocks 0..qb
+  const int row_base = b * p.T;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(Q_FULL), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(K_FULL + s), 1);
+      mbar_init(bar(K_EMPTY + s), 1);
+      mbar_init(bar(V_FULL + s), 1);
+      mbar_init(bar(V_EMPTY + s), 1);
+      mbar_init(bar(S_FULL + s), 1);
+      mbar_init(bar(S_EMPTY + s), 4);   // one arrival per softmax warp
+      mbar_init(bar(P_FULL + s), 4);
+      mbar_init(bar(P_EMPTY + s), 1);
+      mbar_init(bar(O_FULL + s), 1);
+      mbar_init(bar(O_EMPTY + s), 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_qkv)) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t *>(tmem_slot))),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t s_tmem = tmem_base;            // 2 x 128 columns
+  const uint32_t o_tmem = tmem_base + 2 * BKV;  // 2 x 64 columns
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const int q_col = h * HD, k_col = (p.H + h) * HD, v_col = (2 * p.H + h) * HD;
+      mbar_expect_tx(bar(Q_FULL), TILE_BYTES);
+      tma_load_2d(q_smem, &map_qkv, bar(Q_FULL), q_col, row_base + q0);
+      for (int j = 0; j < num_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(bar(K_EMPTY + s), ph ^ 1u, abort_flag)) break;
+        mbar_expect_tx(bar(K_FULL + s), TILE_BYTES);
+        tma_load_2d(k_smem + s * TILE_BYTES, &map_qkv, bar(K_FULL + s), k_col, row_base + j * BKV);
+        if (!mbar_wait(bar(V_EMPTY + s), ph ^ 1u, abort_flag)) break;
+        mbar_expect_tx(bar(V_FULL + s), TILE_BYTES);
+        tma_load_2d(v_smem + s * TILE_BYTES, &map_qkv, bar(V_FULL + s), v_col, row_base + j * BKV);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // S = Q K^T: M=128, N=128, both operands K-major. O_j = P V: M=128, N=64, B (= V) MN-major.
+      const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BKV >> 3) << 17) | (8u << 24);
+      const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (static_cast<uint32_t>(HD >> 3) << 17) | (8u << 24);
+      bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(bar(K_FULL + s), ph, abort_flag)) return false;
+        if (!mbar_wait(bar(S_EMPTY + s), ph ^ 1u, abort_flag)) return false;
+        fence_after();
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          umma(s_tmem + s * BKV, smem_desc(q_smem + k * 32, 16, 1024), smem_desc(k_smem + s * TILE_BYTES + k * 32, 16, 1024), idesc_s,
+               k > 0 ? 1u : 0u);
+        umma_commit(bar(K_EMPTY + s));
+        umma_commit(bar(S_FULL + s));
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; ok && j < num_kv; ++j) {
+        if (j + 1 < num_kv) ok = issue_s(j + 1);  // next scores while the softmax of block j runs
+        if (!ok) break;
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(bar(P_FULL + s), ph, abort_flag)) break;
+        if (!mbar_wait(bar(V_FULL + s), ph, abort_flag)) break;
+        if (!mbar_wait(bar(O_EMPTY + s), ph ^ 1u, abort_flag)) break;
+        fence_after();
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k) {
+          // P: two K-major 64-key halves of 16 KB; V: MN-major, 16 keys = 2 KB per step
+          const uint64_t da = smem_desc(p_smem + s * P_BYTES + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+          const uint64_t db = smem_desc(v_smem + s * TILE_BYTES + k * 2048, 8192, 1024);
+          umma(o_tmem + s * HD, da, db, idesc_o, k > 0 ? 1u : 0u);
+        }
+        umma_commit(bar(V_EMPTY + s));
+        umma_commit(bar(P_EMPTY + s));
+        umma_commit(bar(O_FULL + s));
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;          // query row inside the block
+    const int q_idx = q0 + r;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    float m_run = -INFINITY, l_run = 0.f;
+    float o[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    bool ok = true;
+    for (int j = 0; ok && j < num_kv; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(bar(S_FULL + s), ph, abort_flag)) break;
+      fence_after();
+      // pass 1: row maximum of the (masked) scores
+      const bool diagonal = j == qb;
+      float m_blk = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(s_tmem + s * BKV + c * 32 + lane_addr, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float x = __uint_as_float(v[i]);
+          if (!diagonal || (j * BKV + c * 32 + i) <= q_idx) m_blk = fmaxf(m_blk, x);
+        }
+      }
+      const float m_new = fmaxf(m_run, m_blk);
+      const float alpha = fast_exp2((m_run - m_new) * p.scale_log2e);  // first block: exp2(-inf) = 0
+      const float m_scaled = m_new * p.scale_log2e;
+      // pass 2: probabilities -> shared memory (bf16, swizzled) and their sum
+      if (!mbar_wait(bar(P_EMPTY + s), ph ^ 1u, abort_flag)) break;
+      float l_blk = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(s_tmem + s * BKV + c * 32 + lane_addr, v);
+        tmem_wait_ld();
+        float e[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float x = __uint_as_float(v[i]);
+          const bool keep = !diagonal || (j * BKV + c * 32 + i) <= q_idx;
+          e[i] = keep ? fast_exp2(fmaf(x, p.scale_log2e, -m_scaled)) : 0.f;
+          l_blk += e[i];
+        }
+        // 32 keys = 64 bytes = four 16-byte pieces of this row in half (c >> 1)
+        const uint32_t row_addr = p_smem + s * P_BYTES + (c >> 1) * 16384 + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int piece = (c & 1) * 4 + g;
+          const uint32_t addr = row_addr + ((piece ^ (r & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack2(e[g * 8 + 0], e[g * 8 + 1])),
+                       "r"(pack2(e[g * 8 + 2], e[g * 8 + 3])), "r"(pack2(e[g * 8 + 4], e[g * 8 + 5])),
+                       "r"(pack2(e[g * 8 + 6], e[g * 8 + 7]))
+                       : "memory");
+        }
+      }
+      fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar(S_EMPTY + s));
+        mbar_arrive(bar(P_FULL + s));
+      }
+      l_run = l_run * alpha + l_blk;
+      m_run = m_new;
+      // fold the partial output of this block into the running one
+      if (!mbar_wait(bar(O_FULL + s), ph, abort_flag)) break;
+      fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t v[32];
+        tmem_ld32(o_tmem + s * HD + c * 32 + lane_addr, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(v[i]));
+      }
+      fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(O_EMPTY + s));
+    }
+    if (!*abort_flag && q_idx < p.T) {
+      const float inv = 1.f / l_run;
+      __nv_bfloat16 *dst = p.out + (static_cast<long long>(row_base + q_idx) * p.H + h) * HD;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        uint4 w;
+        w.x = pack2(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv);
+        w.y = pack2(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv);
+        w.z = pack2(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv);
+        w.w = pack2(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv);
+        *reinterpret_cast<uint4 *>(dst + g * 8) = w;
+      }
+      p.lse[(static_cast<long long>(b) * p.H + h) * p.T + q_idx] = m_run * p.scale + __logf(l_run);
+    }
+  }
+
+  fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) {
+    p.status->code = 1;
+    p.status->kernel_id = 3;
+    p.status->block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    p.status->detail = 0;
+  }
+  if (warp == 1) {
+    fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn attn_encode_fn() {
+  static EncodeFn fn = [] {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      return static_cast<EncodeFn>(nullptr);
+    }
+    return reinterpret_cast<EncodeFn>(ptr);
+  }();
+  return fn;
+}
+}  // namespace
+
+int attention_status(DeviceStatus *out) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out, g_attn_status, sizeof(DeviceStatus)));
+}
+
+int attention_forward_packed(stream_t stream, const void *qkv, void *out, float *lse, int64_t B, int64_t T, int64_t H, int64_t D,
+                             float scale) {
+  if (D != HD || T % BQ != 0 || B <= 0 || H <= 0 || T <= 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(out)) & 15) return -1;
+  static const bool disabled = std::getenv("CS_DISABLE_TCGEN05_ATTENTION") != nullptr;
+  if (disabled) return -1;
+  EncodeFn fn = attn_encode_fn();
+  if (!fn) return -1;
+  static std::mutex mu;
+  static std::unordered_map<uint64_t, CUtensorMap> cache;
+  CUtensorMap map;
+  {
+    std::lock_guard<std::mutex> lock{mu};
+    const uint64_t key = reinterpret_cast<uint64_t>(qkv) ^ (static_cast<uint64_t>(B * T) << 40) ^ (static_cast<uint64_t>(H) << 32);
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+      const cuuint64_t dims[2] = {static_cast<cuuint64_t>(3 * H * D), static_cast<cuuint64_t>(B * T)};
+      const cuuint64_t strides[1] = {static_cast<cuuint64_t>(3 * H * D * 2)};
+      const cuuint32_t box[2] = {HD, 128};
+      const cuuint32_t elem[2] = {1, 1};
+      if (fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(qkv), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return -1;
+      if (cache.size() > 4096) cache.clear();
+      cache.emplace(key, map);
+    } else {
+      map = it->second;
+    }
+  }
+  static const bool attr_set =
+      cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) == cudaSuccess;
+  if (!attr_set) return -1;
+  static DeviceStatus *status_ptr = [] {
+    void *ptr = nullptr;
+    cudaGetSymbolAddress(&ptr, g_attn_status);
+    return static_cast<DeviceStatus *>(ptr);
+  }();
+  AttnParams p{};
+  p.out = static_cast<__nv_bfloat16 *>(out);
+  p.lse = lse;
+  p.B = static_cast<int>(B);
+  p.T = static_cast<int>(T);
+  p.H = static_cast<int>(H);
+  p.scale = scale;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.status = status_ptr;
+  dim3 grid(static_cast<unsigned>(T / BQ), static_cast<unsigned>(H), static_cast<unsigned>(B));
+  attention_fwd_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map, p);
+  return finish_launch(1);
+}
+}  // namespace cs::kernels

@@ -117,6 +117,20 @@ PYBIND11_MODULE(_C, m) {
         py::arg("a"), py::arg("b"), py::arg("d"), py::arg("layout") = 0, py::arg("epilogue") = 0, py::arg("aux") = py::none(),
         py::arg("bias") = py::none(), py::arg("d2") = py::none(), py::arg("stats") = py::none(), py::arg("n_valid") = -1);
   m.def("gemm_ce_stat_tiles", &cs::kernels::gemm_ce_stat_tiles);
+  // Raw access to the tcgen05 attention forward kernel (current torch stream).
+  m.def("attention_forward_tcgen05", [](const at::Tensor &qkv, int64_t heads, double scale) {
+    const int64_t B = qkv.size(0), T = qkv.size(1), D = qkv.size(2) / (3 * heads);
+    at::Tensor out = at::empty({B, T, heads * D}, qkv.options());
+    at::Tensor lse = at::empty({B, heads, T}, qkv.options().dtype(at::kFloat));
+    const int rc = cs::kernels::attention_forward_packed(c10::cuda::getCurrentCUDAStream().stream(), qkv.data_ptr(), out.data_ptr(),
+                                                        lse.data_ptr<float>(), B, T, heads, D, static_cast<float>(scale));
+    return py::make_tuple(rc, out, lse);
+  });
+  m.def("attention_status", [] {
+    cs::kernels::DeviceStatus st{};
+    cs::kernels::attention_status(&st);
+    return std::vector<int>{st.code, st.kernel_id, st.block, st.detail};
+  });
 
   py::class_<TaskTiming>(m, "TaskTiming")
       .def_readonly("name", &TaskTiming::name)

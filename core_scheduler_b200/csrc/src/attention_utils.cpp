@@ -79,6 +79,16 @@ bool use_cudnn_engine() {
   return cudnn;
 }
 
+// "tcgen05": this library's forward kernel on the packed qkv tensor (backward then uses the
+// flash-attention library kernels, which accept its output and log-sum-exp).
+bool use_own_forward() {
+  static const bool own = [] {
+    const char *e = std::getenv("CS_ATTENTION_ENGINE");
+    return e != nullptr && std::string(e) == "tcgen05";
+  }();
+  return own;
+}
+
 double resolve_scale(const optional<double> &scale, int64_t head_dim) {
   return scale.has_value() ? *scale : 1.0 / std::sqrt(static_cast<double>(head_dim));
 }
@@ -135,7 +145,8 @@ std::array<at::Tensor, 3> attention_backward_body(const at::Tensor &dout4, const
   const double scale = resolve_scale(args.scale, q.size(-1));
   const at::Tensor &out = bw.out.impl()->tensor;
   const at::Tensor &lse = bw.logsumexp.impl()->tensor;
-  if (library_flash_ok(q) && use_cudnn_engine() && q.size(-1) <= 128) {
+  const bool own_forward = bw.out.impl()->companion.defined();
+  if (library_flash_ok(q) && use_cudnn_engine() && q.size(-1) <= 128 && !own_forward) {
     auto r = at::_scaled_dot_product_cudnn_attention_backward(
         dout.to(q.scalar_type()), q, k, v, out, lse, bw.philox_seed.impl()->tensor, bw.philox_offset.impl()->tensor,
         at::Tensor{}, bw.cum_seq_q.impl()->tensor, bw.cum_seq_k.impl()->tensor, bw.max_q, bw.max_k, args.dropout_p,
@@ -232,6 +243,28 @@ Tensor ScaledDotProductAttention::forward_packed(const Scheduler &scheduler, con
            const at::Tensor &x = qkv.impl()->tensor;  // [B,T,3*H*D]
            CS_ASSERT_TRUE(x.dim() == 3 && x.size(2) % (3 * num_heads) == 0, "packed qkv must be [B,T,3*H*D]");
            const int64_t B = x.size(0), T = x.size(1), D = x.size(2) / (3 * num_heads);
+           if (use_own_forward() && x.is_cuda() && x.scalar_type() == at::kBFloat16 && fused_enabled() && x.is_contiguous() &&
+               state->args.is_causal && state->args.dropout_p == 0.0) {
+             at::Tensor o = at::empty({B, T, num_heads * D}, x.options());
+             at::Tensor lse = at::empty({B, num_heads, T}, x.options().dtype(at::kFloat));
+             const int code = kernels::attention_forward_packed(current_stream(), x.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), B,
+                                                                T, num_heads, D,
+                                                                static_cast<float>(resolve_scale(state->args.scale, D)));
+             if (code == 0) {
+               saved.out.impl()->tensor = o.view({B, T, num_heads, D}).transpose(1, 2);  // [B,H,T,D] view
+               saved.lse.impl()->tensor = lse;
+               saved.cum_q.impl()->tensor = at::Tensor{};
+               saved.cum_k.impl()->tensor = at::Tensor{};
+               state->backward.max_q = T;
+               state->backward.max_k = T;
+               saved.seed.impl()->tensor = at::zeros({}, x.options().dtype(at::kLong));
+               saved.offset.impl()->tensor = at::zeros({}, x.options().dtype(at::kLong));
+               saved.out.impl()->companion = at::empty({0}, x.options());  // marks "own forward"
+               output.impl()->tensor = o;
+               return;
+             }
+             CS_ASSERT_TRUE(code == -1, "attention_forward_packed failed: ", cuda_error_string(code));
+           }
            const at::Tensor x5 = x.view({B, T, 3, num_heads, D});
            at::Tensor o = attention_forward_body(x5.select(2, 0), x5.select(2, 1), x5.select(2, 2), state->args,
                                                  &state->backward, saved);
