@@ -3,13 +3,14 @@
 // per-row log-sum-exp.
 //
 // One CTA per (batch, head, 128-query block), 192 threads:
-//   warp 0     TMA producer: Q once, then K and V tiles (128 keys x 64) through 2-stage rings
-//   warp 1     MMA issuer: S = Q K^T (128x128x64, fp32 in TMEM, double-buffered) and
+//   warp 0     TMA producer: Q once, then K tiles (128 keys x 64, 2 stages) and V tiles (1 stage)
+//   warp 1     MMA issuer: S = Q K^T (128x128x64, fp32 in TMEM) and
 //              O_j = P V (128x64x128; P from shared memory, V as an MN-major operand)
 //   warps 2-5  softmax: one thread per query row reads its S row from TMEM, keeps the running
 //              max / sum, writes P (bf16, 128-byte swizzled) to shared memory for the second MMA,
 //              then folds the partial O_j into fp32 registers with the usual rescaling
-// Scores never touch global memory. Every mbarrier wait is bounded (abort flag + status word).
+// Two CTAs share an SM (97 KB of shared memory and 256 TMEM columns each), so one CTA's softmax
+// overlaps the other's tensor-core work. Scores never touch global memory. Every mbarrier wait is bounded (abort flag + status word).
 //
 // What it replaces in the reference project: at::_scaled_dot_product_flash_attention
 // (src/compute/sdpa_flash_attn.cpp:56-60) and the cuDNN-frontend SDPA graph
@@ -33,8 +34,8 @@ constexpr int TILE_BYTES = 128 * HD * 2;   // 16 KB: Q, K or V tile
 constexpr int P_BYTES = BQ * BKV * 2;      // 32 KB
 constexpr int KV_STAGES = 2;
 constexpr int THREADS = 192;
-constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + 2 * P_BYTES + 1024 + 256;
-constexpr int TMEM_COLS = 512;             // S: 2 x 128 columns, O_j: 2 x 64 columns
+constexpr int SMEM_BYTES = TILE_BYTES * (1 + KV_STAGES + 1) + P_BYTES + 1024 + 256;  // ~97 KB: two CTAs per SM
+constexpr int TMEM_COLS = 256;             // S: 128 columns, O_j: 64 columns; two CTAs share the SM's 512
 constexpr long long kWaitBudgetCycles = 4000000000LL;
 
 __device__ DeviceStatus g_attn_status;
@@ -132,15 +133,15 @@ struct AttnParams {
   DeviceStatus *status;
 };
 
-__global__ void __launch_bounds__(THREADS, 1) attention_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const AttnParams p) {
+__global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *aligned = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t q_smem = base;
   const uint32_t k_smem = q_smem + TILE_BYTES;
   const uint32_t v_smem = k_smem + KV_STAGES * TILE_BYTES;
-  const uint32_t p_smem = v_smem + KV_STAGES * TILE_BYTES;
-  const uint32_t bar_base = p_smem + 2 * P_BYTES;
+  const uint32_t p_smem = v_smem + TILE_BYTES;  // V is single-buffered: it is only needed once P exists
+  const uint32_t bar_base = p_smem + P_BYTES;
   uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + (bar_base - base));
   // barrier slots
   enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13, P_EMPTY = 15,
@@ -184,8 +185,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_fwd_kernel(const __grid_
   __syncthreads();
   fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t s_tmem = tmem_base;            // 2 x 128 columns
-  const uint32_t o_tmem = tmem_base + 2 * BKV;  // 2 x 64 columns
+  const uint32_t s_tmem = tmem_base;        // 128 columns
+  const uint32_t o_tmem = tmem_base + BKV;  // 64 columns
 
   if (warp == 0) {
     if (lane == 0) {
@@ -198,9 +199,9 @@ __global__ void __launch_bounds__(THREADS, 1) attention_fwd_kernel(const __grid_
         if (!mbar_wait(bar(K_EMPTY + s), ph ^ 1u, abort_flag)) break;
         mbar_expect_tx(bar(K_FULL + s), TILE_BYTES);
         tma_load_2d(k_smem + s * TILE_BYTES, &map_qkv, bar(K_FULL + s), k_col, row_base + j * BKV);
-        if (!mbar_wait(bar(V_EMPTY + s), ph ^ 1u, abort_flag)) break;
-        mbar_expect_tx(bar(V_FULL + s), TILE_BYTES);
-        tma_load_2d(v_smem + s * TILE_BYTES, &map_qkv, bar(V_FULL + s), v_col, row_base + j * BKV);
+        if (!mbar_wait(bar(V_EMPTY), (j & 1) ^ 1u, abort_flag)) break;
+        mbar_expect_tx(bar(V_FULL), TILE_BYTES);
+        tma_load_2d(v_smem, &map_qkv, bar(V_FULL), v_col, row_base + j * BKV);
       }
     }
   } else if (warp == 1) {
@@ -210,39 +211,40 @@ __global__ void __launch_bounds__(THREADS, 1) attention_fwd_kernel(const __grid_
       const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (static_cast<uint32_t>(HD >> 3) << 17) | (8u << 24);
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag);
       auto issue_s = [&](int j) -> bool {
-        const int s = j & 1;
+        const int s = j & 1;                    // K/V stage
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(bar(K_FULL + s), ph, abort_flag)) return false;
-        if (!mbar_wait(bar(S_EMPTY + s), ph ^ 1u, abort_flag)) return false;
+        if (!mbar_wait(bar(S_EMPTY), (j & 1) ^ 1u, abort_flag)) return false;  // softmax of block j-1 has read S
         fence_after();
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          umma(s_tmem + s * BKV, smem_desc(q_smem + k * 32, 16, 1024), smem_desc(k_smem + s * TILE_BYTES + k * 32, 16, 1024), idesc_s,
+          umma(s_tmem, smem_desc(q_smem + k * 32, 16, 1024), smem_desc(k_smem + s * TILE_BYTES + k * 32, 16, 1024), idesc_s,
                k > 0 ? 1u : 0u);
         umma_commit(bar(K_EMPTY + s));
-        umma_commit(bar(S_FULL + s));
+        umma_commit(bar(S_FULL));
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int j = 0; ok && j < num_kv; ++j) {
-        if (j + 1 < num_kv) ok = issue_s(j + 1);  // next scores while the softmax of block j runs
-        if (!ok) break;
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(bar(P_FULL + s), ph, abort_flag)) break;
-        if (!mbar_wait(bar(V_FULL + s), ph, abort_flag)) break;
-        if (!mbar_wait(bar(O_EMPTY + s), ph ^ 1u, abort_flag)) break;
+        const uint32_t bph = j & 1;             // phase of the single-buffered S / P / O barriers
+        if (!mbar_wait(bar(P_FULL), bph, abort_flag)) break;
+        if (j + 1 < num_kv) ok = issue_s(j + 1);  // S is free again once P of block j exists
+        if (!ok) break;
+        if (!mbar_wait(bar(V_FULL), bph, abort_flag)) break;
+        if (!mbar_wait(bar(O_EMPTY), bph ^ 1u, abort_flag)) break;
         fence_after();
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
           // P: two K-major 64-key halves of 16 KB; V: MN-major, 16 keys = 2 KB per step
-          const uint64_t da = smem_desc(p_smem + s * P_BYTES + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
-          const uint64_t db = smem_desc(v_smem + s * TILE_BYTES + k * 2048, 8192, 1024);
-          umma(o_tmem + s * HD, da, db, idesc_o, k > 0 ? 1u : 0u);
+          const uint64_t da = smem_desc(p_smem + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+          const uint64_t db = smem_desc(v_smem + k * 2048, 8192, 1024);
+          umma(o_tmem, da, db, idesc_o, k > 0 ? 1u : 0u);
         }
-        umma_commit(bar(V_EMPTY + s));
-        umma_commit(bar(P_EMPTY + s));
-        umma_commit(bar(O_FULL + s));
+        umma_commit(bar(V_EMPTY));
+        umma_commit(bar(P_EMPTY));
+        umma_commit(bar(O_FULL));
       }
     }
   } else {
@@ -256,9 +258,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_fwd_kernel(const __grid_
     for (int i = 0; i < HD; ++i) o[i] = 0.f;
     bool ok = true;
     for (int j = 0; ok && j < num_kv; ++j) {
-      const int s = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      if (!mbar_wait(bar(S_FULL + s), ph, abort_flag)) break;
+      const uint32_t bph = j & 1;
+      if (!mbar_wait(bar(S_FULL), bph, abort_flag)) break;
       fence_after();
       // pass 1: row maximum of the (masked) scores
       const bool diagonal = j == qb;
@@ -266,7 +267,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_fwd_kernel(const __grid_
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
-        tmem_ld32(s_tmem + s * BKV + c * 32 + lane_addr, v);
+        tmem_ld32(s_tmem + c * 32 + lane_addr, v);
         tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -278,12 +279,12 @@ __global__ void __launch_bounds__(THREADS, 1) attention_fwd_kernel(const __grid_
       const float alpha = fast_exp2((m_run - m_new) * p.scale_log2e);  // first block: exp2(-inf) = 0
       const float m_scaled = m_new * p.scale_log2e;
       // pass 2: probabilities -> shared memory (bf16, swizzled) and their sum
-      if (!mbar_wait(bar(P_EMPTY + s), ph ^ 1u, abort_flag)) break;
+      if (!mbar_wait(bar(P_EMPTY), bph ^ 1u, abort_flag)) break;
       float l_blk = 0.f;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
-        tmem_ld32(s_tmem + s * BKV + c * 32 + lane_addr, v);
+        tmem_ld32(s_tmem + c * 32 + lane_addr, v);
         tmem_wait_ld();
         float e[32];
 #pragma unroll
@@ -294,7 +295,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_fwd_kernel(const __grid_
           l_blk += e[i];
         }
         // 32 keys = 64 bytes = four 16-byte pieces of this row in half (c >> 1)
-        const uint32_t row_addr = p_smem + s * P_BYTES + (c >> 1) * 16384 + r * 128;
+        const uint32_t row_addr = p_smem + (c >> 1) * 16384 + r * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           const int piece = (c & 1) * 4 + g;
@@ -309,25 +310,25 @@ __global__ void __launch_bounds__(THREADS, 1) attention_fwd_kernel(const __grid_
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(bar(S_EMPTY + s));
-        mbar_arrive(bar(P_FULL + s));
+        mbar_arrive(bar(S_EMPTY));
+        mbar_arrive(bar(P_FULL));
       }
       l_run = l_run * alpha + l_blk;
       m_run = m_new;
       // fold the partial output of this block into the running one
-      if (!mbar_wait(bar(O_FULL + s), ph, abort_flag)) break;
+      if (!mbar_wait(bar(O_FULL), bph, abort_flag)) break;
       fence_after();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
-        tmem_ld32(o_tmem + s * HD + c * 32 + lane_addr, v);
+        tmem_ld32(o_tmem + c * 32 + lane_addr, v);
         tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(v[i]));
       }
       fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(O_EMPTY + s));
+      if (lane == 0) mbar_arrive(bar(O_EMPTY));
     }
     if (!*abort_flag && q_idx < p.T) {
       const float inv = 1.f / l_run;

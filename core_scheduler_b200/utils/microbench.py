@@ -128,6 +128,22 @@ def bench_elementwise():
     print(f"adamw fp32 master + bf16 copy n={n} {t:.4f} ms {bytes_moved / t / 1e6:.0f} GB/s ({bytes_moved / t / 1e6 / gbs_peak:.2f} of {tag})")
 
 
+def bench_attention():
+    """tcgen05 causal attention forward vs the cuDNN engine, GPT-2 124M shape (B16 H12 T1024 D64)."""
+    tflops_peak, _, tag = peaks()
+    B, T, H, D = 16, 1024, 12, 64
+    qkv = torch.randn(B, T, 3 * H * D, device="cuda").to(BF)
+    scale = D ** -0.5
+    ours = lambda: C.attention_forward_tcgen05(qkv, H, scale)
+    q, k, v = (x.transpose(1, 2) for x in qkv.view(B, T, 3, H, D).unbind(2))
+    lib = lambda: torch.ops.aten._scaled_dot_product_cudnn_attention(q, k, v, None, True, 0.0, True, False, scale=scale)
+    flops = 4.0 * B * H * T * T * D / 2  # causal
+    t_ours, t_lib = time_ms(ours), time_ms(lib)
+    print(f"attention fwd causal B={B} H={H} T={T} D={D}: ours {t_ours * 1e3:.1f} us {flops / t_ours / 1e9:.0f} TFLOP/s "
+          f"({flops / t_ours / 1e9 / tflops_peak:.2f} of {tag})   cuDNN {t_lib * 1e3:.1f} us {flops / t_lib / 1e9:.0f} TFLOP/s   "
+          f"status {C.attention_status()}")
+
+
 def gemm_one():
     """One GPT-2 shape (fc1), a handful of launches: the workload for an ncu capture.
 
@@ -151,4 +167,4 @@ def gemm_one():
 
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    {"gemm": bench_gemm, "elementwise": bench_elementwise, "gemm_one": gemm_one}[what]()
+    {"gemm": bench_gemm, "elementwise": bench_elementwise, "gemm_one": gemm_one, "attention": bench_attention}[what]()
