@@ -64,10 +64,28 @@ class Trainer:
         self.C.set_backend(args.backend)
         cs.manual_seed(1234)  # same weights on every rank
         self.cfg = gpt2_config(args.model, dtype=torch.float32)
-        self.model = cs.GPT2(self.s, self.cfg)
+        self.tp = args.mode == "tp" and world > 1
         self.bucket = None
         self.sync = None
         self.zero = args.mode == "zero" and world > 1
+        if self.tp:
+            # tensor parallel: every rank sees the whole (global) batch; sharded Linears, sequence-parallel
+            # activations; only the replicated parameters' gradients go through the all-reduce bucket
+            import torch.distributed as dist
+
+            pg = dist.distributed_c10d._get_default_group()
+            self.comm = comm = self.C.comm_from_process_group(pg.group_name, "cuda", args.comm == "nvp2p")
+            if args.comm == "nvp2p":
+                self.symm = self.C.create_symmetric_context(comm, 2 << 30)
+            self.model = self.C.TPGPT2(self.s, self.cfg, comm)
+            self.flat = self.C.flatten_parameters(self.s, self.model, lp_dtype=torch.bfloat16)
+            self.opt = cs.AdamW(self.s, self.model, lr=3e-4, beta1=0.9, beta2=0.95, weight_decay=0.1, flat=self.flat)
+            self.opt.set_grad_scale(1.0 / world)
+            self.bucket = cs.AllReduceBucket(int(args.bucket_mb * (1 << 20)), "sum")
+            self.sync = cs.GradientSync(comm, self.bucket, True)
+            self.s.synchronize()
+            return
+        self.model = cs.GPT2(self.s, self.cfg)
         if world > 1 and (args.comm == "nvp2p" or self.zero):
             import torch.distributed as dist
 
@@ -138,7 +156,7 @@ def main():
     vocab = trainer.cfg.vocab_size
 
     # ---- device-resident inputs for the kernel-level number (a few distinct batches) -------------
-    gen = torch.Generator(device="cuda").manual_seed(1000 + rank)
+    gen = torch.Generator(device="cuda").manual_seed(1000 + (0 if trainer.tp else rank))
     batches = []
     for _ in range(4):
         ids = torch.randint(0, vocab, (B, T + 1), generator=gen, device="cuda")
@@ -181,14 +199,14 @@ def main():
     device_ms = max_over_ranks(device_ms, world)
     final_loss = float(cs.to_torch(trainer.s, loss).item())
 
-    tokens_per_step = B * T * world
+    tokens_per_step = B * T * (1 if trainer.tp else world)  # tensor parallel ranks share one global batch
     ms_per_step = device_ms / args.steps
     value = tokens_per_step / (ms_per_step / 1e3)
 
     # ---- end to end: pinned host staging + H2D every step, loss read back every step ----------------
     e2e = None
     if not args.no_e2e:
-        loader = C.SyntheticDataLoader(B, T, vocab, seed=77 + rank)
+        loader = C.SyntheticDataLoader(B, T, vocab, seed=77 + (0 if trainer.tp else rank))
         for _ in range(2):
             d = loader.load(trainer.s)
             float(cs.to_torch(trainer.s, trainer.step(d["input_ids"], d["labels"])).item())
@@ -222,14 +240,14 @@ def main():
             "warmup": args.warmup,
             "ms_per_step": ms_per_step,
             "higher_is_better": True,
-            "scaling": "weak",
+            "scaling": "strong" if trainer.tp else "weak",
             "vs_baseline": None,
             "dtype": "bf16",
             "data": "synthetic uniform token ids, random-init weights N(0,0.02)",
             "impl": "ours",
             "config": {
                 "model": f"GPT-2 {args.model} ({trainer.cfg.parameter_count() / 1e6:.1f}M params, untied lm_head)",
-                "global_batch": B * world,
+                "global_batch": B * (1 if trainer.tp else world),
                 "micro_batch_per_gpu": B,
                 "seq_len": T,
                 "parallelism": f"{args.mode}{world}",

@@ -105,8 +105,7 @@ void wait_work(const c10::intrusive_ptr<c10d::Work> &work) {
   // NCCL: orders the current (comm) stream after the collective without blocking the host.
   // Gloo: blocks the host until the data arrived.
   if (work) work->wait();
-  static const bool host_sync = std::getenv("CS_COMM_HOST_SYNC") != nullptr;
-  if (host_sync && at::hasCUDA() && at::cuda::is_available()) cudaStreamSynchronize(c10::cuda::getCurrentCUDAStream().stream());
+
 }
 
 // Groups tensors that live in one storage (views of a flat arena) into as few contiguous ranges

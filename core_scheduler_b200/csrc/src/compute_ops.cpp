@@ -75,6 +75,17 @@ using namespace detail;
 
 void bump_version(const Tensor &parameter) { ++parameter.impl()->version; }
 
+namespace {
+// The tensor a bf16 kernel should read for a parameter: its bf16 working copy when one exists
+// and is current (it is the only complete copy under a sharded optimizer, where the fp32 master
+// is authoritative only inside the owner's shard), else the parameter itself.
+const at::Tensor &kernel_view(const ReadOnlyTensor &parameter) {
+  const auto &impl = *parameter.impl();
+  if (impl.lp.defined() && impl.lp_version == impl.version && impl.lp.scalar_type() == at::kBFloat16) return impl.lp;
+  return impl.tensor;
+}
+}  // namespace
+
 at::Tensor working_copy(const ReadOnlyTensor &parameter, at::ScalarType dtype) {
   auto &impl = *parameter.impl();
   if (impl.tensor.scalar_type() == dtype) return impl.tensor;
@@ -567,21 +578,25 @@ Tensor LayerNorm::forward(const Scheduler &scheduler, const std::shared_ptr<Stat
            const at::Tensor &wt = w.impl()->tensor;
            if (ln_fused_ok(x, wt, args.normalized_shape.size()) &&
                (!args.bias || b.impl()->tensor.scalar_type() == wt.scalar_type())) {
+             const at::Tensor &wk = kernel_view(w);
+             const at::Tensor &bk = args.bias ? kernel_view(b) : wk;
+             if (wk.scalar_type() == bk.scalar_type()) {
              const int64_t d = x.size(-1), rows = x.numel() / d;
              at::Tensor y = at::empty_like(x);
              auto stat_sizes = x.sizes().vec();
              stat_sizes.back() = 1;
              at::Tensor m = at::empty(stat_sizes, x.options().dtype(at::kFloat));
              at::Tensor r = at::empty(stat_sizes, x.options().dtype(at::kFloat));
-             check_kernel(kernels::layernorm_forward(current_stream(), x.data_ptr(), wt.data_ptr(),
-                                                     args.bias ? b.impl()->tensor.data_ptr() : nullptr,
-                                                     dtype_code(wt.scalar_type()), y.data_ptr(), m.data_ptr<float>(),
-                                                     r.data_ptr<float>(), rows, d, static_cast<float>(args.eps)),
+             check_kernel(kernels::layernorm_forward(current_stream(), x.data_ptr(), wk.data_ptr(),
+                                                     args.bias ? bk.data_ptr() : nullptr, dtype_code(wk.scalar_type()),
+                                                     y.data_ptr(), m.data_ptr<float>(), r.data_ptr<float>(), rows, d,
+                                                     static_cast<float>(args.eps)),
                           "layernorm_forward");
              output.impl()->tensor = y;
              mean.impl()->tensor = m;
              rstd.impl()->tensor = r;
              return;
+             }
            }
            // Library path. Low-precision inputs are normalised in fp32 and cast back.
            const bool upcast = x.scalar_type() != wt.scalar_type() || (amp && x.scalar_type() != at::kDouble &&
@@ -646,8 +661,9 @@ Tensor layer_norm_backward_task(const Scheduler &scheduler, const std::shared_pt
              task.intermediate().push_back(scratch);
              at::Tensor r2;
              if (res) r2 = cast_if(res->impl()->tensor, at::kBFloat16).contiguous();
+             const at::Tensor &wk = kernel_view(w);
              check_kernel(kernels::layernorm_backward(
-                              current_stream(), dy.data_ptr(), x.data_ptr(), wt.data_ptr(), 0,
+                              current_stream(), dy.data_ptr(), x.data_ptr(), wk.data_ptr(), dtype_code(wk.scalar_type()),
                               mean.impl()->tensor.data_ptr<float>(), rstd.impl()->tensor.data_ptr<float>(),
                               res ? r2.data_ptr() : nullptr, dx.data_ptr(), sw.tensor.data_ptr<float>(),
                               sb.tensor.data_ptr<float>(), accumulate ? 1 : 0, scratch.data_ptr<float>(), rows, d),
@@ -827,7 +843,7 @@ Tensor Embedding::forward(const Scheduler &scheduler, const std::shared_ptr<Stat
   submit(scheduler, "cs::compute::Embedding::forward", Task::Impl::kMain, Task::Impl::kCompute, {output},
          {indices, state->forward.weight}, [indices, w = state->forward.weight, output, amp, amp_dt](const FnTask &) {
            const at::Tensor idx = indices.impl()->tensor;
-           const at::Tensor &wt = w.impl()->tensor;
+           const at::Tensor &wt = (amp && amp_dt == at::kBFloat16) ? kernel_view(w) : w.impl()->tensor;
            if (amp && amp_dt == at::kBFloat16 && wt.is_cuda() && fused_enabled() && idx.scalar_type() == at::kLong &&
                wt.size(1) % 8 == 0 && dtype_code(wt.scalar_type()) >= 0 && dtype_code(wt.scalar_type()) <= 1) {
              const at::Tensor ic = idx.contiguous();
@@ -896,8 +912,9 @@ Tensor Embedding::forward_token_position(const Scheduler &scheduler, const std::
          {indices, token->forward.weight, position->forward.weight},
          [indices, wte = token->forward.weight, wpe = position->forward.weight, output, amp, amp_dt](const FnTask &) {
            const at::Tensor idx = indices.impl()->tensor.contiguous();
-           const at::Tensor &te = wte.impl()->tensor;
-           const at::Tensor &pe = wpe.impl()->tensor;
+           const bool lp_tables = amp && amp_dt == at::kBFloat16 && kernel_view(wte).scalar_type() == kernel_view(wpe).scalar_type();
+           const at::Tensor &te = lp_tables ? kernel_view(wte) : wte.impl()->tensor;
+           const at::Tensor &pe = lp_tables ? kernel_view(wpe) : wpe.impl()->tensor;
            CS_ASSERT_TRUE(idx.dim() == 2, "token indices must be [batch, seq]");
            const int64_t T = idx.size(1);
            CS_ASSERT_TRUE(T <= pe.size(0), "sequence length ", T, " exceeds the position table (", pe.size(0), ")");

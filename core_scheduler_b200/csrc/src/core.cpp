@@ -167,8 +167,6 @@ void Event::block() const {
 
 bool Event::query() const {
   if (!impl_->ev) return true;
-  static const bool always_pending = std::getenv("CS_EVENT_ALWAYS_BLOCK") != nullptr;
-  if (always_pending) return false;
   const cudaError_t code = cudaEventQuery(impl_->ev);
   if (code == cudaSuccess) return true;
   if (code == cudaErrorNotReady) {
@@ -197,6 +195,16 @@ void ReadOnlyTensor::reset() { impl_ = std::make_shared<Impl>(); }
 Tensor Tensor::wrap(at::Tensor t) {
   Tensor out;
   out.impl()->tensor = std::move(t);
+  const at::Tensor &held = out.impl()->tensor;
+  if (held.defined() && held.is_cuda() && cuda_usable()) {
+    // The tensor may still be being produced by work queued on the caller's current stream (for
+    // example a copy launched by PyTorch on its default stream). The scheduler's streams do not
+    // synchronise with that stream implicitly, so remember its state: the tag below matches no
+    // scheduler stream, which makes the first consumer on any of them wait for this event.
+    c10::cuda::CUDAGuard guard{held.device()};
+    out.impl()->event.record();
+    out.impl()->stream_class = StreamClass::kNumStreamClass;
+  }
   return out;
 }
 

@@ -319,7 +319,7 @@ def case_tp_training(device, nvp2p, batch_per_rank=2, expect_fused=False):
     if device == "cpu":
         assert abs(sum(gathered).item() / world - loss_full.raw().item()) < 1e-9
     if expect_fused:
-        assert C.fused_tp_launches() >= 8 * 2, C.fused_tp_launches()  # 4 forward + 4 backward per block... at least
+        assert C.fused_tp_launches() >= 12, C.fused_tp_launches()  # per block: 2 AG+GEMM, 2 GEMM+RS forward, 2 GEMM+RS backward
         lf, ltp = loss_full.raw().item(), cs.to_torch(s, loss_tp).item()
         assert abs(lf - ltp) < 0.2, (lf, ltp)
     gt, gf = tp.named_gradients(), full.named_gradients()

@@ -115,3 +115,18 @@ def test_profiling_reports_task_times(gpu_scheduler):
     t = s.drain_timings()
     s.set_profiling(False)
     assert any(r.name == "timed_task" and r.device_ms >= 0 for r in t)
+
+
+@pytest.mark.gpu
+def test_wrapped_tensors_wait_for_their_producer_stream(gpu_scheduler):
+    """A tensor still being written on PyTorch's current stream is not read early by a task."""
+    s = gpu_scheduler
+    n = 1 << 24
+    x = torch.zeros(n, device="cuda")
+    torch.cuda.synchronize()
+    for _ in range(60):  # long chain on the default stream
+        x = x + 1
+    h = cs.from_torch(x)  # wrapped while the chain is still running
+    res = cs.Tensor()
+    s.submit_python("reader", 0, [res], [h], lambda: res.set_raw(h.raw().sum()))
+    assert cs.to_torch(s, res).item() == 60 * n
