@@ -201,6 +201,11 @@ struct ReadOnlyTensor::Impl {
   StreamClass stream_class{StreamClass::kMain};
   StreamClass read_class{StreamClass::kMain};
   bool has_side_reader{false};
+  // Memory that came from the caller's allocator stream (Tensor::wrap): every scheduler stream
+  // that touches it is reported to the caching allocator once (bit per stream class), so a
+  // block freed on the host is not handed out again while a queued kernel still reads it.
+  bool external{false};
+  uint8_t external_streams{0};
   // Mixed-precision stamp set by forward ops running under autocast; backward ops use it to
   // pick the compute dtype.
   bool autocast_enabled{false};

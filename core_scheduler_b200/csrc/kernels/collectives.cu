@@ -101,42 +101,70 @@ __device__ __forceinline__ void slice_of(int64_t vecs, int size, int rank, int64
   if (begin > vecs) begin = vecs;
 }
 
+// Vectors each thread keeps in flight per peer. NVLink round trips are a few microseconds, so
+// hundreds of kilobytes per SM must be outstanding to fill the links from a few dozen CTAs.
+constexpr int kUnroll = 4;
+
 template <int DTYPE>
-__global__ void __launch_bounds__(512) all_reduce_twoshot_kernel(PeerTable t, int64_t offset, int64_t vecs, float scale) {
+__global__ void __launch_bounds__(256) all_reduce_twoshot_kernel(PeerTable t, int64_t offset, int64_t vecs, float scale) {
   int64_t begin, end;
   slice_of(vecs, t.size, t.rank, begin, end);
-  for (int64_t i = begin + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < end;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    int n;
-    V4 v[kMaxPeers];
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i0 = begin + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < end; i0 += stride * kUnroll) {
+    V4 v[kUnroll][kMaxPeers];
 #pragma unroll
-    for (int p = 0; p < kMaxPeers; ++p)
-      if (p < t.size) v[p] = ld_v4(t.base[(t.rank + p) % t.size] + offset + i * 16);  // all loads in flight first
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < end) {
 #pragma unroll
-    for (int p = 0; p < kMaxPeers; ++p)
-      if (p < t.size) accumulate<DTYPE>(acc, v[p], n);
-    const V4 o = finish<DTYPE>(acc, scale);
+        for (int p = 0; p < kMaxPeers; ++p)
+          if (p < t.size) v[u][p] = ld_v4(t.base[(t.rank + p) % t.size] + offset + i * 16);  // all loads in flight first
+      }
+    }
 #pragma unroll
-    for (int p = 0; p < kMaxPeers; ++p)
-      if (p < t.size) st_v4(t.base[(t.rank + p) % t.size] + offset + i * 16, o);
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < end) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        int n;
+#pragma unroll
+        for (int p = 0; p < kMaxPeers; ++p)
+          if (p < t.size) accumulate<DTYPE>(acc, v[u][p], n);
+        const V4 o = finish<DTYPE>(acc, scale);
+#pragma unroll
+        for (int p = 0; p < kMaxPeers; ++p)
+          if (p < t.size) st_v4(t.base[(t.rank + p) % t.size] + offset + i * 16, o);
+      }
+    }
   }
 }
 
 template <int DTYPE>
-__global__ void __launch_bounds__(512) pull_reduce_kernel(PeerTable t, int64_t src_offset, char *dst, int64_t vecs, float scale) {
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < vecs;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    int n;
-    V4 v[kMaxPeers];
+__global__ void __launch_bounds__(256) pull_reduce_kernel(PeerTable t, int64_t src_offset, char *dst, int64_t vecs, float scale) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < vecs; i0 += stride * kUnroll) {
+    V4 v[kUnroll][kMaxPeers];
 #pragma unroll
-    for (int p = 0; p < kMaxPeers; ++p)
-      if (p < t.size) v[p] = ld_v4(t.base[(t.rank + p) % t.size] + src_offset + i * 16);
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < vecs) {
 #pragma unroll
-    for (int p = 0; p < kMaxPeers; ++p)
-      if (p < t.size) accumulate<DTYPE>(acc, v[p], n);
-    st_v4(dst + i * 16, finish<DTYPE>(acc, scale));
+        for (int p = 0; p < kMaxPeers; ++p)
+          if (p < t.size) v[u][p] = ld_v4(t.base[(t.rank + p) % t.size] + src_offset + i * 16);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < vecs) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        int n;
+#pragma unroll
+        for (int p = 0; p < kMaxPeers; ++p)
+          if (p < t.size) accumulate<DTYPE>(acc, v[u][p], n);
+        st_v4(dst + i * 16, finish<DTYPE>(acc, scale));
+      }
+    }
   }
 }
 
@@ -147,10 +175,26 @@ __global__ void __launch_bounds__(512) pull_copy_kernel(PeerTable t, PullCopyArg
   char *dst = a.dst[p];
   const int64_t vec_per_row = a.row_bytes / 16;
   const int64_t total = a.rows * vec_per_row;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t r = i / vec_per_row, c = i - r * vec_per_row;
-    st_v4(dst + r * a.dst_stride + c * 16, ld_v4(src + r * a.src_stride + c * 16));
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  constexpr int U = 8;  // eight 16-byte loads in flight per thread
+  for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += stride * U) {
+    V4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < total) {
+        const int64_t r = i / vec_per_row, c = i - r * vec_per_row;
+        v[u] = ld_v4(src + r * a.src_stride + c * 16);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < total) {
+        const int64_t r = i / vec_per_row, c = i - r * vec_per_row;
+        st_v4(dst + r * a.dst_stride + c * 16, v[u]);
+      }
+    }
   }
 }
 
@@ -206,11 +250,11 @@ __global__ void __launch_bounds__(512) rs_adamw_ag_kernel(PeerTable t, ShardedAd
   }
 }
 
-int comm_grid(int64_t vecs, int threads) {
-  // A few dozen CTAs saturate NVLink; keeping the grid small leaves the SMs to the GEMMs that
-  // run next to the collective.
+int comm_grid(int64_t vecs, int threads, int cap = 64) {
+  // A bounded number of CTAs, each with many loads in flight, fills NVLink; keeping the grid
+  // below the SM count leaves room for the GEMMs that run next to the collective.
   const int64_t blocks = (vecs + threads - 1) / threads;
-  return static_cast<int>(blocks < 1 ? 1 : (blocks > 64 ? 64 : blocks));
+  return static_cast<int>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 }  // namespace
 
@@ -229,9 +273,9 @@ int symm_all_reduce_inplace(stream_t stream, const PeerTable &t, int64_t offset_
   const int64_t per = (vecs + t.size - 1) / t.size;
   auto s = static_cast<cudaStream_t>(stream);
   if (dtype == 0)
-    all_reduce_twoshot_kernel<0><<<comm_grid(per, 512), 512, 0, s>>>(t, offset_bytes, vecs, scale);
+    all_reduce_twoshot_kernel<0><<<comm_grid((per + kUnroll - 1) / kUnroll, 256, 128), 256, 0, s>>>(t, offset_bytes, vecs, scale);
   else
-    all_reduce_twoshot_kernel<1><<<comm_grid(per, 512), 512, 0, s>>>(t, offset_bytes, vecs, scale);
+    all_reduce_twoshot_kernel<1><<<comm_grid((per + kUnroll - 1) / kUnroll, 256, 128), 256, 0, s>>>(t, offset_bytes, vecs, scale);
   return finish_launch(1);
 }
 
@@ -243,9 +287,9 @@ int symm_pull_reduce(stream_t stream, const PeerTable &t, int64_t src_offset_byt
   auto s = static_cast<cudaStream_t>(stream);
   const int64_t vecs = bytes / 16;
   if (dtype == 0)
-    pull_reduce_kernel<0><<<comm_grid(vecs, 512), 512, 0, s>>>(t, src_offset_bytes, static_cast<char *>(dst), vecs, scale);
+    pull_reduce_kernel<0><<<comm_grid((vecs + kUnroll - 1) / kUnroll, 256, 128), 256, 0, s>>>(t, src_offset_bytes, static_cast<char *>(dst), vecs, scale);
   else
-    pull_reduce_kernel<1><<<comm_grid(vecs, 512), 512, 0, s>>>(t, src_offset_bytes, static_cast<char *>(dst), vecs, scale);
+    pull_reduce_kernel<1><<<comm_grid((vecs + kUnroll - 1) / kUnroll, 256, 128), 256, 0, s>>>(t, src_offset_bytes, static_cast<char *>(dst), vecs, scale);
   return finish_launch(1);
 }
 
@@ -259,8 +303,9 @@ int symm_pull_copy(stream_t stream, const PeerTable &t, const PullCopyArgs &a) {
   for (int p = 0; p < t.size; ++p)
     if ((a.src_offset[p] % 16) != 0 || (reinterpret_cast<uintptr_t>(a.dst[p]) & 15)) return static_cast<int>(cudaErrorInvalidValue);
   const int64_t vecs = a.rows * (a.row_bytes / 16);
-  int gx = comm_grid(vecs, 512);
-  if (gx > 16) gx = 16;  // x peers
+  int gx = comm_grid((vecs + 7) / 8, 512);
+  const int per_peer_cap = 64 / t.size > 8 ? 64 / t.size : 8;
+  if (gx > per_peer_cap) gx = per_peer_cap;  // x peers
   dim3 grid(gx, t.size);
   pull_copy_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(t, a);
   return finish_launch(1);

@@ -5,6 +5,7 @@
 #include <ATen/CPUGeneratorImpl.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <ATen/cuda/CUDAGeneratorImpl.h>
+#include <c10/cuda/CUDACachingAllocator.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <cuda_runtime.h>
@@ -204,6 +205,7 @@ Tensor Tensor::wrap(at::Tensor t) {
     c10::cuda::CUDAGuard guard{held.device()};
     out.impl()->event.record();
     out.impl()->stream_class = StreamClass::kNumStreamClass;
+    out.impl()->external = true;
   }
   return out;
 }
@@ -335,12 +337,20 @@ struct CudaImpl final : Scheduler::Impl {
   void run(const Task &task, Task::Impl::Priority tag) {
     const auto &t = *task.impl();
     const auto cls = static_cast<StreamClass>(tag);
+    auto adopt = [&](ReadOnlyTensor::Impl &ti) {  // see Tensor::Impl::external
+      const auto bit = static_cast<uint8_t>(1u << tag);
+      if (!ti.external || (ti.external_streams & bit) || !ti.tensor.defined() || !ti.tensor.is_cuda()) return;
+      ti.external_streams |= bit;
+      if (ti.tensor.has_storage()) c10::cuda::CUDACachingAllocator::recordStream(ti.tensor.storage().data_ptr(), streams_[tag]);
+    };
     for (auto &in : t.input()) {  // read-after-write across streams
       auto &ti = *in.impl();
+      adopt(ti);
       if (ti.stream_class != cls && !ti.event.query()) ti.event.block();
     }
     for (auto &out : t.output()) {  // write-after-write / write-after-read across streams
       auto &ti = *out.impl();
+      adopt(ti);
       if (ti.stream_class != cls && !ti.event.query()) ti.event.block();
       if (ti.has_side_reader && ti.read_class != cls) {
         if (!ti.read_event.query()) ti.read_event.block();

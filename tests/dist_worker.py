@@ -59,6 +59,27 @@ def case_all_reduce(device, nvp2p):
         assert torch.allclose(cs.to_torch(s, h), e, atol=1e-4)
 
 
+def case_all_reduce_arena(device, nvp2p):
+    """In-place all-reduce on ranges of the symmetric arena (the data-parallel gradient path), odd sizes included."""
+    comm, rank, world, s = make_comm(device, True)
+    ctx = C.create_symmetric_context(comm, 64 << 20)
+    for dtype, n in ((torch.float32, 4 * 1000 + 4), (torch.float32, 1 << 20), (torch.bfloat16, 8 * 777), (torch.float32, 4 * 12345)):
+        buf, off, nb = ctx.empty([n], dtype)
+        buf.copy_(seeded(50 * rank + 1, n, dtype=dtype, device=device))
+        expect = sum(seeded(50 * r + 1, n, dtype=dtype, device=device).double() for r in range(world))
+        torch.cuda.synchronize()
+        h = T(buf)
+        C.all_reduce(s, comm, [h], "sum")
+        s.synchronize()
+        tol = dict(rtol=2e-2, atol=1e-1) if dtype == torch.bfloat16 else dict(rtol=1e-6, atol=1e-5)
+        assert torch.allclose(buf.double(), expect, **tol), (rank, dtype, n, (buf.double() - expect).abs().max().item())
+        C.all_reduce(s, comm, [h], "avg")
+        s.synchronize()
+        assert torch.allclose(buf.double(), expect, **tol), (rank, "avg", n)  # (sum over identical copies) / world
+        ctx.release(off, nb)
+    ctx.check_status()
+
+
 def case_bucket(device, nvp2p):
     comm, rank, world, s = make_comm(device, nvp2p)
     bucket = cs.AllReduceBucket(1024 * 4, "sum")  # 1024 fp32 elements
