@@ -34,6 +34,7 @@ CPP_SOURCES = [
     "src/comm_nccl.cpp",
     "src/symmetric.cpp",
     "src/data.cpp",
+    "src/observability.cpp",
     "src/models_gpt2.cpp",
 ]
 CUDA_SOURCES = [

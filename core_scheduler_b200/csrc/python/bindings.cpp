@@ -13,6 +13,7 @@
 #include "cs/data.h"
 #include "cs/models.h"
 #include "cs/modules.h"
+#include "cs/observability.h"
 #include "cs/optimizer.h"
 #include "cs/parallel.h"
 #include "cs/symmetric.h"
@@ -560,6 +561,68 @@ PYBIND11_MODULE(_C, m) {
       .def(py::init<const Comm &, int64_t>())
       .def("beat", &communication::Heartbeat::beat)
       .def("stale_ranks", &communication::Heartbeat::stale_ranks);
+
+  // ---- metrics, watchdog, resumable state ---------------------------------------------------
+  py::class_<metrics::StepRecord>(m, "StepRecord")
+      .def(py::init<>())
+      .def_readwrite("step", &metrics::StepRecord::step)
+      .def_readwrite("loss", &metrics::StepRecord::loss)
+      .def_readwrite("lr", &metrics::StepRecord::lr)
+      .def_readwrite("grad_norm", &metrics::StepRecord::grad_norm)
+      .def_readwrite("dt_host_ms", &metrics::StepRecord::dt_host_ms)
+      .def_readwrite("dt_device_ms", &metrics::StepRecord::dt_device_ms)
+      .def_readwrite("tokens_per_sec", &metrics::StepRecord::tokens_per_sec)
+      .def_readwrite("mfu", &metrics::StepRecord::mfu)
+      .def_readwrite("comm_bytes", &metrics::StepRecord::comm_bytes)
+      .def_readwrite("extra", &metrics::StepRecord::extra);
+  py::class_<metrics::MetricsLogger>(m, "MetricsLogger")
+      .def(py::init([](const std::string &jsonl, const std::string &csv, bool console, int64_t rank, int64_t writer) {
+             return std::make_unique<metrics::MetricsLogger>(
+                 metrics::MetricsLogger::Options{}.jsonl_path(jsonl).csv_path(csv).console(console).rank(rank).writer_rank(writer));
+           }),
+           py::arg("jsonl_path") = "", py::arg("csv_path") = "", py::arg("console") = true, py::arg("rank") = 0,
+           py::arg("writer_rank") = 0)
+      .def("log", &metrics::MetricsLogger::log)
+      .def("records_written", &metrics::MetricsLogger::records_written)
+      .def_static("to_json", &metrics::MetricsLogger::to_json)
+      .def_static("console_line", &metrics::MetricsLogger::console_line);
+  m.def("mfu", &metrics::mfu);
+  py::class_<fault::Watchdog>(m, "Watchdog")
+      .def(py::init([](std::optional<Comm> comm, int64_t timeout_ms, int64_t poll_ms) {
+             auto o = fault::Watchdog::Options{}.timeout_ms(timeout_ms).poll_ms(poll_ms);
+             return comm ? std::make_unique<fault::Watchdog>(*comm, o) : std::make_unique<fault::Watchdog>(o);
+           }),
+           py::arg("comm") = py::none(), py::arg("timeout_ms") = 60000, py::arg("poll_ms") = 50)
+      .def("progress", &fault::Watchdog::progress)
+      .def("stop", &fault::Watchdog::stop, py::call_guard<py::gil_scoped_release>())
+      .def("tripped", &fault::Watchdog::tripped)
+      .def("last_step", &fault::Watchdog::last_step)
+      .def("failed_peers", &fault::Watchdog::failed_peers)
+      .def("check", &fault::Watchdog::check);
+  py::class_<checkpoint::Meta>(m, "CheckpointMeta")
+      .def(py::init<>())
+      .def_readwrite("step", &checkpoint::Meta::step)
+      .def_readwrite("lr", &checkpoint::Meta::lr)
+      .def_readwrite("seed", &checkpoint::Meta::seed)
+      .def_readwrite("data_cursor", &checkpoint::Meta::data_cursor)
+      .def_readwrite("world_size", &checkpoint::Meta::world_size)
+      .def_readwrite("tp_size", &checkpoint::Meta::tp_size)
+      .def_readwrite("zero", &checkpoint::Meta::zero)
+      .def_readwrite("model", &checkpoint::Meta::model);
+  m.def("save_meta", &checkpoint::save_meta);
+  m.def("load_meta", &checkpoint::load_meta);
+  m.def("save_training_state",
+        [](const Scheduler &s, const std::string &dir, const module::Module &model, std::shared_ptr<module::OptimizerModule> opt,
+           const checkpoint::Meta &meta, int64_t rank, int64_t writer_rank) {
+          checkpoint::save_training_state(s, dir, model, opt.get(), meta, rank, writer_rank);
+        },
+        py::arg("scheduler"), py::arg("dir"), py::arg("model"), py::arg("optimizer"), py::arg("meta"), py::arg("rank") = 0,
+        py::arg("writer_rank") = 0);
+  m.def("load_training_state",
+        [](const Scheduler &s, const std::string &dir, const module::Module &model, std::shared_ptr<module::OptimizerModule> opt) {
+          return checkpoint::load_training_state(s, dir, model, opt.get());
+        },
+        py::arg("scheduler"), py::arg("dir"), py::arg("model"), py::arg("optimizer"));
 
   // ---- symmetric memory / parallel strategies -------------------------------------------------
   using communication::SymmetricContext;

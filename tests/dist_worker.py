@@ -356,6 +356,35 @@ def case_tp_training(device, nvp2p, batch_per_rank=2, expect_fused=False):
             assert torch.allclose(got, ref, **tol), (rank, k, (got - ref).abs().max().item())
 
 
+def case_watchdog(device, nvp2p):
+    """A rank whose loop stalls trips its watchdog; the healthy rank learns of it through the store before its next launch."""
+    comm, rank, world, s = make_comm(device, False)
+    dog = C.Watchdog(comm, timeout_ms=300, poll_ms=20)
+    for step in range(3):
+        dog.progress(step)
+        dog.check()
+        time.sleep(0.05)
+    dist.barrier()
+    if rank == world - 1:
+        time.sleep(1.0)  # the stall: no progress() calls
+        assert dog.tripped() and dog.last_step() == 2
+    else:
+        deadline = time.time() + 10
+        while time.time() < deadline and not dog.failed_peers():
+            dog.progress(3)
+            time.sleep(0.05)
+        assert dog.failed_peers() == [world - 1], dog.failed_peers()
+        assert not dog.tripped()
+        try:
+            dog.check()
+            raised = False
+        except RuntimeError as e:
+            raised = "reported a failure" in str(e)
+        assert raised
+    dog.stop()
+    dist.barrier()
+
+
 def case_failure_injection(device, nvp2p):
     """A collective that fails on one rank surfaces as an error there; the others see the rank stop beating."""
     comm, rank, world, s = make_comm(device, False)
