@@ -627,6 +627,16 @@ PYBIND11_MODULE(_C, m) {
   // ---- symmetric memory / parallel strategies -------------------------------------------------
   using communication::SymmetricContext;
   py::class_<SymmetricContext, std::shared_ptr<SymmetricContext>>(m, "SymmetricContext")
+      .def(py::init([](int64_t arena_bytes) {  // offset bookkeeping only (no device memory): allocator tests
+             auto c = std::make_shared<SymmetricContext>();
+             c->arena_bytes = arena_bytes;
+             return c;
+           }),
+           py::arg("arena_bytes"))
+      .def("allocate", [](SymmetricContext &c, int64_t bytes) {
+        const auto b = c.allocate(bytes);
+        return py::make_tuple(b.offset, b.bytes);
+      })
       .def_readonly("rank", &SymmetricContext::rank)
       .def_readonly("size", &SymmetricContext::size)
       .def_readonly("arena_bytes", &SymmetricContext::arena_bytes)

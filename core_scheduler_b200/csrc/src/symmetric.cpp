@@ -58,14 +58,19 @@ SymmetricContext::~SymmetricContext() {
 }
 
 SymmetricBlock SymmetricContext::allocate(int64_t bytes) {
+  // Every rank issues the same sequence of calls, so the deterministic policy below (best fit,
+  // split the remainder, otherwise bump) yields the same offsets everywhere.
   bytes = round_up(std::max<int64_t>(bytes, 1), kAlign);
-  // best fit among cached blocks
   int best = -1;
   for (size_t i = 0; i < free_.size(); ++i)
     if (free_[i].bytes >= bytes && (best < 0 || free_[i].bytes < free_[best].bytes)) best = static_cast<int>(i);
-  if (best >= 0 && free_[best].bytes <= 2 * bytes) {
+  if (best >= 0) {
     SymmetricBlock b = free_[best];
     free_.erase(free_.begin() + best);
+    if (b.bytes > bytes) {
+      free_.push_back(SymmetricBlock{b.offset + bytes, b.bytes - bytes});
+      b.bytes = bytes;
+    }
     in_use_ += b.bytes;
     return b;
   }
@@ -79,7 +84,24 @@ SymmetricBlock SymmetricContext::allocate(int64_t bytes) {
 void SymmetricContext::release(const SymmetricBlock &block) {
   if (block.bytes <= 0) return;
   in_use_ -= block.bytes;
-  free_.push_back(block);
+  SymmetricBlock merged = block;
+  // unite with free neighbours, then give the top of the arena back to the bump pointer
+  for (bool again = true; again;) {
+    again = false;
+    for (size_t i = 0; i < free_.size(); ++i) {
+      const auto &f = free_[i];
+      if (f.offset + f.bytes == merged.offset || merged.offset + merged.bytes == f.offset) {
+        merged = SymmetricBlock{std::min(f.offset, merged.offset), f.bytes + merged.bytes};
+        free_.erase(free_.begin() + static_cast<std::ptrdiff_t>(i));
+        again = true;
+        break;
+      }
+    }
+  }
+  if (merged.offset + merged.bytes == bump_)
+    bump_ = merged.offset;
+  else
+    free_.push_back(merged);
 }
 
 SymmetricBlock SymmetricContext::staging(int64_t bytes) {

@@ -190,3 +190,35 @@ def test_flat_adamw_equals_per_tensor_adamw(cpu_scheduler):
     pa, pb = a.named_parameters(), b.named_parameters()
     for k in pa:
         assert torch.allclose(pa[k].raw(), pb[k].raw(), atol=1e-5), k
+
+
+def test_symmetric_arena_offsets_coalesce_and_return_to_the_top():
+    """The peer-mapped arena hands out offsets; freed neighbours unite, so growing requests keep fitting."""
+    ctx = cs._C.SymmetricContext(arena_bytes=1 << 20)
+    a, b, c = (ctx.allocate(n) for n in (1000, 5000, 300))
+    assert a == (0, 1024) and b == (1024, 5120) and c == (6144, 512)
+    ctx.release(*a)
+    ctx.release(*b)  # unites with a: one cached block of 6144 bytes
+    assert ctx.cached_blocks() == 1
+    d = ctx.allocate(6000)
+    assert d == (0, 6144) and ctx.cached_blocks() == 0
+    e = ctx.allocate(256)
+    assert e[0] == 6656
+    ctx.release(*e)  # top of the arena: goes back to the bump pointer
+    assert ctx.cached_blocks() == 0 and ctx.allocate(512)[0] == 6656
+    # doubling sizes with release in between never exhaust an arena of 3x the largest request
+    small = cs._C.SymmetricContext(arena_bytes=3 << 20)
+    size = 1024
+    while size <= (1 << 20):
+        x, y = small.allocate(size), small.allocate(size)
+        small.release(*x)
+        small.release(*y)
+        size *= 2
+    assert small.bytes_in_use() == 0
+    with pytest.raises(RuntimeError, match="exhausted"):
+        small.allocate(4 << 20)
+    f = small.allocate(100)
+    g = small.allocate(100)
+    small.release(*f)
+    h = small.allocate(50)  # best fit splits nothing smaller than the alignment
+    assert h == f and g[0] == 256
