@@ -360,6 +360,312 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
   }
 }
 
+// ------------------------------------------------------------------------------ backward ----
+// dQ, dK, dV of causal attention from the packed qkv, the forward output, its gradient and the
+// per-row log-sum-exp; results go straight into the packed dqkv [B, T, 3, H, 64].
+//
+// Three launches: (1) delta[b,h,t] = sum_d dO*O; (2) kDKV = true: one CTA per 128-key block keeps
+// K_j, V_j resident and streams 64-query tiles (Q_i, dO_i), accumulating dV_j and dK_j in TMEM;
+// (3) kDKV = false: one CTA per 128-query block keeps Q_i, dO_i resident and streams 64-key tiles
+// (K_j, V_j), accumulating dQ_i in TMEM. No atomics, deterministic. Per streamed tile:
+//   S' = R1 C1^T, dP' = R2 C2^T              (128 x 64 x 64 each, fp32 in TMEM; rows = resident side)
+//   P' = exp(scale S' - lse), dS' = scale P' (dP' - delta)   (softmax warps, one thread per row)
+//   [dV += P' C2]   acc += dS' C1            (128 x 64 x 64; P'/dS' from swizzled shared memory, C as
+//                                             MN-major operands)
+// 256 TMEM columns and ~99 KB of shared memory per CTA: two CTAs per SM overlap each other's softmax.
+constexpr int BC = 64;                          // streamed rows per step
+constexpr int C_TILE_BYTES = BC * HD * 2;       // 8 KB
+constexpr int PS_BYTES = 128 * BC * 2;          // 16 KB: P' or dS'
+constexpr int BWD_STAGES = 2;
+constexpr int BWD_SMEM_BYTES = 2 * TILE_BYTES + BWD_STAGES * (2 * C_TILE_BYTES + 512) + 2 * PS_BYTES + 1024 + 256;
+
+struct AttnBwdParams {
+  __nv_bfloat16 *dqkv;  // [B, T, 3, H, 64]
+  const float *lse;     // [B, H, T]
+  const float *delta;   // [B, H, T]
+  int B, T, H;
+  float scale, scale_log2e;
+  DeviceStatus *status;
+};
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+               "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(256) attention_delta_kernel(const __nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__restrict__ dout,
+                                                              float *__restrict__ delta, int B, int T, int H) {
+  // eight threads per (b, t, h) row of 64 values
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long row = gid >> 3;
+  const int part = static_cast<int>(gid & 7);
+  const long long rows = static_cast<long long>(B) * T * H;
+  float acc = 0.f;
+  if (row < rows) {
+    const uint4 a = *reinterpret_cast<const uint4 *>(out + row * HD + part * 8);
+    const uint4 g = *reinterpret_cast<const uint4 *>(dout + row * HD + part * 8);
+    const __nv_bfloat162 *pa = reinterpret_cast<const __nv_bfloat162 *>(&a);
+    const __nv_bfloat162 *pg = reinterpret_cast<const __nv_bfloat162 *>(&g);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __bfloat1622float2(pa[i]), y = __bfloat1622float2(pg[i]);
+      acc = fmaf(x.x, y.x, acc);
+      acc = fmaf(x.y, y.y, acc);
+    }
+  }
+  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+  if (row < rows && part == 0) {
+    const long long bt = row / H;
+    const int h = static_cast<int>(row - bt * H);
+    const long long b = bt / T;
+    const int t = static_cast<int>(bt - b * T);
+    delta[(b * H + h) * T + t] = acc;
+  }
+}
+
+template <bool kDKV>
+__global__ void __launch_bounds__(THREADS, 2)
+attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_constant__ CUtensorMap qkv_c,
+                     const __grid_constant__ CUtensorMap do_r, const __grid_constant__ CUtensorMap do_c, const AttnBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *aligned = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t r1_smem = base;                      // resident operand of S'
+  const uint32_t r2_smem = r1_smem + TILE_BYTES;      // resident operand of dP'
+  const uint32_t c_smem = r2_smem + TILE_BYTES;       // per stage: C1 tile, C2 tile
+  const uint32_t p_smem = c_smem + BWD_STAGES * 2 * C_TILE_BYTES;
+  const uint32_t ds_smem = p_smem + PS_BYTES;
+  const uint32_t vec_smem = ds_smem + PS_BYTES;       // per stage: lse[64], delta[64] of the streamed queries
+  const uint32_t bar_base = vec_smem + BWD_STAGES * 512;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + (bar_base - base));
+  const float *vec = reinterpret_cast<const float *>(aligned + (vec_smem - base));
+  enum { R_FULL = 0, C_FULL = 1, C_EMPTY = 3, SDP_FULL = 5, SDP_EMPTY = 6, PDS_FULL = 7, PDS_EMPTY = 8, ACC_FULL = 9, NUM_BARS = 10 };
+  auto bar = [&](int i) { return bar_base + 8u * i; };
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars + NUM_BARS);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + NUM_BARS + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Longest loops first: key block 0 streams all queries, query block T/128-1 streams all keys.
+  const int rb = kDKV ? blockIdx.x : gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int r0 = rb * 128;
+  const int row_base = b * p.T;
+  // streamed 64-row tiles: queries r0 .. T (kDKV) or keys 0 .. r0+128
+  const int c_first = kDKV ? 2 * rb : 0;
+  const int n_iter = kDKV ? p.T / BC - c_first : 2 * (rb + 1);
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(R_FULL), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(C_FULL + s), 1);
+      mbar_init(bar(C_EMPTY + s), 1);
+    }
+    mbar_init(bar(SDP_FULL), 1);
+    mbar_init(bar(SDP_EMPTY), 4);
+    mbar_init(bar(PDS_FULL), 4);
+    mbar_init(bar(PDS_EMPTY), 1);
+    mbar_init(bar(ACC_FULL), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t *>(tmem_slot))),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t s_tmem = tmem_base;             // S'   64 columns
+  const uint32_t dp_tmem = tmem_base + BC;       // dP'  64 columns
+  const uint32_t acc1_tmem = tmem_base + 2 * BC; // dV (kDKV only)
+  const uint32_t acc2_tmem = tmem_base + 3 * BC; // dK or dQ
+
+  const int q_col = h * HD, k_col = (p.H + h) * HD, v_col = (2 * p.H + h) * HD;
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(bar(R_FULL), 2 * TILE_BYTES);
+      if (kDKV) {
+        tma_load_2d(r1_smem, &qkv_r, bar(R_FULL), k_col, row_base + r0);
+        tma_load_2d(r2_smem, &qkv_r, bar(R_FULL), v_col, row_base + r0);
+      } else {
+        tma_load_2d(r1_smem, &qkv_r, bar(R_FULL), q_col, row_base + r0);
+        tma_load_2d(r2_smem, &do_r, bar(R_FULL), q_col, row_base + r0);
+      }
+      const float *lse_row = p.lse + (static_cast<long long>(b) * p.H + h) * p.T;
+      const float *delta_row = p.delta + (static_cast<long long>(b) * p.H + h) * p.T;
+      for (int t = 0; t < n_iter; ++t) {
+        const int s = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        const int c0 = (c_first + t) * BC;
+        if (!mbar_wait(bar(C_EMPTY + s), ph ^ 1u, abort_flag)) break;
+        const uint32_t c1 = c_smem + s * 2 * C_TILE_BYTES, c2 = c1 + C_TILE_BYTES;
+        if (kDKV) {
+          mbar_expect_tx(bar(C_FULL + s), 2 * C_TILE_BYTES + 512);
+          tma_load_2d(c1, &qkv_c, bar(C_FULL + s), q_col, row_base + c0);
+          tma_load_2d(c2, &do_c, bar(C_FULL + s), q_col, row_base + c0);
+          bulk_load(vec_smem + s * 512, lse_row + c0, 256, bar(C_FULL + s));
+          bulk_load(vec_smem + s * 512 + 256, delta_row + c0, 256, bar(C_FULL + s));
+        } else {
+          mbar_expect_tx(bar(C_FULL + s), 2 * C_TILE_BYTES);
+          tma_load_2d(c1, &qkv_c, bar(C_FULL + s), k_col, row_base + c0);
+          tma_load_2d(c2, &qkv_c, bar(C_FULL + s), v_col, row_base + c0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // S', dP': M=128, N=64, both operands K-major. Accumulators: M=128, N=64, B MN-major.
+      const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BC >> 3) << 17) | (8u << 24);
+      const uint32_t idesc_a = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (static_cast<uint32_t>(HD >> 3) << 17) | (8u << 24);
+      bool ok = mbar_wait(bar(R_FULL), 0, abort_flag);
+      auto issue_sdp = [&](int t) -> bool {
+        const int s = t & 1;
+        if (!mbar_wait(bar(C_FULL + s), (t >> 1) & 1, abort_flag)) return false;
+        if (!mbar_wait(bar(SDP_EMPTY), (t & 1) ^ 1u, abort_flag)) return false;
+        fence_after();
+        const uint32_t c1 = c_smem + s * 2 * C_TILE_BYTES, c2 = c1 + C_TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          umma(s_tmem, smem_desc(r1_smem + k * 32, 16, 1024), smem_desc(c1 + k * 32, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          umma(dp_tmem, smem_desc(r2_smem + k * 32, 16, 1024), smem_desc(c2 + k * 32, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+        umma_commit(bar(SDP_FULL));
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      int t = 0;
+      for (; ok && t < n_iter; ++t) {
+        const int s = t & 1;
+        if (!mbar_wait(bar(PDS_FULL), t & 1, abort_flag)) break;
+        if (t + 1 < n_iter) ok = issue_sdp(t + 1);
+        if (!ok) break;
+        fence_after();
+        const uint32_t c1 = c_smem + s * 2 * C_TILE_BYTES, c2 = c1 + C_TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < BC / 16; ++k) {
+          if (kDKV) umma(acc1_tmem, smem_desc(p_smem + k * 32, 16, 1024), smem_desc(c2 + k * 2048, 8192, 1024), idesc_a, (t | k) ? 1u : 0u);
+          umma(acc2_tmem, smem_desc(ds_smem + k * 32, 16, 1024), smem_desc(c1 + k * 2048, 8192, 1024), idesc_a, (t | k) ? 1u : 0u);
+        }
+        umma_commit(bar(PDS_EMPTY));
+        umma_commit(bar(C_EMPTY + s));
+      }
+      if (ok && t == n_iter) umma_commit(bar(ACC_FULL));
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;  // row of the resident block
+    const int r_idx = r0 + r;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const float log2e = 1.4426950408889634f;
+    float lse_r = 0.f, delta_r = 0.f;
+    if (!kDKV) {
+      lse_r = p.lse[(static_cast<long long>(b) * p.H + h) * p.T + r_idx] * log2e;
+      delta_r = p.delta[(static_cast<long long>(b) * p.H + h) * p.T + r_idx];
+    }
+    bool ok = true;
+    for (int t = 0; ok && t < n_iter; ++t) {
+      const int s = t & 1;
+      const int c0 = (c_first + t) * BC;
+      if (kDKV && !mbar_wait(bar(C_FULL + s), (t >> 1) & 1, abort_flag)) break;  // lse / delta of the streamed queries
+      if (!mbar_wait(bar(SDP_FULL), t & 1, abort_flag)) break;
+      fence_after();
+      if (!mbar_wait(bar(PDS_EMPTY), (t & 1) ^ 1u, abort_flag)) break;
+      // rows are keys and columns queries (kDKV), or rows queries and columns keys: keep key <= query
+      const bool near_diag = kDKV ? (c0 < r0 + 128) : (c0 + BC > r0);
+      const float *lse_c = vec + s * 128, *delta_c = lse_c + 64;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld32(s_tmem + c * 32 + lane_addr, sv);
+        tmem_ld32(dp_tmem + c * 32 + lane_addr, dv);
+        tmem_wait_ld();
+        float pr[32], ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = c0 + c * 32 + i;
+          const bool keep = !near_diag || (kDKV ? (r_idx <= col) : (col <= r_idx));
+          const float l2 = kDKV ? lse_c[c * 32 + i] * log2e : lse_r;
+          const float dl = kDKV ? delta_c[c * 32 + i] : delta_r;
+          const float e = keep ? fast_exp2(fmaf(__uint_as_float(sv[i]), p.scale_log2e, -l2)) : 0.f;
+          pr[i] = e;
+          ds[i] = e * (__uint_as_float(dv[i]) - dl) * p.scale;
+        }
+        // 32 columns = 64 bytes = four 16-byte pieces of this row
+        const uint32_t row_off = r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int piece = c * 4 + g;
+          const uint32_t off = row_off + ((piece ^ (r & 7)) << 4);
+          if (kDKV)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_smem + off), "r"(pack2(pr[g * 8 + 0], pr[g * 8 + 1])),
+                         "r"(pack2(pr[g * 8 + 2], pr[g * 8 + 3])), "r"(pack2(pr[g * 8 + 4], pr[g * 8 + 5])),
+                         "r"(pack2(pr[g * 8 + 6], pr[g * 8 + 7]))
+                         : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ds_smem + off), "r"(pack2(ds[g * 8 + 0], ds[g * 8 + 1])),
+                       "r"(pack2(ds[g * 8 + 2], ds[g * 8 + 3])), "r"(pack2(ds[g * 8 + 4], ds[g * 8 + 5])),
+                       "r"(pack2(ds[g * 8 + 6], ds[g * 8 + 7]))
+                       : "memory");
+        }
+      }
+      fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar(SDP_EMPTY));
+        mbar_arrive(bar(PDS_FULL));
+      }
+    }
+    if (mbar_wait(bar(ACC_FULL), 0, abort_flag) && !*abort_flag) {
+      fence_after();
+      const long long row = static_cast<long long>(row_base + r_idx) * 3 * p.H;
+      auto store = [&](uint32_t tmem, int part) {
+        __nv_bfloat16 *dst = p.dqkv + (row + static_cast<long long>(part) * p.H + h) * HD;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tmem + c * 32 + lane_addr, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            w.x = pack2(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
+            w.y = pack2(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
+            w.z = pack2(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
+            w.w = pack2(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
+            *reinterpret_cast<uint4 *>(dst + c * 32 + g * 8) = w;
+          }
+        }
+      };
+      if (kDKV) {
+        store(acc1_tmem, 2);  // dV
+        store(acc2_tmem, 1);  // dK
+      } else {
+        store(acc2_tmem, 0);  // dQ
+      }
+    }
+  }
+
+  fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) {
+    p.status->code = 1;
+    p.status->kernel_id = kDKV ? 4 : 5;
+    p.status->block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    p.status->detail = 0;
+  }
+  if (warp == 1) {
+    fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                               const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -382,43 +688,53 @@ int attention_status(DeviceStatus *out) {
   return static_cast<int>(cudaMemcpyFromSymbol(out, g_attn_status, sizeof(DeviceStatus)));
 }
 
+namespace {
+// [rows, cols] bf16 row-major viewed through 64-column boxes of `box_rows` rows, 128-byte swizzle.
+bool attn_map(CUtensorMap *out, const void *ptr, int64_t cols, int64_t rows, int box_rows) {
+  EncodeFn fn = attn_encode_fn();
+  if (!fn) return false;
+  static std::mutex mu;
+  static std::unordered_map<uint64_t, CUtensorMap> cache;
+  std::lock_guard<std::mutex> lock{mu};
+  const uint64_t key = reinterpret_cast<uint64_t>(ptr) ^ (static_cast<uint64_t>(rows) << 40) ^ (static_cast<uint64_t>(cols) << 20) ^
+                       (static_cast<uint64_t>(box_rows) << 56);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return true;
+  }
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols * 2)};
+  const cuuint32_t box[2] = {HD, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  if (fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return true;
+}
+DeviceStatus *attn_status_ptr() {
+  static DeviceStatus *ptr = [] {
+    void *p = nullptr;
+    cudaGetSymbolAddress(&p, g_attn_status);
+    return static_cast<DeviceStatus *>(p);
+  }();
+  return ptr;
+}
+}  // namespace
+
 int attention_forward_packed(stream_t stream, const void *qkv, void *out, float *lse, int64_t B, int64_t T, int64_t H, int64_t D,
                              float scale) {
   if (D != HD || T % BQ != 0 || B <= 0 || H <= 0 || T <= 0) return -1;
   if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(out)) & 15) return -1;
   static const bool disabled = std::getenv("CS_DISABLE_TCGEN05_ATTENTION") != nullptr;
   if (disabled) return -1;
-  EncodeFn fn = attn_encode_fn();
-  if (!fn) return -1;
-  static std::mutex mu;
-  static std::unordered_map<uint64_t, CUtensorMap> cache;
   CUtensorMap map;
-  {
-    std::lock_guard<std::mutex> lock{mu};
-    const uint64_t key = reinterpret_cast<uint64_t>(qkv) ^ (static_cast<uint64_t>(B * T) << 40) ^ (static_cast<uint64_t>(H) << 32);
-    auto it = cache.find(key);
-    if (it == cache.end()) {
-      const cuuint64_t dims[2] = {static_cast<cuuint64_t>(3 * H * D), static_cast<cuuint64_t>(B * T)};
-      const cuuint64_t strides[1] = {static_cast<cuuint64_t>(3 * H * D * 2)};
-      const cuuint32_t box[2] = {HD, 128};
-      const cuuint32_t elem[2] = {1, 1};
-      if (fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(qkv), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return -1;
-      if (cache.size() > 4096) cache.clear();
-      cache.emplace(key, map);
-    } else {
-      map = it->second;
-    }
-  }
+  if (!attn_map(&map, qkv, 3 * H * D, B * T, 128)) return -1;
   static const bool attr_set =
       cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) == cudaSuccess;
   if (!attr_set) return -1;
-  static DeviceStatus *status_ptr = [] {
-    void *ptr = nullptr;
-    cudaGetSymbolAddress(&ptr, g_attn_status);
-    return static_cast<DeviceStatus *>(ptr);
-  }();
   AttnParams p{};
   p.out = static_cast<__nv_bfloat16 *>(out);
   p.lse = lse;
@@ -427,9 +743,46 @@ int attention_forward_packed(stream_t stream, const void *qkv, void *out, float 
   p.H = static_cast<int>(H);
   p.scale = scale;
   p.scale_log2e = scale * 1.4426950408889634f;
-  p.status = status_ptr;
+  p.status = attn_status_ptr();
   dim3 grid(static_cast<unsigned>(T / BQ), static_cast<unsigned>(H), static_cast<unsigned>(B));
   attention_fwd_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map, p);
   return finish_launch(1);
+}
+
+int attention_backward_packed(stream_t stream, const void *qkv, const void *out, const void *dout, const float *lse, float *delta,
+                              void *dqkv, int64_t B, int64_t T, int64_t H, int64_t D, float scale) {
+  if (D != HD || T % 128 != 0 || B <= 0 || H <= 0 || T <= 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(dout) |
+       reinterpret_cast<uintptr_t>(dqkv) | reinterpret_cast<uintptr_t>(lse) | reinterpret_cast<uintptr_t>(delta)) & 15)
+    return -1;
+  static const bool disabled = std::getenv("CS_DISABLE_TCGEN05_ATTENTION") != nullptr;
+  if (disabled) return -1;
+  CUtensorMap qkv_r, qkv_c, do_r, do_c;
+  if (!attn_map(&qkv_r, qkv, 3 * H * D, B * T, 128) || !attn_map(&qkv_c, qkv, 3 * H * D, B * T, BC) ||
+      !attn_map(&do_r, dout, H * D, B * T, 128) || !attn_map(&do_c, dout, H * D, B * T, BC))
+    return -1;
+  static const bool attr_set =
+      cudaFuncSetAttribute(attention_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM_BYTES) == cudaSuccess &&
+      cudaFuncSetAttribute(attention_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM_BYTES) == cudaSuccess;
+  if (!attr_set) return -1;
+  auto s = static_cast<cudaStream_t>(stream);
+  const long long threads = B * T * H * 8;
+  attention_delta_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, s>>>(
+      static_cast<const __nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(dout), delta, static_cast<int>(B), static_cast<int>(T),
+      static_cast<int>(H));
+  AttnBwdParams p{};
+  p.dqkv = static_cast<__nv_bfloat16 *>(dqkv);
+  p.lse = lse;
+  p.delta = delta;
+  p.B = static_cast<int>(B);
+  p.T = static_cast<int>(T);
+  p.H = static_cast<int>(H);
+  p.scale = scale;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.status = attn_status_ptr();
+  dim3 grid(static_cast<unsigned>(T / 128), static_cast<unsigned>(H), static_cast<unsigned>(B));
+  attention_bwd_kernel<true><<<grid, THREADS, BWD_SMEM_BYTES, s>>>(qkv_r, qkv_c, do_r, do_c, p);
+  attention_bwd_kernel<false><<<grid, THREADS, BWD_SMEM_BYTES, s>>>(qkv_r, qkv_c, do_r, do_c, p);
+  return finish_launch(3);
 }
 }  // namespace cs::kernels

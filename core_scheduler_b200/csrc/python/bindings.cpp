@@ -127,6 +127,17 @@ PYBIND11_MODULE(_C, m) {
                                                         lse.data_ptr<float>(), B, T, heads, D, static_cast<float>(scale));
     return py::make_tuple(rc, out, lse);
   });
+  m.def("attention_backward_tcgen05", [](const at::Tensor &qkv, const at::Tensor &out, const at::Tensor &dout, const at::Tensor &lse,
+                                         int64_t heads, double scale) {
+    const int64_t B = qkv.size(0), T = qkv.size(1), D = qkv.size(2) / (3 * heads);
+    at::Tensor dqkv = at::empty_like(qkv);
+    at::Tensor delta = at::empty({B, heads, T}, qkv.options().dtype(at::kFloat));
+    const int rc = cs::kernels::attention_backward_packed(c10::cuda::getCurrentCUDAStream().stream(), qkv.data_ptr(), out.data_ptr(),
+                                                          dout.data_ptr(), lse.data_ptr<float>(), delta.data_ptr<float>(),
+                                                          dqkv.data_ptr(), B, T, heads, D, static_cast<float>(scale));
+    CS_ASSERT_TRUE(rc == 0, "attention_backward_packed returned ", rc);
+    return py::make_tuple(dqkv, delta);
+  });
   m.def("attention_status", [] {
     cs::kernels::DeviceStatus st{};
     cs::kernels::attention_status(&st);

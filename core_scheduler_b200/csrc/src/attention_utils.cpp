@@ -79,14 +79,11 @@ bool use_cudnn_engine() {
   return cudnn;
 }
 
-// "tcgen05": this library's forward kernel on the packed qkv tensor (backward then uses the
-// flash-attention library kernels, which accept its output and log-sum-exp).
+// "tcgen05": this library's forward and backward kernels on the packed qkv tensor. Read at every
+// call (a dozen per step) so that a process can switch engines between models.
 bool use_own_forward() {
-  static const bool own = [] {
-    const char *e = std::getenv("CS_ATTENTION_ENGINE");
-    return e != nullptr && std::string(e) == "tcgen05";
-  }();
-  return own;
+  const char *e = std::getenv("CS_ATTENTION_ENGINE");
+  return e != nullptr && std::string(e) == "tcgen05";
 }
 
 double resolve_scale(const optional<double> &scale, int64_t head_dim) {
@@ -284,8 +281,27 @@ Tensor ScaledDotProductAttention::backward_packed(const Scheduler &scheduler, co
            const at::Tensor &x = bw.qkv.impl()->tensor;
            const at::Tensor &o = bw.out.impl()->tensor;  // [B,H,T,D]
            const int64_t B = x.size(0), T = x.size(1), H = o.size(1), D = o.size(3);
+           const at::Tensor &go = grad_out.impl()->tensor;
+           if (bw.out.impl()->companion.defined() && x.is_cuda() && x.is_contiguous() && go.is_contiguous() &&
+               go.scalar_type() == at::kBFloat16 && fused_enabled()) {
+             // the forward ran on this library's kernel: its output buffer is [B,T,H,D] and the backward kernels
+             // read the packed qkv and write the packed gradient directly
+             const at::Tensor o_bthd = o.transpose(1, 2);
+             if (o_bthd.is_contiguous()) {
+               at::Tensor packed = at::empty({B, T, 3 * H * D}, x.options());
+               at::Tensor delta = at::empty({B, H, T}, x.options().dtype(at::kFloat));
+               const int code = kernels::attention_backward_packed(
+                   current_stream(), x.data_ptr(), o_bthd.data_ptr(), go.data_ptr(), bw.logsumexp.impl()->tensor.data_ptr<float>(),
+                   delta.data_ptr<float>(), packed.data_ptr(), B, T, H, D, static_cast<float>(resolve_scale(args.scale, D)));
+               if (code == 0) {
+                 dqkv.impl()->tensor = packed;
+                 return;
+               }
+               CS_ASSERT_TRUE(code == -1, "attention_backward_packed failed: ", cuda_error_string(code));
+             }
+           }
            const at::Tensor x5 = x.view({B, T, 3, H, D});
-           const at::Tensor do4 = grad_out.impl()->tensor.reshape({B, T, H, D});
+           const at::Tensor do4 = go.reshape({B, T, H, D});
            auto r = attention_backward_body(do4, x5.select(2, 0), x5.select(2, 1), x5.select(2, 2), args, bw);
            at::Tensor packed = at::empty({B, T, 3, H, D}, x.options());
            // r[i] are [B,T,H,D] tensors, either contiguous or views of [B,H,T,D] buffers (depends on

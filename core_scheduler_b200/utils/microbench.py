@@ -2,6 +2,8 @@
 
   python -m core_scheduler_b200.utils.microbench gemm        # tcgen05 GEMM vs torch.matmul (cuBLAS)
   python -m core_scheduler_b200.utils.microbench elementwise # LayerNorm / GELU / AdamW bandwidth
+  python -m core_scheduler_b200.utils.microbench attention    # tcgen05 attention forward vs cuDNN
+  python -m core_scheduler_b200.utils.microbench kernels_once # every non-GEMM kernel twice (profiler workload)
 
 Prints one line per case: achieved TFLOP/s or GB/s and the fraction of the measured peak
 (MEASURED_PEAKS.json at the repository root when present, else the fallback 1.59 PFLOP/s, 6.65 TB/s).
@@ -165,6 +167,99 @@ def gemm_one():
     print(f"gemm_one epilogue={epi}: {start.elapsed_time(stop) / 3 * 1e3:.1f} us per launch")
 
 
+def kernels_once():
+    """Every non-GEMM kernel of the training step, twice each on inputs larger than L2 (a few GB in
+    total): the workload for a profiler capture and a per-kernel bandwidth table (second launch timed)."""
+    _, gbs_peak, tag = peaks()
+    s = cs.DynamicScheduler(0, device="cuda")
+    main = torch.cuda.ExternalStream(s.raw_stream(0))
+    rows, d, V = 65536, 768, 50304
+    T = cs.from_torch
+
+    def run(name, fn, nbytes, stream=None):
+        stream = stream or main
+        fn()
+        s.synchronize()
+        flush_l2()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        fn()
+        b.record(stream)
+        s.synchronize()
+        torch.cuda.synchronize()
+        t = a.elapsed_time(b)
+        print(f"{name:34s} {t * 1e3:9.1f} us  {nbytes / t / 1e6:7.0f} GB/s ({nbytes / t / 1e6 / gbs_peak:.2f} of {tag} copy bandwidth)", flush=True)
+
+    x = torch.randn(rows, d, device="cuda").to(BF)
+    dy = torch.randn(rows, d, device="cuda").to(BF)
+    ln = C.layer_norm_init(s, [d])
+
+    def ln_fwd():
+        with cs.autocast(s, BF):
+            C.layer_norm_forward(s, ln, T(x))
+
+    run("layernorm fwd [65536,768]", ln_fwd, 2 * x.numel() * 2)
+    # backward of the pre-norm block: dx = LN'(dy) + residual gradient, dgamma/dbeta partials
+
+    def ln_fwd_bwd():  # backward consumes the state its forward saved, so the pair runs together
+        ln_fwd()
+        C.layer_norm_backward(s, ln, T(dy), T(dy))
+
+    run("layernorm fwd + bwd(+residual)", ln_fwd_bwd, 6 * x.numel() * 2)
+    g = C.gelu_init(s)
+    h = torch.randn(rows // 2, 4 * d, device="cuda").to(BF)
+    run("gelu fwd [32768,3072]", lambda: C.gelu_forward(s, g, T(h)), 2 * h.numel() * 2)
+
+    def gelu_fwd_bwd():
+        C.gelu_forward(s, g, T(h))
+        C.gelu_backward(s, g, T(h))
+
+    run("gelu fwd + bwd", gelu_fwd_bwd, 5 * h.numel() * 2)
+    run("add bf16", lambda: C.utils_add(s, T(h), T(h)), 3 * h.numel() * 2)
+    n = 32 << 20
+    w = T(torch.randn(n, device="cuda"))
+    C.working_copy(s, w, BF)
+    st = C.adamw_init(s, w)
+    gr = T(torch.randn(n, device="cuda"))
+    assist = torch.cuda.ExternalStream(s.raw_stream(1))
+    run("adamw fp32 master -> bf16 copy 32M", lambda: C.adamw_step(s, st, w, gr), n * (4 * 4 + 3 * 4 + 2), assist)
+    te, pe = C.embedding_init(s, V, d), C.embedding_init(s, 1024, d)
+    idx = torch.randint(0, 50257, (64, 1024), device="cuda")
+    dye = dy.view(64, 1024, d)
+
+    def emb_fwd():
+        with cs.autocast(s, BF):
+            C.embedding_forward_token_position(s, te, pe, T(idx))
+
+    run("embedding fwd (token+position)", emb_fwd, 2 * dye.numel() * 2)
+
+    def emb_fwd_bwd():
+        emb_fwd()
+        C.embedding_backward_token_position(s, te, pe, T(dye))
+
+    run("embedding fwd + bwd (token+position)", emb_fwd_bwd, 3 * dye.numel() * 2 + 2 * dye.numel() * 4)
+    norm_in = [T(torch.randn(n, device="cuda"))]
+    run("grad-norm + clip 32M fp32", lambda: C.utils_clip_grad_norm_(s, norm_in, 1.0), n * 4 * 3)
+    B, Tn, H, D = 16, 1024, 12, 64
+    qkv = torch.randn(B, Tn, 3 * H * D, device="cuda").to(BF)
+    run("attention fwd tcgen05 B16 H12 T1024", lambda: C.attention_forward_tcgen05(qkv, H, D ** -0.5), 4 * B * Tn * H * D * 2,
+        torch.cuda.current_stream())
+    lin = C.linear_init(s, d, V, bias=False)
+    ce = C.linear_cross_entropy_init(s, lin, valid_classes=50257)
+    xs = torch.randn(8192, d, device="cuda").to(BF)
+    tg = torch.randint(0, 50257, (8192,), device="cuda")
+
+    def ce_fwd_bwd():
+        with cs.autocast(s, BF):
+            C.linear_cross_entropy_forward(s, ce, T(xs), T(tg))
+        C.linear_cross_entropy_backward(s, ce)
+
+    run("classifier+cross-entropy fwd+bwd 8192", ce_fwd_bwd, 3 * 8192 * V * 2)
+    print("attention status", C.attention_status(), "gemm status", C.gemm_status())
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    {"gemm": bench_gemm, "elementwise": bench_elementwise, "gemm_one": gemm_one, "attention": bench_attention}[what]()
+    {"gemm": bench_gemm, "elementwise": bench_elementwise, "gemm_one": gemm_one, "attention": bench_attention,
+     "kernels_once": kernels_once}[what]()
