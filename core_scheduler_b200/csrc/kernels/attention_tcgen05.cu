@@ -263,36 +263,48 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
       fence_after();
       // pass 1: row maximum of the (masked) scores
       const bool diagonal = j == qb;
-      float m_blk = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(s_tmem + c * 32 + lane_addr, v);
-        tmem_wait_ld();
+      // Four independent partial maxima / sums keep the dependent chains short, and the TMEM load
+      // of the next 32-column chunk is in flight while the current one is processed.
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      auto max_chunk = [&](const uint32_t (&v)[32], int c) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const float x = __uint_as_float(v[i]);
-          if (!diagonal || (j * BKV + c * 32 + i) <= q_idx) m_blk = fmaxf(m_blk, x);
+          if (!diagonal || (j * BKV + c * 32 + i) <= q_idx) mx[i & 3] = fmaxf(mx[i & 3], x);
         }
-      }
+      };
+      uint32_t va[32], vb[32];
+      tmem_ld32(s_tmem + 0 * 32 + lane_addr, va);
+      tmem_wait_ld();
+      tmem_ld32(s_tmem + 1 * 32 + lane_addr, vb);
+      max_chunk(va, 0);
+      tmem_wait_ld();
+      tmem_ld32(s_tmem + 2 * 32 + lane_addr, va);
+      max_chunk(vb, 1);
+      tmem_wait_ld();
+      tmem_ld32(s_tmem + 3 * 32 + lane_addr, vb);
+      max_chunk(va, 2);
+      tmem_wait_ld();
+      tmem_ld32(s_tmem + 0 * 32 + lane_addr, va);  // first chunk of the second pass
+      max_chunk(vb, 3);
+      const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       const float m_new = fmaxf(m_run, m_blk);
       const float alpha = fast_exp2((m_run - m_new) * p.scale_log2e);  // first block: exp2(-inf) = 0
       const float m_scaled = m_new * p.scale_log2e;
       // pass 2: probabilities -> shared memory (bf16, swizzled) and their sum
-      if (!mbar_wait(bar(P_EMPTY), bph ^ 1u, abort_flag)) break;
-      float l_blk = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(s_tmem + c * 32 + lane_addr, v);
-        tmem_wait_ld();
+      if (!mbar_wait(bar(P_EMPTY), bph ^ 1u, abort_flag)) {
+        tmem_wait_ld();  // no load may be outstanding when the kernel unwinds
+        break;
+      }
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      auto exp_chunk = [&](const uint32_t (&v)[32], int c) {
         float e[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const float x = __uint_as_float(v[i]);
           const bool keep = !diagonal || (j * BKV + c * 32 + i) <= q_idx;
           e[i] = keep ? fast_exp2(fmaf(x, p.scale_log2e, -m_scaled)) : 0.f;
-          l_blk += e[i];
+          ls[i & 3] += e[i];
         }
         // 32 keys = 64 bytes = four 16-byte pieces of this row in half (c >> 1)
         const uint32_t row_addr = p_smem + (c >> 1) * 16384 + r * 128;
@@ -305,7 +317,18 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
                        "r"(pack2(e[g * 8 + 6], e[g * 8 + 7]))
                        : "memory");
         }
-      }
+      };
+      tmem_wait_ld();
+      tmem_ld32(s_tmem + 1 * 32 + lane_addr, vb);
+      exp_chunk(va, 0);
+      tmem_wait_ld();
+      tmem_ld32(s_tmem + 2 * 32 + lane_addr, va);
+      exp_chunk(vb, 1);
+      tmem_wait_ld();
+      tmem_ld32(s_tmem + 3 * 32 + lane_addr, vb);
+      exp_chunk(va, 2);
+      tmem_wait_ld();
+      exp_chunk(vb, 3);
       fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
@@ -313,7 +336,7 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
         mbar_arrive(bar(S_EMPTY));
         mbar_arrive(bar(P_FULL));
       }
-      l_run = l_run * alpha + l_blk;
+      l_run = l_run * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
       m_run = m_new;
       // fold the partial output of this block into the running one
       if (!mbar_wait(bar(O_FULL), bph, abort_flag)) break;

@@ -131,10 +131,11 @@ def bench_elementwise():
 
 
 def bench_attention():
-    """tcgen05 causal attention forward vs the cuDNN engine, GPT-2 124M shape (B16 H12 T1024 D64)."""
+    """tcgen05 causal attention forward and backward vs the cuDNN engine, GPT-2 124M shape (B16 H12 T1024 D64)."""
     tflops_peak, _, tag = peaks()
     B, T, H, D = 16, 1024, 12, 64
     qkv = torch.randn(B, T, 3 * H * D, device="cuda").to(BF)
+    dout = torch.randn(B, T, H * D, device="cuda").to(BF)
     scale = D ** -0.5
     ours = lambda: C.attention_forward_tcgen05(qkv, H, scale)
     q, k, v = (x.transpose(1, 2) for x in qkv.view(B, T, 3, H, D).unbind(2))
@@ -144,6 +145,23 @@ def bench_attention():
     print(f"attention fwd causal B={B} H={H} T={T} D={D}: ours {t_ours * 1e3:.1f} us {flops / t_ours / 1e9:.0f} TFLOP/s "
           f"({flops / t_ours / 1e9 / tflops_peak:.2f} of {tag})   cuDNN {t_lib * 1e3:.1f} us {flops / t_lib / 1e9:.0f} TFLOP/s   "
           f"status {C.attention_status()}")
+    _, out, lse = ours()
+    ours_bwd = lambda: C.attention_backward_tcgen05(qkv, out, dout, lse, H, scale)
+    qa, ka, va = (x.detach().requires_grad_(True) for x in (q, k, v))
+    o_lib = torch.nn.functional.scaled_dot_product_attention(qa, ka, va, is_causal=True, scale=scale)
+    go = dout.view(B, T, H, D).transpose(1, 2)
+
+    def lib_bwd():
+        torch.autograd.grad(o_lib, (qa, ka, va), go, retain_graph=True)
+
+    with torch.nn.attention.sdpa_kernel(torch.nn.attention.SDPBackend.CUDNN_ATTENTION):
+        o_lib = torch.nn.functional.scaled_dot_product_attention(qa, ka, va, is_causal=True, scale=scale)
+        t_lib_b = time_ms(lib_bwd)
+    t_ours_b = time_ms(ours_bwd)
+    fb = 2.5 * flops  # five matrix products in the minimal backward
+    print(f"attention bwd causal (3 launches: delta, dK/dV, dQ): ours {t_ours_b * 1e3:.1f} us {fb / t_ours_b / 1e9:.0f} TFLOP/s "
+          f"(useful; the kernels run 7 products) ({fb / t_ours_b / 1e9 / tflops_peak:.2f} of {tag})   cuDNN {t_lib_b * 1e3:.1f} us "
+          f"{fb / t_lib_b / 1e9:.0f} TFLOP/s   status {C.attention_status()}")
 
 
 def gemm_one():
