@@ -20,7 +20,21 @@ if not _build.is_built():
 
 import pyarrow as _pyarrow  # noqa: F401,E402  (provides libarrow/libparquet for checkpoints and datasets)
 
+if _os.environ.get("CS_BOUNDS_CHECK") == "1":
+    # Diagnostic run: load the library whose kernels check every derived index (same soname, so the
+    # extension binds to it instead of lib/libcs_b200.so). Never falls back silently.
+    import ctypes as _ctypes
+
+    if not _build.is_checked_built():
+        if _os.environ.get("CS_NO_AUTOBUILD") == "1":
+            raise ImportError("CS_BOUNDS_CHECK=1 needs lib_checked/libcs_b200.so; run `python -m core_scheduler_b200.build checked`")
+        _build.build(checked=True)
+    _ctypes.CDLL(str(_build.CHECKED_LIBDIR / "libcs_b200.so"), mode=_ctypes.RTLD_GLOBAL)
+
 from . import _C  # noqa: E402
+
+if _os.environ.get("CS_BOUNDS_CHECK") == "1" and not _C.bounds_check_enabled():
+    raise ImportError("CS_BOUNDS_CHECK=1 but the extension bound to the unchecked library")
 from ._C import (  # noqa: E402,F401
     AdamW,
     AllReduceBucket,

@@ -21,6 +21,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 BUILD = HERE / "build"
 LIBDIR = HERE / "lib"
+CHECKED_LIBDIR = HERE / "lib_checked"
 
 CPP_SOURCES = [
     "src/core.cpp",
@@ -115,10 +116,14 @@ def generate_ninja() -> Path:
         "  command = $nvcc $nvccflags -MD -MF $out.d -c $in -o $out",
         "  depfile = $out.d",
         "  deps = gcc",
+        "rule nvcc_checked",
+        "  command = $nvcc $nvccflags -DCS_BOUNDS_CHECK -MD -MF $out.d -c $in -o $out",
+        "  depfile = $out.d",
+        "  deps = gcc",
         "rule link",
         "  command = $cxx -shared $in -o $out $ldflags",
     ]
-    objs = []
+    objs, checked_objs = [], []
     for src in CPP_SOURCES + extra_cpp:
         obj = BUILD / (src.replace("/", "_") + ".o")
         extra = ""
@@ -128,20 +133,29 @@ def generate_ninja() -> Path:
             extra = f"-I{p['nccl_inc']}"
         lines += [f"build {obj}: cxx {CSRC / src}", f"  extra = {extra}"]
         objs.append(obj)
+        checked_objs.append(obj)
     for src in CUDA_SOURCES + extra_cu:
         obj = BUILD / (src.replace("/", "_") + ".o")
         lines += [f"build {obj}: nvcc {CSRC / src}"]
         objs.append(obj)
+        # diagnostic variant of the same kernels: checked index accessors (kernels/bounds_check.h)
+        cobj = BUILD / (src.replace("/", "_") + ".checked.o")
+        lines += [f"build {cobj}: nvcc_checked {CSRC / src}"]
+        checked_objs.append(cobj)
     cuda_lib = p["cuda_home"] / "lib64"
     lib_ld = [
         f"-L{p['torch_lib']}", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",
         f"-L{p['arrow_lib']}", "-l:libarrow.so.2400", "-l:libparquet.so.2400",
         f"-L{cuda_lib}", "-lcudart", "-ldl", "-lpthread",
         f"-Wl,-rpath,{p['torch_lib']}", f"-Wl,-rpath,{p['arrow_lib']}", f"-Wl,-rpath,{cuda_lib}",
-        "-Wl,--no-as-needed",
+        "-Wl,--no-as-needed", "-Wl,-soname,libcs_b200.so",
     ]
     libcs = LIBDIR / "libcs_b200.so"
     lines += [f"build {libcs}: link {' '.join(map(str, objs))}", f"  ldflags = {' '.join(lib_ld)}"]
+    CHECKED_LIBDIR.mkdir(exist_ok=True)
+    libcs_checked = CHECKED_LIBDIR / "libcs_b200.so"
+    lines += [f"build {libcs_checked}: link {' '.join(map(str, checked_objs))}", f"  ldflags = {' '.join(lib_ld)}",
+              f"build checked: phony {libcs_checked}"]
     bobjs = []
     for src in BINDING_SOURCES:
         obj = BUILD / (src.replace("/", "_") + ".o")
@@ -159,9 +173,13 @@ def generate_ninja() -> Path:
     return ninja_file
 
 
-def build(verbose: bool = False) -> None:
+def build(verbose: bool = False, checked: bool = False) -> None:
+    """Builds the library and the extension; with `checked` also lib_checked/libcs_b200.so, the same
+    library with -DCS_BOUNDS_CHECK kernels (loaded instead of the normal one when CS_BOUNDS_CHECK=1)."""
     ninja_file = generate_ninja()
     cmd = [sys.executable, "-m", "ninja", "-f", str(ninja_file)]
+    if checked:
+        cmd += [str(HERE / f"_C{ext_suffix()}"), "checked"]
     if verbose:
         cmd.append("-v")
     jobs = os.environ.get("CS_BUILD_JOBS")
@@ -191,6 +209,10 @@ def build_examples() -> list[str]:
     return built
 
 
+def is_checked_built() -> bool:
+    return (CHECKED_LIBDIR / "libcs_b200.so").exists()
+
+
 def is_built() -> bool:
     return (HERE / f"_C{ext_suffix()}").exists() and (LIBDIR / "libcs_b200.so").exists()
 
@@ -199,4 +221,4 @@ if __name__ == "__main__":
     if "examples" in sys.argv:
         print("\n".join(build_examples()))
     else:
-        build(verbose="-v" in sys.argv)
+        build(verbose="-v" in sys.argv, checked="checked" in sys.argv)

@@ -162,4 +162,19 @@ struct DeviceStatus {
   int block;
   int detail;
 };
+
+// First out-of-range index seen by a kernel of the diagnostic build (-DCS_BOUNDS_CHECK); see
+// bounds_check.h. `code` 0 = nothing recorded. In the normal build the report is always empty.
+struct BoundsReport {
+  int code;
+  int kernel_id;
+  int block;
+  int thread;
+  long long index;
+  long long limit;
+};
+bool bounds_check_enabled();
+// Copies the report (merged over the kernel translation units; synchronises the device) and
+// optionally clears it.
+int bounds_report(BoundsReport *out, bool reset);
 }  // namespace cs::kernels

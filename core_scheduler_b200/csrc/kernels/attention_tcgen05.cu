@@ -24,6 +24,7 @@
 #include <unordered_map>
 
 #include "api.h"
+#include "bounds_check.h"
 
 namespace cs::kernels {
 namespace {
@@ -353,7 +354,9 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(O_EMPTY));
     }
-    if (!*abort_flag && q_idx < p.T) {
+    if (!*abort_flag && q_idx < p.T &&
+        CS_IN_BOUNDS(kKidAttention, (static_cast<long long>(row_base + q_idx) * p.H + h) * HD + HD - 1,
+                     static_cast<long long>(p.B) * p.T * p.H * HD)) {
       const float inv = 1.f / l_run;
       __nv_bfloat16 *dst = p.out + (static_cast<long long>(row_base + q_idx) * p.H + h) * HD;
 #pragma unroll
@@ -648,6 +651,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
     if (mbar_wait(bar(ACC_FULL), 0, abort_flag) && !*abort_flag) {
       fence_after();
       const long long row = static_cast<long long>(row_base + r_idx) * 3 * p.H;
+      const bool row_in_range =
+          CS_IN_BOUNDS(kKidAttention, (row + 2LL * p.H + h) * HD + HD - 1, static_cast<long long>(p.B) * p.T * 3 * p.H * HD);
       auto store = [&](uint32_t tmem, int part) {
         __nv_bfloat16 *dst = p.dqkv + (row + static_cast<long long>(part) * p.H + h) * HD;
 #pragma unroll
@@ -666,11 +671,13 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
           }
         }
       };
-      if (kDKV) {
-        store(acc1_tmem, 2);  // dV
-        store(acc2_tmem, 1);  // dK
-      } else {
-        store(acc2_tmem, 0);  // dQ
+      if (row_in_range) {
+        if (kDKV) {
+          store(acc1_tmem, 2);  // dV
+          store(acc2_tmem, 1);  // dK
+        } else {
+          store(acc2_tmem, 0);  // dQ
+        }
       }
     }
   }
@@ -808,4 +815,5 @@ int attention_backward_packed(stream_t stream, const void *qkv, const void *out,
   attention_bwd_kernel<false><<<grid, THREADS, BWD_SMEM_BYTES, s>>>(qkv_r, qkv_c, do_r, do_c, p);
   return finish_launch(3);
 }
+CS_DEFINE_BOUNDS_GETTER(bounds_report_attention)
 }  // namespace cs::kernels

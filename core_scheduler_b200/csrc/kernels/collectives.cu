@@ -13,6 +13,7 @@
 #include <atomic>
 
 #include "collectives.h"
+#include "bounds_check.h"
 
 namespace cs::kernels {
 namespace {
@@ -26,6 +27,9 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+
+// Diagnostic build: a peer offset must stay inside the arena (arena_bytes 0 = size unknown).
+#define CS_PEER_OK(t, byte_offset) ((t).arena_bytes == 0 || CS_IN_BOUNDS(kKidCollective, (byte_offset) + 15, (t).arena_bytes))
 
 __global__ void barrier_kernel(PeerTable t, int slot_base, uint32_t epoch, long long budget, DeviceStatus *status) {
   const int p = threadIdx.x;
@@ -115,7 +119,7 @@ __global__ void __launch_bounds__(256) all_reduce_twoshot_kernel(PeerTable t, in
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int64_t i = i0 + u * stride;
-      if (i < end) {
+      if (i < end && CS_PEER_OK(t, offset + i * 16)) {
 #pragma unroll
         for (int p = 0; p < kMaxPeers; ++p)
           if (p < t.size) v[u][p] = ld_v4(t.base[(t.rank + p) % t.size] + offset + i * 16);  // all loads in flight first
@@ -124,7 +128,7 @@ __global__ void __launch_bounds__(256) all_reduce_twoshot_kernel(PeerTable t, in
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int64_t i = i0 + u * stride;
-      if (i < end) {
+      if (i < end && CS_PEER_OK(t, offset + i * 16)) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         int n;
 #pragma unroll
@@ -147,7 +151,7 @@ __global__ void __launch_bounds__(256) pull_reduce_kernel(PeerTable t, int64_t s
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int64_t i = i0 + u * stride;
-      if (i < vecs) {
+      if (i < vecs && CS_PEER_OK(t, src_offset + i * 16)) {
 #pragma unroll
         for (int p = 0; p < kMaxPeers; ++p)
           if (p < t.size) v[u][p] = ld_v4(t.base[(t.rank + p) % t.size] + src_offset + i * 16);
@@ -156,7 +160,7 @@ __global__ void __launch_bounds__(256) pull_reduce_kernel(PeerTable t, int64_t s
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int64_t i = i0 + u * stride;
-      if (i < vecs) {
+      if (i < vecs && CS_PEER_OK(t, src_offset + i * 16)) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         int n;
 #pragma unroll
@@ -184,6 +188,7 @@ __global__ void __launch_bounds__(512) pull_copy_kernel(PeerTable t, PullCopyArg
       const int64_t i = i0 + u * stride;
       if (i < total) {
         const int64_t r = i / vec_per_row, c = i - r * vec_per_row;
+        if (!CS_PEER_OK(t, a.src_offset[p] + r * a.src_stride + c * 16)) continue;
         v[u] = ld_v4(src + r * a.src_stride + c * 16);
       }
     }
@@ -319,4 +324,5 @@ int symm_reduce_scatter_adamw_all_gather(stream_t stream, const PeerTable &t, co
   rs_adamw_ag_kernel<<<comm_grid(a.shard_count / 4, 512) * 2, 512, 0, static_cast<cudaStream_t>(stream)>>>(t, a);
   return finish_launch(1);
 }
+CS_DEFINE_BOUNDS_GETTER(bounds_report_collectives)
 }  // namespace cs::kernels

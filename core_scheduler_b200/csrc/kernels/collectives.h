@@ -15,6 +15,7 @@ struct PeerTable {
   uint32_t *flags[kMaxPeers];  // signal pad of every rank
   int rank;
   int size;
+  long long arena_bytes;       // size of every arena (0 = unknown); limit of the diagnostic build's offset checks
 };
 
 // Wait budget of every peer-flag wait, in clock64() cycles (default ~2 s). Tests shrink it to

@@ -13,6 +13,7 @@
 #include <mutex>
 
 #include "api.h"
+#include "bounds_check.h"
 
 namespace cs::kernels {
 namespace {
@@ -23,6 +24,29 @@ int64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
 int finish_launch(int n) {
   count_launch(n);
   return static_cast<int>(cudaGetLastError());
+}
+CS_DEFINE_BOUNDS_GETTER(bounds_report_elementwise)
+bool bounds_check_enabled() {
+#ifdef CS_BOUNDS_CHECK
+  return true;
+#else
+  return false;
+#endif
+}
+int bounds_report(BoundsReport *out, bool reset) {
+  *out = BoundsReport{};
+  if (!bounds_check_enabled()) return 0;
+  int rc = static_cast<int>(cudaDeviceSynchronize());
+  if (rc != 0) return rc;
+  using Getter = int (*)(BoundsReport *, bool);
+  const Getter getters[] = {bounds_report_elementwise, bounds_report_collectives, bounds_report_gemm, bounds_report_attention};
+  for (Getter g : getters) {
+    BoundsReport r{};
+    rc = g(&r, reset);
+    if (rc != 0) return rc;
+    if (r.code != 0 && out->code == 0) *out = r;
+  }
+  return 0;
 }
 namespace {
 constexpr int kSmCount = 148;
@@ -103,6 +127,7 @@ __global__ void __launch_bounds__(256) adamw_kernel(P *__restrict__ w, const G *
     P wv[VEC], mv[VEC], vv[VEC], xv[VEC];
     G gv[VEC];
     const bool full = base + VEC <= n;
+    if (!CS_IN_BOUNDS(kKidAdamW, base, n)) continue;
     if (full) {
       // 128-bit (fp32 x4) or 64-bit (16-bit x4) vector accesses
       using PV = typename std::conditional<sizeof(P) == 4, float4, float2>::type;
@@ -204,6 +229,7 @@ namespace {
 __global__ void __launch_bounds__(256) gelu_fwd_kernel(const Bf16x8 *__restrict__ x, Bf16x8 *__restrict__ y, int64_t n8) {
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    if (!CS_IN_BOUNDS(kKidElementwise, i, n8)) continue;
     float f[8];
     unpack(x[i], f);
 #pragma unroll
@@ -259,13 +285,13 @@ __global__ void __launch_bounds__(256) transpose_kernel(const T *__restrict__ sr
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const int64_t r = r0 + ty + 8 * k, c = c0 + tx;
-    if (r < rows && c < cols) tile[ty + 8 * k][tx] = to_f<T>(src[r * cols + c]);
+    if (r < rows && c < cols && CS_IN_BOUNDS(kKidTranspose, r * cols + c, rows * cols)) tile[ty + 8 * k][tx] = to_f<T>(src[r * cols + c]);
   }
   __syncthreads();
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const int64_t c = c0 + ty + 8 * k, r = r0 + tx;
-    if (r < rows && c < cols) dst[c * rows + r] = __float2bfloat16_rn(tile[tx][ty + 8 * k]);
+    if (r < rows && c < cols && CS_IN_BOUNDS(kKidTranspose, c * rows + r, rows * cols)) dst[c * rows + r] = __float2bfloat16_rn(tile[tx][ty + 8 * k]);
   }
 }
 }  // namespace
@@ -361,7 +387,9 @@ __global__ void __launch_bounds__(256) pack_qkv_kernel(const Bf16x8 *__restrict_
     const int64_t t = r % T;
     const int64_t b = r / T;
     const Bf16x8 *src = which == 0 ? q : (which == 1 ? k : v);
-    out[i] = src_bthd ? src[((b * T + t) * H + h) * d8 + c] : src[((b * H + h) * T + t) * d8 + c];
+    const int64_t from = src_bthd ? ((b * T + t) * H + h) * d8 + c : ((b * H + h) * T + t) * d8 + c;
+    if (!CS_IN_BOUNDS(kKidPackQkv, from, B * H * T * d8)) continue;
+    out[i] = src[from];
   }
 }
 }  // namespace
@@ -400,7 +428,7 @@ __global__ void __launch_bounds__(kLnWarps * 32) ln_fwd_kernel(const __nv_bfloat
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
       const int chunk = lane + 32 * c;
-      if (chunk < nchunks) {
+      if (chunk < nchunks && CS_IN_BOUNDS(kKidLayerNormFwd, row * d + chunk * 8 + 7, rows * d)) {
         unpack(*reinterpret_cast<const Bf16x8 *>(xr + chunk * 8), v[c]);
 #pragma unroll
         for (int k = 0; k < 8; ++k) sum += v[c][k];
@@ -437,7 +465,7 @@ __global__ void __launch_bounds__(kLnWarps * 32) ln_fwd_kernel(const __nv_bfloat
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) o[k] = (v[c][k] - mu) * rs * g[k] + b[k];
-        *reinterpret_cast<Bf16x8 *>(y + row * d + chunk * 8) = pack(o);
+        if (CS_IN_BOUNDS(kKidLayerNormFwd, row * d + chunk * 8 + 7, rows * d)) *reinterpret_cast<Bf16x8 *>(y + row * d + chunk * 8) = pack(o);
       }
     }
   }
@@ -458,11 +486,11 @@ struct LnRowRegs {
 template <int CHUNKS>
 __device__ __forceinline__ void ln_load_row(LnRowRegs<CHUNKS> &r, const __nv_bfloat16 *x, const __nv_bfloat16 *dy,
                                             const __nv_bfloat16 *dres, const float *mean, const float *rstd, int64_t row,
-                                            int d, int nchunks, int lane) {
+                                            int64_t rows, int d, int nchunks, int lane) {
 #pragma unroll
   for (int c = 0; c < CHUNKS; ++c) {
     const int chunk = lane + 32 * c;
-    if (chunk < nchunks) {
+    if (chunk < nchunks && CS_IN_BOUNDS(kKidLayerNormBwd, row * d + chunk * 8 + 7, rows * d)) {
       r.x[c] = *reinterpret_cast<const Bf16x8 *>(x + row * d + chunk * 8);
       r.dy[c] = *reinterpret_cast<const Bf16x8 *>(dy + row * d + chunk * 8);
       if (dres) r.res[c] = *reinterpret_cast<const Bf16x8 *>(dres + row * d + chunk * 8);
@@ -501,10 +529,10 @@ __global__ void __launch_bounds__(kLnWarps * 32) ln_bwd_kernel(
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kLnWarps;
   int64_t row = static_cast<int64_t>(blockIdx.x) * kLnWarps + warp;
   LnRowRegs<CHUNKS> cur, nxt;
-  if (row < rows) ln_load_row<CHUNKS>(cur, x, dy, dres, mean, rstd, row, d, nchunks, lane);
+  if (row < rows) ln_load_row<CHUNKS>(cur, x, dy, dres, mean, rstd, row, rows, d, nchunks, lane);
   while (row < rows) {
     const int64_t next = row + stride;
-    if (next < rows) ln_load_row<CHUNKS>(nxt, x, dy, dres, mean, rstd, next, d, nchunks, lane);
+    if (next < rows) ln_load_row<CHUNKS>(nxt, x, dy, dres, mean, rstd, next, rows, d, nchunks, lane);
     const float mu = cur.mu, rs = cur.rs;
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
@@ -671,6 +699,7 @@ __global__ void __launch_bounds__(256) embedding_fwd_kernel(const int64_t *__res
     const int64_t row = i / chunks;
     const int chunk = static_cast<int>(i - row * chunks);
     int64_t token = idx[row];
+    (void)CS_IN_BOUNDS(kKidEmbeddingFwd, token, vocab);  // diagnostic build: remember the first bad id
     token = token < 0 ? 0 : (token >= vocab ? vocab - 1 : token);  // clamp instead of faulting
     float a[8];
     load8(wte, token * d + chunk * 8, tdt, a);
@@ -695,6 +724,7 @@ __global__ void __launch_bounds__(256) embedding_bwd_wte_kernel(const int64_t *_
     const int64_t row = i / chunks;
     const int chunk = static_cast<int>(i - row * chunks);
     const int64_t token = idx[row];
+    if (token != padding_idx) (void)CS_IN_BOUNDS(kKidEmbeddingBwd, token, vocab);
     if (token < 0 || token >= vocab || token == padding_idx) continue;
     float g[8];
     unpack(*reinterpret_cast<const Bf16x8 *>(dy + row * d + chunk * 8), g);
@@ -777,7 +807,8 @@ __global__ void __launch_bounds__(256) ce_finalize_kernel(const float *__restric
     if (lane == 0) {
       lse[row] = l;
       const int64_t tg = target[row];
-      if (tg != ignore_index && tg >= 0) {
+      if (tg != ignore_index && tg >= 0) (void)CS_IN_BOUNDS(kKidCrossEntropy, tg, ld);
+      if (tg != ignore_index && tg >= 0 && tg < ld) {  // a label beyond the row is skipped, never dereferenced
         row_loss = l - __bfloat162float(logits[row * ld + tg]);
         row_valid = 1.f;
       }
@@ -807,31 +838,36 @@ __global__ void __launch_bounds__(256) ce_backward_kernel(__nv_bfloat16 *__restr
                                                           const float *__restrict__ lse, const int64_t *__restrict__ target,
                                                           const float *__restrict__ count, float grad_scale, int64_t rows,
                                                           int64_t n, int64_t n_valid, int64_t ignore_index) {
-  const int64_t chunks = n / 8;
-  const int64_t total = rows * chunks;
+  // One CTA walks whole rows (no per-element division); target and lse are read once per row.
+  const int chunks = static_cast<int>(n / 8);
   const float inv = grad_scale / fmaxf(count[0], 1.f);
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t row = i / chunks;
-    const int64_t col = (i - row * chunks) * 8;
+  const float log2e = 1.4426950408889634f;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const int64_t tg = target[row];
-    Bf16x8 *p = reinterpret_cast<Bf16x8 *>(logits + row * ld + col);
-    float f[8];
-    if (tg == ignore_index || tg < 0) {
+    const bool ignored = tg == ignore_index || tg < 0;
+    if (!ignored) (void)CS_IN_BOUNDS(kKidCrossEntropy, tg, n_valid);
+    const float l2 = ignored ? 0.f : lse[row] * log2e;
+    __nv_bfloat16 *row_ptr = logits + row * ld;
+    for (int c8 = threadIdx.x; c8 < chunks; c8 += blockDim.x) {
+      const int64_t col = static_cast<int64_t>(c8) * 8;
+      if (!CS_IN_BOUNDS(kKidCrossEntropy, row * ld + col + 7, rows * ld)) continue;
+      Bf16x8 *p = reinterpret_cast<Bf16x8 *>(row_ptr + col);
+      float f[8];
+      if (ignored) {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) f[k] = 0.f;
-    } else {
-      unpack(*p, f);
-      const float l = lse[row];
+        for (int k = 0; k < 8; ++k) f[k] = 0.f;
+      } else {
+        unpack(*p, f);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const int64_t c = col + k;
-        float v = c < n_valid ? __expf(f[k] - l) : 0.f;
-        if (c == tg) v -= 1.f;
-        f[k] = v * inv;
+        for (int k = 0; k < 8; ++k) {
+          const int64_t c = col + k;
+          float v = c < n_valid ? exp2f(fmaf(f[k], log2e, -l2)) : 0.f;
+          if (c == tg) v -= 1.f;
+          f[k] = v * inv;
+        }
       }
+      *p = pack(f);
     }
-    *p = pack(f);
   }
 }
 }  // namespace
@@ -854,7 +890,8 @@ int cross_entropy_backward_inplace(stream_t stream, void *logits, int64_t ld, co
                                    const float *count, float grad_scale, int64_t rows, int64_t n, int64_t n_valid,
                                    int64_t ignore_index) {
   if (n % 8 != 0 || ld % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
-  ce_backward_kernel<<<grid_for(rows * (n / 8), 256, 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  const int64_t cap = static_cast<int64_t>(kSmCount) * 8;
+  ce_backward_kernel<<<static_cast<unsigned>(rows < cap ? rows : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16 *>(logits), ld, lse, target, count, grad_scale, rows, n, n_valid, ignore_index);
   return finish_launch();
 }

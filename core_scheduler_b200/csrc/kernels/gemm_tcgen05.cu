@@ -33,6 +33,7 @@
 #include <unordered_map>
 
 #include "api.h"
+#include "bounds_check.h"
 
 namespace cs::kernels {
 namespace {
@@ -230,6 +231,7 @@ __device__ __forceinline__ void epilogue_tile(const KParams &p, int m0, int n0, 
     tcgen05_wait_ld();
     const long long gcol = n0 + col0;
     if (!row_ok || gcol >= p.n) continue;
+    if (!CS_IN_BOUNDS(kKidGemmEpilogue, row * p.ldd + gcol, static_cast<long long>(p.m) * p.ldd)) continue;
     float f[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
@@ -1267,4 +1269,5 @@ int gemm_bf16(stream_t stream, const GemmArgs &a) {
   gemm_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(map_a, map_b, p);
   return finish_launch(1);
 }
+CS_DEFINE_BOUNDS_GETTER(bounds_report_gemm)
 }  // namespace cs::kernels

@@ -138,6 +138,13 @@ PYBIND11_MODULE(_C, m) {
     CS_ASSERT_TRUE(rc == 0, "attention_backward_packed returned ", rc);
     return py::make_tuple(dqkv, delta);
   });
+  m.def("bounds_check_enabled", &cs::kernels::bounds_check_enabled);
+  m.def("bounds_report", [](bool reset) {
+    cs::kernels::BoundsReport r{};
+    const int rc = cs::kernels::bounds_report(&r, reset);
+    CS_ASSERT_TRUE(rc == 0, "bounds_report failed: ", rc);
+    return py::make_tuple(r.code, r.kernel_id, r.block, r.thread, static_cast<int64_t>(r.index), static_cast<int64_t>(r.limit));
+  }, py::arg("reset") = true, "(code, kernel id, block, thread, index, limit) of the first out-of-range index; code 0 = none");
   m.def("attention_status", [] {
     cs::kernels::DeviceStatus st{};
     cs::kernels::attention_status(&st);

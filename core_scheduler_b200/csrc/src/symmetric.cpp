@@ -30,6 +30,7 @@ kernels::PeerTable table_of(const SymmetricContext &ctx) {
   }
   t.rank = ctx.rank;
   t.size = ctx.size;
+  t.arena_bytes = ctx.arena_bytes;
   return t;
 }
 
