@@ -14,6 +14,7 @@
 
 #include "api.h"
 #include "bounds_check.h"
+#include "gelu_math.h"
 
 namespace cs::kernels {
 namespace {
@@ -88,13 +89,6 @@ __device__ __forceinline__ void load8(const void *base, int64_t elem, int dtype,
     f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
     f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
   }
-}
-
-__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
-__device__ __forceinline__ float gelu_grad_f(float x) {
-  const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752440f));
-  const float pdf = 0.39894228040143267794f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
 }
 
 int grid_for(int64_t work_items, int threads, int max_ctas_per_sm = 8) {
@@ -411,25 +405,37 @@ constexpr int kLnWarps = 4;       // rows per CTA iteration
 constexpr int kLnMaxChunks = 8;   // register-resident path: d <= 8 * 256 = 2048
 constexpr int kLnBwdCtas = kSmCount * 3;
 
-// One warp per row. Lane l owns the 8-element chunks l, l+32, ... of the row.
+// One warp per row, grid-stride over rows. Lane l owns the 8-element chunks l, l+32, ... of the
+// row. The next row (still packed, in its 128-bit load registers) is fetched before the current
+// one is reduced, so that loads stay in flight during the shuffles; the grid is one resident wave.
+constexpr int ln_fwd_ctas_per_sm(int chunks) { return chunks <= 3 ? 6 : (chunks <= 5 ? 4 : 1); }
 template <int CHUNKS>
-__global__ void __launch_bounds__(kLnWarps * 32) ln_fwd_kernel(const __nv_bfloat16 *__restrict__ x,
-                                                               const void *__restrict__ gamma,
-                                                               const void *__restrict__ beta, int pdt,
-                                                               __nv_bfloat16 *__restrict__ y, float *__restrict__ mean,
-                                                               float *__restrict__ rstd, int64_t rows, int d, float eps) {
+__global__ void __launch_bounds__(kLnWarps * 32, ln_fwd_ctas_per_sm(CHUNKS))
+ln_fwd_kernel(const __nv_bfloat16 *__restrict__ x, const void *__restrict__ gamma, const void *__restrict__ beta, int pdt,
+              __nv_bfloat16 *__restrict__ y, float *__restrict__ mean, float *__restrict__ rstd, int64_t rows, int d, float eps) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nchunks = d / 8;
-  for (int64_t row = static_cast<int64_t>(blockIdx.x) * kLnWarps + warp; row < rows;
-       row += static_cast<int64_t>(gridDim.x) * kLnWarps) {
-    const __nv_bfloat16 *xr = x + row * d;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kLnWarps;
+  int64_t row = static_cast<int64_t>(blockIdx.x) * kLnWarps + warp;
+  Bf16x8 cur[CHUNKS], nxt[CHUNKS];
+  auto load_row = [&](Bf16x8(&dst)[CHUNKS], int64_t r) {
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int chunk = lane + 32 * c;
+      if (chunk < nchunks && CS_IN_BOUNDS(kKidLayerNormFwd, r * d + chunk * 8 + 7, rows * d))
+        dst[c] = *reinterpret_cast<const Bf16x8 *>(x + r * d + chunk * 8);
+    }
+  };
+  if (row < rows) load_row(cur, row);
+  while (row < rows) {
+    const int64_t next = row + stride;
+    if (next < rows) load_row(nxt, next);
     float v[CHUNKS][8];
     float sum = 0.f;
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
-      const int chunk = lane + 32 * c;
-      if (chunk < nchunks && CS_IN_BOUNDS(kKidLayerNormFwd, row * d + chunk * 8 + 7, rows * d)) {
-        unpack(*reinterpret_cast<const Bf16x8 *>(xr + chunk * 8), v[c]);
+      if (lane + 32 * c < nchunks) {
+        unpack(cur[c], v[c]);
 #pragma unroll
         for (int k = 0; k < 8; ++k) sum += v[c][k];
       }
@@ -468,6 +474,9 @@ __global__ void __launch_bounds__(kLnWarps * 32) ln_fwd_kernel(const __nv_bfloat
         if (CS_IN_BOUNDS(kKidLayerNormFwd, row * d + chunk * 8 + 7, rows * d)) *reinterpret_cast<Bf16x8 *>(y + row * d + chunk * 8) = pack(o);
       }
     }
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) cur[c] = nxt[c];
+    row = next;
   }
 }
 
@@ -627,7 +636,8 @@ template <int CHUNKS>
 int launch_ln_fwd(cudaStream_t s, const void *x, const void *gamma, const void *beta, int pdt, void *y, float *mean,
                   float *rstd, int64_t rows, int d, float eps) {
   const int64_t blocks = (rows + kLnWarps - 1) / kLnWarps;
-  const int grid = static_cast<int>(blocks > kSmCount * 16 ? kSmCount * 16 : blocks);
+  const int64_t wave = static_cast<int64_t>(kSmCount) * (CHUNKS <= 8 ? ln_fwd_ctas_per_sm(CHUNKS) * (CHUNKS <= 5 ? 1 : 2) : 2);
+  const int grid = static_cast<int>(blocks > wave ? wave : blocks);
   ln_fwd_kernel<CHUNKS><<<grid, kLnWarps * 32, 0, s>>>(static_cast<const __nv_bfloat16 *>(x), gamma, beta, pdt,
                                                        static_cast<__nv_bfloat16 *>(y), mean, rstd, rows, d, eps);
   return finish_launch();
@@ -898,15 +908,29 @@ int cross_entropy_backward_inplace(stream_t stream, void *logits, int64_t ld, co
 
 // ----------------------------------------------------------------------- gradient norm ----
 namespace {
+// 16-byte loads where the pointer allows it; the scalar loop covers the tail (or everything).
 template <typename T>
 __global__ void __launch_bounds__(256) sumsq_kernel(const T *__restrict__ x, int64_t n, float *__restrict__ out) {
-  float acc = 0.f;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const float v = to_f<T>(x[i]);
-    acc += v * v;
+  constexpr int V = 16 / sizeof(T);
+  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t nv = (reinterpret_cast<uintptr_t>(x) & 15) == 0 ? n / V : 0;
+  float acc0 = 0.f, acc1 = 0.f;
+  for (int64_t i = gid; i < nv; i += stride) {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(x + i * V);
+    const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+    for (int k = 0; k < V; k += 2) {
+      const float a = to_f<T>(e[k]), b = to_f<T>(e[k + 1]);
+      acc0 = fmaf(a, a, acc0);
+      acc1 = fmaf(b, b, acc1);
+    }
   }
-  acc = warp_sum(acc);
+  for (int64_t i = nv * V + gid; i < n; i += stride) {
+    const float v = to_f<T>(x[i]);
+    acc0 = fmaf(v, v, acc0);
+  }
+  float acc = warp_sum(acc0 + acc1);
   __shared__ float red[8];
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
   __syncthreads();
@@ -925,17 +949,26 @@ template <typename T>
 __global__ void __launch_bounds__(256) scale_kernel(T *__restrict__ x, int64_t n, const float *__restrict__ coef) {
   const float c = coef[0];
   if (c == 1.f) return;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
-    x[i] = from_f<T>(to_f<T>(x[i]) * c);
+  constexpr int V = 16 / sizeof(T);
+  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t nv = (reinterpret_cast<uintptr_t>(x) & 15) == 0 ? n / V : 0;
+  for (int64_t i = gid; i < nv; i += stride) {
+    uint4 raw = *reinterpret_cast<const uint4 *>(x + i * V);
+    T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+    for (int k = 0; k < V; ++k) e[k] = from_f<T>(to_f<T>(e[k]) * c);
+    *reinterpret_cast<uint4 *>(x + i * V) = raw;
+  }
+  for (int64_t i = nv * V + gid; i < n; i += stride) x[i] = from_f<T>(to_f<T>(x[i]) * c);
 }
 }  // namespace
 
 int sum_squares(stream_t stream, const void *x, int dtype, int64_t n, float *sumsq) {
   auto s = static_cast<cudaStream_t>(stream);
   if (n == 0) return 0;
-  if (dtype == 0) sumsq_kernel<float><<<grid_for(n, 256, 4), 256, 0, s>>>(static_cast<const float *>(x), n, sumsq);
-  else if (dtype == 1) sumsq_kernel<__nv_bfloat16><<<grid_for(n, 256, 4), 256, 0, s>>>(static_cast<const __nv_bfloat16 *>(x), n, sumsq);
+  if (dtype == 0) sumsq_kernel<float><<<grid_for((n + 3) / 4, 256, 8), 256, 0, s>>>(static_cast<const float *>(x), n, sumsq);
+  else if (dtype == 1) sumsq_kernel<__nv_bfloat16><<<grid_for((n + 7) / 8, 256, 8), 256, 0, s>>>(static_cast<const __nv_bfloat16 *>(x), n, sumsq);
   else return static_cast<int>(cudaErrorInvalidValue);
   return finish_launch();
 }
@@ -946,8 +979,8 @@ int clip_coefficient(stream_t stream, const float *sumsq, float max_norm, float 
 int scale_by_device_scalar(stream_t stream, void *x, int dtype, int64_t n, const float *coef) {
   auto s = static_cast<cudaStream_t>(stream);
   if (n == 0) return 0;
-  if (dtype == 0) scale_kernel<float><<<grid_for(n, 256, 4), 256, 0, s>>>(static_cast<float *>(x), n, coef);
-  else if (dtype == 1) scale_kernel<__nv_bfloat16><<<grid_for(n, 256, 4), 256, 0, s>>>(static_cast<__nv_bfloat16 *>(x), n, coef);
+  if (dtype == 0) scale_kernel<float><<<grid_for((n + 3) / 4, 256, 8), 256, 0, s>>>(static_cast<float *>(x), n, coef);
+  else if (dtype == 1) scale_kernel<__nv_bfloat16><<<grid_for((n + 7) / 8, 256, 8), 256, 0, s>>>(static_cast<__nv_bfloat16 *>(x), n, coef);
   else return static_cast<int>(cudaErrorInvalidValue);
   return finish_launch();
 }
