@@ -68,7 +68,10 @@ struct CS_API TPBlockImpl : module::Module {
   module::GeluLinear fc2{nullptr};
   std::shared_ptr<compute::ScaledDotProductAttention::State> attn_state;
   communication::Comm comm;
+  // Heads [head_begin, head_begin + local_heads) live on this rank. When n_head is not a multiple of the
+  // tensor-parallel size the first (n_head % tp) ranks own one head more (GPT-2 774M: 20 heads over 8 ranks = 3,3,3,3,2,2,2,2).
   int64_t local_heads{0};
+  int64_t head_begin{0};
   Tensor saved_ln1_out, saved_ln2_out;  // row shards kept for the backward re-gather (fused path)
 };
 CS_MODULE(TPBlock);
@@ -83,6 +86,8 @@ struct CS_API TPGPT2Impl : module::Module {
   [[nodiscard]] const models::GPT2Config &config() const { return config_; }
   // Names of the parameters that are replicated on every rank (gradients need the all-reduce).
   [[nodiscard]] std::vector<std::string> replicated_parameters() const;
+  // (first head, number of heads) owned by this rank.
+  [[nodiscard]] std::pair<int64_t, int64_t> head_range() const { return {h.front()->head_begin, h.front()->local_heads}; }
 
   module::Embedding wte{nullptr}, wpe{nullptr};
   std::vector<TPBlock> h;

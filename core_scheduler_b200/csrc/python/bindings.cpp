@@ -700,7 +700,8 @@ PYBIND11_MODULE(_C, m) {
       .def("backward_loss", [](parallel::TPGPT2Impl &g, const Scheduler &s, py::object sync) {
         g.backward_loss(s, sync.is_none() ? models::GradientSync{} : py::cast<models::GradientSync>(sync));
       }, py::arg("scheduler"), py::arg("sync") = py::none())
-      .def("replicated_parameters", &parallel::TPGPT2Impl::replicated_parameters);
+      .def("replicated_parameters", &parallel::TPGPT2Impl::replicated_parameters)
+      .def("head_range", &parallel::TPGPT2Impl::head_range, "(first head, number of heads) of this rank");
   m.def("all_gather_rows", &parallel::all_gather_rows);
   m.def("fused_tp_launches", &parallel::fused_tp_launches);
   m.def("reduce_scatter_rows", [](const Scheduler &s, const Comm &c, const ReadOnlyTensor &full) {

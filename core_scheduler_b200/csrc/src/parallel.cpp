@@ -383,12 +383,17 @@ TPBlockImpl::TPBlockImpl(const Scheduler &scheduler, const models::GPT2Config &c
     : comm{comm_} {
   const int64_t tp = comm.get_size();
   const int64_t d = config.n_embd();
-  CS_ASSERT_TRUE(config.n_head() % tp == 0, "n_head (", config.n_head(), ") must be divisible by the tensor-parallel size ", tp);
-  local_heads = config.n_head() / tp;
+  const int64_t rank = comm.get_rank();
+  CS_ASSERT_TRUE(config.n_head() >= tp, "n_head (", config.n_head(), ") is smaller than the tensor-parallel size ", tp);
+  CS_ASSERT_TRUE(d % config.n_head() == 0 && (4 * d) % tp == 0, "n_embd must be a multiple of n_head, and 4*n_embd of the tensor-parallel size");
+  const int64_t head_dim = d / config.n_head(), extra = config.n_head() % tp;
+  local_heads = config.n_head() / tp + (rank < extra ? 1 : 0);
+  head_begin = rank * (config.n_head() / tp) + std::min<int64_t>(rank, extra);
+  const int64_t d_attn = local_heads * head_dim;  // this rank's slice of the attention width
   auto ln_opts = compute::LayerNorm::Options{d}.device(config.device().value_or(scheduler.device())).dtype(config.dtype());
   ln1 = register_module("ln1", module::LayerNorm{scheduler, ln_opts});
-  c_attn = register_module("c_attn", module::Linear{scheduler, tp_linear(scheduler, config, d, 3 * d / tp)});
-  c_proj = register_module("c_proj", module::Linear{scheduler, tp_linear(scheduler, config, d / tp, d)});
+  c_attn = register_module("c_attn", module::Linear{scheduler, tp_linear(scheduler, config, d, 3 * d_attn)});
+  c_proj = register_module("c_proj", module::Linear{scheduler, tp_linear(scheduler, config, d_attn, d)});
   ln2 = register_module("ln2", module::LayerNorm{scheduler, ln_opts});
   fc1 = register_module("fc1", module::Linear{scheduler, tp_linear(scheduler, config, d, 4 * d / tp).gelu_epilogue(true)});
   fc2 = register_module("fc2", module::GeluLinear{scheduler, tp_linear(scheduler, config, 4 * d / tp, d)});

@@ -267,37 +267,42 @@ def case_zero_training(device, nvp2p):
         assert torch.allclose(pa[k].lp().float(), pa[k].raw().float(), atol=1e-2, rtol=1e-2), (rank, k)
 
 
-def shard_full_into_tp(full, tp_model, rank, world, cfg):
-    """Copies the matching slices of a full GPT-2's parameters into this rank's TP model."""
+def head_range(H, rank, world):
+    """Heads of `rank`: the first H % world ranks own one more (same rule as the library)."""
+    base, extra = divmod(H, world)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def tp_slice(name, t, rank, world, cfg):
+    """The part of a full GPT-2 parameter (or gradient) that tensor-parallel rank `rank` owns."""
     H, d = cfg.n_head, cfg.n_embd
     D = d // H
-    Hl = H // world
+    h0, h1 = head_range(H, rank, world)
+    if name.endswith("c_attn.weight"):
+        return t.view(3, H, D, d)[:, h0:h1].reshape(3 * (h1 - h0) * D, d)
+    if name.endswith("c_proj.weight"):
+        return t[:, h0 * D:h1 * D]
+    if name.endswith("fc1.weight"):
+        return t[rank * 4 * d // world:(rank + 1) * 4 * d // world]
+    if name.endswith("fc2.weight"):
+        return t[:, rank * 4 * d // world:(rank + 1) * 4 * d // world]
+    return t
+
+
+def full_key(k):
+    return k.replace(".c_attn", ".attn.c_attn").replace(".c_proj", ".attn.c_proj").replace(".fc1", ".mlp.fc1").replace(".fc2", ".mlp.fc2")
+
+
+def shard_full_into_tp(full, tp_model, rank, world, cfg):
+    """Copies the matching slices of a full GPT-2's parameters into this rank's TP model."""
     fp, tpp = full.named_parameters(), tp_model.named_parameters()
     for k, dst in tpp.items():
-        src = fp[k.replace(".c_attn", ".attn.c_attn").replace(".c_proj", ".attn.c_proj").replace(".fc1", ".mlp.fc1").replace(".fc2", ".mlp.fc2")].raw()
-        if k.endswith("c_attn.weight"):
-            src = src.view(3, H, D, d)[:, rank * Hl:(rank + 1) * Hl].reshape(3 * Hl * D, d)
-        elif k.endswith("c_proj.weight"):
-            src = src[:, rank * d // world:(rank + 1) * d // world]
-        elif k.endswith("fc1.weight"):
-            src = src[rank * 4 * d // world:(rank + 1) * 4 * d // world]
-        elif k.endswith("fc2.weight"):
-            src = src[:, rank * 4 * d // world:(rank + 1) * 4 * d // world]
-        dst.raw().copy_(src)
+        dst.raw().copy_(tp_slice(k, fp[full_key(k)].raw(), rank, world, cfg))
 
 
 def full_grad_slice(name, g, rank, world, cfg):
-    H, d = cfg.n_head, cfg.n_embd
-    D, Hl = d // H, H // world
-    if name.endswith("c_attn.weight"):
-        return g.view(3, H, D, d)[:, rank * Hl:(rank + 1) * Hl].reshape(3 * Hl * D, d)
-    if name.endswith("c_proj.weight"):
-        return g[:, rank * d // world:(rank + 1) * d // world]
-    if name.endswith("fc1.weight"):
-        return g[rank * 4 * d // world:(rank + 1) * 4 * d // world]
-    if name.endswith("fc2.weight"):
-        return g[:, rank * 4 * d // world:(rank + 1) * 4 * d // world]
-    return g
+    return tp_slice(name, g, rank, world, cfg)
 
 
 def case_tp_training_fused(device, nvp2p):
@@ -305,16 +310,22 @@ def case_tp_training_fused(device, nvp2p):
     case_tp_training(device, True, batch_per_rank=16, expect_fused=True)
 
 
-def case_tp_training(device, nvp2p, batch_per_rank=2, expect_fused=False):
+def case_tp_uneven_heads(device, nvp2p):
+    """Three heads over two ranks (2 + 1): the split GPT-2 774M needs for 20 heads over 8 ranks."""
+    case_tp_training(device, nvp2p, n_head=3, n_embd=96)
+
+
+def case_tp_training(device, nvp2p, batch_per_rank=2, expect_fused=False, n_head=4, n_embd=64):
     """Tensor-parallel GPT-2 (sequence-parallel activations) reproduces the single-device loss and gradients."""
     comm, rank, world, s = make_comm(device, nvp2p)
     amp = device == "cuda"
     dtype = torch.float32 if amp else torch.float64
     cs.manual_seed(3)
-    cfg = cs.GPT2Config(n_layer=2, n_head=4, n_embd=64, block_size=32, vocab_size=128, padded_vocab_size=128, dtype=dtype)
+    cfg = cs.GPT2Config(n_layer=2, n_head=n_head, n_embd=n_embd, block_size=32, vocab_size=128, padded_vocab_size=128, dtype=dtype)
     full = cs.GPT2(s, cfg)
     tp = C.TPGPT2(s, cfg, comm)
     s.synchronize()
+    assert tp.head_range() == (head_range(n_head, rank, world)[0], head_range(n_head, rank, world)[1] - head_range(n_head, rank, world)[0])
     shard_full_into_tp(full, tp, rank, world, cfg)
     g = torch.Generator().manual_seed(5)
     ids = torch.randint(0, 128, (batch_per_rank * world, 33), generator=g).to(device)
@@ -346,8 +357,7 @@ def case_tp_training(device, nvp2p, batch_per_rank=2, expect_fused=False):
     gt, gf = tp.named_gradients(), full.named_gradients()
     tol = dict(atol=3e-2, rtol=5e-2) if amp else dict(atol=1e-9, rtol=1e-7)
     for k, gtp in gt.items():
-        fk = k.replace(".c_attn", ".attn.c_attn").replace(".c_proj", ".attn.c_proj").replace(".fc1", ".mlp.fc1").replace(".fc2", ".mlp.fc2")
-        ref = full_grad_slice(k, gf[fk].raw(), rank, world, cfg)
+        ref = full_grad_slice(k, gf[full_key(k)].raw(), rank, world, cfg)
         got = gtp.raw() / world
         if amp:
             err = (got.float() - ref.float()).norm() / (ref.float().norm() + 1e-12)
