@@ -408,7 +408,7 @@ constexpr int kLnBwdCtas = kSmCount * 3;
 // One warp per row, grid-stride over rows. Lane l owns the 8-element chunks l, l+32, ... of the
 // row. The next row (still packed, in its 128-bit load registers) is fetched before the current
 // one is reduced, so that loads stay in flight during the shuffles; the grid is one resident wave.
-constexpr int ln_fwd_ctas_per_sm(int chunks) { return chunks <= 3 ? 6 : (chunks <= 5 ? 4 : 1); }
+constexpr int ln_fwd_ctas_per_sm(int chunks) { return chunks <= 5 ? 4 : 1; }
 template <int CHUNKS>
 __global__ void __launch_bounds__(kLnWarps * 32, ln_fwd_ctas_per_sm(CHUNKS))
 ln_fwd_kernel(const __nv_bfloat16 *__restrict__ x, const void *__restrict__ gamma, const void *__restrict__ beta, int pdt,
@@ -426,6 +426,25 @@ ln_fwd_kernel(const __nv_bfloat16 *__restrict__ x, const void *__restrict__ gamm
         dst[c] = *reinterpret_cast<const Bf16x8 *>(x + r * d + chunk * 8);
     }
   };
+  // gamma / beta of this lane's chunks stay in registers for narrow rows (they would otherwise be
+  // re-read from L1 for every row: four times the bytes of the row itself)
+  constexpr bool kHoist = CHUNKS <= 3;
+  float gw[kHoist ? CHUNKS : 1][8], bw[kHoist ? CHUNKS : 1][8];
+  if (kHoist) {
+#pragma unroll
+    for (int c = 0; c < (kHoist ? CHUNKS : 1); ++c) {
+      const int chunk = lane + 32 * c;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        gw[c][k] = 0.f;
+        bw[c][k] = 0.f;
+      }
+      if (chunk < nchunks) {
+        load8(gamma, chunk * 8, pdt, gw[c]);
+        if (beta) load8(beta, chunk * 8, pdt, bw[c]);
+      }
+    }
+  }
   if (row < rows) load_row(cur, row);
   while (row < rows) {
     const int64_t next = row + stride;
@@ -462,12 +481,20 @@ ln_fwd_kernel(const __nv_bfloat16 *__restrict__ x, const void *__restrict__ gamm
       const int chunk = lane + 32 * c;
       if (chunk < nchunks) {
         float g[8], b[8], o[8];
-        load8(gamma, chunk * 8, pdt, g);
-        if (beta) {
-          load8(beta, chunk * 8, pdt, b);
-        } else {
+        if (kHoist) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) b[k] = 0.f;
+          for (int k = 0; k < 8; ++k) {
+            g[k] = gw[kHoist ? c : 0][k];
+            b[k] = bw[kHoist ? c : 0][k];
+          }
+        } else {
+          load8(gamma, chunk * 8, pdt, g);
+          if (beta) {
+            load8(beta, chunk * 8, pdt, b);
+          } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) b[k] = 0.f;
+          }
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) o[k] = (v[c][k] - mu) * rs * g[k] + b[k];
