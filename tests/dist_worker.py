@@ -315,6 +315,11 @@ def case_tp_uneven_heads(device, nvp2p):
     case_tp_training(device, nvp2p, n_head=3, n_embd=96)
 
 
+def case_tp_uneven_heads_fused(device, nvp2p):
+    """Uneven heads (2 + 1, head dimension 64) at a size where the fused GEMM + collective kernels engage."""
+    case_tp_training(device, True, batch_per_rank=16, expect_fused=True, n_head=3, n_embd=192)
+
+
 def case_tp_training(device, nvp2p, batch_per_rank=2, expect_fused=False, n_head=4, n_embd=64):
     """Tensor-parallel GPT-2 (sequence-parallel activations) reproduces the single-device loss and gradients."""
     comm, rank, world, s = make_comm(device, nvp2p)

@@ -31,6 +31,11 @@ def test_tensor_parallel_fused_gemm_collectives():
 
 
 @needs2
+def test_tensor_parallel_uneven_heads_fused():
+    run_case("tp_uneven_heads_fused", device="cuda", extra=("nvp2p",), timeout=600)
+
+
+@needs2
 def test_in_place_arena_all_reduce():
     run_case("all_reduce_arena", device="cuda", extra=("nvp2p",), timeout=600)
 
