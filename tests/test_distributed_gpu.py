@@ -3,10 +3,16 @@
 Runs as child processes (one per GPU) with NVLS switched off, as multi-rank GPU tests should on
 shared machines. Skipped when fewer than two GPUs are visible.
 """
+import os
+import subprocess
+import sys
+
 import pytest
 import torch
 
 from test_distributed_cpu import run_case
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 pytestmark = pytest.mark.gpu
 needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
@@ -48,3 +54,27 @@ def test_zero_fused_step_matches_replicated_adamw():
 @needs2
 def test_peer_wait_times_out_with_status_instead_of_hanging():
     run_case("timeout_status", device="cuda", extra=("nvp2p",), timeout=600)
+
+
+@needs2
+@pytest.mark.parametrize("exe,args", [("gpt2_ddp", ["--backend", "nvp2p"]), ("gpt2_ddp", ["--backend", "nccl"]),
+                                      ("gpt2_zero_tp", ["--mode", "zero"]), ("gpt2_zero_tp", ["--mode", "tp"])])
+def test_cpp_multi_gpu_examples(exe, args, tmp_path):
+    """The C++ entry points bootstrap from the launcher's environment and train the tiny model on two GPUs."""
+    path = os.path.join(ROOT, "examples", "bin", exe)
+    if not os.path.exists(path):
+        pytest.skip("examples not built (python -m core_scheduler_b200.build examples)")
+    extra = ["--batch", "16"] if exe == "gpt2_zero_tp" else ["--micro-batch", "4"]
+    if exe == "gpt2_zero_tp":
+        extra += ["--metrics", str(tmp_path / "m.jsonl"), "--save-dir", str(tmp_path / "ckpt")]
+    cmd = [sys.executable, os.path.join(ROOT, "examples", "launch.py"), "--nproc", "2", "--master-port", "29631", "--",
+           path, "--model", "tiny", "--steps", "4", *args, *extra]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, (out.stdout + out.stderr)[-3000:]
+    assert out.stdout.count("tok/s") + out.stdout.count("tok/sec") == 4, out.stdout
+    if exe == "gpt2_zero_tp":
+        import json
+        rows = [json.loads(l) for l in open(tmp_path / "m.jsonl")]
+        assert [r["step"] for r in rows] == [1, 2, 3, 4] and rows[-1]["loss"] < rows[0]["loss"] + 0.5
+        assert os.path.exists(tmp_path / "ckpt" / ("tp_rank0" if "tp" in args else "") / "meta.json")

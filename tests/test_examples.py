@@ -41,3 +41,16 @@ def test_prepare_text_gen_feeds_the_loader(tmp_path, cpu_scheduler):
     ids, lab = batch["input_ids"].raw(), batch["labels"].raw()
     assert ids.shape == (4, 64)
     assert (ids[:, 1:] == lab[:, :-1]).all()
+
+
+def test_launcher_sets_rendezvous_environment_and_propagates_failure():
+    launch = os.path.join(ROOT, "examples", "launch.py")
+    ok = subprocess.run([sys.executable, launch, "--nproc", "3", "--master-port", "29777", "--", sys.executable, "-c",
+                         "import os; print('R', os.environ['RANK'], os.environ['LOCAL_RANK'], os.environ['WORLD_SIZE'], "
+                         "os.environ['MASTER_ADDR'], os.environ['MASTER_PORT'])"], capture_output=True, text=True, timeout=60)
+    assert ok.returncode == 0
+    assert sorted(ok.stdout.split("\n")[:3]) == [f"R {r} {r} 3 127.0.0.1 29777" for r in range(3)]
+    bad = subprocess.run([sys.executable, launch, "--nproc", "2", "--", sys.executable, "-c",
+                          "import os, sys, time; sys.exit(7) if os.environ['RANK'] == '1' else time.sleep(30)"],
+                         capture_output=True, text=True, timeout=60)
+    assert bad.returncode == 7  # rank 1 failed; the sleeping rank 0 was stopped instead of being waited for
