@@ -6,9 +6,11 @@
 //   warp 0     TMA producer: Q once, then K tiles (128 keys x 64, 2 stages) and V tiles (1 stage)
 //   warp 1     MMA issuer: S = Q K^T (128x128x64, fp32 in TMEM) and
 //              O_j = P V (128x64x128; P from shared memory, V as an MN-major operand)
-//   warps 2-5  softmax: one thread per query row reads its S row from TMEM, keeps the running
-//              max / sum, writes P (bf16, 128-byte swizzled) to shared memory for the second MMA,
-//              then folds the partial O_j into fp32 registers with the usual rescaling
+//   warps 2-5  softmax: one thread per query row reads its S row from TMEM, keeps the reference
+//              max / running sum and writes P (bf16, 128-byte swizzled) to shared memory for the
+//              second MMA. O accumulates in TMEM across key blocks; a warp rescales its 32 rows of
+//              O in place only when a row maximum has grown by more than 2^8 since the reference
+//              was taken (probabilities stay below 256, exact after the final division)
 // Two CTAs share an SM (97 KB of shared memory and 256 TMEM columns each), so one CTA's softmax
 // overlaps the other's tensor-core work. Scores never touch global memory. Every mbarrier wait is bounded (abort flag + status word).
 //
@@ -105,7 +107,28 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]),
+        "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]),
+        "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
   uint64_t desc = 0;
   desc |= static_cast<uint64_t>((addr & 0x3FFFF) >> 4);
@@ -234,14 +257,13 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
         if (j + 1 < num_kv) ok = issue_s(j + 1);  // S is free again once P of block j exists
         if (!ok) break;
         if (!mbar_wait(bar(V_FULL), bph, abort_flag)) break;
-        if (!mbar_wait(bar(O_EMPTY), bph ^ 1u, abort_flag)) break;
         fence_after();
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
           // P: two K-major 64-key halves of 16 KB; V: MN-major, 16 keys = 2 KB per step
           const uint64_t da = smem_desc(p_smem + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
           const uint64_t db = smem_desc(v_smem + k * 2048, 8192, 1024);
-          umma(o_tmem, da, db, idesc_o, k > 0 ? 1u : 0u);
+          umma(o_tmem, da, db, idesc_o, (j | k) ? 1u : 0u);  // O accumulates over the key blocks
         }
         umma_commit(bar(V_EMPTY));
         umma_commit(bar(P_EMPTY));
@@ -253,10 +275,7 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
     const int r = q * 32 + lane;          // query row inside the block
     const int q_idx = q0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-    float m_run = -INFINITY, l_run = 0.f;
-    float o[HD];
-#pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;  // m_run: the maximum the exponents refer to (may lag the true one)
     bool ok = true;
     for (int j = 0; ok && j < num_kv; ++j) {
       const uint32_t bph = j & 1;
@@ -289,9 +308,34 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
       tmem_ld32(s_tmem + 0 * 32 + lane_addr, va);  // first chunk of the second pass
       max_chunk(vb, 3);
       const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      const float m_new = fmaxf(m_run, m_blk);
-      const float alpha = fast_exp2((m_run - m_new) * p.scale_log2e);  // first block: exp2(-inf) = 0
-      const float m_scaled = m_new * p.scale_log2e;
+      // Move the reference maximum only when it lags by more than 2^8 (always on the first block).
+      const bool grow = j == 0 || (m_blk - m_run) * p.scale_log2e > 8.0f;
+      float alpha = 1.0f;
+      if (grow) {
+        alpha = fast_exp2((m_run - m_blk) * p.scale_log2e);  // first block: exp2(-inf) = 0
+        m_run = m_blk;
+        l_run *= alpha;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        // rescale this warp's 32 rows of O in place; block j-1's P V must have landed first
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(O_FULL), bph ^ 1u, abort_flag))) {  // the warp leaves as one
+          tmem_wait_ld();
+          break;
+        }
+        fence_after();
+        tmem_wait_ld();  // the prefetched S chunk in `va` is complete before the registers below are reused
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t ov[32];
+          tmem_ld32(o_tmem + c * 32 + lane_addr, ov);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+          tmem_st32(o_tmem + c * 32 + lane_addr, ov);
+        }
+        tmem_wait_st();
+      }
+      const float m_scaled = m_run * p.scale_log2e;
       // pass 2: probabilities -> shared memory (bf16, swizzled) and their sum
       if (!mbar_wait(bar(P_EMPTY), bph ^ 1u, abort_flag)) {
         tmem_wait_ld();  // no load may be outstanding when the kernel unwinds
@@ -337,10 +381,12 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
         mbar_arrive(bar(S_EMPTY));
         mbar_arrive(bar(P_FULL));
       }
-      l_run = l_run * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
-      m_run = m_new;
-      // fold the partial output of this block into the running one
-      if (!mbar_wait(bar(O_FULL), bph, abort_flag)) break;
+      l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+    }
+    // the last block's P V completes the accumulator
+    const bool done = ok && mbar_wait(bar(O_FULL), (num_kv - 1) & 1, abort_flag);
+    float o[HD];
+    if (done) {
       fence_after();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -348,13 +394,10 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
         tmem_ld32(o_tmem + c * 32 + lane_addr, v);
         tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(v[i]));
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = __uint_as_float(v[i]);
       }
-      fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(O_EMPTY));
     }
-    if (!*abort_flag && q_idx < p.T &&
+    if (done && !*abort_flag && q_idx < p.T &&
         CS_IN_BOUNDS(kKidAttention, (static_cast<long long>(row_base + q_idx) * p.H + h) * HD + HD - 1,
                      static_cast<long long>(p.B) * p.T * p.H * HD)) {
       const float inv = 1.f / l_run;
@@ -606,28 +649,24 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
       // rows are keys and columns queries (kDKV), or rows queries and columns keys: keep key <= query
       const bool near_diag = kDKV ? (c0 < r0 + 128) : (c0 + BC > r0);
       const float *lse_c = vec + s * 128, *delta_c = lse_c + 64;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld32(s_tmem + c * 32 + lane_addr, sv);
-        tmem_ld32(dp_tmem + c * 32 + lane_addr, dv);
-        tmem_wait_ld();
-        float pr[32], ds[32];
+      // 16 columns at a time; the TMEM loads of the next 16 are in flight while these are processed
+      auto process = [&](const uint32_t (&sv)[16], const uint32_t (&dv)[16], int c) {
+        float pr[16], ds[16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = c0 + c * 32 + i;
+        for (int i = 0; i < 16; ++i) {
+          const int col = c0 + c * 16 + i;
           const bool keep = !near_diag || (kDKV ? (r_idx <= col) : (col <= r_idx));
-          const float l2 = kDKV ? lse_c[c * 32 + i] * log2e : lse_r;
-          const float dl = kDKV ? delta_c[c * 32 + i] : delta_r;
+          const float l2 = kDKV ? lse_c[c * 16 + i] * log2e : lse_r;
+          const float dl = kDKV ? delta_c[c * 16 + i] : delta_r;
           const float e = keep ? fast_exp2(fmaf(__uint_as_float(sv[i]), p.scale_log2e, -l2)) : 0.f;
           pr[i] = e;
           ds[i] = e * (__uint_as_float(dv[i]) - dl) * p.scale;
         }
-        // 32 columns = 64 bytes = four 16-byte pieces of this row
+        // 16 columns = 32 bytes = two 16-byte pieces of this row
         const uint32_t row_off = r * 128;
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int piece = c * 4 + g;
+        for (int g = 0; g < 2; ++g) {
+          const int piece = c * 2 + g;
           const uint32_t off = row_off + ((piece ^ (r & 7)) << 4);
           if (kDKV)
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_smem + off), "r"(pack2(pr[g * 8 + 0], pr[g * 8 + 1])),
@@ -639,7 +678,24 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
                        "r"(pack2(ds[g * 8 + 6], ds[g * 8 + 7]))
                        : "memory");
         }
-      }
+      };
+      uint32_t sa[16], da[16], sb[16], db[16];
+      tmem_ld16(s_tmem + 0 + lane_addr, sa);
+      tmem_ld16(dp_tmem + 0 + lane_addr, da);
+      tmem_wait_ld();
+      tmem_ld16(s_tmem + 16 + lane_addr, sb);
+      tmem_ld16(dp_tmem + 16 + lane_addr, db);
+      process(sa, da, 0);
+      tmem_wait_ld();
+      tmem_ld16(s_tmem + 32 + lane_addr, sa);
+      tmem_ld16(dp_tmem + 32 + lane_addr, da);
+      process(sb, db, 1);
+      tmem_wait_ld();
+      tmem_ld16(s_tmem + 48 + lane_addr, sb);
+      tmem_ld16(dp_tmem + 48 + lane_addr, db);
+      process(sa, da, 2);
+      tmem_wait_ld();
+      process(sb, db, 3);
       fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();

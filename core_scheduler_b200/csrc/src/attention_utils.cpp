@@ -79,11 +79,13 @@ bool use_cudnn_engine() {
   return cudnn;
 }
 
-// "tcgen05": this library's forward and backward kernels on the packed qkv tensor. Read at every
-// call (a dozen per step) so that a process can switch engines between models.
+// This library's own forward and backward kernels on the packed qkv tensor are the default for
+// the shapes they cover (bf16, causal, head dimension 64, T % 128 == 0, no dropout);
+// CS_ATTENTION_ENGINE=cudnn or =flash selects a library engine instead. Read at every call (a
+// dozen per step) so that a process can switch engines between models.
 bool use_own_forward() {
   const char *e = std::getenv("CS_ATTENTION_ENGINE");
-  return e != nullptr && std::string(e) == "tcgen05";
+  return e == nullptr || std::string(e) == "tcgen05";
 }
 
 double resolve_scale(const optional<double> &scale, int64_t head_dim) {
