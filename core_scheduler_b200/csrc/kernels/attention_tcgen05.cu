@@ -3,16 +3,16 @@
 // per-row log-sum-exp.
 //
 // One CTA per (batch, head, 128-query block), 192 threads:
-//   warp 0     TMA producer: Q once, then K tiles (128 keys x 64, 2 stages) and V tiles (1 stage)
-//   warp 1     MMA issuer: S = Q K^T (128x128x64, fp32 in TMEM) and
-//              O_j = P V (128x64x128; P from shared memory, V as an MN-major operand)
+//   warp 0     TMA producer: Q once, then K and V tiles of 64 keys (one stage each)
+//   warp 1     MMA issuer: S = Q K^T (128x64x64, fp32 in TMEM) and
+//              O += P V (128x64x64; P from shared memory, V as an MN-major operand)
 //   warps 2-5  softmax: one thread per query row reads its S row from TMEM, keeps the reference
 //              max / running sum and writes P (bf16, 128-byte swizzled) to shared memory for the
 //              second MMA. O accumulates in TMEM across key blocks; a warp rescales its 32 rows of
 //              O in place only when a row maximum has grown by more than 2^8 since the reference
 //              was taken (probabilities stay below 256, exact after the final division)
-// Two CTAs share an SM (97 KB of shared memory and 256 TMEM columns each), so one CTA's softmax
-// overlaps the other's tensor-core work. Scores never touch global memory. Every mbarrier wait is bounded (abort flag + status word).
+// Four CTAs share an SM (49 KB of shared memory, 128 TMEM columns and at most 85 registers per
+// thread each): sixteen softmax warps per SM hide each other's TMEM, exp and barrier latencies. Scores never touch global memory. Every mbarrier wait is bounded (abort flag + status word).
 //
 // What it replaces in the reference project: at::_scaled_dot_product_flash_attention
 // (src/compute/sdpa_flash_attn.cpp:56-60) and the cuDNN-frontend SDPA graph
@@ -31,14 +31,16 @@
 namespace cs::kernels {
 namespace {
 constexpr int BQ = 128;      // queries per CTA
-constexpr int BKV = 128;     // keys per step
+constexpr int BKV = 64;      // keys per step
 constexpr int HD = 64;       // head dimension
-constexpr int TILE_BYTES = 128 * HD * 2;   // 16 KB: Q, K or V tile
-constexpr int P_BYTES = BQ * BKV * 2;      // 32 KB
-constexpr int KV_STAGES = 2;
+constexpr int TILE_BYTES = 128 * HD * 2;      // 16 KB: a 128-row tile (Q; resident tiles of the backward)
+constexpr int KV_TILE_BYTES = BKV * HD * 2;   // 8 KB: K or V tile of the forward
+constexpr int P_BYTES = BQ * BKV * 2;         // 16 KB
 constexpr int THREADS = 192;
-constexpr int SMEM_BYTES = TILE_BYTES * (1 + KV_STAGES + 1) + P_BYTES + 1024 + 256;  // ~97 KB: two CTAs per SM
-constexpr int TMEM_COLS = 256;             // S: 128 columns, O_j: 64 columns; two CTAs share the SM's 512
+constexpr int FWD_CTAS_PER_SM = 4;
+constexpr int SMEM_BYTES = TILE_BYTES + 2 * KV_TILE_BYTES + P_BYTES + 1024 + 256;  // ~49 KB: four CTAs per SM
+constexpr int FWD_TMEM_COLS = 128;         // forward: S 64 columns + O 64 columns; four CTAs share the SM's 512
+constexpr int TMEM_COLS = 256;             // backward: S', dP' and two accumulators of 64 columns each
 constexpr long long kWaitBudgetCycles = 4000000000LL;
 
 __device__ DeviceStatus g_attn_status;
@@ -128,6 +130,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32
         "r"(v[30]), "r"(v[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
   uint64_t desc = 0;
@@ -157,19 +167,19 @@ struct AttnParams {
   DeviceStatus *status;
 };
 
-__global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const AttnParams p) {
+__global__ void __launch_bounds__(THREADS, FWD_CTAS_PER_SM) attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                                 const __grid_constant__ CUtensorMap map_kv,
+                                                                                 const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *aligned = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t q_smem = base;
-  const uint32_t k_smem = q_smem + TILE_BYTES;
-  const uint32_t v_smem = k_smem + KV_STAGES * TILE_BYTES;
-  const uint32_t p_smem = v_smem + TILE_BYTES;  // V is single-buffered: it is only needed once P exists
+  const uint32_t q_smem = base;                       // 128 x 64
+  const uint32_t k_smem = q_smem + TILE_BYTES;        // 64 x 64 (one stage: four CTAs per SM hide the reload)
+  const uint32_t v_smem = k_smem + KV_TILE_BYTES;     // 64 x 64
+  const uint32_t p_smem = v_smem + KV_TILE_BYTES;     // 128 x 64 probabilities
   const uint32_t bar_base = p_smem + P_BYTES;
   uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + (bar_base - base));
-  // barrier slots
-  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13, P_EMPTY = 15,
-         O_FULL = 17, O_EMPTY = 19, NUM_BARS = 21 };
+  enum { Q_FULL = 0, K_FULL, K_EMPTY, V_FULL, V_EMPTY, S_FULL, S_EMPTY, P_FULL, P_EMPTY, O_FULL, NUM_BARS };
   auto bar = [&](int i) { return bar_base + 8u * i; };
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars + NUM_BARS);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + NUM_BARS + 1);
@@ -178,30 +188,26 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
   const int qb = gridDim.x - 1 - blockIdx.x;  // longest rows first
   const int h = blockIdx.y, b = blockIdx.z;
   const int q0 = qb * BQ;
-  const int num_kv = qb + 1;  // causal: key blocks 0..qb
+  const int num_kv = 2 * (qb + 1);  // causal: 64-key blocks 0 .. 2 qb + 1
   const int row_base = b * p.T;
 
   if (threadIdx.x == 0) {
     mbar_init(bar(Q_FULL), 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(bar(K_FULL + s), 1);
-      mbar_init(bar(K_EMPTY + s), 1);
-      mbar_init(bar(V_FULL + s), 1);
-      mbar_init(bar(V_EMPTY + s), 1);
-      mbar_init(bar(S_FULL + s), 1);
-      mbar_init(bar(S_EMPTY + s), 4);   // one arrival per softmax warp
-      mbar_init(bar(P_FULL + s), 4);
-      mbar_init(bar(P_EMPTY + s), 1);
-      mbar_init(bar(O_FULL + s), 1);
-      mbar_init(bar(O_EMPTY + s), 4);
-    }
+    mbar_init(bar(K_FULL), 1);
+    mbar_init(bar(K_EMPTY), 1);
+    mbar_init(bar(V_FULL), 1);
+    mbar_init(bar(V_EMPTY), 1);
+    mbar_init(bar(S_FULL), 1);
+    mbar_init(bar(S_EMPTY), 4);  // one arrival per softmax warp
+    mbar_init(bar(P_FULL), 4);
+    mbar_init(bar(P_EMPTY), 1);
+    mbar_init(bar(O_FULL), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_qkv)) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t *>(tmem_slot))),
-                 "r"(TMEM_COLS)
+                 "r"(FWD_TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -209,62 +215,53 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
   __syncthreads();
   fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t s_tmem = tmem_base;        // 128 columns
-  const uint32_t o_tmem = tmem_base + BKV;  // 64 columns
+  const uint32_t s_tmem = tmem_base;        // 64 columns of scores
+  const uint32_t o_tmem = tmem_base + BKV;  // 64 columns of output accumulator
 
   if (warp == 0) {
     if (lane == 0) {
       const int q_col = h * HD, k_col = (p.H + h) * HD, v_col = (2 * p.H + h) * HD;
       mbar_expect_tx(bar(Q_FULL), TILE_BYTES);
-      tma_load_2d(q_smem, &map_qkv, bar(Q_FULL), q_col, row_base + q0);
+      tma_load_2d(q_smem, &map_q, bar(Q_FULL), q_col, row_base + q0);
       for (int j = 0; j < num_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(bar(K_EMPTY + s), ph ^ 1u, abort_flag)) break;
-        mbar_expect_tx(bar(K_FULL + s), TILE_BYTES);
-        tma_load_2d(k_smem + s * TILE_BYTES, &map_qkv, bar(K_FULL + s), k_col, row_base + j * BKV);
-        if (!mbar_wait(bar(V_EMPTY), (j & 1) ^ 1u, abort_flag)) break;
-        mbar_expect_tx(bar(V_FULL), TILE_BYTES);
-        tma_load_2d(v_smem, &map_qkv, bar(V_FULL), v_col, row_base + j * BKV);
+        const uint32_t ph = j & 1;
+        if (!mbar_wait(bar(K_EMPTY), ph ^ 1u, abort_flag)) break;
+        mbar_expect_tx(bar(K_FULL), KV_TILE_BYTES);
+        tma_load_2d(k_smem, &map_kv, bar(K_FULL), k_col, row_base + j * BKV);
+        if (!mbar_wait(bar(V_EMPTY), ph ^ 1u, abort_flag)) break;
+        mbar_expect_tx(bar(V_FULL), KV_TILE_BYTES);
+        tma_load_2d(v_smem, &map_kv, bar(V_FULL), v_col, row_base + j * BKV);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      // S = Q K^T: M=128, N=128, both operands K-major. O_j = P V: M=128, N=64, B (= V) MN-major.
+      // S = Q K^T: M=128, N=64, both operands K-major. O += P V: M=128, N=64, B (= V) MN-major.
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BKV >> 3) << 17) | (8u << 24);
       const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (static_cast<uint32_t>(HD >> 3) << 17) | (8u << 24);
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag);
       auto issue_s = [&](int j) -> bool {
-        const int s = j & 1;                    // K/V stage
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(bar(K_FULL + s), ph, abort_flag)) return false;
-        if (!mbar_wait(bar(S_EMPTY), (j & 1) ^ 1u, abort_flag)) return false;  // softmax of block j-1 has read S
+        const uint32_t ph = j & 1;
+        if (!mbar_wait(bar(K_FULL), ph, abort_flag)) return false;
+        if (!mbar_wait(bar(S_EMPTY), ph ^ 1u, abort_flag)) return false;  // softmax of block j-1 has read S
         fence_after();
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          umma(s_tmem, smem_desc(q_smem + k * 32, 16, 1024), smem_desc(k_smem + s * TILE_BYTES + k * 32, 16, 1024), idesc_s,
-               k > 0 ? 1u : 0u);
-        umma_commit(bar(K_EMPTY + s));
+          umma(s_tmem, smem_desc(q_smem + k * 32, 16, 1024), smem_desc(k_smem + k * 32, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+        umma_commit(bar(K_EMPTY));
         umma_commit(bar(S_FULL));
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int j = 0; ok && j < num_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const uint32_t bph = j & 1;             // phase of the single-buffered S / P / O barriers
-        if (!mbar_wait(bar(P_FULL), bph, abort_flag)) break;
+        const uint32_t ph = j & 1;
+        if (!mbar_wait(bar(P_FULL), ph, abort_flag)) break;
         if (j + 1 < num_kv) ok = issue_s(j + 1);  // S is free again once P of block j exists
         if (!ok) break;
-        if (!mbar_wait(bar(V_FULL), bph, abort_flag)) break;
+        if (!mbar_wait(bar(V_FULL), ph, abort_flag)) break;
         fence_after();
 #pragma unroll
-        for (int k = 0; k < BKV / 16; ++k) {
-          // P: two K-major 64-key halves of 16 KB; V: MN-major, 16 keys = 2 KB per step
-          const uint64_t da = smem_desc(p_smem + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
-          const uint64_t db = smem_desc(v_smem + k * 2048, 8192, 1024);
-          umma(o_tmem, da, db, idesc_o, (j | k) ? 1u : 0u);  // O accumulates over the key blocks
-        }
+        for (int k = 0; k < BKV / 16; ++k)  // P: one K-major tile; V: MN-major, 16 keys = 2 KB per step
+          umma(o_tmem, smem_desc(p_smem + k * 32, 16, 1024), smem_desc(v_smem + k * 2048, 8192, 1024), idesc_o, (j | k) ? 1u : 0u);
         umma_commit(bar(V_EMPTY));
         umma_commit(bar(P_EMPTY));
         umma_commit(bar(O_FULL));
@@ -272,43 +269,44 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
     }
   } else {
     const int q = warp & 3;
-    const int r = q * 32 + lane;          // query row inside the block
+    const int r = q * 32 + lane;  // query row inside the block
     const int q_idx = q0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     float m_run = -INFINITY, l_run = 0.f;  // m_run: the maximum the exponents refer to (may lag the true one)
     bool ok = true;
     for (int j = 0; ok && j < num_kv; ++j) {
-      const uint32_t bph = j & 1;
-      if (!mbar_wait(bar(S_FULL), bph, abort_flag)) break;
+      const uint32_t ph = j & 1;
+      if (!mbar_wait(bar(S_FULL), ph, abort_flag)) break;
       fence_after();
-      // pass 1: row maximum of the (masked) scores
-      const bool diagonal = j == qb;
-      // Four independent partial maxima / sums keep the dependent chains short, and the TMEM load
-      // of the next 32-column chunk is in flight while the current one is processed.
+      const int k0 = j * BKV;
+      const bool diagonal = k0 + BKV - 1 > q0;  // some key of this block lies beyond some query of the tile
+      // pass 1: row maximum of the (masked) scores. Four independent partial maxima / sums keep the
+      // dependent chains short; the TMEM load of the next 16 columns is in flight meanwhile.
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      auto max_chunk = [&](const uint32_t (&v)[32], int c) {
+      auto max_chunk = [&](const uint32_t (&v)[16], int c) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < 16; ++i) {
           const float x = __uint_as_float(v[i]);
-          if (!diagonal || (j * BKV + c * 32 + i) <= q_idx) mx[i & 3] = fmaxf(mx[i & 3], x);
+          if (!diagonal || (k0 + c * 16 + i) <= q_idx) mx[i & 3] = fmaxf(mx[i & 3], x);
         }
       };
-      uint32_t va[32], vb[32];
-      tmem_ld32(s_tmem + 0 * 32 + lane_addr, va);
+      uint32_t va[16], vb[16];
+      tmem_ld16(s_tmem + 0 + lane_addr, va);
       tmem_wait_ld();
-      tmem_ld32(s_tmem + 1 * 32 + lane_addr, vb);
+      tmem_ld16(s_tmem + 16 + lane_addr, vb);
       max_chunk(va, 0);
       tmem_wait_ld();
-      tmem_ld32(s_tmem + 2 * 32 + lane_addr, va);
+      tmem_ld16(s_tmem + 32 + lane_addr, va);
       max_chunk(vb, 1);
       tmem_wait_ld();
-      tmem_ld32(s_tmem + 3 * 32 + lane_addr, vb);
+      tmem_ld16(s_tmem + 48 + lane_addr, vb);
       max_chunk(va, 2);
       tmem_wait_ld();
-      tmem_ld32(s_tmem + 0 * 32 + lane_addr, va);  // first chunk of the second pass
+      tmem_ld16(s_tmem + 0 + lane_addr, va);  // first chunk of the second pass
       max_chunk(vb, 3);
       const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       // Move the reference maximum only when it lags by more than 2^8 (always on the first block).
+      // A fully masked row of a diagonal block has m_blk = -inf and never moves it.
       const bool grow = j == 0 || (m_blk - m_run) * p.scale_log2e > 8.0f;
       float alpha = 1.0f;
       if (grow) {
@@ -318,44 +316,44 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
       }
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
         // rescale this warp's 32 rows of O in place; block j-1's P V must have landed first
-        if (!__all_sync(0xffffffffu, mbar_wait(bar(O_FULL), bph ^ 1u, abort_flag))) {  // the warp leaves as one
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(O_FULL), ph ^ 1u, abort_flag))) {  // the warp leaves as one
           tmem_wait_ld();
           break;
         }
         fence_after();
-        tmem_wait_ld();  // the prefetched S chunk in `va` is complete before the registers below are reused
+        tmem_wait_ld();  // the prefetched S chunk in `va` is complete before more loads are issued
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t ov[32];
-          tmem_ld32(o_tmem + c * 32 + lane_addr, ov);
+        for (int c = 0; c < 4; ++c) {
+          uint32_t ov[16];
+          tmem_ld16(o_tmem + c * 16 + lane_addr, ov);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-          tmem_st32(o_tmem + c * 32 + lane_addr, ov);
+          for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+          tmem_st16(o_tmem + c * 16 + lane_addr, ov);
         }
         tmem_wait_st();
       }
       const float m_scaled = m_run * p.scale_log2e;
       // pass 2: probabilities -> shared memory (bf16, swizzled) and their sum
-      if (!mbar_wait(bar(P_EMPTY), bph ^ 1u, abort_flag)) {
+      if (!mbar_wait(bar(P_EMPTY), ph ^ 1u, abort_flag)) {
         tmem_wait_ld();  // no load may be outstanding when the kernel unwinds
         break;
       }
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
-      auto exp_chunk = [&](const uint32_t (&v)[32], int c) {
-        float e[32];
+      auto exp_chunk = [&](const uint32_t (&v)[16], int c) {
+        float e[16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < 16; ++i) {
           const float x = __uint_as_float(v[i]);
-          const bool keep = !diagonal || (j * BKV + c * 32 + i) <= q_idx;
+          const bool keep = !diagonal || (k0 + c * 16 + i) <= q_idx;
           e[i] = keep ? fast_exp2(fmaf(x, p.scale_log2e, -m_scaled)) : 0.f;
           ls[i & 3] += e[i];
         }
-        // 32 keys = 64 bytes = four 16-byte pieces of this row in half (c >> 1)
-        const uint32_t row_addr = p_smem + (c >> 1) * 16384 + r * 128;
+        // 16 keys = 32 bytes = two 16-byte pieces of this row
+        const uint32_t row_addr = p_smem + r * 128;
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int piece = (c & 1) * 4 + g;
+        for (int g = 0; g < 2; ++g) {
+          const int piece = c * 2 + g;
           const uint32_t addr = row_addr + ((piece ^ (r & 7)) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack2(e[g * 8 + 0], e[g * 8 + 1])),
                        "r"(pack2(e[g * 8 + 2], e[g * 8 + 3])), "r"(pack2(e[g * 8 + 4], e[g * 8 + 5])),
@@ -364,13 +362,13 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
         }
       };
       tmem_wait_ld();
-      tmem_ld32(s_tmem + 1 * 32 + lane_addr, vb);
+      tmem_ld16(s_tmem + 16 + lane_addr, vb);
       exp_chunk(va, 0);
       tmem_wait_ld();
-      tmem_ld32(s_tmem + 2 * 32 + lane_addr, va);
+      tmem_ld16(s_tmem + 32 + lane_addr, va);
       exp_chunk(vb, 1);
       tmem_wait_ld();
-      tmem_ld32(s_tmem + 3 * 32 + lane_addr, vb);
+      tmem_ld16(s_tmem + 48 + lane_addr, vb);
       exp_chunk(va, 2);
       tmem_wait_ld();
       exp_chunk(vb, 3);
@@ -385,31 +383,26 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
     }
     // the last block's P V completes the accumulator
     const bool done = ok && mbar_wait(bar(O_FULL), (num_kv - 1) & 1, abort_flag);
-    float o[HD];
-    if (done) {
-      fence_after();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        tmem_ld32(o_tmem + c * 32 + lane_addr, v);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = __uint_as_float(v[i]);
-      }
-    }
     if (done && !*abort_flag && q_idx < p.T &&
         CS_IN_BOUNDS(kKidAttention, (static_cast<long long>(row_base + q_idx) * p.H + h) * HD + HD - 1,
                      static_cast<long long>(p.B) * p.T * p.H * HD)) {
+      fence_after();
       const float inv = 1.f / l_run;
       __nv_bfloat16 *dst = p.out + (static_cast<long long>(row_base + q_idx) * p.H + h) * HD;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[16];
+        tmem_ld16(o_tmem + c * 16 + lane_addr, v);
+        tmem_wait_ld();
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        uint4 w;
-        w.x = pack2(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv);
-        w.y = pack2(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv);
-        w.z = pack2(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv);
-        w.w = pack2(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv);
-        *reinterpret_cast<uint4 *>(dst + g * 8) = w;
+        for (int g = 0; g < 2; ++g) {
+          uint4 w;
+          w.x = pack2(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
+          w.y = pack2(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
+          w.z = pack2(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
+          w.w = pack2(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
+          *reinterpret_cast<uint4 *>(dst + c * 16 + g * 8) = w;
+        }
       }
       p.lse[(static_cast<long long>(b) * p.H + h) * p.T + q_idx] = m_run * p.scale + __logf(l_run);
     }
@@ -425,7 +418,7 @@ __global__ void __launch_bounds__(THREADS, 2) attention_fwd_kernel(const __grid_
   }
   if (warp == 1) {
     fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(FWD_TMEM_COLS) : "memory");
   }
 }
 
@@ -816,8 +809,8 @@ int attention_forward_packed(stream_t stream, const void *qkv, void *out, float 
   if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(out)) & 15) return -1;
   static const bool disabled = std::getenv("CS_DISABLE_TCGEN05_ATTENTION") != nullptr;
   if (disabled) return -1;
-  CUtensorMap map;
-  if (!attn_map(&map, qkv, 3 * H * D, B * T, 128)) return -1;
+  CUtensorMap map_q, map_kv;
+  if (!attn_map(&map_q, qkv, 3 * H * D, B * T, BQ) || !attn_map(&map_kv, qkv, 3 * H * D, B * T, BKV)) return -1;
   static const bool attr_set =
       cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) == cudaSuccess;
   if (!attr_set) return -1;
@@ -831,7 +824,7 @@ int attention_forward_packed(stream_t stream, const void *qkv, void *out, float 
   p.scale_log2e = scale * 1.4426950408889634f;
   p.status = attn_status_ptr();
   dim3 grid(static_cast<unsigned>(T / BQ), static_cast<unsigned>(H), static_cast<unsigned>(B));
-  attention_fwd_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map, p);
+  attention_fwd_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map_q, map_kv, p);
   return finish_launch(1);
 }
 
