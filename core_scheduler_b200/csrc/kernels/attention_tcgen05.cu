@@ -44,6 +44,13 @@ constexpr int TMEM_COLS = 256;             // backward: S', dP' and two accumula
 constexpr long long kWaitBudgetCycles = 4000000000LL;
 
 __device__ DeviceStatus g_attn_status;
+// Cycle trace of CTA (0,0,0) of the backward dK/dV kernel: clock64() at the phase boundaries of each
+// streamed tile (8 slots per tile, 32 tiles). Written only when the launch asks for it.
+__device__ long long g_attn_trace[256];
+#define CS_TRACE(slot)                                                                            \
+  do {                                                                                            \
+    if (trace_on && t < 32) g_attn_trace[t * 8 + (slot)] = clock64();                             \
+  } while (0)
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -83,6 +90,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
+}
+// Brings a tile into L2 ahead of the TMA load that will need it (no shared memory, no barrier).
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1)
+               : "memory");
 }
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -223,8 +235,17 @@ __global__ void __launch_bounds__(THREADS, FWD_CTAS_PER_SM) attention_fwd_kernel
       const int q_col = h * HD, k_col = (p.H + h) * HD, v_col = (2 * p.H + h) * HD;
       mbar_expect_tx(bar(Q_FULL), TILE_BYTES);
       tma_load_2d(q_smem, &map_q, bar(Q_FULL), q_col, row_base + q0);
+      constexpr int kAhead = 3;  // tiles requested into L2 before their shared-memory stage is free
+      for (int j = 1; j < kAhead && j < num_kv; ++j) {
+        tma_prefetch_2d(&map_kv, k_col, row_base + j * BKV);
+        tma_prefetch_2d(&map_kv, v_col, row_base + j * BKV);
+      }
       for (int j = 0; j < num_kv; ++j) {
         const uint32_t ph = j & 1;
+        if (j + kAhead < num_kv) {
+          tma_prefetch_2d(&map_kv, k_col, row_base + (j + kAhead) * BKV);
+          tma_prefetch_2d(&map_kv, v_col, row_base + (j + kAhead) * BKV);
+        }
         if (!mbar_wait(bar(K_EMPTY), ph ^ 1u, abort_flag)) break;
         mbar_expect_tx(bar(K_FULL), KV_TILE_BYTES);
         tma_load_2d(k_smem, &map_kv, bar(K_FULL), k_col, row_base + j * BKV);
@@ -238,6 +259,10 @@ __global__ void __launch_bounds__(THREADS, FWD_CTAS_PER_SM) attention_fwd_kernel
       // S = Q K^T: M=128, N=64, both operands K-major. O += P V: M=128, N=64, B (= V) MN-major.
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BKV >> 3) << 17) | (8u << 24);
       const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (static_cast<uint32_t>(HD >> 3) << 17) | (8u << 24);
+      // descriptors are built once; a k-step only advances the 16-byte-unit address field
+      const uint64_t d_q = smem_desc(q_smem, 16, 1024), d_k = smem_desc(k_smem, 16, 1024);
+      const uint64_t d_p = smem_desc(p_smem, 16, 1024), d_v = smem_desc(v_smem, 8192, 1024);
+      constexpr uint64_t kStepK = 32 >> 4, kStepMN = 2048 >> 4;
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag);
       auto issue_s = [&](int j) -> bool {
         const uint32_t ph = j & 1;
@@ -245,8 +270,7 @@ __global__ void __launch_bounds__(THREADS, FWD_CTAS_PER_SM) attention_fwd_kernel
         if (!mbar_wait(bar(S_EMPTY), ph ^ 1u, abort_flag)) return false;  // softmax of block j-1 has read S
         fence_after();
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          umma(s_tmem, smem_desc(q_smem + k * 32, 16, 1024), smem_desc(k_smem + k * 32, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+        for (int k = 0; k < HD / 16; ++k) umma(s_tmem, d_q + k * kStepK, d_k + k * kStepK, idesc_s, k > 0 ? 1u : 0u);
         umma_commit(bar(K_EMPTY));
         umma_commit(bar(S_FULL));
         return true;
@@ -254,14 +278,14 @@ __global__ void __launch_bounds__(THREADS, FWD_CTAS_PER_SM) attention_fwd_kernel
       if (ok) ok = issue_s(0);
       for (int j = 0; ok && j < num_kv; ++j) {
         const uint32_t ph = j & 1;
-        if (!mbar_wait(bar(P_FULL), ph, abort_flag)) break;
-        if (j + 1 < num_kv) ok = issue_s(j + 1);  // S is free again once P of block j exists
+        if (j + 1 < num_kv) ok = issue_s(j + 1);  // as soon as the softmax warps have read S of block j (S_EMPTY)
         if (!ok) break;
+        if (!mbar_wait(bar(P_FULL), ph, abort_flag)) break;
         if (!mbar_wait(bar(V_FULL), ph, abort_flag)) break;
         fence_after();
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k)  // P: one K-major tile; V: MN-major, 16 keys = 2 KB per step
-          umma(o_tmem, smem_desc(p_smem + k * 32, 16, 1024), smem_desc(v_smem + k * 2048, 8192, 1024), idesc_o, (j | k) ? 1u : 0u);
+          umma(o_tmem, d_p + k * kStepK, d_v + k * kStepMN, idesc_o, (j | k) ? 1u : 0u);
         umma_commit(bar(V_EMPTY));
         umma_commit(bar(P_EMPTY));
         umma_commit(bar(O_FULL));
@@ -371,14 +395,15 @@ __global__ void __launch_bounds__(THREADS, FWD_CTAS_PER_SM) attention_fwd_kernel
       tmem_ld16(s_tmem + 48 + lane_addr, vb);
       exp_chunk(va, 2);
       tmem_wait_ld();
+      // every score of this block has been read: the tensor core may start the next block's S
+      fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(S_EMPTY));
       exp_chunk(vb, 3);
       fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar(S_EMPTY));
-        mbar_arrive(bar(P_FULL));
-      }
+      if (lane == 0) mbar_arrive(bar(P_FULL));
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
     }
     // the last block's P V completes the accumulator
@@ -434,12 +459,17 @@ __global__ void __launch_bounds__(THREADS, FWD_CTAS_PER_SM) attention_fwd_kernel
 //   P' = exp(scale S' - lse), dS' = scale P' (dP' - delta)   (softmax warps, one thread per row)
 //   [dV += P' C2]   acc += dS' C1            (128 x 64 x 64; P'/dS' from swizzled shared memory, C as
 //                                             MN-major operands)
-// 256 TMEM columns and ~99 KB of shared memory per CTA: two CTAs per SM overlap each other's softmax.
+// 256 TMEM columns and ~99 KB of shared memory per CTA: two CTAs per SM; eight softmax warps per CTA
+// (two threads per row, 32 of the 64 streamed columns each: the backward needs no row reductions).
 constexpr int BC = 64;                          // streamed rows per step
 constexpr int C_TILE_BYTES = BC * HD * 2;       // 8 KB
 constexpr int PS_BYTES = 128 * BC * 2;          // 16 KB: P' or dS'
-constexpr int BWD_STAGES = 2;
-constexpr int BWD_SMEM_BYTES = 2 * TILE_BYTES + BWD_STAGES * (2 * C_TILE_BYTES + 512) + 2 * PS_BYTES + 1024 + 256;
+// streamed-tile stages: the dQ kernel has room for three (no P' tile); the dK/dV kernel for two
+constexpr int bwd_stages(bool dkv) { return dkv ? 2 : 3; }
+constexpr int BWD_THREADS = 320;  // TMA warp, MMA warp, eight softmax warps (two threads per row: 32 columns each)
+constexpr int bwd_smem_bytes(bool dkv) {
+  return 2 * TILE_BYTES + bwd_stages(dkv) * (2 * C_TILE_BYTES + 512) + (dkv ? 2 : 1) * PS_BYTES + 1024 + 256;
+}
 
 struct AttnBwdParams {
   __nv_bfloat16 *dqkv;  // [B, T, 3, H, 64]
@@ -448,6 +478,7 @@ struct AttnBwdParams {
   int B, T, H;
   float scale, scale_log2e;
   DeviceStatus *status;
+  int trace;  // 1: CTA (0,0,0) of the dK/dV kernel records g_attn_trace
 };
 
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
@@ -489,7 +520,7 @@ __global__ void __launch_bounds__(256) attention_delta_kernel(const __nv_bfloat1
 }
 
 template <bool kDKV>
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(BWD_THREADS, 2)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_constant__ CUtensorMap qkv_c,
                      const __grid_constant__ CUtensorMap do_r, const __grid_constant__ CUtensorMap do_c, const AttnBwdParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -498,13 +529,14 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
   const uint32_t r1_smem = base;                      // resident operand of S'
   const uint32_t r2_smem = r1_smem + TILE_BYTES;      // resident operand of dP'
   const uint32_t c_smem = r2_smem + TILE_BYTES;       // per stage: C1 tile, C2 tile
-  const uint32_t p_smem = c_smem + BWD_STAGES * 2 * C_TILE_BYTES;
-  const uint32_t ds_smem = p_smem + PS_BYTES;
+  constexpr int STAGES = bwd_stages(kDKV);
+  const uint32_t p_smem = c_smem + STAGES * 2 * C_TILE_BYTES;  // P' exists only in the dK/dV kernel
+  const uint32_t ds_smem = p_smem + (kDKV ? PS_BYTES : 0);
   const uint32_t vec_smem = ds_smem + PS_BYTES;       // per stage: lse[64], delta[64] of the streamed queries
-  const uint32_t bar_base = vec_smem + BWD_STAGES * 512;
+  const uint32_t bar_base = vec_smem + STAGES * 512;
   uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + (bar_base - base));
   const float *vec = reinterpret_cast<const float *>(aligned + (vec_smem - base));
-  enum { R_FULL = 0, C_FULL = 1, C_EMPTY = 3, SDP_FULL = 5, SDP_EMPTY = 6, PDS_FULL = 7, PDS_EMPTY = 8, ACC_FULL = 9, NUM_BARS = 10 };
+  enum { R_FULL = 0, C_FULL = 1, C_EMPTY = 4, SDP_FULL = 7, SDP_EMPTY = 8, PDS_FULL = 9, PDS_EMPTY = 10, ACC_FULL = 11, NUM_BARS = 12 };
   auto bar = [&](int i) { return bar_base + 8u * i; };
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars + NUM_BARS);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + NUM_BARS + 1);
@@ -518,16 +550,17 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
   // streamed 64-row tiles: queries r0 .. T (kDKV) or keys 0 .. r0+128
   const int c_first = kDKV ? 2 * rb : 0;
   const int n_iter = kDKV ? p.T / BC - c_first : 2 * (rb + 1);
+  const bool trace_on = kDKV && p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 
   if (threadIdx.x == 0) {
     mbar_init(bar(R_FULL), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar(C_FULL + s), 1);
       mbar_init(bar(C_EMPTY + s), 1);
     }
     mbar_init(bar(SDP_FULL), 1);
-    mbar_init(bar(SDP_EMPTY), 4);
-    mbar_init(bar(PDS_FULL), 4);
+    mbar_init(bar(SDP_EMPTY), 8);  // one arrival per softmax warp
+    mbar_init(bar(PDS_FULL), 8);
     mbar_init(bar(PDS_EMPTY), 1);
     mbar_init(bar(ACC_FULL), 1);
     *abort_flag = 0;
@@ -561,11 +594,25 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
       }
       const float *lse_row = p.lse + (static_cast<long long>(b) * p.H + h) * p.T;
       const float *delta_row = p.delta + (static_cast<long long>(b) * p.H + h) * p.T;
-      for (int t = 0; t < n_iter; ++t) {
-        const int s = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
+      constexpr int kAhead = 4;  // tiles requested into L2 before their shared-memory stage is free
+      auto prefetch = [&](int t) {
         const int c0 = (c_first + t) * BC;
+        if (kDKV) {
+          tma_prefetch_2d(&qkv_c, q_col, row_base + c0);
+          tma_prefetch_2d(&do_c, q_col, row_base + c0);
+        } else {
+          tma_prefetch_2d(&qkv_c, k_col, row_base + c0);
+          tma_prefetch_2d(&qkv_c, v_col, row_base + c0);
+        }
+      };
+      for (int t = STAGES; t < kAhead && t < n_iter; ++t) prefetch(t);
+      for (int t = 0; t < n_iter; ++t) {
+        const int s = t % STAGES;
+        const uint32_t ph = (t / STAGES) & 1;
+        const int c0 = (c_first + t) * BC;
+        if (t + kAhead < n_iter) prefetch(t + kAhead);
         if (!mbar_wait(bar(C_EMPTY + s), ph ^ 1u, abort_flag)) break;
+        CS_TRACE(0);
         const uint32_t c1 = c_smem + s * 2 * C_TILE_BYTES, c2 = c1 + C_TILE_BYTES;
         if (kDKV) {
           mbar_expect_tx(bar(C_FULL + s), 2 * C_TILE_BYTES + 512);
@@ -585,44 +632,55 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
       // S', dP': M=128, N=64, both operands K-major. Accumulators: M=128, N=64, B MN-major.
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BC >> 3) << 17) | (8u << 24);
       const uint32_t idesc_a = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (static_cast<uint32_t>(HD >> 3) << 17) | (8u << 24);
+      // Descriptors are built once; a k-step only advances the 16-byte-unit address field (the MMA thread
+      // shares its scheduler with softmax warps, so every instruction it saves shortens the critical path).
+      const uint64_t d_r1 = smem_desc(r1_smem, 16, 1024), d_r2 = smem_desc(r2_smem, 16, 1024);
+      const uint64_t d_p = smem_desc(p_smem, 16, 1024), d_ds = smem_desc(ds_smem, 16, 1024);
+      // stage 1 lies 2 * C_TILE_BYTES behind stage 0: one more constant added to the address field
+      const uint64_t d_c1k0 = smem_desc(c_smem, 16, 1024), d_c2k0 = smem_desc(c_smem + C_TILE_BYTES, 16, 1024);
+      const uint64_t d_c1m0 = smem_desc(c_smem, 8192, 1024), d_c2m0 = smem_desc(c_smem + C_TILE_BYTES, 8192, 1024);
+      constexpr uint64_t kStage = (2 * C_TILE_BYTES) >> 4;
+      constexpr uint64_t kStepK = 32 >> 4, kStepMN = 2048 >> 4;  // 16 elements along K: 32 bytes K-major, 2 KB MN-major
       bool ok = mbar_wait(bar(R_FULL), 0, abort_flag);
       auto issue_sdp = [&](int t) -> bool {
-        const int s = t & 1;
-        if (!mbar_wait(bar(C_FULL + s), (t >> 1) & 1, abort_flag)) return false;
+        const int s = t % STAGES;
+        if (!mbar_wait(bar(C_FULL + s), (t / STAGES) & 1, abort_flag)) return false;
         if (!mbar_wait(bar(SDP_EMPTY), (t & 1) ^ 1u, abort_flag)) return false;
         fence_after();
-        const uint32_t c1 = c_smem + s * 2 * C_TILE_BYTES, c2 = c1 + C_TILE_BYTES;
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          umma(s_tmem, smem_desc(r1_smem + k * 32, 16, 1024), smem_desc(c1 + k * 32, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+        for (int k = 0; k < HD / 16; ++k) umma(s_tmem, d_r1 + k * kStepK, d_c1k0 + s * kStage + k * kStepK, idesc_s, k > 0 ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          umma(dp_tmem, smem_desc(r2_smem + k * 32, 16, 1024), smem_desc(c2 + k * 32, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+        for (int k = 0; k < HD / 16; ++k) umma(dp_tmem, d_r2 + k * kStepK, d_c2k0 + s * kStage + k * kStepK, idesc_s, k > 0 ? 1u : 0u);
         umma_commit(bar(SDP_FULL));
         return true;
       };
       if (ok) ok = issue_sdp(0);
       int t = 0;
       for (; ok && t < n_iter; ++t) {
-        const int s = t & 1;
-        if (!mbar_wait(bar(PDS_FULL), t & 1, abort_flag)) break;
+        const int s = t % STAGES;
+        // The scores of tile t+1 are issued as soon as the softmax warps hold tile t's S' / dP' in registers
+        // (SDP_EMPTY), i.e. while they still compute; the accumulating MMAs of tile t follow once P' / dS' exist.
         if (t + 1 < n_iter) ok = issue_sdp(t + 1);
         if (!ok) break;
+        CS_TRACE(2);
+        if (!mbar_wait(bar(PDS_FULL), t & 1, abort_flag)) break;
+        CS_TRACE(1);
         fence_after();
-        const uint32_t c1 = c_smem + s * 2 * C_TILE_BYTES, c2 = c1 + C_TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < BC / 16; ++k) {
-          if (kDKV) umma(acc1_tmem, smem_desc(p_smem + k * 32, 16, 1024), smem_desc(c2 + k * 2048, 8192, 1024), idesc_a, (t | k) ? 1u : 0u);
-          umma(acc2_tmem, smem_desc(ds_smem + k * 32, 16, 1024), smem_desc(c1 + k * 2048, 8192, 1024), idesc_a, (t | k) ? 1u : 0u);
+          if (kDKV) umma(acc1_tmem, d_p + k * kStepK, d_c2m0 + s * kStage + k * kStepMN, idesc_a, (t | k) ? 1u : 0u);
+          umma(acc2_tmem, d_ds + k * kStepK, d_c1m0 + s * kStage + k * kStepMN, idesc_a, (t | k) ? 1u : 0u);
         }
         umma_commit(bar(PDS_EMPTY));
         umma_commit(bar(C_EMPTY + s));
+        CS_TRACE(3);
       }
       if (ok && t == n_iter) umma_commit(bar(ACC_FULL));
     }
   } else {
-    const int q = warp & 3;
-    const int r = q * 32 + lane;  // row of the resident block
+    const int q = warp & 3;            // TMEM lane quarter this warp may access
+    const int half = (warp - 2) >> 2;  // which 32 of the 64 streamed columns this thread handles
+    const int r = q * 32 + lane;       // row of the resident block
     const int r_idx = r0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const float log2e = 1.4426950408889634f;
@@ -633,28 +691,34 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
     }
     bool ok = true;
     for (int t = 0; ok && t < n_iter; ++t) {
-      const int s = t & 1;
+      const int s = t % STAGES;
       const int c0 = (c_first + t) * BC;
-      if (kDKV && !mbar_wait(bar(C_FULL + s), (t >> 1) & 1, abort_flag)) break;  // lse / delta of the streamed queries
+      if (kDKV && !mbar_wait(bar(C_FULL + s), (t / STAGES) & 1, abort_flag)) break;  // lse / delta of the streamed queries
       if (!mbar_wait(bar(SDP_FULL), t & 1, abort_flag)) break;
+      if (threadIdx.x == 64) CS_TRACE(4);
       fence_after();
-      if (!mbar_wait(bar(PDS_EMPTY), (t & 1) ^ 1u, abort_flag)) break;
       // rows are keys and columns queries (kDKV), or rows queries and columns keys: keep key <= query
       const bool near_diag = kDKV ? (c0 < r0 + 128) : (c0 + BC > r0);
       const float *lse_c = vec + s * 128, *delta_c = lse_c + 64;
       // 16 columns at a time; the TMEM loads of the next 16 are in flight while these are processed
-      auto process = [&](const uint32_t (&sv)[16], const uint32_t (&dv)[16], int c) {
-        float pr[16], ds[16];
+      auto compute = [&](const uint32_t (&sv)[16], const uint32_t (&dv)[16], int c, uint32_t (&pp)[8], uint32_t (&dd)[8]) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int col = c0 + c * 16 + i;
-          const bool keep = !near_diag || (kDKV ? (r_idx <= col) : (col <= r_idx));
-          const float l2 = kDKV ? lse_c[c * 16 + i] * log2e : lse_r;
-          const float dl = kDKV ? delta_c[c * 16 + i] : delta_r;
-          const float e = keep ? fast_exp2(fmaf(__uint_as_float(sv[i]), p.scale_log2e, -l2)) : 0.f;
-          pr[i] = e;
-          ds[i] = e * (__uint_as_float(dv[i]) - dl) * p.scale;
+        for (int i = 0; i < 16; i += 2) {
+          float e2[2], d2[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = c0 + c * 16 + i + u;
+            const bool keep = !near_diag || (kDKV ? (r_idx <= col) : (col <= r_idx));
+            const float l2 = kDKV ? lse_c[c * 16 + i + u] * log2e : lse_r;
+            const float dl = kDKV ? delta_c[c * 16 + i + u] : delta_r;
+            e2[u] = keep ? fast_exp2(fmaf(__uint_as_float(sv[i + u]), p.scale_log2e, -l2)) : 0.f;
+            d2[u] = e2[u] * (__uint_as_float(dv[i + u]) - dl) * p.scale;
+          }
+          pp[i >> 1] = pack2(e2[0], e2[1]);
+          dd[i >> 1] = pack2(d2[0], d2[1]);
         }
+      };
+      auto store = [&](const uint32_t (&pp)[8], const uint32_t (&dd)[8], int c) {
         // 16 columns = 32 bytes = two 16-byte pieces of this row
         const uint32_t row_off = r * 128;
 #pragma unroll
@@ -662,40 +726,40 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
           const int piece = c * 2 + g;
           const uint32_t off = row_off + ((piece ^ (r & 7)) << 4);
           if (kDKV)
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_smem + off), "r"(pack2(pr[g * 8 + 0], pr[g * 8 + 1])),
-                         "r"(pack2(pr[g * 8 + 2], pr[g * 8 + 3])), "r"(pack2(pr[g * 8 + 4], pr[g * 8 + 5])),
-                         "r"(pack2(pr[g * 8 + 6], pr[g * 8 + 7]))
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_smem + off), "r"(pp[g * 4 + 0]), "r"(pp[g * 4 + 1]),
+                         "r"(pp[g * 4 + 2]), "r"(pp[g * 4 + 3])
                          : "memory");
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ds_smem + off), "r"(pack2(ds[g * 8 + 0], ds[g * 8 + 1])),
-                       "r"(pack2(ds[g * 8 + 2], ds[g * 8 + 3])), "r"(pack2(ds[g * 8 + 4], ds[g * 8 + 5])),
-                       "r"(pack2(ds[g * 8 + 6], ds[g * 8 + 7]))
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ds_smem + off), "r"(dd[g * 4 + 0]), "r"(dd[g * 4 + 1]),
+                       "r"(dd[g * 4 + 2]), "r"(dd[g * 4 + 3])
                        : "memory");
         }
       };
       uint32_t sa[16], da[16], sb[16], db[16];
-      tmem_ld16(s_tmem + 0 + lane_addr, sa);
-      tmem_ld16(dp_tmem + 0 + lane_addr, da);
+      uint32_t pa[8], qa[8], pb[8], qb2[8];
+      const int cb = half * 2;  // first 16-column chunk of this thread
+      tmem_ld16(s_tmem + cb * 16 + lane_addr, sa);
+      tmem_ld16(dp_tmem + cb * 16 + lane_addr, da);
       tmem_wait_ld();
-      tmem_ld16(s_tmem + 16 + lane_addr, sb);
-      tmem_ld16(dp_tmem + 16 + lane_addr, db);
-      process(sa, da, 0);
+      tmem_ld16(s_tmem + cb * 16 + 16 + lane_addr, sb);
+      tmem_ld16(dp_tmem + cb * 16 + 16 + lane_addr, db);
+      compute(sa, da, cb, pa, qa);
       tmem_wait_ld();
-      tmem_ld16(s_tmem + 32 + lane_addr, sa);
-      tmem_ld16(dp_tmem + 32 + lane_addr, da);
-      process(sb, db, 1);
-      tmem_wait_ld();
-      tmem_ld16(s_tmem + 48 + lane_addr, sb);
-      tmem_ld16(dp_tmem + 48 + lane_addr, db);
-      process(sa, da, 2);
-      tmem_wait_ld();
-      process(sb, db, 3);
+      // S' and dP' of this tile now live in registers: the tensor core may overwrite them with the next tile
+      fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(SDP_EMPTY));
+      compute(sb, db, cb + 1, pb, qb2);
+      // the previous tile's accumulating MMAs must have read P' / dS' before they are overwritten
+      if (!mbar_wait(bar(PDS_EMPTY), (t & 1) ^ 1u, abort_flag)) break;
+      if (threadIdx.x == 64) CS_TRACE(5);
+      store(pa, qa, cb);
+      store(pb, qb2, cb + 1);
+      if (threadIdx.x == 64) CS_TRACE(6);
       fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar(SDP_EMPTY));
-        mbar_arrive(bar(PDS_FULL));
-      }
+      if (lane == 0) mbar_arrive(bar(PDS_FULL));
+      if (threadIdx.x == 64) CS_TRACE(7);
     }
     if (mbar_wait(bar(ACC_FULL), 0, abort_flag) && !*abort_flag) {
       fence_after();
@@ -703,21 +767,18 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
       const bool row_in_range =
           CS_IN_BOUNDS(kKidAttention, (row + 2LL * p.H + h) * HD + HD - 1, static_cast<long long>(p.B) * p.T * 3 * p.H * HD);
       auto store = [&](uint32_t tmem, int part) {
-        __nv_bfloat16 *dst = p.dqkv + (row + static_cast<long long>(part) * p.H + h) * HD;
+        __nv_bfloat16 *dst = p.dqkv + (row + static_cast<long long>(part) * p.H + h) * HD + half * 32;
+        uint32_t v[32];
+        tmem_ld32(tmem + half * 32 + lane_addr, v);
+        tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t v[32];
-          tmem_ld32(tmem + c * 32 + lane_addr, v);
-          tmem_wait_ld();
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 w;
-            w.x = pack2(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
-            w.y = pack2(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
-            w.z = pack2(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
-            w.w = pack2(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
-            *reinterpret_cast<uint4 *>(dst + c * 32 + g * 8) = w;
-          }
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = pack2(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
+          w.y = pack2(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
+          w.z = pack2(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
+          w.w = pack2(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
+          *reinterpret_cast<uint4 *>(dst + g * 8) = w;
         }
       };
       if (row_in_range) {
@@ -828,6 +889,10 @@ int attention_forward_packed(stream_t stream, const void *qkv, void *out, float 
   return finish_launch(1);
 }
 
+int attention_trace(long long *out, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out, g_attn_trace, sizeof(long long) * static_cast<size_t>(n < 256 ? n : 256)));
+}
+
 int attention_backward_packed(stream_t stream, const void *qkv, const void *out, const void *dout, const float *lse, float *delta,
                               void *dqkv, int64_t B, int64_t T, int64_t H, int64_t D, float scale) {
   if (D != HD || T % 128 != 0 || B <= 0 || H <= 0 || T <= 0) return -1;
@@ -841,8 +906,8 @@ int attention_backward_packed(stream_t stream, const void *qkv, const void *out,
       !attn_map(&do_r, dout, H * D, B * T, 128) || !attn_map(&do_c, dout, H * D, B * T, BC))
     return -1;
   static const bool attr_set =
-      cudaFuncSetAttribute(attention_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM_BYTES) == cudaSuccess &&
-      cudaFuncSetAttribute(attention_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM_BYTES) == cudaSuccess;
+      cudaFuncSetAttribute(attention_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_smem_bytes(true)) == cudaSuccess &&
+      cudaFuncSetAttribute(attention_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_smem_bytes(false)) == cudaSuccess;
   if (!attr_set) return -1;
   auto s = static_cast<cudaStream_t>(stream);
   const long long threads = B * T * H * 8;
@@ -859,9 +924,11 @@ int attention_backward_packed(stream_t stream, const void *qkv, const void *out,
   p.scale = scale;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.status = attn_status_ptr();
+  static const bool trace = std::getenv("CS_ATTENTION_TRACE") != nullptr;
+  p.trace = trace ? 1 : 0;
   dim3 grid(static_cast<unsigned>(T / 128), static_cast<unsigned>(H), static_cast<unsigned>(B));
-  attention_bwd_kernel<true><<<grid, THREADS, BWD_SMEM_BYTES, s>>>(qkv_r, qkv_c, do_r, do_c, p);
-  attention_bwd_kernel<false><<<grid, THREADS, BWD_SMEM_BYTES, s>>>(qkv_r, qkv_c, do_r, do_c, p);
+  attention_bwd_kernel<true><<<grid, BWD_THREADS, bwd_smem_bytes(true), s>>>(qkv_r, qkv_c, do_r, do_c, p);
+  attention_bwd_kernel<false><<<grid, BWD_THREADS, bwd_smem_bytes(false), s>>>(qkv_r, qkv_c, do_r, do_c, p);
   return finish_launch(3);
 }
 CS_DEFINE_BOUNDS_GETTER(bounds_report_attention)

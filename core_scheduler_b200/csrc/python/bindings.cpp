@@ -145,6 +145,11 @@ PYBIND11_MODULE(_C, m) {
     CS_ASSERT_TRUE(rc == 0, "bounds_report failed: ", rc);
     return py::make_tuple(r.code, r.kernel_id, r.block, r.thread, static_cast<int64_t>(r.index), static_cast<int64_t>(r.limit));
   }, py::arg("reset") = true, "(code, kernel id, block, thread, index, limit) of the first out-of-range index; code 0 = none");
+  m.def("attention_trace", [] {
+    std::vector<long long> v(256);
+    cs::kernels::attention_trace(v.data(), 256);
+    return v;
+  });
   m.def("attention_status", [] {
     cs::kernels::DeviceStatus st{};
     cs::kernels::attention_status(&st);
