@@ -44,11 +44,60 @@ def parse_args():
 
 
 def reference_arm(args):
-    # The reference is a CMake C++ project without setup.py/pyproject.toml, so the prescribed
-    # `pip install --target baseline/_ref /root/reference` stops with "not installable".
-    print(json.dumps({"impl": "reference",
-                      "unavailable": "reference is a CMake C++ library (no setup.py/pyproject.toml): pip install "
-                                     "--target baseline/_ref fails; it also needs MPI/hwloc/cxxopts which the image lacks"}))
+    """Runs the unmodified reference library (built by baseline/build_reference.py into baseline/_ref/) through
+    its own public API: baseline/_ref/ref_gpt2 is a GPT-2 driver that links only that library. One driver process
+    per rank; it times K steps on the device between two full synchronisations and takes the max over ranks."""
+    import subprocess
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    exe = os.path.join(here, "baseline", "_ref", "ref_gpt2")
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not os.path.exists(exe):
+        if rank == 0:
+            print(json.dumps({"impl": "reference",
+                              "unavailable": "baseline/_ref/ref_gpt2 is not built: run python baseline/build_reference.py "
+                                             "(the reference is a CMake C++ project; pip install of it is not possible)"}))
+        return 0
+    if args.mode != "dp":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": f"the reference has no {args.mode} mode (data parallel only)"}))
+        return 0
+    # the clock sampler is loaded by file so that nothing of this repository's package (and none of its
+    # native libraries) is imported into the reference arm's processes
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("cs_clocks", os.path.join(here, "core_scheduler_b200", "utils", "clocks.py"))
+    clocks_mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(clocks_mod)
+    ClockSampler = clocks_mod.ClockSampler
+
+    env = dict(os.environ, CS_MPISHIM_KEY=f"{os.getppid()}")
+    cmd = [exe, "--model", args.model, "--micro-batch", str(args.micro_batch), "--seq", str(args.seq_len), "--steps", str(args.steps),
+           "--warmup", str(args.warmup), "--bucket-mb", str(args.bucket_mb)]
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True)
+    clocks = sampler.stop() if sampler else None
+    line = next((l for l in proc.stdout.splitlines() if l.startswith("REF_RESULT")), None)
+    if rank != 0:
+        return 0 if proc.returncode == 0 else 1
+    if proc.returncode != 0 or line is None:
+        tail = (proc.stdout + proc.stderr).strip().splitlines()[-3:]
+        print(json.dumps({"impl": "reference", "unavailable": "reference driver failed: " + " | ".join(tail)[:400]}))
+        return 0
+    fields = dict(kv.split("=") for kv in line.split()[1:])
+    ms = float(fields["ms_per_step"])
+    print(json.dumps({
+        "metric": "GPT-2 train tokens/sec, device-timed max over ranks", "value": float(fields["tokens_per_s"]), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights N(0,0.02)", "impl": "reference",
+        "config": {"model": f"GPT-2 {args.model}", "global_batch": args.micro_batch * world, "micro_batch_per_gpu": args.micro_batch,
+                   "seq_len": args.seq_len, "parallelism": f"dp{world}", "precision": "fp32 parameters under a bf16 autocast guard",
+                   "backend": "reference library (cuBLAS / ATen / flash attention / NCCL), unmodified sources",
+                   "bucket_mb": args.bucket_mb, "l2": "per-step working set exceeds the 126 MB L2; no flush needed"},
+        "final_loss": float(fields["final_loss"]), "clocks": clocks, "e2e": None, "gpu_launches": None}))
     return 0
 
 
