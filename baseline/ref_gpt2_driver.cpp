@@ -211,8 +211,10 @@ int main(int argc, char **argv) {
 
   cs::DynamicScheduler scheduler{local_rank};
   cs::manual_seed(1234);  // identical initial weights on every rank
-  Model model{scheduler, cfg};
-  cs::module::AdamW optimizer{scheduler, model, cs::optimizer::AdamW::Options{}.lr(3e-4).beta1(0.9).beta2(0.95).weight_decay(0.1)};
+  // the optimizer module keeps a weak reference to the model, which therefore has to be shared-owned
+  auto model_ptr = std::make_shared<Model>(scheduler, cfg);
+  Model &model = *model_ptr;
+  cs::module::AdamW optimizer{scheduler, model_ptr, cs::optimizer::AdamW::Options{}.lr(3e-4).beta1(0.9).beta2(0.95).weight_decay(0.1)};
   std::unique_ptr<cs::communication::Comm> comm;
   std::unique_ptr<cs::communication::AllReduceBucket> bucket;
   GradientQueue queue;
