@@ -130,7 +130,8 @@ int attention_forward_packed(stream_t stream, const void *qkv, void *out, float 
                              float scale);
 struct DeviceStatus;
 // Backward of the same attention: dqkv [B, T, 3, H, 64] from qkv, the forward output `out`, its
-// gradient `dout` [B, T, H*64] and `lse`; `delta` is a [B, H, T] fp32 workspace. Same shape limits.
+// gradient `dout` [B, T, H*64] and `lse`; `delta` is a [3, B, H, T] fp32 workspace (plane 0 receives
+// rowsum(dout * out)). Same shape limits.
 int attention_backward_packed(stream_t stream, const void *qkv, const void *out, const void *dout, const float *lse, float *delta,
                               void *dqkv, int64_t B, int64_t T, int64_t H, int64_t D, float scale);
 int attention_status(DeviceStatus *out);

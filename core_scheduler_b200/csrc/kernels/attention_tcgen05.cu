@@ -473,8 +473,8 @@ constexpr int bwd_smem_bytes(bool dkv) {
 
 struct AttnBwdParams {
   __nv_bfloat16 *dqkv;  // [B, T, 3, H, 64]
-  const float *lse;     // [B, H, T]
-  const float *delta;   // [B, H, T]
+  const float *lse;     // [B, H, T]: lse * log2(e)
+  const float *delta;   // [B, H, T]: delta * scale
   int B, T, H;
   float scale, scale_log2e;
   DeviceStatus *status;
@@ -488,7 +488,8 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
 }
 
 __global__ void __launch_bounds__(256) attention_delta_kernel(const __nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__restrict__ dout,
-                                                              float *__restrict__ delta, int B, int T, int H) {
+                                                              const float *__restrict__ lse, float *__restrict__ delta, int B, int T,
+                                                              int H, float scale) {
   // eight threads per (b, t, h) row of 64 values
   const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long row = gid >> 3;
@@ -515,7 +516,11 @@ __global__ void __launch_bounds__(256) attention_delta_kernel(const __nv_bfloat1
     const int h = static_cast<int>(row - bt * H);
     const long long b = bt / T;
     const int t = static_cast<int>(bt - b * T);
-    delta[(b * H + h) * T + t] = acc;
+    // plane 0: delta; plane 1: lse * log2(e); plane 2: delta * scale (what the two backward kernels consume)
+    const long long plane = static_cast<long long>(B) * H * T, at = (b * H + h) * T + t;
+    delta[at] = acc;
+    delta[plane + at] = lse[at] * 1.4426950408889634f;
+    delta[2 * plane + at] = acc * scale;
   }
 }
 
@@ -683,10 +688,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
     const int r = q * 32 + lane;       // row of the resident block
     const int r_idx = r0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-    const float log2e = 1.4426950408889634f;
     float lse_r = 0.f, delta_r = 0.f;
     if (!kDKV) {
-      lse_r = p.lse[(static_cast<long long>(b) * p.H + h) * p.T + r_idx] * log2e;
+      lse_r = p.lse[(static_cast<long long>(b) * p.H + h) * p.T + r_idx];
       delta_r = p.delta[(static_cast<long long>(b) * p.H + h) * p.T + r_idx];
     }
     bool ok = true;
@@ -701,21 +705,30 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
       const bool near_diag = kDKV ? (c0 < r0 + 128) : (c0 + BC > r0);
       const float *lse_c = vec + s * 128, *delta_c = lse_c + 64;
       // 16 columns at a time; the TMEM loads of the next 16 are in flight while these are processed
+      // per element: P' = exp2(S' * scale*log2e - lse*log2e), dS' = P' * (dP' * scale - delta*scale); the per-column
+      // constants (dK/dV kernel) come from shared memory four at a time
       auto compute = [&](const uint32_t (&sv)[16], const uint32_t (&dv)[16], int c, uint32_t (&pp)[8], uint32_t (&dd)[8]) {
 #pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          float e2[2], d2[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = c0 + c * 16 + i + u;
-            const bool keep = !near_diag || (kDKV ? (r_idx <= col) : (col <= r_idx));
-            const float l2 = kDKV ? lse_c[c * 16 + i + u] * log2e : lse_r;
-            const float dl = kDKV ? delta_c[c * 16 + i + u] : delta_r;
-            e2[u] = keep ? fast_exp2(fmaf(__uint_as_float(sv[i + u]), p.scale_log2e, -l2)) : 0.f;
-            d2[u] = e2[u] * (__uint_as_float(dv[i + u]) - dl) * p.scale;
+        for (int i = 0; i < 16; i += 4) {
+          float l2[4] = {lse_r, lse_r, lse_r, lse_r}, dl[4] = {delta_r, delta_r, delta_r, delta_r};
+          if (kDKV) {
+            const float4 a = *reinterpret_cast<const float4 *>(lse_c + c * 16 + i);
+            const float4 d = *reinterpret_cast<const float4 *>(delta_c + c * 16 + i);
+            l2[0] = a.x; l2[1] = a.y; l2[2] = a.z; l2[3] = a.w;
+            dl[0] = d.x; dl[1] = d.y; dl[2] = d.z; dl[3] = d.w;
           }
-          pp[i >> 1] = pack2(e2[0], e2[1]);
-          dd[i >> 1] = pack2(d2[0], d2[1]);
+          float e4[4], d4[4];
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = c0 + c * 16 + i + v;
+            const bool keep = !near_diag || (kDKV ? (r_idx <= col) : (col <= r_idx));
+            e4[v] = keep ? fast_exp2(fmaf(__uint_as_float(sv[i + v]), p.scale_log2e, -l2[v])) : 0.f;
+            d4[v] = e4[v] * fmaf(__uint_as_float(dv[i + v]), p.scale, -dl[v]);
+          }
+          pp[i >> 1] = pack2(e4[0], e4[1]);
+          pp[(i >> 1) + 1] = pack2(e4[2], e4[3]);
+          dd[i >> 1] = pack2(d4[0], d4[1]);
+          dd[(i >> 1) + 1] = pack2(d4[2], d4[3]);
         }
       };
       auto store = [&](const uint32_t (&pp)[8], const uint32_t (&dd)[8], int c) {
@@ -912,12 +925,12 @@ int attention_backward_packed(stream_t stream, const void *qkv, const void *out,
   auto s = static_cast<cudaStream_t>(stream);
   const long long threads = B * T * H * 8;
   attention_delta_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, s>>>(
-      static_cast<const __nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(dout), delta, static_cast<int>(B), static_cast<int>(T),
-      static_cast<int>(H));
+      static_cast<const __nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(dout), lse, delta, static_cast<int>(B),
+      static_cast<int>(T), static_cast<int>(H), scale);
   AttnBwdParams p{};
   p.dqkv = static_cast<__nv_bfloat16 *>(dqkv);
-  p.lse = lse;
-  p.delta = delta;
+  p.lse = delta + B * H * T;        // plane 1 of the workspace: lse * log2(e)
+  p.delta = delta + 2 * B * H * T;  // plane 2: delta * scale
   p.B = static_cast<int>(B);
   p.T = static_cast<int>(T);
   p.H = static_cast<int>(H);

@@ -131,12 +131,12 @@ PYBIND11_MODULE(_C, m) {
                                          int64_t heads, double scale) {
     const int64_t B = qkv.size(0), T = qkv.size(1), D = qkv.size(2) / (3 * heads);
     at::Tensor dqkv = at::empty_like(qkv);
-    at::Tensor delta = at::empty({B, heads, T}, qkv.options().dtype(at::kFloat));
+    at::Tensor delta = at::empty({3, B, heads, T}, qkv.options().dtype(at::kFloat));
     const int rc = cs::kernels::attention_backward_packed(c10::cuda::getCurrentCUDAStream().stream(), qkv.data_ptr(), out.data_ptr(),
                                                           dout.data_ptr(), lse.data_ptr<float>(), delta.data_ptr<float>(),
                                                           dqkv.data_ptr(), B, T, heads, D, static_cast<float>(scale));
     CS_ASSERT_TRUE(rc == 0, "attention_backward_packed returned ", rc);
-    return py::make_tuple(dqkv, delta);
+    return py::make_tuple(dqkv, delta.select(0, 0));
   });
   m.def("bounds_check_enabled", &cs::kernels::bounds_check_enabled);
   m.def("bounds_report", [](bool reset) {

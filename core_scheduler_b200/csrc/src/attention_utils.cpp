@@ -291,7 +291,7 @@ Tensor ScaledDotProductAttention::backward_packed(const Scheduler &scheduler, co
              const at::Tensor o_bthd = o.transpose(1, 2);
              if (o_bthd.is_contiguous()) {
                at::Tensor packed = at::empty({B, T, 3 * H * D}, x.options());
-               at::Tensor delta = at::empty({B, H, T}, x.options().dtype(at::kFloat));
+               at::Tensor delta = at::empty({3, B, H, T}, x.options().dtype(at::kFloat));
                const int code = kernels::attention_backward_packed(
                    current_stream(), x.data_ptr(), o_bthd.data_ptr(), go.data_ptr(), bw.logsumexp.impl()->tensor.data_ptr<float>(),
                    delta.data_ptr<float>(), packed.data_ptr(), B, T, H, D, static_cast<float>(resolve_scale(args.scale, D)));
