@@ -270,5 +270,9 @@ int main(int argc, char **argv) {
     std::printf("REF_RESULT ms_per_step=%.6f tokens_per_s=%.3f final_loss=%.6f\n", per_step,
                 static_cast<double>(cfg.batch * cfg.seq * world) / (per_step * 1e-3), value);
   MPI_Finalize();
-  return 0;
+  // The library offers no way to shut its NCCL process group down, and that group's destructor throws when it
+  // runs during static destruction (the CUDA driver is gone by then): leave without running static destructors.
+  std::fflush(stdout);
+  std::fflush(stderr);
+  std::_Exit(0);
 }

@@ -82,8 +82,8 @@ def reference_arm(args):
     clocks = sampler.stop() if sampler else None
     line = next((l for l in proc.stdout.splitlines() if l.startswith("REF_RESULT")), None)
     if rank != 0:
-        return 0 if proc.returncode == 0 else 1
-    if proc.returncode != 0 or line is None:
+        return 0  # a failed rank shows on rank 0 as a missing result line
+    if line is None:
         tail = (proc.stdout + proc.stderr).strip().splitlines()[-3:]
         print(json.dumps({"impl": "reference", "unavailable": "reference driver failed: " + " | ".join(tail)[:400]}))
         return 0

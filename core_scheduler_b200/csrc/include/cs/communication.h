@@ -63,6 +63,9 @@ CS_API Comm wrap_backend(c10::intrusive_ptr<c10d::Backend> backend, int64_t rank
                          c10::intrusive_ptr<c10d::Store> store = {});
 // Single-process communicator of size 1.
 CS_API Comm get_comm_self();
+// Shuts down and forgets the communicators created from the environment (get_comm_world / get_comm_node). Call
+// it before main() returns: their NCCL process groups must go while the CUDA driver is still up.
+CS_API void finalize();
 
 struct CS_API AllReduce {
   static void run_inplace(const Scheduler &scheduler, const Comm &comm, const std::vector<Tensor> &tensors,

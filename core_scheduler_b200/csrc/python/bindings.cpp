@@ -563,6 +563,7 @@ PYBIND11_MODULE(_C, m) {
     return communication::get_comm_world(backend == "nvp2p" ? communication::kNVP2P : communication::kNCCL);
   }, py::arg("backend") = "nccl");
   m.def("get_comm_self", &communication::get_comm_self);
+  m.def("finalize_communicators", &communication::finalize);
   m.def("all_reduce", [](const Scheduler &s, const Comm &c, const std::vector<Tensor> &t, const std::string &op) {
     communication::AllReduce::run_inplace(s, c, t, op == "avg" ? communication::kAVG : communication::kSUM);
   }, py::arg("scheduler"), py::arg("comm"), py::arg("tensors"), py::arg("op") = "sum");

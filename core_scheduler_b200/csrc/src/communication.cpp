@@ -48,7 +48,9 @@ int64_t env_int(const char *name, int64_t fallback) {
 }
 
 std::mutex g_comm_mutex;
-std::map<std::pair<int, int>, Comm> g_comms;  // (backend, scope) -> communicator
+// (backend, scope) -> communicator. Heap-allocated and never destroyed: a ProcessGroupNCCL destructor that runs
+// during static destruction finds the CUDA driver already shut down and throws; finalize() releases them earlier.
+std::map<std::pair<int, int>, Comm> &g_comms = *new std::map<std::pair<int, int>, Comm>();
 
 Comm create_from_env(BackendType type) {
   auto impl = std::make_shared<Comm::Impl>();
@@ -352,6 +354,21 @@ void AllToAll::run(const Scheduler &scheduler, const Comm &comm, const std::vect
            a2a_opts.asyncOp = false;
            wait_work(impl.backend->alltoall(r, s, a2a_opts));
          });
+}
+
+void finalize() {
+  std::lock_guard<std::mutex> lock{g_comm_mutex};
+  for (auto &kv : g_comms) {
+    auto &impl = *kv.second.impl();
+    impl.symmetric.reset();
+    if (impl.backend) {
+      try {
+        impl.backend->shutdown();
+      } catch (...) {  // a peer may already be gone; nothing left to do
+      }
+    }
+  }
+  g_comms.clear();
 }
 
 // -------------------------------------------------------------------------- heartbeat ----

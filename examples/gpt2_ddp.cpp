@@ -75,5 +75,7 @@ int main(int argc, char **argv) {
       std::printf("step %4ld/%ld | loss %.6f | %.2f ms | %.0f tok/s (all ranks)\n", static_cast<long>(step + 1),
                   static_cast<long>(steps), value, dt * 1e3, static_cast<double>(micro_batch * seq * world) / dt);
   }
+  scheduler.impl()->synchronize();
+  cs::communication::finalize();
   return 0;
 }

@@ -127,5 +127,7 @@ int main(int argc, char **argv) {
     cs::checkpoint::save_training_state(scheduler, dir, m, tp ? optimizer.get() : nullptr, meta, rank, tp ? rank : 0);
   }
   watchdog.stop();
+  scheduler.impl()->synchronize();
+  cs::communication::finalize();
   return 0;
 }
