@@ -80,11 +80,15 @@ def reference_arm(args):
         sampler.start()
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True)
     clocks = sampler.stop() if sampler else None
+    if os.environ.get("CS_REF_LOG"):  # keep the driver's full output for diagnosis
+        with open(f"{os.environ['CS_REF_LOG']}.rank{rank}", "w") as f:
+            f.write(proc.stdout + proc.stderr)
     line = next((l for l in proc.stdout.splitlines() if l.startswith("REF_RESULT")), None)
     if rank != 0:
         return 0  # a failed rank shows on rank 0 as a missing result line
     if line is None:
-        tail = (proc.stdout + proc.stderr).strip().splitlines()[-3:]
+        text = [l for l in (proc.stdout + proc.stderr).strip().splitlines() if "Warning" not in l and not l.startswith("frame #")]
+        tail = text[-3:]
         print(json.dumps({"impl": "reference", "unavailable": "reference driver failed: " + " | ".join(tail)[:400]}))
         return 0
     fields = dict(kv.split("=") for kv in line.split()[1:])
