@@ -190,10 +190,14 @@ std::string raw_value(const std::string &text, const std::string &key) {
   while (e < text.size() && text[e] != ',' && text[e] != '}' && text[e] != '\n') ++e;
   return text.substr(p, e - p);
 }
-void make_dir(const std::string &dir) {
-  if (::mkdir(dir.c_str(), 0755) != 0) {
-    struct stat st {};
-    CS_ASSERT_TRUE(::stat(dir.c_str(), &st) == 0 && S_ISDIR(st.st_mode), "cannot create directory ", dir);
+void make_dir(const std::string &dir) {  // like mkdir -p
+  for (size_t pos = 1; pos <= dir.size(); ++pos) {
+    if (pos != dir.size() && dir[pos] != '/') continue;
+    const std::string part = dir.substr(0, pos);
+    if (::mkdir(part.c_str(), 0755) != 0) {
+      struct stat st {};
+      CS_ASSERT_TRUE(::stat(part.c_str(), &st) == 0 && S_ISDIR(st.st_mode), "cannot create directory ", part);
+    }
   }
 }
 }  // namespace

@@ -88,7 +88,8 @@ def test_training_state_resume_continues_bit_identically(tmp_path):
         step(model, opt, b)
     meta = C.CheckpointMeta()
     meta.step, meta.data_cursor, meta.model = 2, 2, "tiny"
-    C.save_training_state(s, str(tmp_path / "ckpt"), model, opt, meta)
+    C.save_training_state(s, str(tmp_path / "nested" / "ckpt"), model, opt, meta)  # parents are created
+    os.rename(tmp_path / "nested" / "ckpt", tmp_path / "ckpt")
     assert sorted(os.listdir(tmp_path / "ckpt")) == ["meta.json", "model.parquet", "optimizer.parquet"]
 
     cs.manual_seed(1234)  # a different init: everything must come from the files
