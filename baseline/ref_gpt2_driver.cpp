@@ -50,8 +50,19 @@ struct Config {
 struct GradientQueue {  // data-parallel: gradients go into the byte-threshold bucket as they are produced
   const cs::communication::Comm *comm = nullptr;
   const cs::communication::AllReduceBucket *bucket = nullptr;
-  void push(const cs::Scheduler &s, const cs::Tensor &g) const {
-    if (bucket) bucket->push_back(s, *comm, g);
+  int64_t threshold = 0;
+  mutable int64_t pending = 0;  // bytes the bucket still holds (same rule as the library: flush at >= threshold)
+  void push(const cs::Scheduler &s, const cs::Tensor &g, int64_t elements) const {
+    if (!bucket) return;
+    bucket->push_back(s, *comm, g);
+    pending += elements * 4;  // fp32 gradients
+    if (pending >= threshold) pending = 0;
+  }
+  // The library's sync() concatenates its pending list and throws on an empty one, so it is only called
+  // when something is pending.
+  void flush(const cs::Scheduler &s) const {
+    if (bucket && pending > 0) bucket->sync(s, *comm);
+    pending = 0;
   }
 };
 
@@ -94,29 +105,30 @@ struct Layer : cs::module::Module {
   cs::Tensor backward(const cs::Scheduler &s, const cs::Tensor &dy, const GradientQueue &queue) {
     namespace U = cs::compute::Utils;
     const int64_t B = cfg.batch, T = cfg.seq, H = cfg.n_head, D = cfg.n_embd / cfg.n_head;
-    auto linear_backward = [&](const cs::module::Linear &layer, const cs::Tensor &grad) {
+    const int64_t d = cfg.n_embd;
+    auto linear_backward = [&](const cs::module::Linear &layer, const cs::Tensor &grad, int64_t elements) {
       auto dx = layer->backward_input(s, grad);  // main stream
       layer->backward_parameter(s, grad);        // assist stream
-      queue.push(s, layer->state()->forward.grad_weight);
+      queue.push(s, layer->state()->forward.grad_weight, elements);
       return dx;
     };
     auto norm_backward = [&](const cs::module::LayerNorm &layer, const cs::Tensor &grad) {
       auto dx = layer->backward(s, grad);
-      queue.push(s, layer->state()->forward.grad_weight);
-      queue.push(s, layer->state()->forward.grad_bias);
+      queue.push(s, layer->state()->forward.grad_weight, d);
+      queue.push(s, layer->state()->forward.grad_bias, d);
       return dx;
     };
     mark(" mlp backward");
-    auto dh = cs::compute::GeLU::backward(s, gelu, linear_backward(fc2, dy));
-    auto dx1 = U::add(s, norm_backward(ln2, linear_backward(fc1, dh)), dy);
+    auto dh = cs::compute::GeLU::backward(s, gelu, linear_backward(fc2, dy, 4 * d * d));
+    auto dx1 = U::add(s, norm_backward(ln2, linear_backward(fc1, dh, 4 * d * d)), dy);
     mark(" attention backward");
-    auto dctx = U::view(s, linear_backward(proj, dx1), {B, T, H, D});
+    auto dctx = U::view(s, linear_backward(proj, dx1, d * d), {B, T, H, D});
     auto dqkv = cs::compute::ScaledDotProductFlashAttention::backward(s, attention, dctx);
     auto packed = U::cat(s,
                          {U::view(s, dqkv[0], {B, T, cfg.n_embd}), U::view(s, dqkv[1], {B, T, cfg.n_embd}),
                           U::view(s, dqkv[2], {B, T, cfg.n_embd})},
                          -1);
-    return U::add(s, norm_backward(ln1, linear_backward(qkv, packed)), dx1);
+    return U::add(s, norm_backward(ln1, linear_backward(qkv, packed, 3 * d * d)), dx1);
   }
 };
 
@@ -161,18 +173,18 @@ struct Model : cs::module::Module {
     mark("lm_head backward");
     auto dx = lm_head->backward_input(s, dlogits);
     lm_head->backward_parameter(s, dlogits);
-    queue.push(s, lm_head->state()->forward.grad_weight);
+    queue.push(s, lm_head->state()->forward.grad_weight, cfg.vocab * cfg.n_embd);
     mark("lnf backward");
     dx = lnf->backward(s, dx);
-    queue.push(s, lnf->state()->forward.grad_weight);
-    queue.push(s, lnf->state()->forward.grad_bias);
+    queue.push(s, lnf->state()->forward.grad_weight, cfg.n_embd);
+    queue.push(s, lnf->state()->forward.grad_bias, cfg.n_embd);
     mark("layers backward");
     for (auto it = layers.rbegin(); it != layers.rend(); ++it) dx = (*it)->backward(s, dx, queue);
     mark("embedding backward");
     wpe->backward(s, U::sum(s, dx, 0));
-    queue.push(s, wpe->state()->forward.grad_weight);
+    queue.push(s, wpe->state()->forward.grad_weight, cfg.seq * cfg.n_embd);
     wte->backward(s, dx);
-    queue.push(s, wte->state()->forward.grad_weight);
+    queue.push(s, wte->state()->forward.grad_weight, cfg.vocab * cfg.n_embd);
   }
 };
 }  // namespace
@@ -223,6 +235,7 @@ int main(int argc, char **argv) {
     bucket = std::make_unique<cs::communication::AllReduceBucket>(static_cast<int64_t>(bucket_mb * (1 << 20)), cs::communication::kSUM);
     queue.comm = comm.get();
     queue.bucket = bucket.get();
+    queue.threshold = static_cast<int64_t>(bucket_mb * (1 << 20));
   }
   cs::manual_seed(100 + rank);  // different tokens on every rank
 
@@ -241,7 +254,7 @@ int main(int argc, char **argv) {
     }
     mark("forward done");
     model.backward(scheduler, queue);
-    if (bucket) bucket->sync(scheduler, *comm);
+    queue.flush(scheduler);
     mark("optimizer step");
     optimizer->step(scheduler);
     optimizer->zero_grad(scheduler);
