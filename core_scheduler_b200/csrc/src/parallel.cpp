@@ -268,7 +268,12 @@ int64_t fused_tp_launches() { return g_fused_tp_launches.load(); }
 Tensor column_parallel_forward(const Scheduler &scheduler, const communication::Comm &comm,
                                const std::shared_ptr<compute::Linear::State> &state, const ReadOnlyTensor &x_shard) {
   const int64_t tp = comm.get_size();
-  const bool can_fuse = x_shard.defined() && fused_tp_ok(comm, x_shard.impl()->tensor, x_shard.size(0) * tp) &&
+  // The fused kernel fetches the other ranks' rows by TMA straight from peer memory, once per output-column tile
+  // (peer data is not cached in the local L2): for wide layers that is several times the bytes of one
+  // all-gather. CS_TP_FUSED_ALL_GATHER=1 selects it; the default gathers the rows once with the peer-copy kernel
+  // and runs the GEMM on local memory.
+  static const bool fused_gather = std::getenv("CS_TP_FUSED_ALL_GATHER") != nullptr;
+  const bool can_fuse = fused_gather && x_shard.defined() && fused_tp_ok(comm, x_shard.impl()->tensor, x_shard.size(0) * tp) &&
                         scheduler.impl()->autocast_enabled && !state->args.bias;
   if (!can_fuse) {
     Tensor full = all_gather_rows(scheduler, comm, x_shard);

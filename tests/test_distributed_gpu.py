@@ -32,12 +32,14 @@ def test_tensor_parallel_matches_single_device(backend):
 
 
 @needs2
-def test_tensor_parallel_fused_gemm_collectives():
+def test_tensor_parallel_fused_gemm_collectives(monkeypatch):
+    monkeypatch.setenv("CS_TP_FUSED_ALL_GATHER", "1")  # also exercise the all-gather -> GEMM kernel (off by default)
     run_case("tp_training_fused", device="cuda", extra=("nvp2p",), timeout=600)
 
 
 @needs2
-def test_tensor_parallel_uneven_heads_fused():
+def test_tensor_parallel_uneven_heads_fused(monkeypatch):
+    monkeypatch.setenv("CS_TP_FUSED_ALL_GATHER", "1")
     run_case("tp_uneven_heads_fused", device="cuda", extra=("nvp2p",), timeout=600)
 
 
