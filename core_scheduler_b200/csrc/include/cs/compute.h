@@ -311,59 +311,60 @@ struct CS_API ScaledDotProductAttention {
 using ScaledDotProductFlashAttention = ScaledDotProductAttention;
 using ScaledDotProductCuDnn = ScaledDotProductAttention;
 
-struct CS_API Utils {
-  static Tensor sum(const Scheduler &scheduler, const ReadOnlyTensor &input, IntArrayRef dim, bool keep_dim = false,
+// A namespace, as in the reference (include/compute/utils.h:21): `namespace U = cs::compute::Utils;` must compile.
+namespace Utils {
+  CS_API Tensor sum(const Scheduler &scheduler, const ReadOnlyTensor &input, IntArrayRef dim, bool keep_dim = false,
                     optional<at::ScalarType> dtype = {});
-  static Tensor sum(const Scheduler &scheduler, const ReadOnlyTensor &input, int64_t dim, bool keep_dim = false,
+  CS_API Tensor sum(const Scheduler &scheduler, const ReadOnlyTensor &input, int64_t dim, bool keep_dim = false,
                     optional<at::ScalarType> dtype = {});
-  static Tensor range(const Scheduler &scheduler, const Scalar &start, const Scalar &end, TensorOptions options = {});
-  static Tensor arange(const Scheduler &scheduler, const Scalar &start, const Scalar &end, TensorOptions options = {});
-  static Tensor arange(const Scheduler &scheduler, const Scalar &start, const Scalar &end, const Scalar &step,
+  CS_API Tensor range(const Scheduler &scheduler, const Scalar &start, const Scalar &end, TensorOptions options = {});
+  CS_API Tensor arange(const Scheduler &scheduler, const Scalar &start, const Scalar &end, TensorOptions options = {});
+  CS_API Tensor arange(const Scheduler &scheduler, const Scalar &start, const Scalar &end, const Scalar &step,
                        TensorOptions options = {});
-  static Tensor randint(const Scheduler &scheduler, int64_t low, int64_t high, IntArrayRef size,
+  CS_API Tensor randint(const Scheduler &scheduler, int64_t low, int64_t high, IntArrayRef size,
                         TensorOptions options = at::kLong);
-  static Tensor empty(const Scheduler &scheduler, IntArrayRef size, TensorOptions options = {});
-  static Tensor empty_like(const Scheduler &scheduler, const ReadOnlyTensor &src);
-  static Tensor ones(const Scheduler &scheduler, IntArrayRef size, TensorOptions options = {});
-  static Tensor ones_like(const Scheduler &scheduler, const ReadOnlyTensor &src);
-  static Tensor zeros(const Scheduler &scheduler, IntArrayRef size, TensorOptions options = {});
-  static Tensor zeros_like(const Scheduler &scheduler, const ReadOnlyTensor &src);
-  static Tensor rand(const Scheduler &scheduler, IntArrayRef size, TensorOptions options = {});
-  static Tensor rand_like(const Scheduler &scheduler, const ReadOnlyTensor &src);
-  static Tensor randn(const Scheduler &scheduler, IntArrayRef size, TensorOptions options = {});
-  static Tensor randn_like(const Scheduler &scheduler, const ReadOnlyTensor &src);
-  static std::vector<Tensor> split(const Scheduler &scheduler, const ReadOnlyTensor &src, int64_t split_size,
+  CS_API Tensor empty(const Scheduler &scheduler, IntArrayRef size, TensorOptions options = {});
+  CS_API Tensor empty_like(const Scheduler &scheduler, const ReadOnlyTensor &src);
+  CS_API Tensor ones(const Scheduler &scheduler, IntArrayRef size, TensorOptions options = {});
+  CS_API Tensor ones_like(const Scheduler &scheduler, const ReadOnlyTensor &src);
+  CS_API Tensor zeros(const Scheduler &scheduler, IntArrayRef size, TensorOptions options = {});
+  CS_API Tensor zeros_like(const Scheduler &scheduler, const ReadOnlyTensor &src);
+  CS_API Tensor rand(const Scheduler &scheduler, IntArrayRef size, TensorOptions options = {});
+  CS_API Tensor rand_like(const Scheduler &scheduler, const ReadOnlyTensor &src);
+  CS_API Tensor randn(const Scheduler &scheduler, IntArrayRef size, TensorOptions options = {});
+  CS_API Tensor randn_like(const Scheduler &scheduler, const ReadOnlyTensor &src);
+  CS_API std::vector<Tensor> split(const Scheduler &scheduler, const ReadOnlyTensor &src, int64_t split_size,
                                    int64_t dim);
-  static Tensor view(const Scheduler &scheduler, const ReadOnlyTensor &input, IntArrayRef size);
-  static Tensor as_strided(const Scheduler &scheduler, const ReadOnlyTensor &input, IntArrayRef size,
+  CS_API Tensor view(const Scheduler &scheduler, const ReadOnlyTensor &input, IntArrayRef size);
+  CS_API Tensor as_strided(const Scheduler &scheduler, const ReadOnlyTensor &input, IntArrayRef size,
                            IntArrayRef stride, optional<int64_t> storage_offset = {});
-  static Tensor broadcast_to(const Scheduler &scheduler, const ReadOnlyTensor &input, IntArrayRef size);
-  static Tensor cat(const Scheduler &scheduler, const std::vector<ReadOnlyTensor> &input, int64_t dim);
-  static Tensor add(const Scheduler &scheduler, const ReadOnlyTensor &x, const ReadOnlyTensor &y);
-  static void zero_(const Scheduler &scheduler, const Tensor &tensor);
-  static void uniform_(const Scheduler &scheduler, const Tensor &tensor, double from = 0, double to = 1);
-  static void normal_(const Scheduler &scheduler, const Tensor &tensor, double mean = 0, double std = 1);
-  static Tensor clone(const Scheduler &scheduler, const Tensor &tensor);
-  static Tensor linalg_vector_norm(const Scheduler &scheduler, const ReadOnlyTensor &self, const Scalar &ord = 2,
+  CS_API Tensor broadcast_to(const Scheduler &scheduler, const ReadOnlyTensor &input, IntArrayRef size);
+  CS_API Tensor cat(const Scheduler &scheduler, const std::vector<ReadOnlyTensor> &input, int64_t dim);
+  CS_API Tensor add(const Scheduler &scheduler, const ReadOnlyTensor &x, const ReadOnlyTensor &y);
+  CS_API void zero_(const Scheduler &scheduler, const Tensor &tensor);
+  CS_API void uniform_(const Scheduler &scheduler, const Tensor &tensor, double from = 0, double to = 1);
+  CS_API void normal_(const Scheduler &scheduler, const Tensor &tensor, double mean = 0, double std = 1);
+  CS_API Tensor clone(const Scheduler &scheduler, const Tensor &tensor);
+  CS_API Tensor linalg_vector_norm(const Scheduler &scheduler, const ReadOnlyTensor &self, const Scalar &ord = 2,
                                    at::OptionalIntArrayRef dim = c10::nullopt, bool keepdim = false,
                                    optional<at::ScalarType> dtype = {});
   // Scales the gradients in place so that their joint norm is at most max_norm; returns the
   // norm measured before scaling.
-  static Tensor clip_grad_norm_(const Scheduler &scheduler, const std::vector<Tensor> &tensors, double max_norm,
+  CS_API Tensor clip_grad_norm_(const Scheduler &scheduler, const std::vector<Tensor> &tensors, double max_norm,
                                 double norm_type = 2.0);
   // extension: casts/moves a tensor.
-  static Tensor to(const Scheduler &scheduler, const ReadOnlyTensor &input, TensorOptions options);
-};
+  CS_API Tensor to(const Scheduler &scheduler, const ReadOnlyTensor &input, TensorOptions options);
+}  // namespace Utils
 
 enum class FanMode : int { kFanIn = 0, kFanOut = 1 };
 enum class Nonlinearity : int { kLinear = 0, kSigmoid, kTanh, kReLU, kLeakyReLU };
 
-struct CS_API Init {
-  static void kaiming_normal_(const Scheduler &scheduler, const Tensor &tensor, double a = 0,
+namespace Init {  // a namespace in the reference too (include/compute/init.h:23)
+  CS_API void kaiming_normal_(const Scheduler &scheduler, const Tensor &tensor, double a = 0,
                               FanMode mode = FanMode::kFanIn, Nonlinearity nonlinearity = Nonlinearity::kLeakyReLU);
-  static void kaiming_uniform_(const Scheduler &scheduler, const Tensor &tensor, double a = 0,
+  CS_API void kaiming_uniform_(const Scheduler &scheduler, const Tensor &tensor, double a = 0,
                                FanMode mode = FanMode::kFanIn, Nonlinearity nonlinearity = Nonlinearity::kLeakyReLU);
-};
+}  // namespace Init
 
 // Marks a parameter as changed (invalidates low-precision working copies).
 CS_API void bump_version(const Tensor &parameter);

@@ -400,7 +400,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("attention_backward_packed", &ScaledDotProductAttention::backward_packed);
 
   // Utils (the subset tests and examples use from Python; everything is reachable from C++)
-  using compute::Utils;
+  namespace Utils = compute::Utils;
   m.def("utils_sum", [](const Scheduler &s, const ReadOnlyTensor &x, std::vector<int64_t> dim, bool keep) {
     return Utils::sum(s, x, at::IntArrayRef(dim), keep);
   }, py::arg("scheduler"), py::arg("input"), py::arg("dim"), py::arg("keep_dim") = false);

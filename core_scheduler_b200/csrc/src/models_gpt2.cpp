@@ -4,7 +4,7 @@
 #include "cs/models.h"
 
 namespace cs::models {
-using compute::Utils;
+namespace Utils = compute::Utils;
 
 GPT2Config GPT2Config::tiny() {
   return GPT2Config{}.n_layer(2).n_head(4).n_embd(128).block_size(64).vocab_size(512).padded_vocab_size(512);

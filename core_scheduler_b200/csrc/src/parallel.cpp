@@ -409,7 +409,7 @@ TPBlockImpl::TPBlockImpl(const Scheduler &scheduler, const models::GPT2Config &c
 }
 
 Tensor TPBlockImpl::forward(const Scheduler &scheduler, const ReadOnlyTensor &x_shard, int64_t batch, int64_t seq) {
-  using compute::Utils;
+  namespace Utils = compute::Utils;
   const int64_t d_local = c_proj->state()->forward.weight.size(1);
   const bool fuse = x_shard.defined() && fused_tp_ok(comm, x_shard.impl()->tensor, batch * seq) &&
                     scheduler.impl()->autocast_enabled;
@@ -458,7 +458,7 @@ Tensor TPBlockImpl::forward(const Scheduler &scheduler, const ReadOnlyTensor &x_
 }
 
 Tensor TPBlockImpl::backward(const Scheduler &scheduler, const ReadOnlyTensor &grad_shard, const models::GradientSync &sync) {
-  using compute::Utils;
+  namespace Utils = compute::Utils;
   // MLP: reduce-scatter backward = all-gather of the incoming row shard
   Tensor dz = all_gather_rows(scheduler, comm, grad_shard);      // [M, d]
   Tensor d_pre = fc2->backward_input(scheduler, dz);
@@ -521,7 +521,7 @@ std::vector<std::string> TPGPT2Impl::replicated_parameters() const {
 }
 
 Tensor TPGPT2Impl::forward_loss(const Scheduler &scheduler, const ReadOnlyTensor &input_ids, const ReadOnlyTensor &labels) {
-  using compute::Utils;
+  namespace Utils = compute::Utils;
   CS_ASSERT_TRUE(input_ids.defined() && input_ids.sizes().size() == 2, "input_ids must be a materialised [B,T] tensor");
   batch_ = input_ids.size(0);
   seq_ = input_ids.size(1);
@@ -549,7 +549,7 @@ Tensor TPGPT2Impl::forward_loss(const Scheduler &scheduler, const ReadOnlyTensor
 }
 
 void TPGPT2Impl::backward_loss(const Scheduler &scheduler, const models::GradientSync &sync) {
-  using compute::Utils;
+  namespace Utils = compute::Utils;
   Tensor grad = compute::LinearCrossEntropy::backward(scheduler, lce_state_);
   sync.push(scheduler, lm_head->state()->forward.grad_weight);
   grad = lnf->backward(scheduler, grad);

@@ -1,5 +1,7 @@
 """C++ entry points and the data preparation script."""
 import os
+
+import pytest
 import subprocess
 import sys
 
@@ -54,3 +56,33 @@ def test_launcher_sets_rendezvous_environment_and_propagates_failure():
                           "import os, sys, time; sys.exit(7) if os.environ['RANK'] == '1' else time.sleep(30)"],
                          capture_output=True, text=True, timeout=60)
     assert bad.returncode == 7, (bad.returncode, bad.stdout + bad.stderr)  # rank 1 failed; the sleeping rank 0 was stopped, not waited for
+
+
+@pytest.mark.gpu
+def test_program_written_for_the_reference_api_runs_on_this_library(tmp_path):
+    """baseline/ref_gpt2_driver.cpp uses only the reference's public headers (include/compute/*.h, module/*.h, ...).
+    Compiled unchanged against this repository's compatibility headers and library it must train the tiny model."""
+    import torch
+
+    from core_scheduler_b200.build import _paths
+
+    p = _paths()
+    csrc = os.path.join(ROOT, "core_scheduler_b200", "csrc")
+    lib = os.path.join(ROOT, "core_scheduler_b200", "lib")
+    shim = os.path.join(ROOT, "baseline", "shims")
+    exe = tmp_path / "ref_api_gpt2"
+    subprocess.run(["gcc", "-O1", "-c", os.path.join(shim, "mpi_shim.c"), f"-I{shim}", "-o", str(tmp_path / "mpi_shim.o")], check=True)
+    cmd = ["g++", "-std=c++20", "-O1", "-w", f"-D_GLIBCXX_USE_CXX11_ABI={p['cxx11_abi']}", "-DUSE_C10D_NCCL", "-DUSE_DISTRIBUTED",
+           f"-I{shim}", f"-I{csrc}/include", f"-I{csrc}"] + [f"-I{i}" for i in p["torch_inc"]] + [f"-I{p['cuda_home'] / 'include'}",
+           os.path.join(ROOT, "baseline", "ref_gpt2_driver.cpp"), str(tmp_path / "mpi_shim.o"), "-o", str(exe), f"-L{lib}", "-lcs_b200",
+           f"-L{p['torch_lib']}", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda", f"-L{p['cuda_home'] / 'lib64'}", "-lcudart",
+           f"-Wl,-rpath,{lib}", f"-Wl,-rpath,{p['torch_lib']}", f"-Wl,-rpath,{p['arrow_lib']}", "-Wl,--no-as-needed"]
+    build = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert build.returncode == 0, build.stderr[-3000:]
+    env = dict(os.environ, CS_MPISHIM_KEY=f"api{os.getpid()}")
+    run = subprocess.run([str(exe), "--model", "tiny", "--micro-batch", "2", "--seq", "64", "--steps", "3", "--warmup", "1"], env=env,
+                         capture_output=True, text=True, timeout=300)
+    line = next((l for l in run.stdout.splitlines() if l.startswith("REF_RESULT")), None)
+    assert line is not None, (run.stdout + run.stderr)[-2000:]
+    fields = dict(kv.split("=") for kv in line.split()[1:])
+    assert 0.0 < float(fields["final_loss"]) < 7.0 and float(fields["ms_per_step"]) > 0.0
