@@ -86,3 +86,21 @@ def test_program_written_for_the_reference_api_runs_on_this_library(tmp_path):
     assert line is not None, (run.stdout + run.stderr)[-2000:]
     fields = dict(kv.split("=") for kv in line.split()[1:])
     assert 0.0 < float(fields["final_loss"]) < 7.0 and float(fields["ms_per_step"]) > 0.0
+
+
+def test_cmake_project_configures_and_builds_the_library(tmp_path):
+    """The CMake entry (for C++ projects that linked the reference's `core_scheduler` target) builds the same sources."""
+    import shutil
+
+    if shutil.which("cmake") is None:
+        pytest.skip("cmake not installed")
+    cfg = subprocess.run(["cmake", "-S", ROOT, "-B", str(tmp_path / "b"), f"-DPython3_EXECUTABLE={sys.executable}",
+                          "-DCORE_SCHEDULER_ENABLE_EXAMPLES=ON"], capture_output=True, text=True, timeout=600)
+    assert cfg.returncode == 0, cfg.stdout[-2000:] + cfg.stderr[-2000:]
+    build = subprocess.run(["cmake", "--build", str(tmp_path / "b"), "-j", "16", "--target", "gpt2_single_device"],
+                           capture_output=True, text=True, timeout=3000)
+    assert build.returncode == 0, build.stdout[-3000:] + build.stderr[-3000:]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    run = subprocess.run([str(tmp_path / "b" / "gpt2_single_device"), "--model", "tiny", "--steps", "2"], env=env,
+                         capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0 and run.stdout.count("tok/s") == 2, run.stdout + run.stderr
