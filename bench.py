@@ -40,6 +40,7 @@ def parse_args():
                    help="gradient collectives: this library's peer-memory kernels, or NCCL")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--profile", action="store_true", help="print per-task device time of one step (not a bench value)")
+    p.add_argument("--trace", default="", help="with --profile: also write that step as a chrome trace (JSON) to this file")
     return p.parse_args()
 
 
@@ -234,6 +235,10 @@ def main():
             print(f"per-task device time of one step (sum over streams {total:.3f} ms; tasks overlap across streams)", file=sys.stderr)
             for (name, cls), (n, ms) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
                 print(f"  {ms:8.3f} ms  x{n:4d}  stream{cls}  {name}", file=sys.stderr)
+            if args.trace:
+                from core_scheduler_b200.utils.trace import write_chrome_trace
+
+                print(f"wrote {write_chrome_trace(rows, args.trace)} task events to {args.trace}", file=sys.stderr)
 
     sampler = ClockSampler(local_rank).start() if rank == 0 else None
     launches_before = C.kernel_launch_count()

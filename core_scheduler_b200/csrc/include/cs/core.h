@@ -288,6 +288,7 @@ struct TaskTiming {
   std::string name;
   int stream_class;
   double device_ms;
+  double start_ms{0};  // start on the device, relative to the first task of the drained batch
 };
 
 struct CS_API Scheduler {

@@ -159,7 +159,8 @@ PYBIND11_MODULE(_C, m) {
   py::class_<TaskTiming>(m, "TaskTiming")
       .def_readonly("name", &TaskTiming::name)
       .def_readonly("stream_class", &TaskTiming::stream_class)
-      .def_readonly("device_ms", &TaskTiming::device_ms);
+      .def_readonly("device_ms", &TaskTiming::device_ms)
+      .def_readonly("start_ms", &TaskTiming::start_ms);
 
   py::class_<Scheduler>(m, "Scheduler")
       .def("get_device_rank", &Scheduler::get_device_rank)

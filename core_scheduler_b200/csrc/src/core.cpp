@@ -317,7 +317,11 @@ struct CudaImpl final : Scheduler::Impl {
     for (auto &t : timed_) {
       float ms = 0.f;
       CS_CHECK_CUDART(cudaEventElapsedTime(&ms, t.start, t.stop));
-      out.push_back({t.name, t.stream_class, static_cast<double>(ms)});
+      float since_first = 0.f;
+      if (&t != &timed_.front()) (void)cudaEventElapsedTime(&since_first, timed_.front().start, t.start);
+      out.push_back({t.name, t.stream_class, static_cast<double>(ms), static_cast<double>(since_first)});
+    }
+    for (auto &t : timed_) {  // only now: the first start event anchors every offset above
       cudaEventDestroy(t.start);
       cudaEventDestroy(t.stop);
     }

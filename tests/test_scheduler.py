@@ -118,6 +118,30 @@ def test_profiling_reports_task_times(gpu_scheduler):
 
 
 @pytest.mark.gpu
+def test_chrome_trace_export_orders_tasks_by_device_start(gpu_scheduler, tmp_path):
+    import json
+
+    from core_scheduler_b200.utils.trace import write_chrome_trace
+
+    s = gpu_scheduler
+    s.set_profiling(True)
+    x = cs.from_torch(torch.ones(1 << 22, device="cuda"))
+    outs = [cs.Tensor() for _ in range(3)]
+    prev = x
+    for i, o in enumerate(outs):
+        s.submit_python(f"stage{i}", i % 2, [o], [prev], lambda o=o, prev=prev: o.set_raw(prev.raw() * 2))
+        prev = o
+    rows = s.drain_timings()
+    s.set_profiling(False)
+    n = write_chrome_trace(rows, str(tmp_path / "t.json"))
+    assert n == len(rows) >= 3
+    trace = json.load(open(tmp_path / "t.json"))["traceEvents"]
+    tasks = {e["name"]: e for e in trace if e["ph"] == "X"}
+    assert tasks["stage0"]["ts"] == 0 and tasks["stage0"]["ts"] <= tasks["stage1"]["ts"] <= tasks["stage2"]["ts"]
+    assert tasks["stage1"]["tid"] == 1 and tasks["stage0"]["tid"] == 0  # lanes are the stream classes
+
+
+@pytest.mark.gpu
 def test_wrapped_tensors_wait_for_their_producer_stream(gpu_scheduler):
     """A tensor still being written on PyTorch's current stream is not read early by a task."""
     s = gpu_scheduler
