@@ -101,7 +101,7 @@ def main() -> int:
     if driver_src.exists():
         cmd = [c for c in cxx if c != "-fvisibility=hidden"] + [str(driver_src), "-o", str(exe), f"-L{OUT}", "-lcore_scheduler_core",
               f"-L{p['torch'] / 'lib'}", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda", f"-L{cuda_lib}", "-lcudart",
-              "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{p['torch'] / 'lib'}", f"-Wl,-rpath,{p['arrow_lib']}", f"-Wl,-rpath,{cuda_lib}",
+              f"-L{p['arrow_lib']}", "-l:libarrow.so.2400", "-l:libarrow_compute.so.2400", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{p['torch'] / 'lib'}", f"-Wl,-rpath,{p['arrow_lib']}", f"-Wl,-rpath,{cuda_lib}",
               f"-Wl,-rpath,{p['site'] / 'nvidia' / 'cudnn' / 'lib'}", "-Wl,--no-as-needed"]
         rc, out = run(cmd)
         if rc != 0:

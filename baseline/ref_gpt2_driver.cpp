@@ -7,18 +7,27 @@
 // The reference's own example programs are hard-coded to one configuration and a dataset path;
 // this program takes the model size, micro-batch and step counts from the command line instead.
 //
-//   ref_gpt2 --model 124M --micro-batch 16 --seq 1024 --steps 20 --warmup 5 [--bucket-mb 25]
+//   ref_gpt2 --model 124M --micro-batch 16 --seq 1024 --steps 20 --warmup 5 [--bucket-mb 25] [--dataset DIR]
 //
 // One process per GPU (RANK / LOCAL_RANK / WORLD_SIZE / MASTER_PORT in the environment; the MPI
 // calls of the library are served by baseline/shims). Rank 0 prints one line
 //   REF_RESULT ms_per_step=<device time, max over ranks> tokens_per_s=<all ranks> final_loss=<value>
+// and, when --dataset names a directory of Parquet files with list<int64> columns input_ids and labels, a
+// second line for the same steps fed by the library's own data path (LlmDataset + LlmDataLoader: a worker
+// thread fills pinned host buffers, a loader task copies them to the device) with the loss read back to the
+// host after every step, timed by the host clock between two full synchronisations:
+//   REF_E2E ms_per_step=<max over ranks> tokens_per_s=<all ranks> h2d_bytes=<per step> d2h_bytes=<per step>
+#include <arrow/compute/initialize.h>
 #include <cuda_runtime.h>
 #include <mpi.h>
 
+#include <atomic>
+#include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <memory>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "autocast.h"
@@ -28,6 +37,8 @@
 #include "compute/gelu.h"
 #include "compute/scaled_dot_product_attention.h"
 #include "compute/utils.h"
+#include "data/dataloader.h"
+#include "data/dataset.h"
 #include "memory/to_torch.h"
 #include "module/adamw.h"
 #include "module/embedding.h"
@@ -39,6 +50,7 @@
 
 namespace {
 bool g_debug = false;
+std::atomic<bool> g_e2e_done{false};
 void mark(const char *what) {  // REF_DEBUG=1: progress marks on stderr (the reference aborts rather than throws)
   if (g_debug) std::fprintf(stderr, "[ref_gpt2] %s\n", what), std::fflush(stderr);
 }
@@ -193,6 +205,7 @@ int main(int argc, char **argv) {
   std::string model_name = "124M";
   int64_t steps = 10, warmup = 3, micro_batch = 16, seq = 1024;
   double bucket_mb = 25.0;
+  std::string dataset_dir;
   for (int i = 1; i + 1 < argc; i += 2) {
     const std::string k = argv[i], v = argv[i + 1];
     if (k == "--model") model_name = v;
@@ -201,6 +214,7 @@ int main(int argc, char **argv) {
     else if (k == "--micro-batch") micro_batch = std::stoll(v);
     else if (k == "--seq") seq = std::stoll(v);
     else if (k == "--bucket-mb") bucket_mb = std::stod(v);
+    else if (k == "--dataset") dataset_dir = v;
   }
   g_debug = std::getenv("REF_DEBUG") != nullptr;
   MPI_Init(&argc, &argv);
@@ -240,14 +254,7 @@ int main(int argc, char **argv) {
   cs::manual_seed(100 + rank);  // different tokens on every rank
 
   cs::Tensor loss;
-  auto one_step = [&] {
-    namespace U = cs::compute::Utils;
-    // uniform token ids; the labels are the same stream shifted by one position
-    auto ids = U::randint(scheduler, 0, cfg.valid_vocab, {cfg.batch, cfg.seq + 1}, at::TensorOptions{}.dtype(at::kLong).device(cfg.device));
-    auto tokens = U::as_strided(scheduler, ids, {cfg.batch, cfg.seq}, {cfg.seq + 1, 1}, 0);
-    auto labels = U::view(scheduler, U::add(scheduler, U::as_strided(scheduler, ids, {cfg.batch, cfg.seq}, {cfg.seq + 1, 1}, 1),
-                                            U::zeros(scheduler, {1}, at::TensorOptions{}.dtype(at::kLong).device(cfg.device))),
-                          {cfg.batch * cfg.seq});
+  auto train_on = [&](const cs::Tensor &tokens, const cs::Tensor &labels) {
     {
       cs::autocast::ContextGuard guard{scheduler, at::kBFloat16};
       loss = model.forward(scheduler, tokens, labels);
@@ -259,6 +266,16 @@ int main(int argc, char **argv) {
     optimizer->step(scheduler);
     optimizer->zero_grad(scheduler);
     mark("step done");
+  };
+  auto one_step = [&] {
+    namespace U = cs::compute::Utils;
+    // uniform token ids; the labels are the same stream shifted by one position
+    auto ids = U::randint(scheduler, 0, cfg.valid_vocab, {cfg.batch, cfg.seq + 1}, at::TensorOptions{}.dtype(at::kLong).device(cfg.device));
+    auto tokens = U::as_strided(scheduler, ids, {cfg.batch, cfg.seq}, {cfg.seq + 1, 1}, 0);
+    auto labels = U::view(scheduler, U::add(scheduler, U::as_strided(scheduler, ids, {cfg.batch, cfg.seq}, {cfg.seq + 1, 1}, 1),
+                                            U::zeros(scheduler, {1}, at::TensorOptions{}.dtype(at::kLong).device(cfg.device))),
+                          {cfg.batch * cfg.seq});
+    train_on(tokens, labels);
   };
 
   for (int64_t i = 0; i < warmup; ++i) one_step();
@@ -278,10 +295,56 @@ int main(int argc, char **argv) {
   cudaEventElapsedTime(&ms, begin, end);
   double per_step = static_cast<double>(ms) / static_cast<double>(steps);
   MPI_Shim_max_double(&per_step);
-  const double value = cs::memory::to_torch(scheduler, loss).item<double>();
+  const at::Tensor loss_tensor = cs::memory::to_torch(scheduler, loss);
+  const double value = loss_tensor.item<double>();
+  const int64_t loss_bytes = static_cast<int64_t>(loss_tensor.element_size());
   if (rank == 0)
     std::printf("REF_RESULT ms_per_step=%.6f tokens_per_s=%.3f final_loss=%.6f\n", per_step,
                 static_cast<double>(cfg.batch * cfg.seq * world) / (per_step * 1e-3), value);
+  std::fflush(stdout);
+
+  if (!dataset_dir.empty()) {
+    // The device-timed line above is already out. If the data path stalls (its worker threads meet the
+    // caller on host barriers), this process leaves after a limit instead of holding the other ranks.
+    const double limit_s = 60.0 + static_cast<double>(steps + 2) * per_step * 10.0 * 1e-3;
+    std::thread([limit_s, rank] {
+      const auto give_up = std::chrono::steady_clock::now() + std::chrono::duration<double>(limit_s);
+      while (!g_e2e_done.load() && std::chrono::steady_clock::now() < give_up) std::this_thread::sleep_for(std::chrono::milliseconds(50));
+      if (g_e2e_done.load()) return;
+      std::fprintf(stderr, "ref_gpt2: rank %d: end-to-end phase exceeded %.0f s, leaving\n", rank, limit_s);
+      std::fflush(stderr);
+      std::_Exit(0);
+    }).detach();
+    mark("end-to-end phase");
+    namespace U = cs::compute::Utils;
+    // Arrow 21 and later keep the compute kernels that a dataset scan's projection calls in a library of their
+    // own, which the program has to initialise; the reference was written before that split.
+    const auto arrow_ready = arrow::compute::Initialize();
+    if (!arrow_ready.ok()) std::fprintf(stderr, "ref_gpt2: arrow::compute::Initialize: %s\n", arrow_ready.ToString().c_str());
+    cs::data::LlmDataset dataset{dataset_dir};
+    auto loader = world > 1 ? std::make_unique<cs::data::LlmDataLoader>(dataset, *comm, cfg.batch, 1, false)
+                            : std::make_unique<cs::data::LlmDataLoader>(dataset, cfg.batch, 1, false);
+    auto e2e_step = [&] {
+      auto data = loader->load(scheduler);  // pinned host buffers -> device, on the scheduler's main stream
+      train_on(data.at("input_ids"), U::view(scheduler, data.at("labels"), {cfg.batch * cfg.seq}));
+      return cs::memory::to_torch(scheduler, loss).item<double>();  // device -> host read of the step's loss
+    };
+    double last = 0.0;
+    for (int i = 0; i < 2; ++i) last = e2e_step();
+    cudaDeviceSynchronize();
+    MPI_Barrier(MPI_COMM_WORLD);
+    const auto t0 = std::chrono::steady_clock::now();
+    for (int64_t i = 0; i < steps; ++i) last = e2e_step();
+    cudaDeviceSynchronize();
+    double e2e_per_step = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count() / static_cast<double>(steps);
+    MPI_Shim_max_double(&e2e_per_step);
+    if (rank == 0)
+      std::printf("REF_E2E ms_per_step=%.6f tokens_per_s=%.3f h2d_bytes=%lld d2h_bytes=%lld final_loss=%.6f\n", e2e_per_step,
+                  static_cast<double>(cfg.batch * cfg.seq * world) / (e2e_per_step * 1e-3),
+                  static_cast<long long>(2 * cfg.batch * cfg.seq * 8), static_cast<long long>(loss_bytes), last);
+    std::fflush(stdout);
+    g_e2e_done.store(true);
+  }
   MPI_Finalize();
   // The library offers no way to shut its NCCL process group down, and that group's destructor throws when it
   // runs during static destruction (the CUDA driver is gone by then): leave without running static destructors.

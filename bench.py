@@ -44,6 +44,28 @@ def parse_args():
     return p.parse_args()
 
 
+def write_reference_dataset(batch, seq_len, vocab, world, tag, batches_per_rank=8):
+    """Writes one Parquet file in the layout the reference's LlmDataLoader scans (list<int64> columns `input_ids`
+    and `labels`, one row per sequence, one row group per batch) with uniform random token ids, and returns its
+    directory. `batches_per_rank` batches per rank are enough: the loader wraps around at the end of its shard."""
+    import tempfile
+
+    import numpy as np
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+
+    rows = batch * batches_per_rank * world
+    rng = np.random.default_rng(20240611)
+    ids = rng.integers(0, vocab, size=(rows, seq_len + 1), dtype=np.int64)
+    offsets = np.arange(rows + 1, dtype=np.int32) * seq_len
+    columns = [pa.ListArray.from_arrays(pa.array(offsets), pa.array(np.ascontiguousarray(part).reshape(-1)))
+               for part in (ids[:, :-1], ids[:, 1:])]
+    directory = os.path.join(tempfile.gettempdir(), f"cs_ref_dataset_{tag}")
+    os.makedirs(directory, exist_ok=True)
+    pq.write_table(pa.table(columns, names=["input_ids", "labels"]), os.path.join(directory, "train.parquet"), row_group_size=batch)
+    return directory
+
+
 def reference_arm(args):
     """Runs the unmodified reference library (built by baseline/build_reference.py into baseline/_ref/) through
     its own public API: baseline/_ref/ref_gpt2 is a GPT-2 driver that links only that library. One driver process
@@ -76,11 +98,25 @@ def reference_arm(args):
     env = dict(os.environ, CS_MPISHIM_KEY=f"{os.getppid()}")
     cmd = [exe, "--model", args.model, "--micro-batch", str(args.micro_batch), "--seq", str(args.seq_len), "--steps", str(args.steps),
            "--warmup", str(args.warmup), "--bucket-mb", str(args.bucket_mb)]
+    dataset_dir = None
+    if not args.no_e2e:
+        # end-to-end arm: the reference's own data path reads Parquet files, so every rank writes the same
+        # synthetic file (same seed) into a directory of its own and the loader shards it by rank
+        try:
+            dataset_dir = write_reference_dataset(args.micro_batch, args.seq_len, 512 if args.model == "tiny" else 50257, world,
+                                                  f"{os.getppid()}_{rank}")
+            cmd += ["--dataset", dataset_dir]
+        except Exception as e:  # no pyarrow, no space: the device-timed number does not depend on it
+            print(f"reference arm: no end-to-end dataset ({e})", file=sys.stderr)
     sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) if rank == 0 else None
     if sampler:
         sampler.start()
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True)
     clocks = sampler.stop() if sampler else None
+    if dataset_dir:
+        import shutil
+
+        shutil.rmtree(dataset_dir, ignore_errors=True)
     if os.environ.get("CS_REF_LOG"):  # keep the driver's full output for diagnosis
         with open(f"{os.environ['CS_REF_LOG']}.rank{rank}", "w") as f:
             f.write(proc.stdout + proc.stderr)
@@ -94,6 +130,13 @@ def reference_arm(args):
         return 0
     fields = dict(kv.split("=") for kv in line.split()[1:])
     ms = float(fields["ms_per_step"])
+    e2e = None
+    e2e_line = next((l for l in proc.stdout.splitlines() if l.startswith("REF_E2E")), None)
+    if e2e_line:
+        f2 = dict(kv.split("=") for kv in e2e_line.split()[1:])
+        e2e = {"value": float(f2["tokens_per_s"]), "unit": "tokens/s", "ms_per_step": float(f2["ms_per_step"]),
+               "h2d_bytes_per_step": int(f2["h2d_bytes"]), "d2h_bytes_per_step": int(f2["d2h_bytes"]),
+               "path": "reference LlmDataset + LlmDataLoader (Parquet -> pinned host -> device), loss read back every step"}
     print(json.dumps({
         "metric": "GPT-2 train tokens/sec, device-timed max over ranks", "value": float(fields["tokens_per_s"]), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
@@ -102,7 +145,7 @@ def reference_arm(args):
                    "seq_len": args.seq_len, "parallelism": f"dp{world}", "precision": "fp32 parameters under a bf16 autocast guard",
                    "backend": "reference library (cuBLAS / ATen / flash attention / NCCL), unmodified sources",
                    "bucket_mb": args.bucket_mb, "l2": "per-step working set exceeds the 126 MB L2; no flush needed"},
-        "final_loss": float(fields["final_loss"]), "clocks": clocks, "e2e": None, "gpu_launches": None}))
+        "final_loss": float(fields["final_loss"]), "clocks": clocks, "e2e": e2e, "gpu_launches": None}))
     return 0
 
 

@@ -178,6 +178,7 @@ std::string raw_value(const std::string &text, const std::string &key) {
   CS_ASSERT_TRUE(p != std::string::npos, "meta file: malformed entry `", key, "`");
   ++p;
   while (p < text.size() && std::isspace(static_cast<unsigned char>(text[p]))) ++p;
+  CS_ASSERT_TRUE(p < text.size(), "meta file: entry `", key, "` has no value");
   if (text[p] == '"') {
     std::string out;
     for (++p; p < text.size() && text[p] != '"'; ++p) {

@@ -55,3 +55,34 @@ def test_reference_arm_prints_one_json_line_and_exits_zero_without_a_gpu():
     zero = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--mode", "zero"], env=env,
                           capture_output=True, text=True, timeout=300)
     assert zero.returncode == 0 and "unavailable" in json.loads(zero.stdout.strip().splitlines()[-1])
+
+
+def test_reference_dataset_has_the_layout_the_reference_loader_scans():
+    """The reference's loader projects `input_ids` and `labels`, asks for batches of the micro-batch size, casts each
+    column to a list array of int32/int64 and takes the sequence length from the first row (src/data/dataloader.cpp)."""
+    import importlib.util
+    import shutil
+
+    import pyarrow as pa
+    import pyarrow.dataset as ds
+
+    spec = importlib.util.spec_from_file_location("cs_bench", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    directory = bench.write_reference_dataset(4, 32, 512, 3, f"test{os.getpid()}", batches_per_rank=5)
+    try:
+        files = sorted(os.listdir(directory))
+        assert files == ["train.parquet"]
+        scanner = ds.dataset([os.path.join(directory, files[0])], format="parquet").scanner(
+            columns=["input_ids", "labels"], batch_size=4, batch_readahead=0)
+        batches = list(scanner.to_batches())
+        assert len(batches) == 5 * 3  # every rank's shard holds `batches_per_rank` whole batches
+        for batch in batches:
+            for column in (batch.column(0), batch.column(1)):
+                assert isinstance(column, pa.ListArray) and column.type.value_type == pa.int64()
+                assert len(column) == 4 and set(column.value_lengths().to_pylist()) == {32}
+            tokens = batch.column(0).values.to_numpy().reshape(4, 32)
+            labels = batch.column(1).values.to_numpy().reshape(4, 32)
+            assert (tokens[:, 1:] == labels[:, :-1]).all() and 0 <= tokens.min() and max(tokens.max(), labels.max()) < 512
+    finally:
+        shutil.rmtree(directory, ignore_errors=True)
