@@ -39,6 +39,8 @@ def parse_args():
     p.add_argument("--comm", default="nvp2p", choices=["nvp2p", "nccl"],
                    help="gradient collectives: this library's peer-memory kernels, or NCCL")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--assist-gap", type=int, default=2, help="main-stream tasks after which an assist-stream task is re-joined")
+    p.add_argument("--comm-gap", type=int, default=5, help="main-stream tasks after which a communication task is re-joined")
     p.add_argument("--profile", action="store_true", help="print per-task device time of one step (not a bench value)")
     p.add_argument("--trace", default="", help="with --profile: also write that step as a chrome trace (JSON) to this file")
     return p.parse_args()
@@ -157,7 +159,7 @@ class Trainer:
 
         self.cs, self.C = cs, cs._C
         self.comm, self.rank, self.world = comm, rank, world
-        self.s = cs.DynamicScheduler(local_rank, device="cuda")
+        self.s = cs.DynamicScheduler(local_rank, device="cuda", assist_task_gap=args.assist_gap, comm_task_gap=args.comm_gap)
         self.C.set_backend(args.backend)
         cs.manual_seed(1234)  # same weights on every rank
         self.cfg = gpt2_config(args.model, dtype=torch.float32)
@@ -355,6 +357,7 @@ def main():
                 "precision": "bf16 compute, fp32 master weights + AdamW moments",
                 "backend": args.backend,
                 "bucket_mb": args.bucket_mb,
+                "scheduler_gaps": {"assist": args.assist_gap, "comm": args.comm_gap},
                 "collectives": (args.comm if world > 1 else "none"),
                 "l2": f"per-step working set (~{weights_gb:.1f} GB weights/optimizer + activations) exceeds the 126 MB L2; no flush needed",
             },
