@@ -190,15 +190,27 @@ def build(verbose: bool = False, checked: bool = False) -> None:
 
 def build_examples() -> list[str]:
     """Compiles the C++ programs under examples/ against libcs_b200.so into examples/bin/."""
+    return _build_programs(HERE.parent / "examples", [])
+
+
+def build_cpp_tests() -> list[str]:
+    """Compiles the C++ test programs under tests/cpp/ (cs_b200_tests, cs_b200_communication_tests) into tests/cpp/bin/."""
+    root = HERE.parent / "tests" / "cpp"
+    return _build_programs(root, [root], {"test_ops": "cs_b200_tests", "test_communication": "cs_b200_communication_tests"})
+
+
+def _build_programs(root: Path, extra_inc: list, names: dict | None = None) -> list[str]:
     build()
     p = _paths()
-    root = HERE.parent / "examples"
     out_dir = root / "bin"
     out_dir.mkdir(exist_ok=True)
-    inc = [CSRC / "include", CSRC] + p["torch_inc"] + [p["cuda_home"] / "include"]
+    inc = [CSRC / "include", CSRC] + p["torch_inc"] + [p["cuda_home"] / "include"] + extra_inc
     built = []
     for src in sorted(root.glob("*.cpp")):
-        exe = out_dir / src.stem
+        exe = out_dir / (names or {}).get(src.stem, src.stem)
+        if exe.exists() and exe.stat().st_mtime > max(f.stat().st_mtime for f in [src, LIBDIR / "libcs_b200.so", *root.glob("*.h")]):
+            built.append(str(exe))
+            continue
         cmd = [os.environ.get("CS_CXX", "g++"), "-std=c++20", "-O2", "-Wno-interference-size",
                f"-D_GLIBCXX_USE_CXX11_ABI={p['cxx11_abi']}", "-DUSE_C10D_NCCL", "-DUSE_DISTRIBUTED"]
         cmd += [f"-I{i}" for i in inc] + [str(src), "-o", str(exe), f"-L{LIBDIR}", "-lcs_b200", f"-L{p['torch_lib']}",
@@ -220,5 +232,7 @@ def is_built() -> bool:
 if __name__ == "__main__":
     if "examples" in sys.argv:
         print("\n".join(build_examples()))
+    elif "tests" in sys.argv:
+        print("\n".join(build_cpp_tests()))
     else:
         build(verbose="-v" in sys.argv, checked="checked" in sys.argv)

@@ -1,0 +1,128 @@
+// Multi-rank tests of the collectives through the C++ API (the counterpart of the reference project's
+// core_scheduler_communication_tests: test/test_all_reduce.cpp, test_all_gather.cpp, test_reduce_scatter.cpp,
+// test_all_to_all.cpp). One process per GPU, started by examples/launch.py or torchrun (RANK, LOCAL_RANK,
+// WORLD_SIZE, MASTER_ADDR, MASTER_PORT); every rank regenerates every other rank's data from its seed, so
+// the expected values are computed locally. Unlike the reference's all-reduce test, the expectation here is
+// the sum over all ranks' regenerated inputs, not the output compared with itself. Without a launcher the
+// program runs as a single rank (on the CPU when there is no GPU) and checks the one-rank semantics.
+//
+//   python examples/launch.py --nproc 2 -- tests/cpp/bin/cs_b200_communication_tests [--filter SUBSTRING]
+#include <cuda_runtime.h>
+#include <torch/torch.h>
+
+#include <cstdlib>
+
+#include "cs/communication.h"
+#include "cs/compute.h"
+#include "cs_test.h"
+
+namespace {
+int env_int(const char *name, int fallback) {
+  const char *v = std::getenv(name);
+  return v ? std::atoi(v) : fallback;
+}
+cs::DynamicScheduler &scheduler() {
+  static cs::DynamicScheduler s{env_int("LOCAL_RANK", 0)};
+  return s;
+}
+// Owned by main(): the communicator has to go before main returns, while the CUDA driver is still up.
+cs::communication::Comm *g_comm = nullptr;
+cs::communication::Comm &comm() { return *g_comm; }
+at::Device device() { return scheduler().device(); }
+int64_t rank() { return comm().get_rank(); }
+int64_t world() { return comm().get_size(); }
+at::Tensor host(const cs::ReadOnlyTensor &t) { return cs::memory::to_torch(scheduler(), t); }
+// the tensor that the rank with this seed draws: generated on the CPU so that every rank can reproduce it
+at::Tensor draw(int64_t seed, int64_t n, at::ScalarType dtype) {
+  auto generator = at::detail::createCPUGenerator(static_cast<uint64_t>(seed));
+  return at::rand({n}, generator, at::TensorOptions{}.dtype(dtype)).to(device());
+}
+cs::Tensor wrap(const at::Tensor &t) { return cs::Tensor::wrap(t.detach().clone()); }
+const std::vector<at::ScalarType> kTypes{at::kFloat, at::kDouble};
+const std::vector<int64_t> kSizes{128, 1 << 18};
+}  // namespace
+
+CS_TEST(AllReduce, SumAndAverageOfTwoTensors) {
+  for (auto dtype : kTypes)
+    for (auto n : kSizes)
+      for (auto op : {cs::communication::kSUM, cs::communication::kAVG}) {
+        auto a = wrap(draw(rank() + 1, n, dtype)), b = wrap(draw(100 + rank() + 1, n / 2, dtype));
+        cs::communication::AllReduce::run_inplace(scheduler(), comm(), {a, b}, op);
+        at::Tensor expect_a = at::zeros({n}, a.options()), expect_b = at::zeros({n / 2}, b.options());
+        for (int64_t r = 0; r < world(); ++r) {
+          expect_a += draw(r + 1, n, dtype);
+          expect_b += draw(100 + r + 1, n / 2, dtype);
+        }
+        if (op == cs::communication::kAVG) {
+          expect_a /= static_cast<double>(world());
+          expect_b /= static_cast<double>(world());
+        }
+        EXPECT_CLOSE(host(a), expect_a, 1e-5, 1e-6);
+        EXPECT_CLOSE(host(b), expect_b, 1e-5, 1e-6);
+      }
+}
+
+CS_TEST(AllReduceBucket, FlushesAtTheByteThresholdAndOnSync) {
+  const int64_t n = 1024;  // 4 KB per float tensor; threshold 10 KB -> a launch after every third tensor
+  cs::communication::AllReduceBucket bucket{10 * 1024, cs::communication::kSUM};
+  std::vector<cs::Tensor> tensors;
+  for (int i = 0; i < 7; ++i) {
+    tensors.push_back(wrap(draw(1000 * (i + 1) + rank(), n, at::kFloat)));
+    bucket.push_back(scheduler(), comm(), tensors.back());
+  }
+  bucket.sync(scheduler(), comm());
+  EXPECT_TRUE(bucket.launches() == 3);  // 3 + 3 tensors by threshold, the last one by sync
+  for (int i = 0; i < 7; ++i) {
+    at::Tensor expected = at::zeros({n}, tensors[i].options());
+    for (int64_t r = 0; r < world(); ++r) expected += draw(1000 * (i + 1) + r, n, at::kFloat);
+    EXPECT_CLOSE(host(tensors[i]), expected, 1e-5, 1e-6);
+  }
+}
+
+CS_TEST(AllGather, EveryBlockIsItsOwnersDraw) {
+  for (auto dtype : kTypes)
+    for (auto n : kSizes) {
+      std::vector<cs::Tensor> blocks;
+      for (int64_t r = 0; r < world(); ++r) blocks.push_back(wrap(at::zeros({n}, at::TensorOptions{}.dtype(dtype).device(device()))));
+      cs::communication::AllGather::run(scheduler(), comm(), {blocks}, {wrap(draw(rank() + 1, n, dtype))});
+      for (int64_t r = 0; r < world(); ++r) EXPECT_CLOSE(host(blocks[r]), draw(r + 1, n, dtype), 0, 0);
+    }
+}
+
+CS_TEST(ReduceScatter, MyBlockIsTheSumOfEveryRanksBlockForMe) {
+  for (auto dtype : kTypes)
+    for (auto n : kSizes) {
+      std::vector<cs::ReadOnlyTensor> send;
+      for (int64_t j = 0; j < world(); ++j) send.push_back(wrap(draw(rank() * world() + j + 1, n, dtype)));
+      auto recv = wrap(at::zeros({n}, at::TensorOptions{}.dtype(dtype).device(device())));
+      cs::communication::ReduceScatter::run(scheduler(), comm(), {recv}, {send}, cs::communication::kSUM);
+      at::Tensor expected = at::zeros({n}, recv.options());
+      for (int64_t r = 0; r < world(); ++r) expected += draw(r * world() + rank() + 1, n, dtype);
+      EXPECT_CLOSE(host(recv), expected, 1e-5, 1e-6);
+    }
+}
+
+CS_TEST(AllToAll, BlockFromRankJIsItsDrawForMe) {
+  for (auto dtype : kTypes)
+    for (auto n : kSizes) {
+      std::vector<cs::ReadOnlyTensor> send;
+      std::vector<cs::Tensor> recv;
+      for (int64_t j = 0; j < world(); ++j) {
+        send.push_back(wrap(draw(rank() * world() + j + 1, n, dtype)));
+        recv.push_back(wrap(at::zeros({n}, at::TensorOptions{}.dtype(dtype).device(device()))));
+      }
+      cs::communication::AllToAll::run(scheduler(), comm(), recv, send);
+      for (int64_t j = 0; j < world(); ++j) EXPECT_CLOSE(host(recv[j]), draw(j * world() + rank() + 1, n, dtype), 0, 0);
+    }
+}
+
+int main(int argc, char **argv) {
+  if (torch::cuda::is_available()) cudaSetDevice(env_int("LOCAL_RANK", 0));
+  g_comm = new cs::communication::Comm{cs::communication::get_comm_world(cs::communication::kNCCL)};
+  std::printf("rank %ld of %ld on %s\n", static_cast<long>(rank()), static_cast<long>(world()), device().str().c_str());
+  const int failed = cs_test::run_all(argc, argv);
+  scheduler().impl()->synchronize();
+  cs::communication::finalize();
+  delete g_comm;
+  return failed;
+}

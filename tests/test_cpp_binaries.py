@@ -1,0 +1,60 @@
+"""The C++ test programs (tests/cpp/): cs_b200_tests for one device, cs_b200_communication_tests for the collectives.
+They mirror the reference project's two GoogleTest executables (test/CMakeLists.txt:15-48) with a small harness of
+their own, since the image has no GoogleTest."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from core_scheduler_b200 import build as native_build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def program(name):
+    return [e for e in native_build.build_cpp_tests() if e.endswith(name)][0]
+
+
+def check(out, tests):
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert f"{tests} tests ran, 0 failed" in out.stdout, out.stdout[-3000:]
+
+
+def test_cpp_single_device_tests_on_the_cpu():
+    out = subprocess.run([program("cs_b200_tests")], env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), capture_output=True, text=True,
+                         timeout=600)
+    assert "device: cpu" in out.stdout
+    check(out, 15)
+
+
+def test_cpp_communication_tests_as_a_single_rank_on_the_cpu():
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
+    out = subprocess.run([program("cs_b200_communication_tests")], env=dict(env, CUDA_VISIBLE_DEVICES=""), capture_output=True,
+                         text=True, timeout=600)
+    assert "rank 0 of 1 on cpu" in out.stdout
+    check(out, 5)
+
+
+def test_cpp_harness_reports_a_filter_and_counts(tmp_path):
+    out = subprocess.run([program("cs_b200_tests"), "--filter", "GeLU"], env=dict(os.environ, CUDA_VISIBLE_DEVICES=""),
+                         capture_output=True, text=True, timeout=600)
+    check(out, 1)
+
+
+@pytest.mark.gpu
+def test_cpp_single_device_tests_on_the_gpu():
+    out = subprocess.run([program("cs_b200_tests")], capture_output=True, text=True, timeout=600)
+    assert "device: cuda" in out.stdout
+    check(out, 15)
+
+
+@pytest.mark.gpu
+def test_cpp_communication_tests_on_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "launch.py"), "--nproc", "2", "--master-port", "29613", "--",
+                          program("cs_b200_communication_tests")], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert out.stdout.count("5 tests ran, 0 failed") == 2, out.stdout[-3000:]
