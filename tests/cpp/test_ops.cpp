@@ -12,6 +12,8 @@
 #include <cstdio>
 
 #include "cs/compute.h"
+#include "cs/data.h"
+#include "cs/models.h"
 #include "cs/module.h"
 #include "cs/modules.h"
 #include "cs/optimizer.h"
@@ -323,6 +325,69 @@ CS_TEST(Scheduler, AssistStreamResultsReachTheMainStreamInOrder) {
     expected = expected + dy.t().matmul(x);
     EXPECT_CLOSE(host(doubled), 2 * expected, 1e-4, 1e-3);
   }
+}
+
+CS_TEST(GeluLinear, MatchesLinearOfGeluAutograd) {
+  for (bool bias : {false, true}) {
+    torch::manual_seed(10);
+    const auto dtype = at::kDouble;
+    auto state = cs::compute::GeluLinear::init(scheduler(), cs::compute::GeluLinear::Options{128, 64}.bias(bias).device(device()).dtype(dtype));
+    auto x = torch::randn({12, 3, 128}, opts(dtype)).requires_grad_(true);
+    auto w = host(state->forward.weight).requires_grad_(true);
+    at::Tensor b = bias ? host(state->forward.bias).requires_grad_(true) : at::Tensor{};
+    auto reference = torch::linear(at::gelu(x), w, b);
+    auto dy = torch::randn_like(reference);
+    reference.backward(dy);
+    auto y = cs::compute::GeluLinear::forward(scheduler(), state, wrap(x));
+    auto dx = cs::compute::GeluLinear::backward_input(scheduler(), state, wrap(dy));
+    cs::compute::GeluLinear::backward_parameter(scheduler(), state, wrap(dy));
+    EXPECT_CLOSE(host(y), reference, 1e-8, 1e-10);
+    EXPECT_CLOSE(host(dx), x.grad(), 1e-8, 1e-10);
+    EXPECT_CLOSE(host(state->forward.grad_weight), w.grad(), 1e-8, 1e-10);
+    if (bias) EXPECT_CLOSE(host(state->forward.grad_bias), b.grad(), 1e-8, 1e-10);
+  }
+}
+
+CS_TEST(Module, ParameterKeysAreDottedPathsInRegistrationOrder) {
+  struct Block : cs::module::Module {
+    cs::module::LayerNorm norm{nullptr};
+    cs::module::Linear proj{nullptr};
+    explicit Block(const cs::Scheduler &s) {
+      norm = register_module("ln", cs::module::LayerNorm{s, cs::compute::LayerNorm::Options{{8}}.device(device()).dtype(at::kFloat)});
+      proj = register_module("c_proj", cs::module::Linear{s, cs::compute::Linear::Options{8, 8}.bias(false).device(device()).dtype(at::kFloat)});
+    }
+  };
+  struct Net : cs::module::Module {
+    explicit Net(const cs::Scheduler &s) {
+      register_module("wte", cs::module::Embedding{s, cs::compute::Embedding::Options{16, 8}.device(device()).dtype(at::kFloat)});
+      for (int i = 0; i < 2; ++i) register_module(std::to_string(i), std::make_shared<Block>(s));
+    }
+  };
+  auto net = std::make_shared<Net>(scheduler());
+  std::vector<std::string> keys;
+  for (auto &item : net->named_parameters()) keys.push_back(item.key());
+  const std::vector<std::string> expected{"wte.weight", "0.ln.weight", "0.ln.bias", "0.c_proj.weight", "1.ln.weight", "1.ln.bias", "1.c_proj.weight"};
+  EXPECT_TRUE(keys == expected);
+}
+
+CS_TEST(Model, TinyGpt2LossFallsOverAFewSteps) {
+  cs::manual_seed(11);
+  cs::models::GPT2 model{scheduler(), cs::models::GPT2Config::tiny()};
+  auto flat = cs::module::flatten_parameters(scheduler(), *model, cs::module::FlattenOptions{});
+  cs::module::AdamW optimizer{scheduler(), *model, flat, cs::optimizer::AdamW::Options{}.lr(3e-3).beta1(0.9).beta2(0.95).weight_decay(0.0)};
+  cs::data::SyntheticDataLoader loader{4, 64, 512, 5};
+  auto batch = loader.load(scheduler());  // one fixed batch: the model has to memorise it
+  double first = 0, last = 0;
+  for (int step = 0; step < 8; ++step) {
+    auto loss = model->forward_loss(scheduler(), batch["input_ids"], batch["labels"]);
+    model->backward_loss(scheduler());
+    optimizer->step(scheduler());
+    optimizer->zero_grad(scheduler());
+    last = host(loss).item<double>();
+    if (step == 0) first = last;
+  }
+  EXPECT_TRUE(std::abs(first - std::log(512.0)) < 0.3);  // random init: close to log(vocab)
+  EXPECT_TRUE(last < first - 0.5);
 }
 
 int main(int argc, char **argv) {
