@@ -48,8 +48,7 @@ void write_float_list_table(const std::string &path, const std::vector<std::stri
 FloatListTable read_float_list_table(const std::string &path) {
   auto input = take(arrow::io::ReadableFile::Open(path), "open checkpoint");
   auto reader = take(parquet::arrow::OpenFile(input, arrow::default_memory_pool()), "open parquet reader");
-  std::shared_ptr<arrow::Table> table;
-  check(reader->ReadTable(&table), "read table");
+  std::shared_ptr<arrow::Table> table = take(reader->ReadTable(), "read table");
   if (table->num_columns() < 2) throw std::runtime_error("checkpoint needs the columns key and value");
   FloatListTable out;
   auto key_col = table->column(0);
