@@ -233,6 +233,62 @@ def case_dp_training(device, nvp2p):
     assert bucket.launches() >= 3
 
 
+def case_resume_smaller_world(device, nvp2p):
+    """After a lost rank the job restarts from the last checkpoint with fewer ranks: the checkpoint is rank-agnostic
+    (full parameters and moments, written by one rank), so one process that accumulates the micro-batches of both
+    former ranks continues exactly where the two-rank job would have."""
+    import shutil
+
+    comm, rank, world, s = make_comm(device, nvp2p)
+    directory = f"/tmp/cs_resume_{os.environ.get('MASTER_PORT', '0')}"
+    g = torch.Generator().manual_seed(11)
+    batches = [torch.randint(0, 128, (world, 2, 33), generator=g) for _ in range(3)]
+
+    def micro_step(m, x, sync=None):
+        m.forward_loss(s, T(x[:, :-1].contiguous()), T(x[:, 1:].contiguous()))
+        m.backward_loss(s, sync) if sync is not None else m.backward_loss(s)
+
+    _, model = tiny_model(s)
+    opt = cs.AdamW(s, model, lr=1e-2, weight_decay=0.1, flat=C.flatten_parameters(s, model))
+    opt.set_grad_scale(1.0 / world)
+    bucket = cs.AllReduceBucket(64 * 1024, "sum")
+    sync = cs.GradientSync(comm, bucket, True)
+
+    def dp_step(ids):
+        micro_step(model, ids[rank], sync)
+        bucket.sync(s, comm)
+        opt.step(s)
+        opt.zero_grad(s)
+
+    for ids in batches[:2]:
+        dp_step(ids)
+    meta = C.CheckpointMeta()
+    meta.step, meta.data_cursor, meta.world_size, meta.model = 2, 2, world, "tiny"
+    C.save_training_state(s, directory, model, opt, meta, rank, 0)  # every rank drains, rank 0 writes
+    dist.barrier()
+    dp_step(batches[2])  # the uninterrupted two-rank job
+    s.synchronize()
+
+    # the restarted job: one rank, a different initialisation, everything from the files
+    _, alone = tiny_model(s, seed=99)
+    opt1 = cs.AdamW(s, alone, lr=1e-2, weight_decay=0.1, flat=C.flatten_parameters(s, alone))
+    got = C.load_training_state(s, directory, alone, opt1)
+    assert got.step == 2 and got.world_size == world
+    opt1.set_grad_scale(1.0 / got.world_size)  # the global batch stays the same: accumulate the former ranks' micro-batches
+    for r in range(got.world_size):
+        micro_step(alone, batches[got.data_cursor][r])
+    opt1.step(s)
+    opt1.zero_grad(s)
+    s.synchronize()
+    pa, pb = alone.named_parameters(), model.named_parameters()
+    for k in pa:
+        a, b = pa[k].raw().float(), pb[k].raw().float()
+        assert torch.allclose(a, b, atol=1e-5), (rank, k, (a - b).abs().max().item())
+    dist.barrier()
+    if rank == 0:
+        shutil.rmtree(directory, ignore_errors=True)
+
+
 def case_zero_training(device, nvp2p):
     """ZeRO (fused reduce-scatter + AdamW + all-gather) equals replicated data-parallel AdamW."""
     comm, rank, world, s = make_comm(device, True)
