@@ -222,3 +222,38 @@ def test_symmetric_arena_offsets_coalesce_and_return_to_the_top():
     small.release(*f)
     h = small.allocate(50)  # best fit splits nothing smaller than the alignment
     assert h == f and g[0] == 256
+
+
+def test_symmetric_arena_random_sequences_never_overlap_and_fully_coalesce():
+    """Property test of the offset allocator: live blocks are disjoint, aligned and inside the arena whatever the order
+    of requests and releases, and once everything is released the arena is whole again."""
+    from hypothesis import given, settings, strategies as st
+
+    arena = 1 << 20
+
+    @settings(max_examples=60, deadline=None)
+    @given(st.lists(st.tuples(st.booleans(), st.integers(1, 200_000), st.integers(0, 1 << 30)), min_size=1, max_size=60))
+    def run(ops):
+        ctx = cs._C.SymmetricContext(arena_bytes=arena)
+        live = []
+        for is_alloc, size, pick in ops:
+            if is_alloc or not live:
+                try:
+                    block = ctx.allocate(size)
+                except RuntimeError as e:
+                    assert "exhausted" in str(e)
+                    continue
+                off, n = block
+                assert off % 256 == 0 and n % 256 == 0 and n >= size and off + n <= arena
+                for o, m in live:
+                    assert off + n <= o or o + m <= off, (block, (o, m))
+                live.append(block)
+            else:
+                ctx.release(*live.pop(pick % len(live)))
+            assert ctx.bytes_in_use() == sum(m for _, m in live)
+        for block in live:
+            ctx.release(*block)
+        assert ctx.bytes_in_use() == 0 and ctx.cached_blocks() == 0
+        assert ctx.allocate(arena) == (0, arena)
+
+    run()
