@@ -233,6 +233,46 @@ def case_dp_training(device, nvp2p):
     assert bucket.launches() >= 3
 
 
+def case_loader_shards_by_rank(device, nvp2p):
+    """rows / world rows per rank starting at rank * rows / world, split again over the workers, batches handed out
+    worker by worker (the reference's arithmetic, src/data/dataloader.cpp:371-420); iterations per epoch = rows / (batch * world)."""
+    import shutil
+
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+
+    comm, rank, world, s = make_comm(device, nvp2p)
+    directory = f"/tmp/cs_loader_{os.environ.get('MASTER_PORT', '0')}"
+    rows_per_file, cols = [10, 6, 16], 8  # 32 rows in three files; boundaries do not coincide with the shards
+    if rank == 0:
+        os.makedirs(directory, exist_ok=True)
+        start = 0
+        for i, rows in enumerate(rows_per_file):
+            ids = [[(start + r) * 1000 + c for c in range(cols)] for r in range(rows)]
+            table = pa.table({"input_ids": pa.array(ids, type=pa.list_(pa.int32())),
+                              "labels": pa.array([[v + 1 for v in row] for row in ids], type=pa.list_(pa.int32()))})
+            pq.write_table(table, os.path.join(directory, f"data-{i:05d}-of-00003.parquet"))
+            start += rows
+    dist.barrier()
+    ds = C.LlmDataset(directory)
+    assert ds.size() == 32
+    loader = C.LlmDataLoader(ds, comm, 2, 2, False)  # 16 rows per rank, 8 per worker, 4 batches of 2 per worker
+    assert loader.iterations_per_epoch() == 32 // (2 * world)
+    base = rank * (32 // world)
+    per_worker = (32 // world) // 2
+    seen = [(loader.load(s)["input_ids"].raw()[:, 0] // 1000).tolist() for _ in range(8)]
+    expected = []
+    for i in range(4):
+        for w in range(2):
+            first = base + w * per_worker + 2 * i
+            expected.append([first, first + 1])
+    assert seen == expected, (rank, seen, expected)
+    del loader
+    dist.barrier()
+    if rank == 0:
+        shutil.rmtree(directory, ignore_errors=True)
+
+
 def case_resume_smaller_world(device, nvp2p):
     """After a lost rank the job restarts from the last checkpoint with fewer ranks: the checkpoint is rank-agnostic
     (full parameters and moments, written by one rank), so one process that accumulates the micro-batches of both
