@@ -33,6 +33,7 @@ CPP_SOURCES = [
     "src/parquet_io.cpp",
     "src/communication.cpp",
     "src/comm_nccl.cpp",
+    "src/comm_threads.cpp",
     "src/symmetric.cpp",
     "src/data.cpp",
     "src/observability.cpp",

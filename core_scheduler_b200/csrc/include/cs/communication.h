@@ -18,7 +18,7 @@
 #include "cs/core.h"
 
 namespace cs::communication {
-enum BackendType { kMPI = 0, kNCCL, kNVP2P, kGLOO };
+enum BackendType { kMPI = 0, kNCCL, kNVP2P, kGLOO, kTHREADS };
 enum Operation { kSUM = 0, kAVG };
 
 struct SymmetricContext;  // cs/symmetric.h
@@ -63,6 +63,14 @@ CS_API Comm wrap_backend(c10::intrusive_ptr<c10d::Backend> backend, int64_t rank
                          c10::intrusive_ptr<c10d::Store> store = {});
 // Single-process communicator of size 1.
 CS_API Comm get_comm_self();
+// In-process group for host-side tests (kTHREADS): `size` communicators, one per rank, to be used from `size`
+// threads of this process (each with a scheduler of its own). A collective that not every rank joins within
+// `timeout_ms` raises cs::Error on the ranks that did, and the group stays broken afterwards.
+CS_API std::vector<Comm> create_thread_comms(int64_t size, int64_t timeout_ms = 30000);
+// Fault injection for such a group: this rank sleeps `delay_ms` before it joins each collective.
+CS_API void set_thread_comm_delay(const Comm &comm, int64_t delay_ms);
+// Collectives the group has started so far.
+CS_API int64_t thread_comm_collectives(const Comm &comm);
 // Shuts down and forgets the communicators created from the environment (get_comm_world / get_comm_node). Call
 // it before main() returns: their NCCL process groups must go while the CUDA driver is still up.
 CS_API void finalize();

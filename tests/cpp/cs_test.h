@@ -4,9 +4,11 @@
 //
 //   CS_TEST(Linear, ForwardBackwardFloat32) { EXPECT_TRUE(...); EXPECT_CLOSE(a, b, rtol, atol); }
 //   int main(int argc, char **argv) { return cs_test::run_all(argc, argv); }      [--filter SUBSTRING]
+// Options come in "--name value" pairs; run_all reads --filter and ignores the others.
 #pragma once
 #include <ATen/ATen.h>
 
+#include <atomic>
 #include <cstdio>
 #include <exception>
 #include <functional>
@@ -22,8 +24,8 @@ inline std::vector<Case> &registry() {
   static std::vector<Case> cases;
   return cases;
 }
-inline int &failures_of_current() {
-  static int n = 0;
+inline std::atomic<int> &failures_of_current() {  // atomic: a test body may run on several rank threads at once
+  static std::atomic<int> n{0};
   return n;
 }
 struct Registrar {
@@ -47,7 +49,17 @@ inline bool close(const at::Tensor &a, const at::Tensor &b, double rtol, double 
   if (a.sizes() != b.sizes()) return false;
   return at::allclose(a.detach().to(at::kCPU, at::kDouble), b.detach().to(at::kCPU, at::kDouble), rtol, atol);
 }
-inline int run_all(int argc, char **argv) {
+// Runs a test body and turns an exception into a recorded failure (also used by rank threads).
+inline void guarded(const std::function<void()> &body) {
+  try {
+    body();
+  } catch (const std::exception &e) {
+    report(false, "exception", 0, e.what());
+  }
+}
+// `runner` executes a test body; the default calls it on this thread, a multi-rank program passes one that runs it
+// on every rank thread.
+inline int run_all(int argc, char **argv, const std::function<void(const std::function<void()> &)> &runner = guarded) {
   std::string filter;
   for (int i = 1; i + 1 < argc; i += 2)
     if (std::string(argv[i]) == "--filter") filter = argv[i + 1];
@@ -57,14 +69,10 @@ inline int run_all(int argc, char **argv) {
     std::printf("[ RUN    ] %s\n", c.name.c_str());
     std::fflush(stdout);
     failures_of_current() = 0;
-    try {
-      c.body();
-    } catch (const std::exception &e) {
-      report(false, "exception", 0, e.what());
-    }
+    runner(c.body);
     ++ran;
-    if (failures_of_current()) ++failed;
-    std::printf("[ %s ] %s\n", failures_of_current() ? "FAILED" : "    OK", c.name.c_str());
+    if (failures_of_current() > 0) ++failed;
+    std::printf("[ %s ] %s\n", failures_of_current() > 0 ? "FAILED" : "    OK", c.name.c_str());
   }
   std::printf("%d tests ran, %d failed\n", ran, failed);
   std::fflush(stdout);

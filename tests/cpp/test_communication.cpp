@@ -7,10 +7,15 @@
 // program runs as a single rank (on the CPU when there is no GPU) and checks the one-rank semantics.
 //
 //   python examples/launch.py --nproc 2 -- tests/cpp/bin/cs_b200_communication_tests [--filter SUBSTRING]
+//   tests/cpp/bin/cs_b200_communication_tests --threads 4      (ranks as threads of one process, on the CPU)
 #include <cuda_runtime.h>
 #include <torch/torch.h>
 
+#include <chrono>
 #include <cstdlib>
+#include <memory>
+#include <mutex>
+#include <thread>
 
 #include "cs/communication.h"
 #include "cs/compute.h"
@@ -21,13 +26,15 @@ int env_int(const char *name, int fallback) {
   const char *v = std::getenv(name);
   return v ? std::atoi(v) : fallback;
 }
-cs::DynamicScheduler &scheduler() {
-  static cs::DynamicScheduler s{env_int("LOCAL_RANK", 0)};
-  return s;
-}
-// Owned by main(): the communicator has to go before main returns, while the CUDA driver is still up.
-cs::communication::Comm *g_comm = nullptr;
-cs::communication::Comm &comm() { return *g_comm; }
+// One per rank: the process itself (launcher mode) or a thread of it (--threads N).
+struct RankContext {
+  std::unique_ptr<cs::DynamicScheduler> scheduler;
+  cs::communication::Comm comm;
+};
+thread_local RankContext *g_rank = nullptr;
+std::vector<cs::communication::Comm> g_doomed;  // --threads mode: a second group with a 300 ms rendezvous timeout
+cs::DynamicScheduler &scheduler() { return *g_rank->scheduler; }
+cs::communication::Comm &comm() { return g_rank->comm; }
 at::Device device() { return scheduler().device(); }
 int64_t rank() { return comm().get_rank(); }
 int64_t world() { return comm().get_size(); }
@@ -116,13 +123,72 @@ CS_TEST(AllToAll, BlockFromRankJIsItsDrawForMe) {
     }
 }
 
+CS_TEST(FailureDetection, ARankThatNeverJoinsEndsTheCollectiveWithAnError) {
+  // host-side only: the in-process group's rendezvous has a timeout; main() made a second group with a short one
+  if (g_doomed.empty()) return;
+  auto all_reduce = [&](const cs::communication::Comm &c, int64_t seed) {
+    cs::communication::AllReduce::run_inplace(scheduler(), c, {wrap(draw(seed, 8, at::kFloat))}, cs::communication::kSUM);
+  };
+  all_reduce(comm(), 1);  // everybody is here
+  if (rank() != world() - 1) {  // the last rank stays away from the next one
+    bool raised = false;
+    try {
+      all_reduce(g_doomed[static_cast<size_t>(rank())], 2);
+    } catch (const std::exception &e) {
+      raised = std::string(e.what()).find("did not join") != std::string::npos || std::string(e.what()).find("broken") != std::string::npos;
+    }
+    EXPECT_TRUE(raised);
+  }
+  all_reduce(comm(), 3);  // the healthy group is unaffected
+}
+
+CS_TEST(FailureDetection, ASlowRankOnlyDelaysTheOthers) {
+  if (comm().impl()->type != cs::communication::kTHREADS || world() < 2) return;
+  if (rank() == 0) cs::communication::set_thread_comm_delay(comm(), 100);
+  const auto t0 = std::chrono::steady_clock::now();
+  auto x = wrap(draw(rank() + 1, 16, at::kFloat));
+  cs::communication::AllReduce::run_inplace(scheduler(), comm(), {x}, cs::communication::kSUM);
+  const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+  at::Tensor expected = at::zeros({16});
+  for (int64_t r = 0; r < world(); ++r) expected += draw(r + 1, 16, at::kFloat);
+  EXPECT_CLOSE(host(x), expected, 1e-5, 1e-6);
+  EXPECT_TRUE(ms >= 90.0);  // nobody got past the rendezvous before the slow rank arrived
+  if (rank() == 0) cs::communication::set_thread_comm_delay(comm(), 0);
+}
+
 int main(int argc, char **argv) {
+  int threads = 0;
+  for (int i = 1; i + 1 < argc; i += 2)
+    if (std::string(argv[i]) == "--threads") threads = std::atoi(argv[i + 1]);
+  if (threads > 0) {
+    // every rank is a thread of this process with a CPU scheduler of its own; collectives go through shared memory
+    auto comms = cs::communication::create_thread_comms(threads);
+    g_doomed = cs::communication::create_thread_comms(threads, 300);
+    std::vector<RankContext> ranks(static_cast<size_t>(threads));
+    for (int r = 0; r < threads; ++r) {
+      ranks[static_cast<size_t>(r)].scheduler = std::make_unique<cs::DynamicScheduler>(0, cs::DynamicScheduler::Options{}.device_type(at::kCPU));
+      ranks[static_cast<size_t>(r)].comm = comms[static_cast<size_t>(r)];
+    }
+    std::printf("%d rank threads on cpu\n", threads);
+    return cs_test::run_all(argc, argv, [&](const std::function<void()> &body) {
+      std::vector<std::thread> pool;
+      for (int r = 0; r < threads; ++r)
+        pool.emplace_back([&, r] {
+          g_rank = &ranks[static_cast<size_t>(r)];
+          cs_test::guarded(body);
+        });
+      for (auto &t : pool) t.join();
+    });
+  }
   if (torch::cuda::is_available()) cudaSetDevice(env_int("LOCAL_RANK", 0));
-  g_comm = new cs::communication::Comm{cs::communication::get_comm_world(cs::communication::kNCCL)};
+  RankContext self;
+  self.scheduler = std::make_unique<cs::DynamicScheduler>(env_int("LOCAL_RANK", 0));
+  self.comm = cs::communication::get_comm_world(cs::communication::kNCCL);
+  g_rank = &self;
   std::printf("rank %ld of %ld on %s\n", static_cast<long>(rank()), static_cast<long>(world()), device().str().c_str());
   const int failed = cs_test::run_all(argc, argv);
   scheduler().impl()->synchronize();
   cs::communication::finalize();
-  delete g_comm;
+  self.comm = cs::communication::Comm{};
   return failed;
 }
