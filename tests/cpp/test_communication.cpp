@@ -19,6 +19,7 @@
 
 #include "cs/communication.h"
 #include "cs/compute.h"
+#include "cs/models.h"
 #include "cs_test.h"
 
 namespace {
@@ -123,6 +124,52 @@ CS_TEST(AllToAll, BlockFromRankJIsItsDrawForMe) {
     }
 }
 
+CS_TEST(DataParallel, BucketedGradientSyncEqualsOneProcessOnTheWholeBatch) {
+  // every rank trains on its own micro-batches with the bucketed all-reduce overlapping backward; a second model on
+  // the same rank accumulates all ranks' micro-batches locally; after three AdamW steps the parameters agree
+  if (device().is_cuda()) return;  // fp32 on the CPU is deterministic; the GPU variant lives in the Python tests
+  static std::mutex init_mutex;  // model initialisation draws from the process-wide generator
+  auto config = cs::models::GPT2Config::tiny();
+  auto make = [&] {
+    std::lock_guard<std::mutex> lock{init_mutex};
+    cs::manual_seed(21);
+    return cs::models::GPT2{scheduler(), config};
+  };
+  auto model = make(), reference = make();
+  auto optimizer_of = [&](cs::models::GPT2 &m) {
+    auto flat = cs::module::flatten_parameters(scheduler(), *m, cs::module::FlattenOptions{});
+    cs::module::AdamW opt{scheduler(), *m, flat, cs::optimizer::AdamW::Options{}.lr(1e-2).beta1(0.9).beta2(0.95).weight_decay(0.1)};
+    opt->set_grad_scale(1.0 / static_cast<double>(world()));
+    return opt;
+  };
+  auto optimizer = optimizer_of(model), reference_optimizer = optimizer_of(reference);
+  cs::communication::AllReduceBucket bucket{64 * 1024, cs::communication::kSUM};
+  cs::models::GradientSync sync{comm(), &bucket, true};
+  auto batch_of = [&](int step, int64_t r) {
+    auto generator = at::detail::createCPUGenerator(static_cast<uint64_t>(1000 * step + r + 1));
+    return at::randint(0, config.vocab_size(), {2, 33}, generator, at::TensorOptions{}.dtype(at::kLong));
+  };
+  auto forward = [&](cs::models::GPT2 &m, const at::Tensor &ids) {
+    return m->forward_loss(scheduler(), wrap(ids.slice(1, 0, 32).contiguous()), wrap(ids.slice(1, 1, 33).contiguous()));
+  };
+  for (int step = 0; step < 3; ++step) {
+    forward(model, batch_of(step, rank()));
+    model->backward_loss(scheduler(), sync);
+    bucket.sync(scheduler(), comm());
+    optimizer->step(scheduler());
+    optimizer->zero_grad(scheduler());
+    for (int64_t r = 0; r < world(); ++r) {
+      forward(reference, batch_of(step, r));
+      reference->backward_loss(scheduler());
+    }
+    reference_optimizer->step(scheduler());
+    reference_optimizer->zero_grad(scheduler());
+  }
+  auto mine = model->named_parameters(), expected = reference->named_parameters();
+  for (auto &item : mine) EXPECT_CLOSE(host(item.value()), host(expected[item.key()]), 1e-4, 1e-5);
+  EXPECT_TRUE(bucket.launches() >= 3);
+}
+
 CS_TEST(FailureDetection, ARankThatNeverJoinsEndsTheCollectiveWithAnError) {
   // host-side only: the in-process group's rendezvous has a timeout; main() made a second group with a short one
   if (g_doomed.empty()) return;
@@ -157,6 +204,9 @@ CS_TEST(FailureDetection, ASlowRankOnlyDelaysTheOthers) {
 }
 
 int main(int argc, char **argv) {
+  // one intra-op thread: reductions then add in a fixed order, so two runs of the same arithmetic agree bit for bit
+  // (AdamW's normalised update turns a last-bit difference of a near-zero gradient into a visible one)
+  at::set_num_threads(1);
   int threads = 0;
   for (int i = 1; i + 1 < argc; i += 2)
     if (std::string(argv[i]) == "--threads") threads = std::atoi(argv[i + 1]);
@@ -175,6 +225,7 @@ int main(int argc, char **argv) {
       for (int r = 0; r < threads; ++r)
         pool.emplace_back([&, r] {
           g_rank = &ranks[static_cast<size_t>(r)];
+          at::set_num_threads(1);  // the setting is per calling thread
           cs_test::guarded(body);
         });
       for (auto &t : pool) t.join();
