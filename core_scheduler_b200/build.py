@@ -200,8 +200,21 @@ def build_cpp_tests() -> list[str]:
     return _build_programs(root, [root], {"test_ops": "cs_b200_tests", "test_communication": "cs_b200_communication_tests"})
 
 
+def _sources_digest(files) -> str:
+    import hashlib
+
+    h = hashlib.sha256()
+    for f in sorted(files):
+        h.update(str(f.name).encode())
+        h.update(f.read_bytes())
+    return h.hexdigest()
+
+
 def _build_programs(root: Path, extra_inc: list, names: dict | None = None) -> list[str]:
-    build()
+    # A shipped snapshot carries the built library but not the object files: there is nothing to bring up to date
+    # there, and running the build would compile every kernel again.
+    if not (is_built() and not any(BUILD.glob("*.o"))):
+        build()
     p = _paths()
     out_dir = root / "bin"
     out_dir.mkdir(exist_ok=True)
@@ -209,7 +222,11 @@ def _build_programs(root: Path, extra_inc: list, names: dict | None = None) -> l
     built = []
     for src in sorted(root.glob("*.cpp")):
         exe = out_dir / (names or {}).get(src.stem, src.stem)
-        if exe.exists() and exe.stat().st_mtime > max(f.stat().st_mtime for f in [src, LIBDIR / "libcs_b200.so", *root.glob("*.h")]):
+        # up to date = same program source and same headers as when it was compiled (content, not time stamps, which
+        # a copy of the tree does not keep); the library itself is linked dynamically
+        stamp = out_dir / (exe.name + ".stamp")
+        digest = _sources_digest([src, *root.glob("*.h"), *(f for f in (CSRC / "include").rglob("*.h"))])
+        if exe.exists() and stamp.exists() and stamp.read_text() == digest:
             built.append(str(exe))
             continue
         cmd = [os.environ.get("CS_CXX", "g++"), "-std=c++20", "-O2", "-Wno-interference-size",
@@ -218,6 +235,7 @@ def _build_programs(root: Path, extra_inc: list, names: dict | None = None) -> l
                 "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda", f"-L{p['cuda_home'] / 'lib64'}", "-lcudart",
                 f"-Wl,-rpath,{LIBDIR}", f"-Wl,-rpath,{p['torch_lib']}", f"-Wl,-rpath,{p['arrow_lib']}", "-Wl,--no-as-needed"]
         subprocess.run(cmd, check=True)
+        stamp.write_text(digest)
         built.append(str(exe))
     return built
 
