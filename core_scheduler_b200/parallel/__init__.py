@@ -32,3 +32,81 @@ def init_distributed(device: str = "cuda", timeout_s: float = 600.0):
     pg = dist.distributed_c10d._get_default_group()
     comm = _C.comm_from_process_group(pg.group_name, device)
     return comm, rank, world, local_rank
+
+
+class GPT2Trainer:
+    """One training step of GPT-2 under a parallelisation strategy, assembled from the native pieces.
+
+    mode "dp"   data parallel: every rank owns the model; gradient ranges are all-reduced in buckets while the
+                backward pass continues, and the average is folded into the optimizer kernel (the reference's
+                example/gpt2/gpt2_ddp.cpp does the same with NCCL buckets).
+         "zero" data parallel with the sharded optimizer: reduce-scatter + AdamW + all-gather in one kernel (GPUs).
+         "tp"   tensor + sequence parallel over all ranks; every rank sees the whole batch (GPUs, or Gloo ranks).
+    collectives "nvp2p" runs this library's peer-memory kernels (GPUs with peer access), "nccl" the library's.
+    On GPUs the parameters are fp32 masters with bf16 working copies and the step runs under bf16 autocast; on the
+    CPU everything is fp32.
+
+        comm, rank, world, local_rank = init_distributed("cuda")
+        trainer = GPT2Trainer(gpt2_config("124M"), comm, world, local_rank, mode="dp")
+        loss = trainer.step(input_ids, labels)          # core_scheduler_b200.Tensor handles
+    """
+
+    def __init__(self, config, comm=None, world: int = 1, local_rank: int = 0, mode: str = "dp", collectives: str = "nvp2p",
+                 device: str = "cuda", lr: float = 3e-4, beta1: float = 0.9, beta2: float = 0.95, weight_decay: float = 0.1,
+                 bucket_mb: float = 25.0, seed: int = 1234, scheduler=None):
+        import core_scheduler_b200 as cs
+
+        assert mode in ("dp", "zero", "tp") and collectives in ("nvp2p", "nccl")
+        self.config, self.world, self.mode, self.device = config, world, mode, device
+        self.amp = device == "cuda"
+        self.scheduler = scheduler or cs.DynamicScheduler(local_rank if device == "cuda" else 0, device=device)
+        s = self.scheduler
+        self.comm = comm if comm is not None else _C.get_comm_self()
+        self.bucket = self.sync = self.symmetric = None
+        peer = device == "cuda" and world > 1 and (collectives == "nvp2p" or mode == "zero")
+        if peer:  # the same ranks, with collectives on peer-mapped symmetric memory
+            pg = dist.distributed_c10d._get_default_group()
+            self.comm = _C.comm_from_process_group(pg.group_name, "cuda", True)
+        cs.manual_seed(seed)  # identical initial weights on every rank
+        lp = dict(lp_dtype=torch.bfloat16) if self.amp else {}
+        if mode == "tp" and world > 1:
+            if peer:
+                self.symmetric = _C.create_symmetric_context(self.comm, 2 << 30)
+            self.model = _C.TPGPT2(s, config, self.comm)
+            self.flat = _C.flatten_parameters(s, self.model, **lp)
+        else:
+            self.model = cs.GPT2(s, config)
+            if peer:
+                arena = config.parameter_count() * 6 + (256 << 20)  # fp32 gradients + bf16 copies + staging
+                self.symmetric = _C.create_symmetric_context(self.comm, int(arena))
+                self.flat = _C.flatten_symmetric(s, self.model, self.comm)
+            else:
+                self.flat = _C.flatten_parameters(s, self.model, **lp)
+        if mode == "zero" and world > 1:
+            assert peer, "the sharded optimizer runs on GPUs with peer access"
+            self.optimizer = _C.ZeroAdamW(s, self.model, self.flat, self.comm, lr=lr, beta1=beta1, beta2=beta2,
+                                          weight_decay=weight_decay)
+        else:
+            self.optimizer = cs.AdamW(s, self.model, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay, flat=self.flat)
+            if world > 1:
+                self.optimizer.set_grad_scale(1.0 / world)
+                self.bucket = cs.AllReduceBucket(int(bucket_mb * (1 << 20)), "sum")
+                self.sync = cs.GradientSync(self.comm, self.bucket, True)
+        s.synchronize()
+
+    def step(self, input_ids, labels):
+        """Forward, backward (gradient communication overlapped), optimizer update; returns the loss handle."""
+        import core_scheduler_b200 as cs
+
+        s, m = self.scheduler, self.model
+        if self.amp:
+            with cs.autocast(s, torch.bfloat16):
+                loss = m.forward_loss(s, input_ids, labels)
+        else:
+            loss = m.forward_loss(s, input_ids, labels)
+        m.backward_loss(s, self.sync) if self.sync is not None else m.backward_loss(s)
+        if self.bucket is not None:
+            self.bucket.sync(s, self.comm)
+        self.optimizer.step(s)
+        self.optimizer.zero_grad(s)
+        return loss

@@ -233,6 +233,45 @@ def case_dp_training(device, nvp2p):
     assert bucket.launches() >= 3
 
 
+def case_trainer(device, nvp2p):
+    """parallel.GPT2Trainer: two data-parallel ranks follow one process that accumulates both micro-batches; the
+    tensor-parallel trainer's loss falls on every rank."""
+    from core_scheduler_b200.parallel import GPT2Trainer
+
+    comm, rank, world, s = make_comm(device, nvp2p)
+    cfg = cs.GPT2Config(n_layer=2, n_head=2, n_embd=64, block_size=32, vocab_size=128, padded_vocab_size=128)
+    kind = "nvp2p" if nvp2p else "nccl"
+    dp = GPT2Trainer(cfg, comm, world, int(os.environ.get("LOCAL_RANK", "0")), mode="dp", collectives=kind, device=device, lr=1e-2,
+                     bucket_mb=0.0625, scheduler=s)
+    alone = GPT2Trainer(cfg, None, 1, 0, mode="dp", device=device, lr=1e-2, scheduler=s)
+    alone.optimizer.set_grad_scale(1.0 / world)
+    init = {k: v.raw().float().clone() for k, v in alone.model.named_parameters().items()}
+    g = torch.Generator().manual_seed(13)
+    for step in range(3):
+        ids = torch.randint(0, 128, (world, 2, 33), generator=g).to(device)
+        dp.step(T(ids[rank][:, :-1].contiguous()), T(ids[rank][:, 1:].contiguous()))
+        for r in range(world):  # the single process accumulates every rank's micro-batch before its update
+            x, y = T(ids[r][:, :-1].contiguous()), T(ids[r][:, 1:].contiguous())
+            if alone.amp:
+                with cs.autocast(s, torch.bfloat16):
+                    alone.model.forward_loss(s, x, y)
+            else:
+                alone.model.forward_loss(s, x, y)
+            alone.model.backward_loss(s)
+        alone.optimizer.step(s)
+        alone.optimizer.zero_grad(s)
+    s.synchronize()
+    assert_same_training(dp.model, alone.model, init, rank, dp.amp)
+    assert dp.bucket.launches() >= 3
+
+    tp = GPT2Trainer(cfg, comm, world, int(os.environ.get("LOCAL_RANK", "0")), mode="tp", collectives=kind, device=device, lr=1e-2,
+                     scheduler=s)
+    ids = torch.randint(0, 128, (2 * world, 33), generator=torch.Generator().manual_seed(17)).to(device)
+    losses = [tp.step(T(ids[:, :-1].contiguous()), T(ids[:, 1:].contiguous())).raw().float().item() for _ in range(5)]
+    assert losses[-1] < losses[0] - 0.2, losses
+    # sequence parallel: each rank's loss is the mean over its own share of the token rows
+
+
 def case_loader_shards_by_rank(device, nvp2p):
     """rows / world rows per rank starting at rank * rows / world, split again over the workers, batches handed out
     worker by worker (the reference's arithmetic, src/data/dataloader.cpp:371-420); iterations per epoch = rows / (batch * world)."""
