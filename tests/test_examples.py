@@ -49,12 +49,12 @@ def test_launcher_sets_rendezvous_environment_and_propagates_failure():
     launch = os.path.join(ROOT, "examples", "launch.py")
     ok = subprocess.run([sys.executable, launch, "--nproc", "3", "--master-port", "29777", "--", sys.executable, "-c",
                          "import os; print('R', os.environ['RANK'], os.environ['LOCAL_RANK'], os.environ['WORLD_SIZE'], "
-                         "os.environ['MASTER_ADDR'], os.environ['MASTER_PORT'])"], capture_output=True, text=True, timeout=60)
+                         "os.environ['MASTER_ADDR'], os.environ['MASTER_PORT'])"], capture_output=True, text=True, timeout=180)
     assert ok.returncode == 0, ok.stdout + ok.stderr
     assert sorted(l for l in ok.stdout.splitlines() if l.startswith("R ")) == [f"R {r} {r} 3 127.0.0.1 29777" for r in range(3)]
     bad = subprocess.run([sys.executable, launch, "--nproc", "2", "--", sys.executable, "-c",
                           "import os, sys, time; sys.exit(7) if os.environ['RANK'] == '1' else time.sleep(30)"],
-                         capture_output=True, text=True, timeout=60)
+                         capture_output=True, text=True, timeout=180)
     assert bad.returncode == 7, (bad.returncode, bad.stdout + bad.stderr)  # rank 1 failed; the sleeping rank 0 was stopped, not waited for
 
 
