@@ -506,6 +506,46 @@ def case_tp_training(device, nvp2p, batch_per_rank=2, expect_fused=False, n_head
             assert torch.allclose(got, ref, **tol), (rank, k, (got - ref).abs().max().item())
 
 
+def case_tp_checkpoint_merge(device, nvp2p):
+    """Per-rank parameter files of a tensor-parallel model (uneven heads: 3 over 2 ranks) unite into a file that the
+    unsharded model loads, and that model then computes the tensor-parallel ranks' mean loss."""
+    import shutil
+
+    from core_scheduler_b200.utils.checkpoint import merge_tensor_parallel, read_parameters, write_parameters
+
+    comm, rank, world, s = make_comm(device, nvp2p)
+    cs.manual_seed(23 + rank)  # the ranks' own shards must differ for the test to mean anything
+    cfg = cs.GPT2Config(n_layer=2, n_head=3, n_embd=48, block_size=32, vocab_size=128, padded_vocab_size=128, dtype=torch.float64)
+    tp = C.TPGPT2(s, cfg, comm)
+    replicated = tp.replicated_parameters()
+    for k, p in tp.named_parameters().items():  # replicated parameters have to agree across the ranks
+        if k in replicated:
+            dist.broadcast(p.raw(), src=0)
+    directory = f"/tmp/cs_tp_merge_{os.environ.get('MASTER_PORT', '0')}"
+    os.makedirs(f"{directory}/tp_rank{rank}", exist_ok=True)
+    tp.save(f"{directory}/tp_rank{rank}/model.parquet")
+    dist.barrier()
+    merged = merge_tensor_parallel([read_parameters(f"{directory}/tp_rank{r}/model.parquet") for r in range(world)], cfg.n_head, cfg.n_embd)
+    write_parameters(merged, f"{directory}/model.rank{rank}.parquet")
+    cs.manual_seed(99)
+    full = cs.GPT2(s, cfg)
+    full.load(f"{directory}/model.rank{rank}.parquet")  # unknown or missing keys would raise
+    fp = full.named_parameters()
+    for k, p in tp.named_parameters().items():
+        mine = tp_slice(k, fp[full_key(k)].raw(), rank, world, cfg)
+        assert torch.allclose(mine, p.raw(), atol=1e-6), (rank, k)  # the file holds float32 values
+    ids = torch.randint(0, 128, (2 * world, 33), generator=torch.Generator().manual_seed(29))
+    x, y = T(ids[:, :-1].contiguous()), T(ids[:, 1:].contiguous())
+    mine = tp.forward_loss(s, x, y).raw().double().reshape(1)
+    parts = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine)
+    whole = full.forward_loss(s, x, y).raw().item()
+    assert abs(sum(p.item() for p in parts) / world - whole) < 1e-5, (parts, whole)
+    dist.barrier()
+    if rank == 0:
+        shutil.rmtree(directory, ignore_errors=True)
+
+
 def case_watchdog(device, nvp2p):
     """A rank whose loop stalls trips its watchdog; the healthy rank learns of it through the store before its next launch."""
     comm, rank, world, s = make_comm(device, False)
