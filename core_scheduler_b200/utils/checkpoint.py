@@ -98,6 +98,11 @@ def main(argv=None) -> int:
     show.add_argument("file")
     args = parser.parse_args(argv)
     if args.command == "merge":
+        import re
+
+        ranks = [re.search(r"tp_rank(\d+)", p) for p in args.shards]
+        if all(ranks):  # a shell glob lists tp_rank10 before tp_rank2
+            args.shards = [p for _, p in sorted(zip((int(m.group(1)) for m in ranks), args.shards))]
         merged = merge_tensor_parallel([read_parameters(p) for p in args.shards], args.n_head, args.n_embd)
         write_parameters(merged, args.out)
         print(f"wrote {len(merged)} parameters, {sum(v.size for v in merged.values())} values to {args.out}")
