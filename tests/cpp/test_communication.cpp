@@ -20,6 +20,7 @@
 #include "cs/communication.h"
 #include "cs/compute.h"
 #include "cs/models.h"
+#include "cs/parallel.h"
 #include "cs_test.h"
 
 namespace {
@@ -168,6 +169,40 @@ CS_TEST(DataParallel, BucketedGradientSyncEqualsOneProcessOnTheWholeBatch) {
   auto mine = model->named_parameters(), expected = reference->named_parameters();
   for (auto &item : mine) EXPECT_CLOSE(host(item.value()), host(expected[item.key()]), 1e-4, 1e-5);
   EXPECT_TRUE(bucket.launches() >= 3);
+}
+
+CS_TEST(TensorParallel, ShardedModelTrainsOnRankThreads) {
+  // sequence-parallel activations, column/row-parallel Linears: all-gather and reduce-scatter carry the activations,
+  // the bucket carries the replicated parameters' gradients
+  auto config = cs::models::GPT2Config::tiny();  // 4 heads
+  if (device().is_cuda() || world() < 2 || config.n_head() % world() != 0) return;
+  static std::mutex init_mutex;
+  cs::parallel::TPGPT2 model{nullptr};
+  {
+    std::lock_guard<std::mutex> lock{init_mutex};
+    cs::manual_seed(31);
+    model = cs::parallel::TPGPT2{scheduler(), config, comm()};
+  }
+  auto flat = cs::module::flatten_parameters(scheduler(), *model, cs::module::FlattenOptions{});
+  cs::module::AdamW optimizer{scheduler(), *model, flat, cs::optimizer::AdamW::Options{}.lr(3e-3).beta1(0.9).beta2(0.95).weight_decay(0.0)};
+  optimizer->set_grad_scale(1.0 / static_cast<double>(world()));
+  cs::communication::AllReduceBucket bucket{64 * 1024, cs::communication::kSUM};
+  cs::models::GradientSync sync{comm(), &bucket, true};
+  auto generator = at::detail::createCPUGenerator(41);  // every rank sees the whole batch
+  auto ids = at::randint(0, config.vocab_size(), {2 * world(), 33}, generator, at::TensorOptions{}.dtype(at::kLong));
+  auto x = wrap(ids.slice(1, 0, 32).contiguous()), y = wrap(ids.slice(1, 1, 33).contiguous());
+  double first = 0, last = 0;
+  for (int step = 0; step < 6; ++step) {
+    auto loss = model->forward_loss(scheduler(), x, y);
+    model->backward_loss(scheduler(), sync);
+    bucket.sync(scheduler(), comm());
+    optimizer->step(scheduler());
+    optimizer->zero_grad(scheduler());
+    last = host(loss).item<double>();
+    if (step == 0) first = last;
+  }
+  EXPECT_TRUE(std::abs(first - std::log(static_cast<double>(config.vocab_size()))) < 0.4);
+  EXPECT_TRUE(last < first - 0.3);
 }
 
 CS_TEST(FailureDetection, ARankThatNeverJoinsEndsTheCollectiveWithAnError) {

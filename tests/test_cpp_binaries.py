@@ -34,7 +34,7 @@ def test_cpp_communication_tests_as_a_single_rank_on_the_cpu():
     out = subprocess.run([program("cs_b200_communication_tests")], env=dict(env, CUDA_VISIBLE_DEVICES=""), capture_output=True,
                          text=True, timeout=600)
     assert "rank 0 of 1 on cpu" in out.stdout
-    check(out, 8)
+    check(out, 9)
 
 
 @pytest.mark.parametrize("ranks", [2, 4])
@@ -44,7 +44,7 @@ def test_cpp_communication_tests_with_rank_threads(ranks):
     out = subprocess.run([program("cs_b200_communication_tests"), "--threads", str(ranks)],
                          env=dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1"), capture_output=True, text=True, timeout=600)
     assert f"{ranks} rank threads on cpu" in out.stdout
-    check(out, 8)
+    check(out, 9)
 
 
 def test_cpp_harness_reports_a_filter_and_counts(tmp_path):
@@ -67,4 +67,4 @@ def test_cpp_communication_tests_on_two_gpus():
     out = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "launch.py"), "--nproc", "2", "--master-port", "29613", "--",
                           program("cs_b200_communication_tests")], capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
-    assert out.stdout.count("8 tests ran, 0 failed") == 2, out.stdout[-3000:]
+    assert out.stdout.count("9 tests ran, 0 failed") == 2, out.stdout[-3000:]
