@@ -39,6 +39,8 @@ def parse_args():
     p.add_argument("--comm", default="nvp2p", choices=["nvp2p", "nccl"],
                    help="gradient collectives: this library's peer-memory kernels, or NCCL")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-overlap-optimizer", action="store_true",
+                   help="one whole-model AdamW launch after the backward pass instead of per-bucket updates during it")
     p.add_argument("--assist-gap", type=int, default=2, help="main-stream tasks after which an assist-stream task is re-joined")
     p.add_argument("--comm-gap", type=int, default=5, help="main-stream tasks after which a communication task is re-joined")
     p.add_argument("--profile", action="store_true", help="print per-task device time of one step (not a bench value)")
@@ -143,79 +145,33 @@ def reference_arm(args):
         "metric": "GPT-2 train tokens/sec, device-timed max over ranks", "value": float(fields["tokens_per_s"]), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights N(0,0.02)", "impl": "reference",
-        "config": {"model": f"GPT-2 {args.model}", "global_batch": args.micro_batch * world, "micro_batch_per_gpu": args.micro_batch,
-                   "seq_len": args.seq_len, "parallelism": f"dp{world}", "precision": "fp32 parameters under a bf16 autocast guard",
-                   "backend": "reference library (cuBLAS / ATen / flash attention / NCCL), unmodified sources",
-                   "bucket_mb": args.bucket_mb, "l2": "per-step working set exceeds the 126 MB L2; no flush needed"},
+        "config": config_labels(args, world, False),
+        "implementation": {"precision": "fp32 parameters under a bf16 autocast guard",
+                           "backend": "reference library (cuBLAS / ATen / flash attention / NCCL), unmodified sources"},
         "final_loss": float(fields["final_loss"]), "clocks": clocks, "e2e": e2e, "gpu_launches": None}))
     return 0
 
 
-class Trainer:
-    """One optimizer step of GPT-2 through the framework's public API."""
+def make_trainer(args, cs, comm, world, local_rank):
+    """The training step a user of the package gets: core_scheduler_b200.parallel.GPT2Trainer."""
+    from core_scheduler_b200.models import gpt2_config
+    from core_scheduler_b200.parallel import GPT2Trainer
 
-    def __init__(self, args, cs, comm, rank, world, local_rank):
-        from core_scheduler_b200.models import gpt2_config
+    scheduler = cs.DynamicScheduler(local_rank, device="cuda", assist_task_gap=args.assist_gap, comm_task_gap=args.comm_gap)
+    cs._C.set_backend(args.backend)
+    trainer = GPT2Trainer(gpt2_config(args.model, dtype=torch.float32), comm, world, local_rank, mode=args.mode, collectives=args.comm,
+                          device="cuda", lr=3e-4, beta1=0.9, beta2=0.95, weight_decay=0.1, bucket_mb=args.bucket_mb, seed=1234,
+                          scheduler=scheduler, overlap_optimizer=not args.no_overlap_optimizer)
+    trainer.s, trainer.cfg = scheduler, trainer.config
+    trainer.tp = args.mode == "tp" and world > 1
+    return trainer
 
-        self.cs, self.C = cs, cs._C
-        self.comm, self.rank, self.world = comm, rank, world
-        self.s = cs.DynamicScheduler(local_rank, device="cuda", assist_task_gap=args.assist_gap, comm_task_gap=args.comm_gap)
-        self.C.set_backend(args.backend)
-        cs.manual_seed(1234)  # same weights on every rank
-        self.cfg = gpt2_config(args.model, dtype=torch.float32)
-        self.tp = args.mode == "tp" and world > 1
-        self.bucket = None
-        self.sync = None
-        self.zero = args.mode == "zero" and world > 1
-        if self.tp:
-            # tensor parallel: every rank sees the whole (global) batch; sharded Linears, sequence-parallel
-            # activations; only the replicated parameters' gradients go through the all-reduce bucket
-            import torch.distributed as dist
 
-            pg = dist.distributed_c10d._get_default_group()
-            self.comm = comm = self.C.comm_from_process_group(pg.group_name, "cuda", args.comm == "nvp2p")
-            if args.comm == "nvp2p":
-                self.symm = self.C.create_symmetric_context(comm, 2 << 30)
-            self.model = self.C.TPGPT2(self.s, self.cfg, comm)
-            self.flat = self.C.flatten_parameters(self.s, self.model, lp_dtype=torch.bfloat16)
-            self.opt = cs.AdamW(self.s, self.model, lr=3e-4, beta1=0.9, beta2=0.95, weight_decay=0.1, flat=self.flat)
-            self.opt.set_grad_scale(1.0 / world)
-            self.bucket = cs.AllReduceBucket(int(args.bucket_mb * (1 << 20)), "sum")
-            self.sync = cs.GradientSync(comm, self.bucket, True)
-            self.s.synchronize()
-            return
-        self.model = cs.GPT2(self.s, self.cfg)
-        if world > 1 and (args.comm == "nvp2p" or self.zero):
-            import torch.distributed as dist
-
-            pg = dist.distributed_c10d._get_default_group()
-            self.comm = comm = self.C.comm_from_process_group(pg.group_name, "cuda", True)
-            arena = self.cfg.parameter_count() * 6 + (256 << 20)  # fp32 grads + bf16 copies + staging
-            self.symm = self.C.create_symmetric_context(comm, int(arena))
-            self.flat = self.C.flatten_symmetric(self.s, self.model, comm)
-        else:
-            self.flat = self.C.flatten_parameters(self.s, self.model, lp_dtype=torch.bfloat16)
-        if self.zero:
-            self.opt = self.C.ZeroAdamW(self.s, self.model, self.flat, comm, lr=3e-4, beta1=0.9, beta2=0.95, weight_decay=0.1)
-            self.s.synchronize()
-            return
-        self.opt = cs.AdamW(self.s, self.model, lr=3e-4, beta1=0.9, beta2=0.95, weight_decay=0.1, flat=self.flat)
-        if world > 1:
-            self.bucket = cs.AllReduceBucket(int(args.bucket_mb * (1 << 20)), "sum")
-            self.sync = cs.GradientSync(comm, self.bucket, True)
-            self.opt.set_grad_scale(1.0 / world)  # the average is folded into the optimizer kernel
-        self.s.synchronize()
-
-    def step(self, ids, labels):
-        s, m = self.s, self.model
-        with self.cs.autocast(s, torch.bfloat16):
-            loss = m.forward_loss(s, ids, labels)
-        m.backward_loss(s, self.sync)
-        if self.bucket is not None:
-            self.bucket.sync(s, self.comm)
-        self.opt.step(s)
-        self.opt.zero_grad(s)
-        return loss
+def config_labels(args, world, tensor_parallel):
+    """The workload description, identical for both arms when the workload is identical."""
+    return {"model": f"GPT-2 {args.model}", "global_batch": args.micro_batch * (1 if tensor_parallel else world),
+            "micro_batch_per_gpu": args.micro_batch, "seq_len": args.seq_len, "parallelism": f"{args.mode}{world}",
+            "bucket_mb": args.bucket_mb, "l2": "per-step working set exceeds the 126 MB L2; no flush needed"}
 
 
 def max_over_ranks(value: float, world: int) -> float:
@@ -250,7 +206,7 @@ def main():
     comm, rank, world, local_rank = init_distributed("cuda")
     torch.cuda.set_device(local_rank)
     C = cs._C
-    trainer = Trainer(args, cs, comm, rank, world, local_rank)
+    trainer = make_trainer(args, cs, comm, world, local_rank)
     B, T = args.micro_batch, args.seq_len
     vocab = trainer.cfg.vocab_size
 
@@ -348,18 +304,16 @@ def main():
             "dtype": "bf16",
             "data": "synthetic uniform token ids, random-init weights N(0,0.02)",
             "impl": "ours",
-            "config": {
-                "model": f"GPT-2 {args.model} ({trainer.cfg.parameter_count() / 1e6:.1f}M params, untied lm_head)",
-                "global_batch": B * (1 if trainer.tp else world),
-                "micro_batch_per_gpu": B,
-                "seq_len": T,
-                "parallelism": f"{args.mode}{world}",
+            "config": config_labels(args, world, trainer.tp),
+            "implementation": {
+                "parameters": f"{trainer.cfg.parameter_count() / 1e6:.1f}M, untied lm_head",
                 "precision": "bf16 compute, fp32 master weights + AdamW moments",
                 "backend": args.backend,
-                "bucket_mb": args.bucket_mb,
                 "scheduler_gaps": {"assist": args.assist_gap, "comm": args.comm_gap},
                 "collectives": (args.comm if world > 1 else "none"),
-                "l2": f"per-step working set (~{weights_gb:.1f} GB weights/optimizer + activations) exceeds the 126 MB L2; no flush needed",
+                "optimizer": "per-bucket AdamW overlapped with backward" if not args.no_overlap_optimizer and args.mode != "zero" else "after backward",
+                "working_set": f"~{weights_gb:.1f} GB weights/optimizer + activations per step",
+                "library_fallbacks": int(C.library_fallbacks()),
             },
             "final_loss": final_loss,
             "mfu_vs_measured_sustained": None,

@@ -12,6 +12,7 @@
 // bucket receives the reduced value; kNVP2P is implemented: collectives run as this
 // library's own kernels over peer-mapped symmetric memory (see cs/symmetric.h).
 #pragma once
+#include <functional>
 #include <torch/csrc/distributed/c10d/Backend.hpp>
 #include <torch/csrc/distributed/c10d/Store.hpp>
 
@@ -89,6 +90,12 @@ struct CS_API AllReduceBucket : Bucket {
   void sync(const Scheduler &scheduler, const Comm &comm) const;
   void apply(const Scheduler &scheduler, const Comm &comm) const override { sync(scheduler, comm); }
   [[nodiscard]] int64_t launches() const;
+  // Hook that runs after every flush: it receives the tensors of the bucket that was just reduced and the
+  // stream class that orders work after the reduction (the communication stream, or the assist stream for a
+  // single rank, where nothing is reduced). An optimizer attached here updates a bucket's parameters while
+  // the backward pass of the earlier layers is still running (module::AdamWImpl::step_partial).
+  using ReducedCallback = std::function<void(const Scheduler &, const std::vector<Tensor> &, Task::Impl::Priority)>;
+  void on_reduced(ReducedCallback callback) const;
 
  private:
   struct Impl;

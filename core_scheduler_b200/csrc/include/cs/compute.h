@@ -21,6 +21,9 @@ namespace cs::compute {
 enum class Backend : int { kFused = 0, kLibrary = 1 };
 CS_API void set_backend(Backend backend);
 CS_API Backend get_backend();
+// Number of ops that ran a library kernel although the fused backend was selected (each distinct case is
+// also logged once as a warning): a benchmark on an uncovered shape shows up here instead of passing silently.
+CS_API int64_t library_fallbacks();
 
 struct CS_API Linear {
   struct State : virtual module::State {

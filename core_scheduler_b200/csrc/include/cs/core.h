@@ -197,10 +197,11 @@ struct CS_API Tensor : ReadOnlyTensor {
 struct ReadOnlyTensor::Impl {
   at::Tensor tensor;                       // undefined until the producing task ran
   Event event;                             // completion of the last writer
-  Event read_event;                        // completion of the last side-stream reader
+  // Completion of the last reader on each side stream (index = stream class; bit set in
+  // side_readers while that reader has not been waited for by a later writer).
+  Event read_event[static_cast<int>(StreamClass::kNumStreamClass)];
   StreamClass stream_class{StreamClass::kMain};
-  StreamClass read_class{StreamClass::kMain};
-  bool has_side_reader{false};
+  uint8_t side_readers{0};
   // Memory that came from the caller's allocator stream (Tensor::wrap): every scheduler stream
   // that touches it is reported to the caching allocator once (bit per stream class), so a
   // block freed on the host is not handed out again while a queued kernel still reads it.

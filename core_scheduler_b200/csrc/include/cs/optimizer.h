@@ -10,6 +10,8 @@
 // model when its parameters live in flat arenas, and it refreshes the bf16 working copies
 // in the same pass.
 #pragma once
+#include <unordered_map>
+
 #include "cs/core.h"
 #include "cs/module.h"
 
@@ -74,6 +76,13 @@ struct CS_API AdamWImpl : OptimizerModule {
   AdamWImpl(const Scheduler &scheduler, const Module &module, const std::shared_ptr<FlatParameters> &flat,
             const Options &options);
   void step(const Scheduler &scheduler) override;
+  // extension (flat arenas only): updates just the parameters whose gradient handles are given, as one launch
+  // per contiguous arena range, on the stream class `priority`. The first call after step() opens a new
+  // optimizer step (advances the step counter once); step() then updates whatever is left and closes it.
+  // Meant to be driven from communication::AllReduceBucket::on_reduced so that the update of a bucket's
+  // parameters overlaps the rest of the backward pass. Does nothing while a clip coefficient is set (the
+  // global gradient norm is only known after the whole backward pass): step() then updates everything.
+  void step_partial(const Scheduler &scheduler, const std::vector<Tensor> &gradients, Task::Impl::Priority priority);
   [[nodiscard]] OrderedDict<std::string, Tensor> named_state_tensors() const override;
   [[nodiscard]] int64_t step_count() const override;
   void set_step_count(int64_t t) override;
@@ -85,8 +94,14 @@ struct CS_API AdamWImpl : OptimizerModule {
 
  private:
   void build(const Scheduler &scheduler, const Module &module, const Options &options);
+  void open_step();
   std::shared_ptr<FlatParameters> flat_;
   std::shared_ptr<optimizer::AdamW::State> flat_state_;
+  // step_partial bookkeeping: slot index of every gradient handle, which slots the open step has updated
+  std::unordered_map<const void *, size_t> slot_of_grad_;
+  std::vector<Tensor> slot_params_;
+  std::vector<char> slot_done_;
+  bool step_open_{false};
 };
 CS_MODULE(AdamW);
 }  // namespace cs::module

@@ -135,10 +135,6 @@ struct DeviceStatus;
 int attention_backward_packed(stream_t stream, const void *qkv, const void *out, const void *dout, const float *lse, float *delta,
                               void *dqkv, int64_t B, int64_t T, int64_t H, int64_t D, float scale);
 int attention_status(DeviceStatus *out);
-// With CS_ATTENTION_TRACE set, CTA (0,0,0) of the backward dK/dV kernel records clock64() at its phase boundaries
-// (8 slots per streamed tile: producer stage free, MMA woke, scores issued, accumulators issued, softmax woke,
-// shared tiles free, probabilities written, arrived); this copies the first n values out.
-int attention_trace(long long *out, int n);
 
 // ---- fused cross-entropy helpers -----------------------------------------------------------
 // Reduces the per-tile partials to lse[row], computes loss_row = lse - logit[target] and the

@@ -44,13 +44,6 @@ constexpr int TMEM_COLS = 256;             // backward: S', dP' and two accumula
 constexpr long long kWaitBudgetCycles = 4000000000LL;
 
 __device__ DeviceStatus g_attn_status;
-// Cycle trace of CTA (0,0,0) of the backward dK/dV kernel: clock64() at the phase boundaries of each
-// streamed tile (8 slots per tile, 32 tiles). Written only when the launch asks for it.
-__device__ long long g_attn_trace[256];
-#define CS_TRACE(slot)                                                                            \
-  do {                                                                                            \
-    if (trace_on && t < 32) g_attn_trace[t * 8 + (slot)] = clock64();                             \
-  } while (0)
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -467,7 +460,6 @@ struct AttnBwdParams {
   int B, T, H;
   float scale, scale_log2e;
   DeviceStatus *status;
-  int trace;  // 1: CTA (0,0,0) of the dK/dV kernel records g_attn_trace
 };
 
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
@@ -544,7 +536,6 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
   // streamed 64-row tiles: queries r0 .. T (kDKV) or keys 0 .. r0+128
   const int c_first = kDKV ? 2 * rb : 0;
   const int n_iter = kDKV ? p.T / BC - c_first : 2 * (rb + 1);
-  const bool trace_on = kDKV && p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 
   if (threadIdx.x == 0) {
     mbar_init(bar(R_FULL), 1);
@@ -606,7 +597,6 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
         const int c0 = (c_first + t) * BC;
         if (t + kAhead < n_iter) prefetch(t + kAhead);
         if (!mbar_wait(bar(C_EMPTY + s), ph ^ 1u, abort_flag)) break;
-        CS_TRACE(0);
         const uint32_t c1 = c_smem + s * 2 * C_TILE_BYTES, c2 = c1 + C_TILE_BYTES;
         if (kDKV) {
           mbar_expect_tx(bar(C_FULL + s), 2 * C_TILE_BYTES + 512);
@@ -656,9 +646,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
         // (SDP_EMPTY), i.e. while they still compute; the accumulating MMAs of tile t follow once P' / dS' exist.
         if (t + 1 < n_iter) ok = issue_sdp(t + 1);
         if (!ok) break;
-        CS_TRACE(2);
         if (!mbar_wait(bar(PDS_FULL), t & 1, abort_flag)) break;
-        CS_TRACE(1);
         fence_after();
 #pragma unroll
         for (int k = 0; k < BC / 16; ++k) {
@@ -667,7 +655,6 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
         }
         umma_commit(bar(PDS_EMPTY));
         umma_commit(bar(C_EMPTY + s));
-        CS_TRACE(3);
       }
       if (ok && t == n_iter) umma_commit(bar(ACC_FULL));
     }
@@ -688,7 +675,6 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
       const int c0 = (c_first + t) * BC;
       if (kDKV && !mbar_wait(bar(C_FULL + s), (t / STAGES) & 1, abort_flag)) break;  // lse / delta of the streamed queries
       if (!mbar_wait(bar(SDP_FULL), t & 1, abort_flag)) break;
-      if (threadIdx.x == 64) CS_TRACE(4);
       fence_after();
       // rows are keys and columns queries (kDKV), or rows queries and columns keys: keep key <= query
       const bool near_diag = kDKV ? (c0 < r0 + 128) : (c0 + BC > r0);
@@ -753,15 +739,12 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
       compute(sb, db, cb + 1, pb, qb2);
       // the previous tile's accumulating MMAs must have read P' / dS' before they are overwritten
       if (!mbar_wait(bar(PDS_EMPTY), (t & 1) ^ 1u, abort_flag)) break;
-      if (threadIdx.x == 64) CS_TRACE(5);
       store(pa, qa, cb);
       store(pb, qb2, cb + 1);
-      if (threadIdx.x == 64) CS_TRACE(6);
       fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(PDS_FULL));
-      if (threadIdx.x == 64) CS_TRACE(7);
     }
     if (mbar_wait(bar(ACC_FULL), 0, abort_flag) && !*abort_flag) {
       fence_after();
@@ -891,10 +874,6 @@ int attention_forward_packed(stream_t stream, const void *qkv, void *out, float 
   return finish_launch(1);
 }
 
-int attention_trace(long long *out, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(out, g_attn_trace, sizeof(long long) * static_cast<size_t>(n < 256 ? n : 256)));
-}
-
 int attention_backward_packed(stream_t stream, const void *qkv, const void *out, const void *dout, const float *lse, float *delta,
                               void *dqkv, int64_t B, int64_t T, int64_t H, int64_t D, float scale) {
   if (D != HD || T % 128 != 0 || B <= 0 || H <= 0 || T <= 0) return -1;
@@ -926,8 +905,6 @@ int attention_backward_packed(stream_t stream, const void *qkv, const void *out,
   p.scale = scale;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.status = attn_status_ptr();
-  static const bool trace = std::getenv("CS_ATTENTION_TRACE") != nullptr;
-  p.trace = trace ? 1 : 0;
   dim3 grid(static_cast<unsigned>(T / 128), static_cast<unsigned>(H), static_cast<unsigned>(B));
   attention_bwd_kernel<true><<<grid, BWD_THREADS, bwd_smem_bytes(true), s>>>(qkv_r, qkv_c, do_r, do_c, p);
   attention_bwd_kernel<false><<<grid, BWD_THREADS, bwd_smem_bytes(false), s>>>(qkv_r, qkv_c, do_r, do_c, p);

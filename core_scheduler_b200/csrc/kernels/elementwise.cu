@@ -674,7 +674,17 @@ int launch_ln_bwd(cudaStream_t s, const void *dy, const void *x, const void *gam
                   const float *rstd, const void *dres, void *dx, float *scratch, int64_t rows, int d, int parts) {
   const size_t smem = (static_cast<size_t>(kLnWarps) * 2 * d + d) * sizeof(float);
   if (smem > 48 * 1024) {
-    cudaFuncSetAttribute(ln_bwd_kernel<CHUNKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    // Opt in to the larger dynamic shared memory once per width class and device, and report a refusal.
+    constexpr int kMaxDevices = 64;
+    static std::atomic<size_t> granted[kMaxDevices];
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (device < 0 || device >= kMaxDevices || granted[device].load(std::memory_order_acquire) < smem) {
+      e = cudaFuncSetAttribute(ln_bwd_kernel<CHUNKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      if (device >= 0 && device < kMaxDevices) granted[device].store(smem, std::memory_order_release);
+    }
   }
   ln_bwd_kernel<CHUNKS><<<parts, kLnWarps * 32, smem, s>>>(
       static_cast<const __nv_bfloat16 *>(dy), static_cast<const __nv_bfloat16 *>(x), gamma, pdt, mean, rstd,

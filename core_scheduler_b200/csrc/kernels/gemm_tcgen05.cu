@@ -1043,10 +1043,6 @@ bool get_tensor_map(const void *ptr, uint64_t inner, uint64_t outer, uint64_t st
   return true;
 }
 
-unsigned env_unsigned(const char *name, unsigned fallback) {
-  const char *v = std::getenv(name);
-  return v ? static_cast<unsigned>(std::strtoul(v, nullptr, 0)) : fallback;
-}
 }  // namespace
 
 int64_t gemm_ce_stat_tiles(int64_t n) { return 2 * ((n + BN - 1) / BN); }  // one (max, sum) pair per 128-column half tile
@@ -1197,9 +1193,10 @@ int gemm_bf16(stream_t stream, const GemmArgs &a) {
     p.kb_per_split = p.kb_total;
     p.atomic_out = 1;
   }
-  p.lbo_mn = env_unsigned("CS_GEMM_MN_LBO", 8192);
-  p.sbo_mn = env_unsigned("CS_GEMM_MN_SBO", 1024);
-  p.kstep_mn = env_unsigned("CS_GEMM_MN_KSTEP", 2048);
+  // MN-major operand descriptors: next 64-element block 8192 B on, next 8 k-rows 1024 B on, one UMMA_K step = 16 k-rows
+  p.lbo_mn = 8192;
+  p.sbo_mn = 1024;
+  p.kstep_mn = 2048;
   static DeviceStatus *status_ptr = [] {
     void *ptr = nullptr;
     cudaGetSymbolAddress(&ptr, g_gemm_status);

@@ -36,7 +36,10 @@ extern "C" {
 //
 // The call performs no cudaMalloc/cudaFree and calls no allocating library routine. The first
 // call on each device resolves the device address of the scratch array (a one-time set-up with
-// that device current); make that first call outside of any stream capture.
+// that device current). The first call on each device for each width class (d up to 512, 768,
+// 1024, 1280, 2048) also loads that kernel variant and, for d above about 1360, raises its
+// shared-memory limit. Make those first calls outside of any stream capture, e.g. one warm-up
+// call per width you will use.
 // All calls share the one scratch array: each call fully rewrites the part it reads, so nothing
 // has to be cleared between calls, but two calls that overlap on the GPU (different streams, or
 // different host threads without ordering) race on it. Serialise them on one stream.

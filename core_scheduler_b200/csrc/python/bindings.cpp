@@ -145,11 +145,6 @@ PYBIND11_MODULE(_C, m) {
     CS_ASSERT_TRUE(rc == 0, "bounds_report failed: ", rc);
     return py::make_tuple(r.code, r.kernel_id, r.block, r.thread, static_cast<int64_t>(r.index), static_cast<int64_t>(r.limit));
   }, py::arg("reset") = true, "(code, kernel id, block, thread, index, limit) of the first out-of-range index; code 0 = none");
-  m.def("attention_trace", [] {
-    std::vector<long long> v(256);
-    cs::kernels::attention_trace(v.data(), 256);
-    return v;
-  });
   m.def("attention_status", [] {
     cs::kernels::DeviceStatus st{};
     cs::kernels::attention_status(&st);
@@ -210,6 +205,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("set_backend", [](const std::string &name) {
     compute::set_backend(name == "library" ? compute::Backend::kLibrary : compute::Backend::kFused);
   });
+  m.def("library_fallbacks", &compute::library_fallbacks);
   m.def("get_backend", [] { return compute::get_backend() == compute::Backend::kFused ? "fused" : "library"; });
   m.def("working_copy", [](const Scheduler &s, const Tensor &p, at::ScalarType dt) {
     Tensor out;
@@ -575,7 +571,14 @@ PYBIND11_MODULE(_C, m) {
            py::arg("byte_threshold"), py::arg("op") = "sum")
       .def("push_back", &communication::AllReduceBucket::push_back)
       .def("sync", &communication::AllReduceBucket::sync)
-      .def("launches", &communication::AllReduceBucket::launches);
+      .def("launches", &communication::AllReduceBucket::launches)
+      .def("attach_optimizer", [](const communication::AllReduceBucket &b, const std::shared_ptr<module::AdamWImpl> &opt) {
+        // the optimizer updates each bucket's parameters right after the bucket was reduced
+        std::weak_ptr<module::AdamWImpl> weak = opt;
+        b.on_reduced([weak](const Scheduler &s, const std::vector<Tensor> &grads, Task::Impl::Priority prio) {
+          if (auto o = weak.lock()) o->step_partial(s, grads, prio);
+        });
+      }, "AdamW over flat arenas: update every bucket's parameters as soon as the bucket has been reduced");
   m.def("all_gather", &communication::AllGather::run);
   m.def("reduce_scatter", [](const Scheduler &s, const Comm &c, const std::vector<Tensor> &recv,
                              const std::vector<std::vector<ReadOnlyTensor>> &send, const std::string &op) {

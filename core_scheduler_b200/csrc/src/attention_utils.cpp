@@ -264,6 +264,11 @@ Tensor ScaledDotProductAttention::forward_packed(const Scheduler &scheduler, con
              }
              CS_ASSERT_TRUE(code == -1, "attention_forward_packed failed: ", cuda_error_string(code));
            }
+           if (x.is_cuda() && x.scalar_type() == at::kBFloat16 && fused_enabled())
+             note_library_fallback("ScaledDotProductAttention::forward_packed",
+                                   use_own_forward() ? str_cat("T=", T, " D=", D, " causal=", state->args.is_causal, " dropout=",
+                                                               state->args.dropout_p).c_str()
+                                                     : "library engine selected by CS_ATTENTION_ENGINE");
            const at::Tensor x5 = x.view({B, T, 3, num_heads, D});
            at::Tensor o = attention_forward_body(x5.select(2, 0), x5.select(2, 1), x5.select(2, 2), state->args,
                                                  &state->backward, saved);

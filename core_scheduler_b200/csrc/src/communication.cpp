@@ -13,6 +13,7 @@
 #include <map>
 #include <mutex>
 
+#include "cs/module.h"
 #include "cs/symmetric.h"
 
 namespace cs::communication {
@@ -113,16 +114,19 @@ void wait_work(const c10::intrusive_ptr<c10d::Work> &work) {
 // Groups tensors that live in one storage (views of a flat arena) into as few contiguous ranges
 // as possible so that a bucket needs one collective and no staging copies. The tensors are
 // sorted by address and their byte intervals are united (an interval that lies inside or
-// overlaps a previous one is absorbed, so nothing is ever reduced twice); intervals separated
-// by no more than the arena's alignment padding are joined, the padding being zeros on every
-// rank. Non-contiguous tensors are returned as they are.
+// overlaps a previous one is absorbed, so nothing is ever reduced twice). Two intervals are joined across a gap only when
+// the second starts exactly where the first one's slot ends, i.e. at the first interval's end
+// rounded up to the arena's slot alignment (module::FlatParameters::alignment elements from the
+// start of the storage): such a gap is the first slot's own padding, zeros on every rank, and
+// cannot hold another tensor. Any wider gap may hold a gradient that belongs to another bucket,
+// so it is never bridged. Non-contiguous tensors are returned as they are.
 std::vector<at::Tensor> merge_adjacent(const std::vector<at::Tensor> &tensors) {
   struct Piece {
     const char *lo, *hi;
   };
   std::vector<at::Tensor> out;
   std::vector<bool> used(tensors.size(), false);
-  constexpr int64_t slack = 4096;  // arena alignment padding between slots
+  constexpr int64_t slot_elems = module::FlatParameters::alignment;
   // Ranges are emitted in the order in which their arena first appears in the bucket and, inside
   // an arena, by address: both are the same on every rank, so all ranks issue the same sequence
   // of collectives (sorting unrelated allocations by address would not be).
@@ -153,7 +157,10 @@ std::vector<at::Tensor> merge_adjacent(const std::vector<at::Tensor> &tensors) {
     while (k < pieces.size()) {
       const char *lo = pieces[k].lo, *hi = pieces[k].hi;
       size_t j = k + 1;
-      while (j < pieces.size() && pieces[j].lo <= hi + slack) {
+      while (j < pieces.size()) {
+        const int64_t slot_bytes = slot_elems * elem;
+        const char *slot_end = storage_base + ((hi - storage_base) + slot_bytes - 1) / slot_bytes * slot_bytes;
+        if (pieces[j].lo > hi && pieces[j].lo != slot_end) break;
         if (pieces[j].hi > hi) hi = pieces[j].hi;
         ++j;
       }
@@ -223,10 +230,13 @@ struct AllReduceBucket::Impl {
   std::vector<Tensor> pending;
   int64_t pending_bytes{0};
   int64_t launches{0};
+  ReducedCallback callback{};
 };
 
 AllReduceBucket::AllReduceBucket(int64_t byteThreshold, Operation operation)
-    : impl_{std::make_shared<Impl>(Impl{byteThreshold, operation, {}, 0, 0})} {}
+    : impl_{std::make_shared<Impl>(Impl{byteThreshold, operation, {}, 0, 0, {}})} {}
+
+void AllReduceBucket::on_reduced(ReducedCallback callback) const { impl_->callback = std::move(callback); }
 
 int64_t AllReduceBucket::launches() const { return impl_->launches; }
 
@@ -239,8 +249,10 @@ void AllReduceBucket::push_back(const Scheduler &scheduler, const Comm &comm, Te
 
 void AllReduceBucket::sync(const Scheduler &scheduler, const Comm &comm) const {
   if (impl_->pending.empty()) return;
-  AllReduce::run_inplace(scheduler, comm, impl_->pending, impl_->op);
+  const bool alone = comm.get_size() <= 1;
+  if (!alone) AllReduce::run_inplace(scheduler, comm, impl_->pending, impl_->op);
   ++impl_->launches;
+  if (impl_->callback) impl_->callback(scheduler, impl_->pending, alone ? Task::Impl::kAssist : Task::Impl::kComm);
   impl_->pending.clear();
   impl_->pending_bytes = 0;
 }

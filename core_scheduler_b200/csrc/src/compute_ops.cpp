@@ -11,6 +11,8 @@
 
 #include <atomic>
 #include <cmath>
+#include <mutex>
+#include <set>
 
 #include "cs/compute.h"
 #include "kernels/api.h"
@@ -63,15 +65,33 @@ bool grad_slot_ready_for_fused(const Tensor &slot) {
 
 at::Tensor as2d(const at::Tensor &t) { return t.reshape({-1, t.size(-1)}).contiguous(); }
 
+namespace {
+std::atomic<int64_t> g_library_fallbacks{0};
+}
+int64_t library_fallback_count() { return g_library_fallbacks.load(); }
+void note_library_fallback(const char *op, const char *reason) {
+  g_library_fallbacks.fetch_add(1);
+  static std::mutex mu;
+  static std::set<std::string> seen;
+  const std::string key = str_cat(op, ": ", reason);
+  std::lock_guard<std::mutex> lock{mu};
+  if (!seen.insert(key).second) return;
+  logger().warn("library fallback in ", key, " (this library's sm_100a kernel does not cover the case; reported once)");
+}
+
 // D = A[M,K] * B[N,K]^T through the tcgen05 kernel; false when the shape is not covered.
 bool fused_gemm(const kernels::GemmArgs &args) {
   const int code = kernels::gemm_bf16(current_stream(), args);
-  if (code == -1) return false;
+  if (code == -1) {
+    note_library_fallback("gemm_bf16", str_cat("m=", args.m, " n=", args.n, " k=", args.k, " layout=", args.layout).c_str());
+    return false;
+  }
   check_kernel(code, "gemm_bf16");
   return true;
 }
 }  // namespace detail
 using namespace detail;
+int64_t library_fallbacks() { return detail::library_fallback_count(); }
 
 void bump_version(const Tensor &parameter) { ++parameter.impl()->version; }
 

@@ -356,10 +356,14 @@ struct CudaImpl final : Scheduler::Impl {
       auto &ti = *out.impl();
       adopt(ti);
       if (ti.stream_class != cls && !ti.event.query()) ti.event.block();
-      if (ti.has_side_reader && ti.read_class != cls) {
-        if (!ti.read_event.query()) ti.read_event.block();
-        ti.has_side_reader = false;
+      // a writer waits for the readers of every side stream other than its own (its own stream
+      // orders them already)
+      for (int c = 0; c < static_cast<int>(StreamClass::kNumStreamClass); ++c) {
+        const auto bit = static_cast<uint8_t>(1u << c);
+        if (!(ti.side_readers & bit) || c == static_cast<int>(cls)) continue;
+        if (!ti.read_event[c].query()) ti.read_event[c].block();
       }
+      ti.side_readers = 0;
     }
     TimedTask timed{};
     if (profiling_) {
@@ -426,9 +430,8 @@ struct CudaImpl final : Scheduler::Impl {
     entry.event.record();
     for (auto &in : t.input()) {
       auto &ti = *in.impl();
-      ti.read_event = entry.event;
-      ti.read_class = static_cast<StreamClass>(tag);
-      ti.has_side_reader = true;
+      ti.read_event[tag] = entry.event;
+      ti.side_readers |= static_cast<uint8_t>(1u << tag);
     }
     queues_[tag].push_back(std::move(entry));
   }

@@ -93,11 +93,19 @@ struct Producer {
   bool stop{false};
   std::string error;
   std::thread thread;
+  int device{-1};  // CUDA device of the thread that created the loader (-1: none); the worker selects it
 
   // `make(slot)` fills ids/labels/rows/cols; returns false when it failed (error set).
   template <typename Make>
   void start(Make make) {
+    if (cuda_present() && cudaGetDevice(&device) != cudaSuccess) {
+      (void)cudaGetLastError();
+      device = -1;
+    }
     thread = std::thread([this, make] {
+      // Pinned allocations and event waits of this thread belong to the creating rank's device;
+      // without this every rank's worker would open a context on device 0.
+      if (device >= 0 && cudaSetDevice(device) != cudaSuccess) (void)cudaGetLastError();
       for (;;) {
         Slot *slot;
         {
@@ -213,24 +221,21 @@ struct RowStream {
     int64_t done = 0;
     int64_t width = cols;
     while (done < batch) {
+      // The staging buffers are sized from the row length, which the first row of the stream fixes.
+      if (width <= 0) width = reader->row_width();
+      int64_t got = 0;
       if (width > 0) {
         slot.ids.ensure(batch * width, pinned);
         slot.labels.ensure(batch * width, pinned);
-      } else {
-        // Row width still unknown: read one row into a scratch buffer sized generously.
-        slot.ids.ensure(batch * 8192, pinned);
-        slot.labels.ensure(batch * 8192, pinned);
+        int64_t w = width;
+        got = reader->next(slot.ids.ptr + done * width, slot.labels.ptr + done * width, batch - done, &w);
       }
-      int64_t w = width;
-      const int64_t got = reader->next(slot.ids.ptr + done * std::max<int64_t>(width, 0),
-                                       slot.labels.ptr + done * std::max<int64_t>(width, 0), batch - done, &w);
       if (got == 0) {  // end of file: continue in the next one
         ++file;
         CS_ASSERT_TRUE(file < ds->files.size(), "ran past the last dataset file");
         reader = std::make_unique<io::TokenFileReader>(ds->files[file], batch);
         continue;
       }
-      width = w;
       done += got;
     }
     cols = width;

@@ -13,4 +13,8 @@ void store_grad(const Tensor &slot, const at::Tensor &value, at::ScalarType stor
 bool grad_slot_ready_for_fused(const Tensor &slot);
 at::Tensor as2d(const at::Tensor &t);
 bool fused_gemm(const kernels::GemmArgs &args);
+// An op that was expected on this library's kernels (CUDA, bf16, fused backend) runs a library
+// kernel instead: warns once per (op, reason) and counts every occurrence.
+void note_library_fallback(const char *op, const char *reason);
+int64_t library_fallback_count();
 }  // namespace cs::compute::detail

@@ -1,6 +1,7 @@
 // AdamW / AmpAdamW functional ops and module::AdamW. See cs/optimizer.h for the parity map.
 #include "cs/optimizer.h"
 
+#include <algorithm>
 #include <cmath>
 
 #include "cs/compute.h"
@@ -221,9 +222,98 @@ OrderedDict<std::string, Tensor> AdamWImpl::named_state_tensors() const {
   return out;
 }
 
+void AdamWImpl::open_step() {
+  step_open_ = true;
+  for (auto &s : states_) {  // set_lr() touches the per-parameter views; the flat state follows
+    flat_state_->options.lr = s.second->get_lr();
+    break;
+  }
+  ++flat_state_->options.t;
+  for (auto &s : states_) std::dynamic_pointer_cast<OptAdamW::State>(s.second)->options.t = flat_state_->options.t;
+  if (slot_params_.empty()) {
+    const Module *m = model();
+    CS_ASSERT_TRUE(m != nullptr, "the optimised module is gone");
+    auto named = m->named_parameters();
+    for (size_t i = 0; i < flat_->slots.size(); ++i) {
+      slot_params_.push_back(named[flat_->slots[i].key]);
+      slot_of_grad_.emplace(flat_->grad_handles[i].impl().get(), i);
+    }
+  }
+  slot_done_.assign(flat_->slots.size(), 0);
+}
+
+void AdamWImpl::step_partial(const Scheduler &scheduler, const std::vector<Tensor> &gradients, Task::Impl::Priority priority) {
+  CS_ASSERT_TRUE(flat_ != nullptr, "step_partial needs an optimizer over flat arenas");
+  if (flat_state_->clip_coef.defined()) return;
+  if (!step_open_) open_step();
+  std::vector<size_t> picked;
+  for (auto &g : gradients) {
+    auto it = slot_of_grad_.find(g.impl().get());
+    if (it == slot_of_grad_.end() || slot_done_[it->second]) continue;
+    slot_done_[it->second] = 1;
+    picked.push_back(it->second);
+  }
+  if (picked.empty()) return;
+  std::sort(picked.begin(), picked.end());
+  // neighbouring slots are contiguous in the arenas (padding included): one launch per run of slots
+  struct Range {
+    int64_t begin, end;
+  };
+  std::vector<Range> ranges;
+  std::vector<Tensor> outs;
+  std::vector<ReadOnlyTensor> ins;
+  auto slot_end = [&](size_t i) {
+    return i + 1 < flat_->slots.size() ? flat_->slots[i + 1].offset : flat_->total;
+  };
+  for (size_t k = 0; k < picked.size(); ++k) {
+    const size_t i = picked[k];
+    if (k > 0 && picked[k - 1] + 1 == i)
+      ranges.back().end = slot_end(i);
+    else
+      ranges.push_back({flat_->slots[i].offset, slot_end(i)});
+    outs.push_back(slot_params_[i]);
+    ins.push_back(flat_->grad_handles[i]);
+  }
+  submit(scheduler, "cs::module::AdamW::step_partial", priority, Task::Impl::kCompute, outs, ins,
+         [flat = flat_, fs = flat_state_, o = flat_state_->options, ranges, outs, handles = ins](const FnTask &) {
+           const at::Tensor &P = flat->params.impl()->tensor, &G = flat->grads.impl()->tensor;
+           const at::Tensor &M = fs->tensors.m.impl()->tensor, &V = fs->tensors.v.impl()->tensor;
+           const at::Tensor &VM = fs->tensors.v_max.impl()->tensor;
+           const at::Tensor L = flat->lp.defined() ? flat->lp.impl()->tensor : at::Tensor{};
+           for (auto &h : handles)  // a slot nobody wrote this step must not contribute stale values
+             if (h.impl()->fresh && h.impl()->tensor.defined()) const_cast<at::Tensor &>(h.impl()->tensor).zero_();
+           for (auto &r : ranges) {
+             const int64_t n = r.end - r.begin;
+             optimizer::adamw_update(P.narrow(0, r.begin, n), G.narrow(0, r.begin, n), M.narrow(0, r.begin, n), V.narrow(0, r.begin, n),
+                                     o.amsgrad ? VM.narrow(0, r.begin, n) : at::Tensor{}, o, o.t, at::Tensor{}, nullptr,
+                                     L.defined() ? L.narrow(0, r.begin, n) : at::Tensor{});
+           }
+           for (auto &p : outs) {
+             auto &impl = *p.impl();
+             ++impl.version;
+             if (impl.lp.defined()) impl.lp_version = impl.version;  // written by the kernel
+             if (impl.lp_t.defined()) compute::working_copy_transposed(p, impl.lp_t.scalar_type());
+           }
+         });
+}
+
 void AdamWImpl::step(const Scheduler &scheduler) {
   const Module *m = model();
   CS_ASSERT_TRUE(m != nullptr, "the optimised module is gone");
+  if (flat_ && step_open_) {
+    // Buckets were updated while the backward pass ran: update what is left, then tie the arena handles
+    // to everything that touched them.
+    std::vector<Tensor> rest;
+    for (size_t i = 0; i < flat_->slots.size(); ++i)
+      if (!slot_done_[i]) rest.push_back(flat_->grad_handles[i]);
+    step_partial(scheduler, rest, Task::Impl::kAssist);
+    step_open_ = false;
+    std::vector<ReadOnlyTensor> ins(slot_params_.begin(), slot_params_.end());
+    std::vector<Tensor> outs{flat_->params, flat_state_->tensors.m, flat_state_->tensors.v};
+    if (flat_->lp.defined()) outs.push_back(flat_->lp);
+    submit(scheduler, "cs::module::AdamW::close_step", Task::Impl::kAssist, Task::Impl::kCompute, outs, ins, [](const FnTask &) {});
+    return;
+  }
   if (flat_) {
     // Keep the learning rate of the flat state in sync with set_lr() (which touches the views).
     for (auto &s : states_) {

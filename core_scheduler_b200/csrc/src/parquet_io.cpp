@@ -161,6 +161,15 @@ void TokenFileReader::skip_rows(int64_t rows) {
   }
 }
 
+int64_t TokenFileReader::row_width() {
+  if (!impl_->current || impl_->cursor >= impl_->current->num_rows()) {
+    if (!impl_->pull()) return -1;
+  }
+  auto lists = std::dynamic_pointer_cast<arrow::ListArray>(impl_->current->GetColumnByName("input_ids"));
+  if (!lists) throw std::runtime_error("token columns must be list arrays");
+  return lists->value_length(impl_->cursor);
+}
+
 int64_t TokenFileReader::next(int64_t *input_ids, int64_t *labels, int64_t capacity_rows, int64_t *cols) {
   int64_t done = 0;
   int64_t width = *cols > 0 ? *cols : -1;

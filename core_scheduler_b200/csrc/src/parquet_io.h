@@ -30,6 +30,8 @@ class TokenFileReader {
   // receives the row length; every row must have that many items.
   int64_t next(int64_t *input_ids, int64_t *labels, int64_t capacity_rows, int64_t *cols);
   [[nodiscard]] int64_t rows() const;
+  // Length of the row at the current position (-1 at end of file); reads ahead, consumes nothing.
+  int64_t row_width();
 
  private:
   struct Impl;

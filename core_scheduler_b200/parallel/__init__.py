@@ -53,7 +53,7 @@ class GPT2Trainer:
 
     def __init__(self, config, comm=None, world: int = 1, local_rank: int = 0, mode: str = "dp", collectives: str = "nvp2p",
                  device: str = "cuda", lr: float = 3e-4, beta1: float = 0.9, beta2: float = 0.95, weight_decay: float = 0.1,
-                 bucket_mb: float = 25.0, seed: int = 1234, scheduler=None):
+                 bucket_mb: float = 25.0, seed: int = 1234, scheduler=None, overlap_optimizer: bool = True):
         import core_scheduler_b200 as cs
 
         assert mode in ("dp", "zero", "tp") and collectives in ("nvp2p", "nccl")
@@ -90,8 +90,13 @@ class GPT2Trainer:
             self.optimizer = cs.AdamW(s, self.model, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay, flat=self.flat)
             if world > 1:
                 self.optimizer.set_grad_scale(1.0 / world)
+            if world > 1 or overlap_optimizer:
+                # gradients leave the backward pass in buckets; with overlap_optimizer each bucket's parameters
+                # are updated right after its all-reduce, while the backward pass of the earlier layers runs
                 self.bucket = cs.AllReduceBucket(int(bucket_mb * (1 << 20)), "sum")
                 self.sync = cs.GradientSync(self.comm, self.bucket, True)
+                if overlap_optimizer:
+                    self.bucket.attach_optimizer(self.optimizer)
         s.synchronize()
 
     def step(self, input_ids, labels):

@@ -164,34 +164,6 @@ def bench_attention():
           f"{fb / t_lib_b / 1e9:.0f} TFLOP/s   status {C.attention_status()}")
 
 
-def attention_trace():
-    """clock64() trace of CTA (0,0,0) of the backward dK/dV attention kernel (run with CS_ATTENTION_TRACE=1).
-
-    One line per streamed 128 x 64 tile: cycles since the first mark at which the producer's stage became free, the MMA
-    thread woke on P'/dS', issued the next scores, issued the accumulation, and at which the first softmax warp woke on
-    the scores, got its shared tiles, finished its math and arrived."""
-    import os
-
-    if not os.environ.get("CS_ATTENTION_TRACE"):
-        sys.exit("set CS_ATTENTION_TRACE=1")
-    B, T, H, D = 16, 1024, 12, 64
-    qkv = torch.randn(B, T, 3 * H * D, device="cuda").to(BF)
-    dout = torch.randn(B, T, H * D, device="cuda").to(BF)
-    _, out, lse = C.attention_forward_tcgen05(qkv, H, D ** -0.5)
-    for _ in range(3):
-        C.attention_backward_tcgen05(qkv, out, dout, lse, H, D ** -0.5)
-    torch.cuda.synchronize()
-    v = C.attention_trace()
-    marks = [x for x in v[:128] if x > 0]
-    if not marks:
-        sys.exit("no trace recorded")
-    base = min(marks)
-    names = ["stage_free", "mma_woke", "scores_issued", "acc_issued", "softmax_woke", "tiles_free", "computed", "arrived"]
-    for t in range(16):
-        row = v[t * 8:(t + 1) * 8]
-        print(f"tile {t:2d} " + " ".join(f"{n}={x - base if x else -1:7d}" for n, x in zip(names, row)))
-
-
 def gemm_one():
     """One GPT-2 shape (fc1), a handful of launches: the workload for an ncu capture.
 
@@ -308,4 +280,4 @@ def kernels_once():
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     {"gemm": bench_gemm, "elementwise": bench_elementwise, "gemm_one": gemm_one, "attention": bench_attention,
-     "kernels_once": kernels_once, "attention_trace": attention_trace}[what]()
+     "kernels_once": kernels_once}[what]()

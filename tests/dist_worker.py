@@ -113,6 +113,45 @@ def case_bucket_arena_order(device, nvp2p):
     assert bucket.launches() == 1
 
 
+def case_bucket_gradients_bias(device, nvp2p):
+    """Bucketed gradients of a model with biases equal the sum of every rank's local gradients, for several
+    bucket thresholds. A bias is pushed right after its weight, so a bucket often closes between the two; a merge
+    of arena views that bridged the gap would then reduce the bias in this bucket and again in the next."""
+    comm, rank, world, s = make_comm(device, nvp2p)
+    g = torch.Generator().manual_seed(23)
+    ids = torch.randint(0, 128, (world, 2, 33), generator=g).to(device)
+
+    def build():
+        cs.manual_seed(3)
+        cfg = cs.GPT2Config(n_layer=2, n_head=2, n_embd=64, block_size=32, vocab_size=128, padded_vocab_size=128, use_bias=True)
+        m = cs.GPT2(s, cfg)
+        symmetric = symm and device == "cuda" and nvp2p
+        return m, (C.flatten_symmetric(s, m, comm) if symmetric else C.flatten_parameters(s, m))
+
+    symm = False
+    ref, rflat = build()
+    symm = True
+    for r in range(world):  # the sum over ranks, accumulated locally
+        ref.forward_loss(s, T(ids[r][:, :-1].contiguous()), T(ids[r][:, 1:].contiguous()))
+        ref.backward_loss(s)
+    s.synchronize()
+    expect = {k: v.raw().double().clone() for k, v in ref.named_gradients().items()}
+    assert any(k.endswith(".bias") for k in expect)
+    for threshold in (1, 20 << 10, 48 << 10, 64 << 10, 100 << 10, 200 << 10, 1 << 30):
+        model, flat = build()
+        bucket = cs.AllReduceBucket(threshold, "sum")
+        sync = cs.GradientSync(comm, bucket, True)
+        model.forward_loss(s, T(ids[rank][:, :-1].contiguous()), T(ids[rank][:, 1:].contiguous()))
+        model.backward_loss(s, sync)
+        bucket.sync(s, comm)
+        s.synchronize()
+        for k, v in model.named_gradients().items():
+            got = v.raw().double()
+            err = (got - expect[k]).abs().max().item()
+            rel = 1e-4 if device == "cpu" else 5e-3
+            assert err <= 1e-5 + rel * expect[k].abs().max().item(), (rank, threshold, k, err)
+
+
 def case_all_gather(device, nvp2p):
     comm, rank, world, s = make_comm(device, nvp2p)
     send = T(seeded(rank + 1, 128, device=device))

@@ -19,7 +19,7 @@ needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs"
 
 
 @needs2
-@pytest.mark.parametrize("case", ["all_reduce", "bucket", "bucket_arena_order", "all_gather", "reduce_scatter", "all_to_all", "dp_training"])
+@pytest.mark.parametrize("case", ["all_reduce", "bucket", "bucket_arena_order", "bucket_gradients_bias", "all_gather", "reduce_scatter", "all_to_all", "dp_training"])
 @pytest.mark.parametrize("backend", ["nccl", "nvp2p"])
 def test_two_gpu_ranks(case, backend):
     run_case(case, device="cuda", extra=(backend,), timeout=600)

@@ -71,12 +71,16 @@ def test_program_written_for_the_reference_api_runs_on_this_library(tmp_path):
     lib = os.path.join(ROOT, "core_scheduler_b200", "lib")
     shim = os.path.join(ROOT, "baseline", "shims")
     exe = tmp_path / "ref_api_gpt2"
+    # the driver initialises Arrow's compute kernels for its data path: Arrow headers and both Arrow libraries
+    import glob
+    arrow_libs = ["-l:" + os.path.basename(sorted(glob.glob(os.path.join(str(p["arrow_lib"]), pat)))[0])
+                  for pat in ("libarrow_compute.so.*", "libarrow.so.*")]
     subprocess.run(["gcc", "-O1", "-c", os.path.join(shim, "mpi_shim.c"), f"-I{shim}", "-o", str(tmp_path / "mpi_shim.o")], check=True)
     cmd = ["g++", "-std=c++20", "-O1", "-w", f"-D_GLIBCXX_USE_CXX11_ABI={p['cxx11_abi']}", "-DUSE_C10D_NCCL", "-DUSE_DISTRIBUTED",
-           f"-I{shim}", f"-I{csrc}/include", f"-I{csrc}"] + [f"-I{i}" for i in p["torch_inc"]] + [f"-I{p['cuda_home'] / 'include'}",
+           f"-I{shim}", f"-I{csrc}/include", f"-I{csrc}", f"-I{p['arrow_inc']}"] + [f"-I{i}" for i in p["torch_inc"]] + [f"-I{p['cuda_home'] / 'include'}",
            os.path.join(ROOT, "baseline", "ref_gpt2_driver.cpp"), str(tmp_path / "mpi_shim.o"), "-o", str(exe), f"-L{lib}", "-lcs_b200",
            f"-L{p['torch_lib']}", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda", f"-L{p['cuda_home'] / 'lib64'}", "-lcudart",
-           f"-Wl,-rpath,{lib}", f"-Wl,-rpath,{p['torch_lib']}", f"-Wl,-rpath,{p['arrow_lib']}", "-Wl,--no-as-needed"]
+           f"-L{p['arrow_lib']}", *arrow_libs, f"-Wl,-rpath,{lib}", f"-Wl,-rpath,{p['torch_lib']}", f"-Wl,-rpath,{p['arrow_lib']}", "-Wl,--no-as-needed"]
     build = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert build.returncode == 0, build.stderr[-3000:]
     env = dict(os.environ, CS_MPISHIM_KEY=f"api{os.getpid()}")

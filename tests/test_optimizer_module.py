@@ -257,3 +257,34 @@ def test_symmetric_arena_random_sequences_never_overlap_and_fully_coalesce():
         assert ctx.allocate(arena) == (0, arena)
 
     run()
+
+
+@pytest.mark.parametrize("bucket_kb", [1, 64, 1 << 20])
+def test_optimizer_overlapped_with_backward_equals_one_step_at_the_end(bucket_kb):
+    """With `overlap_optimizer` every bucket of gradients is turned into a parameter update as soon as the backward
+    pass has produced it (module::AdamW::step_partial driven by the bucket); the parameters and the optimizer state
+    after a few steps are the same as with one whole-model update after the backward pass."""
+    from core_scheduler_b200.parallel import GPT2Trainer
+
+    cfg = cs.GPT2Config(n_layer=2, n_head=2, n_embd=64, block_size=32, vocab_size=128, padded_vocab_size=128, use_bias=True)
+    s = cs.DynamicScheduler(0, device="cpu")
+    a = GPT2Trainer(cfg, None, 1, 0, device="cpu", lr=1e-2, bucket_mb=bucket_kb / 1024, scheduler=s, overlap_optimizer=True)
+    b = GPT2Trainer(cfg, None, 1, 0, device="cpu", lr=1e-2, scheduler=s, overlap_optimizer=False)
+    assert a.bucket is not None and b.bucket is None
+    g = torch.Generator().manual_seed(5)
+    losses = []
+    for _ in range(3):
+        ids = torch.randint(0, 128, (2, 33), generator=g)
+        x, y = T(ids[:, :-1].contiguous()), T(ids[:, 1:].contiguous())
+        la, lb = a.step(x, y), b.step(x, y)
+        losses.append((cs.to_torch(s, la).item(), cs.to_torch(s, lb).item()))
+    s.synchronize()
+    assert all(abs(p - q) < 1e-6 for p, q in losses), losses
+    pa_, pb_ = a.model.named_parameters(), b.model.named_parameters()
+    for k in pa_:
+        assert torch.equal(pa_[k].raw(), pb_[k].raw()), k
+    sa, sb = a.optimizer.named_state_tensors(), b.optimizer.named_state_tensors()
+    for k in sa:
+        assert torch.equal(sa[k].raw(), sb[k].raw()), k
+    assert a.optimizer.step_count() == b.optimizer.step_count() == 3
+    assert a.bucket.launches() >= 3

@@ -91,6 +91,29 @@ def test_write_after_read_across_streams_is_ordered(gpu_scheduler):
 
 
 @pytest.mark.gpu
+def test_writer_waits_for_readers_on_both_side_streams(gpu_scheduler):
+    """An assist-stream reader followed by a comm-stream reader of the same tensor: a later main-stream writer
+    must wait for both, not only for the most recent one."""
+    s = gpu_scheduler
+    n = 1 << 24
+    buf = cs.from_torch(torch.ones(n, device="cuda"))
+    slow, fast = cs.Tensor(), cs.Tensor()
+
+    def slow_reader():
+        t = buf.raw()
+        acc = torch.zeros((), device="cuda")
+        for _ in range(60):
+            acc = acc + t.sum()
+        slow.set_raw(acc)
+
+    s.submit_python("slow_assist_reader", 1, [slow], [buf], slow_reader)
+    s.submit_python("fast_comm_reader", 2, [fast], [buf], lambda: fast.set_raw(buf.raw()[:16].sum()))
+    s.submit_python("overwriter", 0, [buf], [], lambda: buf.raw().zero_())
+    assert cs.to_torch(s, slow).item() == 60 * n
+    assert cs.to_torch(s, fast).item() == 16
+
+
+@pytest.mark.gpu
 def test_side_tasks_rejoin_and_events_are_pooled(gpu_scheduler):
     s = gpu_scheduler
     x = cs.from_torch(torch.ones(1024, device="cuda"))
