@@ -35,6 +35,7 @@ CPP_SOURCES = [
     "src/comm_nccl.cpp",
     "src/comm_threads.cpp",
     "src/symmetric.cpp",
+    "src/vmm.cpp",
     "src/data.cpp",
     "src/observability.cpp",
     "src/models_gpt2.cpp",

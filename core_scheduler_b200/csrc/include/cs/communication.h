@@ -91,8 +91,8 @@ struct CS_API AllReduceBucket : Bucket {
   void apply(const Scheduler &scheduler, const Comm &comm) const override { sync(scheduler, comm); }
   [[nodiscard]] int64_t launches() const;
   // Hook that runs after every flush: it receives the tensors of the bucket that was just reduced and the
-  // stream class that orders work after the reduction (the communication stream, or the assist stream for a
-  // single rank, where nothing is reduced). An optimizer attached here updates a bucket's parameters while
+  // stream class that orders work after the reduction (the communication stream; a single rank reduces nothing
+  // but still hands its buckets over there). An optimizer attached here updates a bucket's parameters while
   // the backward pass of the earlier layers is still running (module::AdamWImpl::step_partial).
   using ReducedCallback = std::function<void(const Scheduler &, const std::vector<Tensor> &, Task::Impl::Priority)>;
   void on_reduced(ReducedCallback callback) const;

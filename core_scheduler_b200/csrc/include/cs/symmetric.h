@@ -4,10 +4,17 @@
 //
 // The reference declares an NVLink peer-to-peer backend (BackendType::kNVP2P,
 // include/communication/communication.h:51 of the reference project) without implementing it;
-// this is that backend. Every rank allocates one arena with cudaMalloc, exports it with CUDA
-// IPC through the communicator's store and maps every peer's arena, so a kernel on rank r can
-// load/store rank p's buffer at the same offset. Waits on peer flags are bounded: a kernel that
-// gives up records a status word that the host turns into cs::Error.
+// this is that backend. Every rank creates one arena with the driver's virtual-memory API
+// (cuMemCreate), shares it with the other processes as a file descriptor through the
+// communicator's store and maps every peer's arena, so a kernel on rank r can load/store rank
+// p's buffer at the same offset. On NVSwitch systems an NVLink multicast object is bound over the
+// same pages: `multicast_base + offset` addresses every rank's copy at once, which lets kernels
+// reduce inside the switch (multimem.ld_reduce) and broadcast with one store (multimem.st).
+// When the virtual-memory path is unavailable (or CS_SYMMETRIC_IPC=1 asks for it) the arena is a
+// cudaMalloc block shared through CUDA IPC, without multicast. NCCL_NVLS_ENABLE=0 also switches
+// the multicast object off (multi-rank tests in which a rank may leave early run that way).
+// Waits on peer flags are bounded: a kernel that gives up records a status word that the host
+// turns into cs::Error.
 #pragma once
 #include "cs/communication.h"
 
@@ -24,8 +31,14 @@ struct CS_API SymmetricContext {
   int64_t arena_bytes{0};
   std::vector<char *> bases;       // bases[p]: rank p's arena as mapped into this process
   std::vector<uint32_t *> flags;   // flags[p]: rank p's signal pad (kFlagWords words)
+  char *multicast_base{nullptr};   // the arena of every rank at once (NVLink multicast mapping); null = none
+  bool virtual_memory{false};      // arena created with cuMemCreate (else cudaMalloc + CUDA IPC)
   void *status{nullptr};           // kernels::DeviceStatus in device memory
-  uint32_t epoch{0};               // monotonically increasing barrier/flag generation
+  uint32_t epoch{0};               // monotonically increasing generation of the stand-alone barrier
+  // Per-channel state of the barriers that the collective kernels carry inside them: launches so far and
+  // blocks launched so far (kernels/collectives.h describes the channels).
+  uint32_t channel_epoch[16] = {};
+  uint32_t channel_blocks[16] = {};
   static constexpr int kFlagWords = 4096;
 
   // Caching sub-allocator. Blocks are handed out in the same order on every rank, so equal
@@ -53,6 +66,7 @@ struct CS_API SymmetricContext {
   SymmetricBlock staging_{};
   bool owns_{false};
   std::vector<void *> opened_;  // IPC mappings to close
+  std::shared_ptr<void> vmm_;   // virtual-memory arena state (vmm::Arena), released with the context
 };
 
 // Collective: every rank of `comm` must call it with the same size. Attaches the context to

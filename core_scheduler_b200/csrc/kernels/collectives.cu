@@ -5,8 +5,9 @@
 // (src/communication/{all_reduce,all_gather,reduce_scatter,all_to_all}.cpp) and stages
 // multi-tensor all-reduces with at::cat / copy_ (all_reduce.cpp:149-163); its kNVP2P backend
 // is declared but not implemented (include/communication/communication.h:51). These kernels
-// are that backend: the reduction, the scale/cast and, for ZeRO, the AdamW update happen in
-// the same kernel that moves the data.
+// are that backend: the cross-rank barriers, the reduction (inside the switch when the arena has
+// a multicast mapping), the scale/cast and, for ZeRO, the AdamW update happen in the one kernel
+// that moves the data.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -27,28 +28,95 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ void st_release_gpu(uint32_t *p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 
 // Diagnostic build: a peer offset must stay inside the arena (arena_bytes 0 = size unknown).
 #define CS_PEER_OK(t, byte_offset) ((t).arena_bytes == 0 || CS_IN_BOUNDS(kKidCollective, (byte_offset) + 15, (t).arena_bytes))
 
-__global__ void barrier_kernel(PeerTable t, int slot_base, uint32_t epoch, long long budget, DeviceStatus *status) {
+constexpr int kThreads = 256;
+// 256 threads x 40 registers fit beside a GEMM CTA (320 threads x 168 registers) on one SM.
+#define CS_COMM_BOUNDS __launch_bounds__(kThreads, 6)
+
+__device__ __forceinline__ uint32_t *channel_words(const PeerTable &t, int peer, int channel) {
+  return t.flags[peer] + kChannelBase + channel * kChannelWords;
+}
+
+// epochs only grow; a later epoch also satisfies an earlier wait
+__device__ __forceinline__ bool reached(uint32_t seen, uint32_t epoch) { return static_cast<int32_t>(seen - epoch) >= 0; }
+
+__device__ __forceinline__ void report_timeout(const Handshake &h, int kernel_id, int who) {
+  h.status->code = 2;
+  h.status->kernel_id = kernel_id;
+  h.status->block = who;
+  h.status->detail = static_cast<int>(h.epoch);
+}
+
+// Flag exchange with every peer through slots [first, first + size) of the channel: "this rank reached
+// the point" is stored into slot `rank` of every peer, then this rank's own slots are polled.
+// Run by the first `size` threads of one block. A wait that exceeds the budget records a status and gives up.
+__device__ __forceinline__ void exchange_flags(const PeerTable &t, const Handshake &h, int first, int kernel_id) {
   const int p = threadIdx.x;
   if (p >= t.size) return;
   __threadfence_system();
-  st_release_sys(t.flags[p] + slot_base + t.rank, epoch);
-  const uint32_t *mine = t.flags[t.rank] + slot_base + p;
+  st_release_sys(channel_words(t, p, h.channel) + first + t.rank, h.epoch);
+  const uint32_t *mine = channel_words(t, t.rank, h.channel) + first + p;
   const long long t0 = clock64();
-  // epochs only grow; a later epoch also satisfies an earlier wait
-  while (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) < 0) {
-    if (clock64() - t0 > budget) {
-      status->code = 2;
-      status->kernel_id = 10;
-      status->block = p;
-      status->detail = static_cast<int>(epoch);
+  while (!reached(ld_acquire_sys(mine), h.epoch)) {
+    if (clock64() - t0 > h.budget) {
+      report_timeout(h, kernel_id, p);
       return;
     }
-    __nanosleep(64);
+    __nanosleep(32);
   }
+}
+
+// Opening barrier: every rank's contribution to this launch is complete (the peers' kernels have started,
+// which their streams allow only after the producers of their data). Block 0 talks to the peers and
+// releases the other blocks through a local flag.
+__device__ __forceinline__ void open_collective(const PeerTable &t, const Handshake &h, int kernel_id) {
+  uint32_t *local = channel_words(t, t.rank, h.channel);
+  if (blockIdx.x == 0) {
+    exchange_flags(t, h, 0, kernel_id);
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_gpu(local + 16, h.epoch);
+  } else {
+    if (threadIdx.x == 0) {
+      const long long t0 = clock64();
+      while (!reached(ld_acquire_gpu(local + 16), h.epoch)) {
+        if (clock64() - t0 > h.budget) {
+          report_timeout(h, kernel_id, 100 + static_cast<int>(blockIdx.x));
+          break;
+        }
+        __nanosleep(64);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// Closing barrier: the last block of this rank to finish tells the peers "everything this rank wrote into
+// your memory has landed, and it no longer reads yours" and waits for the same word from them, so that the
+// kernel ends only when this rank's buffers are complete and free to be overwritten.
+__device__ __forceinline__ void close_collective(const PeerTable &t, const Handshake &h, int kernel_id) {
+  __shared__ int last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t *local = channel_words(t, t.rank, h.channel);
+    const uint32_t done = atomicAdd(local + 17, 1u) + 1u;
+    last = done == h.blocks_before + gridDim.x;
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  exchange_flags(t, h, 8, kernel_id);
 }
 
 struct alignas(16) V4 {
@@ -57,14 +125,38 @@ struct alignas(16) V4 {
 __device__ __forceinline__ V4 ld_v4(const void *p) { return *reinterpret_cast<const V4 *>(p); }
 __device__ __forceinline__ void st_v4(void *p, const V4 &v) { *reinterpret_cast<V4 *>(p) = v; }
 
+// ---- multimem (NVLink multicast) accesses: one instruction addresses every rank's copy ----
+__device__ __forceinline__ V4 mc_ld_reduce_f32(const void *p) {
+  V4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ V4 mc_ld_reduce_bf16(const void *p) {
+  V4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void mc_st(void *p, const V4 &v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void mc_st_v2(void *p, uint32_t a, uint32_t b) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+
 template <int DTYPE>
-__device__ __forceinline__ void accumulate(float (&acc)[8], const V4 &v, int &n) {
+__device__ __forceinline__ void accumulate(float (&acc)[8], const V4 &v) {
   if (DTYPE == 0) {
     acc[0] += __uint_as_float(v.x);
     acc[1] += __uint_as_float(v.y);
     acc[2] += __uint_as_float(v.z);
     acc[3] += __uint_as_float(v.w);
-    n = 4;
   } else {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -73,7 +165,6 @@ __device__ __forceinline__ void accumulate(float (&acc)[8], const V4 &v, int &n)
       acc[2 * i] += f.x;
       acc[2 * i + 1] += f.y;
     }
-    n = 8;
   }
 }
 template <int DTYPE>
@@ -96,6 +187,44 @@ __device__ __forceinline__ V4 finish(const float (&acc)[8], float scale) {
   }
   return o;
 }
+// scale applied to a vector that the switch already summed
+template <int DTYPE>
+__device__ __forceinline__ V4 scaled(const V4 &v, float scale) {
+  if (scale == 1.0f) return v;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  accumulate<DTYPE>(acc, v);
+  return finish<DTYPE>(acc, scale);
+}
+
+// Sum over all ranks of the 16-byte vector at `offset`: one switch-side reduction, or one load per peer.
+// Peer loads are issued in groups of four so that the register budget of the kernel holds.
+template <int DTYPE>
+__device__ __forceinline__ V4 reduce_vector(const PeerTable &t, int64_t offset, float scale) {
+  if (t.mc) return scaled<DTYPE>(DTYPE == 0 ? mc_ld_reduce_f32(t.mc + offset) : mc_ld_reduce_bf16(t.mc + offset), scale);
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+  for (int g = 0; g < kMaxPeers; g += 4) {
+    if (g >= t.size) break;
+    V4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (g + j < t.size) v[j] = ld_v4(t.base[(t.rank + g + j) % t.size] + offset);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (g + j < t.size) accumulate<DTYPE>(acc, v[j]);
+  }
+  return finish<DTYPE>(acc, scale);
+}
+// Writes a 16-byte vector into every rank's arena at `offset`.
+__device__ __forceinline__ void broadcast_vector(const PeerTable &t, int64_t offset, const V4 &v) {
+  if (t.mc) {
+    mc_st(t.mc + offset, v);
+    return;
+  }
+#pragma unroll
+  for (int p = 0; p < kMaxPeers; ++p)
+    if (p < t.size) st_v4(t.base[(t.rank + p) % t.size] + offset, v);
+}
 
 // Slice [begin, end) in 16-byte vectors owned by `rank` out of `vecs` vectors.
 __device__ __forceinline__ void slice_of(int64_t vecs, int size, int rank, int64_t &begin, int64_t &end) {
@@ -105,124 +234,153 @@ __device__ __forceinline__ void slice_of(int64_t vecs, int size, int rank, int64
   if (begin > vecs) begin = vecs;
 }
 
-// Vectors each thread keeps in flight per peer. NVLink round trips are a few microseconds, so
-// hundreds of kilobytes per SM must be outstanding to fill the links from a few dozen CTAs.
+__global__ void barrier_kernel(PeerTable t, int slot_base, uint32_t epoch, long long budget, DeviceStatus *status) {
+  const int p = threadIdx.x;
+  if (p >= t.size) return;
+  __threadfence_system();
+  st_release_sys(t.flags[p] + slot_base + t.rank, epoch);
+  const uint32_t *mine = t.flags[t.rank] + slot_base + p;
+  const long long t0 = clock64();
+  while (!reached(ld_acquire_sys(mine), epoch)) {
+    if (clock64() - t0 > budget) {
+      status->code = 2;
+      status->kernel_id = 10;
+      status->block = p;
+      status->detail = static_cast<int>(epoch);
+      return;
+    }
+    __nanosleep(64);
+  }
+}
+
+// Vectors each thread keeps in flight. NVLink round trips are a few microseconds, so megabytes must be
+// outstanding per GPU; the grid supplies them (up to one light block per SM), not the per-thread depth.
 constexpr int kUnroll = 4;
 
 template <int DTYPE>
-__global__ void __launch_bounds__(256) all_reduce_twoshot_kernel(PeerTable t, int64_t offset, int64_t vecs, float scale) {
+__global__ void CS_COMM_BOUNDS all_reduce_kernel(PeerTable t, Handshake h, int64_t offset, int64_t vecs, float scale) {
+  open_collective(t, h, 11);
   int64_t begin, end;
   slice_of(vecs, t.size, t.rank, begin, end);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i0 = begin + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < end; i0 += stride * kUnroll) {
-    V4 v[kUnroll][kMaxPeers];
+    if (t.mc) {
+      V4 v[kUnroll];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int64_t i = i0 + u * stride;
-      if (i < end && CS_PEER_OK(t, offset + i * 16)) {
-#pragma unroll
-        for (int p = 0; p < kMaxPeers; ++p)
-          if (p < t.size) v[u][p] = ld_v4(t.base[(t.rank + p) % t.size] + offset + i * 16);  // all loads in flight first
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t i = i0 + u * stride;
+        if (i < end && CS_PEER_OK(t, offset + i * 16))
+          v[u] = DTYPE == 0 ? mc_ld_reduce_f32(t.mc + offset + i * 16) : mc_ld_reduce_bf16(t.mc + offset + i * 16);
       }
-    }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int64_t i = i0 + u * stride;
-      if (i < end && CS_PEER_OK(t, offset + i * 16)) {
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        int n;
-#pragma unroll
-        for (int p = 0; p < kMaxPeers; ++p)
-          if (p < t.size) accumulate<DTYPE>(acc, v[u][p], n);
-        const V4 o = finish<DTYPE>(acc, scale);
-#pragma unroll
-        for (int p = 0; p < kMaxPeers; ++p)
-          if (p < t.size) st_v4(t.base[(t.rank + p) % t.size] + offset + i * 16, o);
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t i = i0 + u * stride;
+        if (i < end && CS_PEER_OK(t, offset + i * 16)) mc_st(t.mc + offset + i * 16, scaled<DTYPE>(v[u], scale));
+      }
+    } else {
+#pragma unroll 1
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t i = i0 + u * stride;
+        if (i < end && CS_PEER_OK(t, offset + i * 16)) broadcast_vector(t, offset + i * 16, reduce_vector<DTYPE>(t, offset + i * 16, scale));
       }
     }
   }
+  close_collective(t, h, 11);
 }
 
 template <int DTYPE>
-__global__ void __launch_bounds__(256) pull_reduce_kernel(PeerTable t, int64_t src_offset, char *dst, int64_t vecs, float scale) {
+__global__ void CS_COMM_BOUNDS reduce_scatter_kernel(PeerTable t, Handshake h, int64_t src_offset, char *dst, int64_t vecs, float scale) {
+  open_collective(t, h, 12);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < vecs; i0 += stride * kUnroll) {
-    V4 v[kUnroll][kMaxPeers];
+    if (t.mc) {
+      V4 v[kUnroll];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int64_t i = i0 + u * stride;
-      if (i < vecs && CS_PEER_OK(t, src_offset + i * 16)) {
-#pragma unroll
-        for (int p = 0; p < kMaxPeers; ++p)
-          if (p < t.size) v[u][p] = ld_v4(t.base[(t.rank + p) % t.size] + src_offset + i * 16);
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t i = i0 + u * stride;
+        if (i < vecs && CS_PEER_OK(t, src_offset + i * 16))
+          v[u] = DTYPE == 0 ? mc_ld_reduce_f32(t.mc + src_offset + i * 16) : mc_ld_reduce_bf16(t.mc + src_offset + i * 16);
       }
-    }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int64_t i = i0 + u * stride;
-      if (i < vecs && CS_PEER_OK(t, src_offset + i * 16)) {
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        int n;
-#pragma unroll
-        for (int p = 0; p < kMaxPeers; ++p)
-          if (p < t.size) accumulate<DTYPE>(acc, v[u][p], n);
-        st_v4(dst + i * 16, finish<DTYPE>(acc, scale));
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t i = i0 + u * stride;
+        if (i < vecs && CS_PEER_OK(t, src_offset + i * 16)) st_v4(dst + i * 16, scaled<DTYPE>(v[u], scale));
+      }
+    } else {
+#pragma unroll 1
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t i = i0 + u * stride;
+        if (i < vecs && CS_PEER_OK(t, src_offset + i * 16)) st_v4(dst + i * 16, reduce_vector<DTYPE>(t, src_offset + i * 16, scale));
       }
     }
   }
+  close_collective(t, h, 12);
 }
 
-__global__ void __launch_bounds__(512) pull_copy_kernel(PeerTable t, PullCopyArgs a) {
-  // blockIdx.y = peer (starting with ourselves so that local data is ready first)
-  const int p = (t.rank + blockIdx.y) % t.size;
-  const char *src = t.base[p] + a.src_offset[p];
-  char *dst = a.dst[p];
-  const int64_t vec_per_row = a.row_bytes / 16;
-  const int64_t total = a.rows * vec_per_row;
+__global__ void CS_COMM_BOUNDS all_gather_push_kernel(PeerTable t, Handshake h, int64_t src_offset, int64_t dst_offset, int64_t vecs) {
+  open_collective(t, h, 13);
+  const char *src = t.base[t.rank] + src_offset;
+  const int64_t mine = dst_offset + static_cast<int64_t>(t.rank) * vecs * 16;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  constexpr int U = 8;  // eight 16-byte loads in flight per thread
-  for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += stride * U) {
-    V4 v[U];
+  for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < vecs; i0 += stride * kUnroll) {
+    V4 v[kUnroll];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < vecs) v[u] = ld_v4(src + i * 16);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < vecs && CS_PEER_OK(t, mine + i * 16)) broadcast_vector(t, mine + i * 16, v[u]);
+    }
+  }
+  close_collective(t, h, 13);
+}
+
+__global__ void CS_COMM_BOUNDS pull_copy_kernel(PeerTable t, Handshake h, PullCopyArgs a) {
+  open_collective(t, h, 14);
+  // work item = (peer, vector); peers are visited starting with ourselves so that local data moves first
+  const int64_t vec_per_row = a.row_bytes / 16;
+  const int64_t per_peer = a.rows * vec_per_row;
+  const int64_t total = per_peer * t.size;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += stride * kUnroll) {
+    V4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
       const int64_t i = i0 + u * stride;
       if (i < total) {
-        const int64_t r = i / vec_per_row, c = i - r * vec_per_row;
+        const int p = (t.rank + static_cast<int>(i / per_peer)) % t.size;
+        const int64_t j = i % per_peer;
+        const int64_t r = j / vec_per_row, c = j - r * vec_per_row;
         if (!CS_PEER_OK(t, a.src_offset[p] + r * a.src_stride + c * 16)) continue;
-        v[u] = ld_v4(src + r * a.src_stride + c * 16);
+        v[u] = ld_v4(t.base[p] + a.src_offset[p] + r * a.src_stride + c * 16);
       }
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
+    for (int u = 0; u < kUnroll; ++u) {
       const int64_t i = i0 + u * stride;
       if (i < total) {
-        const int64_t r = i / vec_per_row, c = i - r * vec_per_row;
-        st_v4(dst + r * a.dst_stride + c * 16, v[u]);
+        const int p = (t.rank + static_cast<int>(i / per_peer)) % t.size;
+        const int64_t j = i % per_peer;
+        const int64_t r = j / vec_per_row, c = j - r * vec_per_row;
+        st_v4(a.dst[p] + r * a.dst_stride + c * 16, v[u]);
       }
     }
   }
+  close_collective(t, h, 14);
 }
 
-__global__ void __launch_bounds__(512) rs_adamw_ag_kernel(PeerTable t, ShardedAdamWArgs a) {
+__global__ void CS_COMM_BOUNDS rs_adamw_ag_kernel(PeerTable t, Handshake h, ShardedAdamWArgs a) {
+  open_collective(t, h, 15);
   const float gscale = a.clip_coef ? a.grad_scale * a.clip_coef[0] : a.grad_scale;
   const int64_t vecs = a.shard_count / 4;  // four fp32 per vector
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < vecs;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t elem = a.shard_begin + i * 4;
-    V4 gv[kMaxPeers];
-#pragma unroll
-    for (int p = 0; p < kMaxPeers; ++p)
-      if (p < t.size) gv[p] = ld_v4(t.base[(t.rank + p) % t.size] + a.grad_offset_bytes + elem * 4);
-    float g[4] = {0, 0, 0, 0};
-#pragma unroll
-    for (int p = 0; p < kMaxPeers; ++p) {
-      if (p < t.size) {
-        g[0] += __uint_as_float(gv[p].x);
-        g[1] += __uint_as_float(gv[p].y);
-        g[2] += __uint_as_float(gv[p].z);
-        g[3] += __uint_as_float(gv[p].w);
-      }
-    }
+    const V4 gsum = reduce_vector<0>(t, a.grad_offset_bytes + elem * 4, 1.0f);
+    const float g[4] = {__uint_as_float(gsum.x), __uint_as_float(gsum.y), __uint_as_float(gsum.z), __uint_as_float(gsum.w)};
     float4 w = *reinterpret_cast<float4 *>(a.master + i * 4);
     float4 m = *reinterpret_cast<float4 *>(a.exp_avg + i * 4);
     float4 v = *reinterpret_cast<float4 *>(a.exp_avg_sq + i * 4);
@@ -244,21 +402,24 @@ __global__ void __launch_bounds__(512) rs_adamw_ag_kernel(PeerTable t, ShardedAd
     *reinterpret_cast<float4 *>(a.exp_avg_sq + i * 4) = v;
     if (a.lp_offset_bytes >= 0) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(w.x, w.y), hi = __floats2bfloat162_rn(w.z, w.w);
-      uint2 packed;
-      packed.x = *reinterpret_cast<uint32_t *>(&lo);
-      packed.y = *reinterpret_cast<uint32_t *>(&hi);
+      const uint32_t p0 = *reinterpret_cast<uint32_t *>(&lo), p1 = *reinterpret_cast<uint32_t *>(&hi);
+      const int64_t off = a.lp_offset_bytes + elem * 2;
+      if (t.mc) {
+        mc_st_v2(t.mc + off, p0, p1);
+      } else {
 #pragma unroll
-      for (int p = 0; p < kMaxPeers; ++p)
-        if (p < t.size)
-          *reinterpret_cast<uint2 *>(t.base[(t.rank + p) % t.size] + a.lp_offset_bytes + elem * 2) = packed;
+        for (int p = 0; p < kMaxPeers; ++p)
+          if (p < t.size) *reinterpret_cast<uint2 *>(t.base[(t.rank + p) % t.size] + off) = make_uint2(p0, p1);
+      }
     }
   }
+  close_collective(t, h, 15);
 }
 
-int comm_grid(int64_t vecs, int threads, int cap = 64) {
-  // A bounded number of CTAs, each with many loads in flight, fills NVLink; keeping the grid
-  // below the SM count leaves room for the GEMMs that run next to the collective.
-  const int64_t blocks = (vecs + threads - 1) / threads;
+// One light block per SM at most; small messages get proportionally fewer blocks.
+int comm_grid(int64_t vecs_per_rank, int cap = 128) {
+  const int64_t per_block = static_cast<int64_t>(kThreads) * kUnroll;
+  const int64_t blocks = (vecs_per_rank + per_block - 1) / per_block;
   return static_cast<int>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 }  // namespace
@@ -271,57 +432,66 @@ int symm_barrier(stream_t stream, const PeerTable &t, int slot_base, uint32_t ep
   return finish_launch(1);
 }
 
-int symm_all_reduce_inplace(stream_t stream, const PeerTable &t, int64_t offset_bytes, int64_t count, int dtype, float scale) {
+int symm_all_reduce(stream_t stream, const PeerTable &t, const Handshake &h, int64_t offset_bytes, int64_t count, int dtype,
+                    float scale, int *blocks) {
   const int64_t bytes = count * (dtype == 0 ? 4 : 2);
   if (bytes % 16 != 0 || offset_bytes % 16 != 0) return static_cast<int>(cudaErrorInvalidValue);
   const int64_t vecs = bytes / 16;
-  const int64_t per = (vecs + t.size - 1) / t.size;
+  const int grid = comm_grid((vecs + t.size - 1) / t.size);
+  *blocks = grid;
   auto s = static_cast<cudaStream_t>(stream);
   if (dtype == 0)
-    all_reduce_twoshot_kernel<0><<<comm_grid((per + kUnroll - 1) / kUnroll, 256, 128), 256, 0, s>>>(t, offset_bytes, vecs, scale);
+    all_reduce_kernel<0><<<grid, kThreads, 0, s>>>(t, h, offset_bytes, vecs, scale);
   else
-    all_reduce_twoshot_kernel<1><<<comm_grid((per + kUnroll - 1) / kUnroll, 256, 128), 256, 0, s>>>(t, offset_bytes, vecs, scale);
+    all_reduce_kernel<1><<<grid, kThreads, 0, s>>>(t, h, offset_bytes, vecs, scale);
   return finish_launch(1);
 }
 
-int symm_pull_reduce(stream_t stream, const PeerTable &t, int64_t src_offset_bytes, void *dst, int64_t count, int dtype,
-                     float scale) {
+int symm_reduce_scatter(stream_t stream, const PeerTable &t, const Handshake &h, int64_t src_offset_bytes, void *dst, int64_t count,
+                        int dtype, float scale, int *blocks) {
   const int64_t bytes = count * (dtype == 0 ? 4 : 2);
   if (bytes % 16 != 0 || src_offset_bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(dst) & 15))
     return static_cast<int>(cudaErrorInvalidValue);
-  auto s = static_cast<cudaStream_t>(stream);
   const int64_t vecs = bytes / 16;
+  const int grid = comm_grid(vecs);
+  *blocks = grid;
+  auto s = static_cast<cudaStream_t>(stream);
   if (dtype == 0)
-    pull_reduce_kernel<0><<<comm_grid((vecs + kUnroll - 1) / kUnroll, 256, 128), 256, 0, s>>>(t, src_offset_bytes, static_cast<char *>(dst), vecs, scale);
+    reduce_scatter_kernel<0><<<grid, kThreads, 0, s>>>(t, h, src_offset_bytes, static_cast<char *>(dst), vecs, scale);
   else
-    pull_reduce_kernel<1><<<comm_grid((vecs + kUnroll - 1) / kUnroll, 256, 128), 256, 0, s>>>(t, src_offset_bytes, static_cast<char *>(dst), vecs, scale);
+    reduce_scatter_kernel<1><<<grid, kThreads, 0, s>>>(t, h, src_offset_bytes, static_cast<char *>(dst), vecs, scale);
   return finish_launch(1);
 }
 
-int symm_all_reduce_oneshot(stream_t stream, const PeerTable &t, int64_t staging_offset, void *dst, int64_t count, int dtype,
-                            float scale) {
-  return symm_pull_reduce(stream, t, staging_offset, dst, count, dtype, scale);
+int symm_all_gather_push(stream_t stream, const PeerTable &t, const Handshake &h, int64_t src_offset_bytes, int64_t dst_offset_bytes,
+                         int64_t bytes, int *blocks) {
+  if (bytes % 16 != 0 || src_offset_bytes % 16 != 0 || dst_offset_bytes % 16 != 0) return static_cast<int>(cudaErrorInvalidValue);
+  const int64_t vecs = bytes / 16;
+  const int grid = comm_grid(vecs);
+  *blocks = grid;
+  all_gather_push_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(t, h, src_offset_bytes, dst_offset_bytes, vecs);
+  return finish_launch(1);
 }
 
-int symm_pull_copy(stream_t stream, const PeerTable &t, const PullCopyArgs &a) {
+int symm_pull_copy(stream_t stream, const PeerTable &t, const Handshake &h, const PullCopyArgs &a, int *blocks) {
   if (a.row_bytes % 16 != 0 || a.src_stride % 16 != 0 || a.dst_stride % 16 != 0) return static_cast<int>(cudaErrorInvalidValue);
   for (int p = 0; p < t.size; ++p)
     if ((a.src_offset[p] % 16) != 0 || (reinterpret_cast<uintptr_t>(a.dst[p]) & 15)) return static_cast<int>(cudaErrorInvalidValue);
-  const int64_t vecs = a.rows * (a.row_bytes / 16);
-  int gx = comm_grid((vecs + 7) / 8, 512);
-  const int per_peer_cap = 64 / t.size > 8 ? 64 / t.size : 8;
-  if (gx > per_peer_cap) gx = per_peer_cap;  // x peers
-  dim3 grid(gx, t.size);
-  pull_copy_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(t, a);
+  const int64_t vecs = a.rows * (a.row_bytes / 16) * t.size;
+  const int grid = comm_grid(vecs);
+  *blocks = grid;
+  pull_copy_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(t, h, a);
   return finish_launch(1);
 }
 
-int symm_reduce_scatter_adamw_all_gather(stream_t stream, const PeerTable &t, const ShardedAdamWArgs &a) {
+int symm_reduce_scatter_adamw_all_gather(stream_t stream, const PeerTable &t, const Handshake &h, const ShardedAdamWArgs &a,
+                                         int *blocks) {
   if (a.shard_count % 4 != 0 || a.shard_begin % 4 != 0 || a.grad_offset_bytes % 16 != 0 ||
-      (a.lp_offset_bytes >= 0 && a.lp_offset_bytes % 16 != 0))
+      (a.lp_offset_bytes >= 0 && a.lp_offset_bytes % 16 != 0) || a.shard_count <= 0)
     return static_cast<int>(cudaErrorInvalidValue);
-  if (a.shard_count == 0) return 0;
-  rs_adamw_ag_kernel<<<comm_grid(a.shard_count / 4, 512) * 2, 512, 0, static_cast<cudaStream_t>(stream)>>>(t, a);
+  const int grid = comm_grid(a.shard_count / 4 * kUnroll);  // one vector per thread and trip: more blocks per byte
+  *blocks = grid;
+  rs_adamw_ag_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(t, h, a);
   return finish_launch(1);
 }
 CS_DEFINE_BOUNDS_GETTER(bounds_report_collectives)

@@ -1,7 +1,16 @@
 // Launch interface of the peer-memory collective kernels (kernels/collectives.cu).
 // All ranks of one NVSwitch domain map each other's symmetric arena; a kernel on rank r
-// addresses rank p's copy of a buffer as table.base[p] + offset. No kernel here uses TMA or
-// multicast loads: remote data moves with plain 128-bit peer loads and stores.
+// addresses rank p's copy of a buffer as table.base[p] + offset and, when the arena has an
+// NVLink multicast mapping, every rank's copy at once as table.mc + offset (multimem.ld_reduce
+// sums the copies inside the switch, multimem.st writes all of them). No kernel here uses TMA:
+// remote data moves with plain 128-bit peer loads and stores or with multimem instructions.
+//
+// Every collective is ONE launch: the cross-rank barrier that must precede it (all contributions
+// complete) and the one that must follow it (all results written, all sources read) are part of
+// the kernel. Block 0 exchanges flags with the peers, the other blocks wait on a local flag; at
+// the end the last block to finish does the closing exchange. The kernels are built to stay
+// resident next to a GEMM CTA (256 threads, at most 40 registers, no shared memory), so a
+// collective on the communication stream never has to wait for a whole GEMM wave to drain.
 #pragma once
 #include <cstdint>
 
@@ -13,9 +22,41 @@ constexpr int kMaxPeers = 8;
 struct PeerTable {
   char *base[kMaxPeers];       // arena of every rank as mapped here
   uint32_t *flags[kMaxPeers];  // signal pad of every rank
+  char *mc;                    // multicast mapping of the arena (null: none)
   int rank;
   int size;
   long long arena_bytes;       // size of every arena (0 = unknown); limit of the diagnostic build's offset checks
+};
+
+// Signal-pad layout (32-bit words). Words [0, 64) belong to the stand-alone barrier below. From
+// kChannelBase on, every "channel" owns kChannelWords words:
+//   [0, 8)   entry flags, one per source rank      [8, 16)  exit flags, one per source rank
+//   [16]     local go flag (epoch)                  [17]     local count of finished blocks
+//   [18]     local done flag (epoch)
+// Two kernels may be in flight at the same time only on different channels.
+constexpr int kChannelBase = 64;
+constexpr int kChannelWords = 32;
+enum Channel : int {
+  kChanAllReduce = 0,
+  kChanReduceScatter = 1,
+  kChanAllGather = 2,
+  kChanAllToAll = 3,
+  kChanZero = 4,
+  kChanGatherRows = 5,   // tensor parallel: row gathers on the main stream
+  kChanScatterRows = 6,  // tensor parallel: row reduce-scatters on the main stream
+  kChanGemmGather = 7,   // all-gather -> GEMM kernel
+  kChanGemmScatter = 8,  // GEMM -> reduce-scatter kernel
+  kChanCrossEntropy = 9, // vocabulary-parallel loss statistics
+  kNumChannels = 16,
+};
+
+// What the host passes for the in-kernel barriers of one launch.
+struct Handshake {
+  int channel;
+  uint32_t epoch;          // grows by one per launch on the channel (same on every rank)
+  uint32_t blocks_before;  // blocks launched on this channel before this launch (local counter target base)
+  long long budget;        // wait budget in clock64() cycles
+  DeviceStatus *status;
 };
 
 // Wait budget of every peer-flag wait, in clock64() cycles (default ~2 s). Tests shrink it to
@@ -27,34 +68,37 @@ long long peer_wait_budget();
 // peer's pad and waits until its own pad shows `epoch` from every peer. One CTA.
 int symm_barrier(stream_t stream, const PeerTable &t, int slot_base, uint32_t epoch, DeviceStatus *status);
 
-// Two-shot all-reduce in place on the same arena range of every rank. Rank r sums slice r of all
-// ranks (fp32 accumulation), multiplies by `scale` and stores the result into slice r of every
-// rank's buffer. dtype: 0 fp32, 1 bf16. The caller brackets it with symm_barrier.
-int symm_all_reduce_inplace(stream_t stream, const PeerTable &t, int64_t offset_bytes, int64_t count, int dtype, float scale);
+// All-reduce in place on the same arena range of every rank, one launch. Rank r owns slice r:
+// with a multicast mapping it loads the sum of all copies from the switch (multimem.ld_reduce,
+// fp32 accumulation), scales, and writes all copies with one multimem.st; without one it pulls
+// the slice from every peer, sums in fp32 and pushes the result to every peer. dtype: 0 fp32, 1 bf16.
+// `blocks` receives the grid size (the caller advances Handshake::blocks_before by it).
+int symm_all_reduce(stream_t stream, const PeerTable &t, const Handshake &h, int64_t offset_bytes, int64_t count, int dtype,
+                    float scale, int *blocks);
 
-// One-shot variant for small messages: every rank sums all copies into its own (no peer stores).
-// `staging_offset` is where every rank put its contribution; dst is local memory.
-int symm_all_reduce_oneshot(stream_t stream, const PeerTable &t, int64_t staging_offset, void *dst, int64_t count, int dtype,
-                            float scale);
+// dst[i] = scale * sum_p src_p[src_offset + i] for count elements (reduce-scatter: pass the offset
+// of this rank's slice inside every rank's send buffer). dst is local memory. One launch.
+int symm_reduce_scatter(stream_t stream, const PeerTable &t, const Handshake &h, int64_t src_offset_bytes, void *dst, int64_t count,
+                        int dtype, float scale, int *blocks);
 
-// dst[i] = scale * sum_p src_p[src_offset + i] for count elements (pull reduce-scatter: pass the
-// offset of this rank's slice inside every peer's send buffer). dst is local memory.
-int symm_pull_reduce(stream_t stream, const PeerTable &t, int64_t src_offset_bytes, void *dst, int64_t count, int dtype,
-                     float scale);
+// All-gather into a symmetric destination: this rank's `bytes` at base[rank] + src_offset are written
+// to dst_offset + rank * bytes of every rank (multimem.st, or one peer store per rank). One launch.
+int symm_all_gather_push(stream_t stream, const PeerTable &t, const Handshake &h, int64_t src_offset_bytes, int64_t dst_offset_bytes,
+                         int64_t bytes, int *blocks);
 
 // Strided chunk copies from peers (pull all-gather / all-to-all with pack and unpack fused):
 // for each peer p: rows x row_bytes from base[p] + src_offset[p] (row stride src_stride) to
-// dst[p] (row stride dst_stride). row_bytes, strides and addresses are multiples of 16.
+// dst[p] (row stride dst_stride). row_bytes, strides and addresses are multiples of 16. One launch.
 struct PullCopyArgs {
   int64_t src_offset[kMaxPeers];
   char *dst[kMaxPeers];
   int64_t rows, row_bytes, src_stride, dst_stride;
 };
-int symm_pull_copy(stream_t stream, const PeerTable &t, const PullCopyArgs &args);
+int symm_pull_copy(stream_t stream, const PeerTable &t, const Handshake &h, const PullCopyArgs &args, int *blocks);
 
-// ZeRO step in one kernel: reduce-scatter of the gradient arena (pull, fp32 accumulate),
-// AdamW on this rank's shard of (master weights, moments), and all-gather of the updated bf16
-// working copy by pushing it into every rank's bf16 arena.
+// ZeRO step in one kernel: reduce-scatter of a gradient range (switch reduction or pull, fp32
+// accumulate), AdamW on this rank's shard of (master weights, moments), and all-gather of the
+// updated bf16 working copy by writing it into every rank's bf16 arena.
 struct ShardedAdamWArgs {
   int64_t grad_offset_bytes;   // gradient arena inside the symmetric arena (fp32)
   int64_t lp_offset_bytes;     // bf16 working-copy arena inside the symmetric arena (may be < 0: none)
@@ -65,5 +109,6 @@ struct ShardedAdamWArgs {
   float lr, beta1, beta2, eps, weight_decay, inv_bias_correction1, inv_bias_correction2, grad_scale;
   const float *clip_coef;
 };
-int symm_reduce_scatter_adamw_all_gather(stream_t stream, const PeerTable &t, const ShardedAdamWArgs &args);
+int symm_reduce_scatter_adamw_all_gather(stream_t stream, const PeerTable &t, const Handshake &h, const ShardedAdamWArgs &args,
+                                         int *blocks);
 }  // namespace cs::kernels

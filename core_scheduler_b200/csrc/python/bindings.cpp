@@ -17,6 +17,7 @@
 #include "cs/optimizer.h"
 #include "cs/parallel.h"
 #include "cs/symmetric.h"
+#include "src/vmm.h"
 #include "kernels/collectives.h"
 #include "kernels/api.h"
 
@@ -668,6 +669,8 @@ PYBIND11_MODULE(_C, m) {
       .def_readonly("rank", &SymmetricContext::rank)
       .def_readonly("size", &SymmetricContext::size)
       .def_readonly("arena_bytes", &SymmetricContext::arena_bytes)
+      .def_readonly("virtual_memory", &SymmetricContext::virtual_memory)
+      .def_property_readonly("has_multicast", [](const SymmetricContext &c) { return c.multicast_base != nullptr; })
       .def("bytes_in_use", &SymmetricContext::bytes_in_use)
       .def("cached_blocks", &SymmetricContext::cached_blocks)
       .def("empty", [](SymmetricContext &c, std::vector<int64_t> sizes, at::ScalarType dt) {
@@ -680,6 +683,8 @@ PYBIND11_MODULE(_C, m) {
         c.release(communication::SymmetricBlock{offset, bytes});
       })
       .def("check_status", [](SymmetricContext &c) { communication::check_device_status(c, "python"); });
+  m.def("duplicate_descriptor", &communication::vmm::duplicate_descriptor, py::arg("pid"), py::arg("fd"),
+        "Duplicates descriptor `fd` of process `pid` into this process (how arena handles cross process boundaries); -1 on failure");
   m.def("create_symmetric_context", &communication::create_symmetric_context, py::arg("comm"), py::arg("arena_bytes"));
   m.def("symmetric_barrier", [](const Scheduler &s, const Comm &c) {
     cs::submit(s, "cs::communication::barrier", Task::Impl::kComm, Task::Impl::kNccl, {}, {},

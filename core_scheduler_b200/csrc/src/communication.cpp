@@ -252,7 +252,9 @@ void AllReduceBucket::sync(const Scheduler &scheduler, const Comm &comm) const {
   const bool alone = comm.get_size() <= 1;
   if (!alone) AllReduce::run_inplace(scheduler, comm, impl_->pending, impl_->op);
   ++impl_->launches;
-  if (impl_->callback) impl_->callback(scheduler, impl_->pending, alone ? Task::Impl::kAssist : Task::Impl::kComm);
+  // The communication stream has the highest priority and the longest re-join gap, so work hooked in here runs
+  // beside the backward pass instead of holding up the weight-gradient GEMMs of the assist stream.
+  if (impl_->callback) impl_->callback(scheduler, impl_->pending, Task::Impl::kComm);
   impl_->pending.clear();
   impl_->pending_bytes = 0;
 }

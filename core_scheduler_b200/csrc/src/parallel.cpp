@@ -8,6 +8,7 @@
 #include <unordered_map>
 
 #include "kernels/collectives.h"
+#include "symm_internal.h"
 
 namespace cs::parallel {
 using communication::SymmetricContext;
@@ -88,13 +89,7 @@ void ZeroAdamWImpl::step(const Scheduler &scheduler) {
              if (L.defined())
                CS_ASSERT_TRUE(ctx->locate(L.data_ptr(), static_cast<int64_t>(L.nbytes()), &l_off),
                               "ZeroAdamW needs the bf16 arena in symmetric memory (use flatten_symmetric)");
-             kernels::PeerTable table{};
-             for (int p = 0; p < ctx->size; ++p) {
-               table.base[p] = ctx->bases[p];
-               table.flags[p] = ctx->flags[p];
-             }
-             table.rank = ctx->rank;
-             table.size = ctx->size;
+             const kernels::PeerTable table = communication::table_of(*ctx);
              kernels::ShardedAdamWArgs a{};
              a.grad_offset_bytes = g_off;
              a.lp_offset_bytes = l_off;
@@ -112,10 +107,13 @@ void ZeroAdamWImpl::step(const Scheduler &scheduler) {
              a.inv_bias_correction2 = static_cast<float>(1.0 / bc2);
              a.grad_scale = static_cast<float>(o.grad_scale / static_cast<double>(world));
              a.clip_coef = state->clip_coef.impl()->tensor.defined() ? state->clip_coef.impl()->tensor.data_ptr<float>() : nullptr;
-             ctx->barrier();  // every rank's gradients are complete
-             const int code = kernels::symm_reduce_scatter_adamw_all_gather(c10::cuda::getCurrentCUDAStream().stream(), table, a);
+             // one launch: "every rank's gradients are complete" and "every rank's bf16 arena received all
+             // shards" are the barriers at the two ends of the kernel
+             int blocks = 0;
+             const auto h = communication::begin_collective(*ctx, kernels::kChanZero);
+             const int code = kernels::symm_reduce_scatter_adamw_all_gather(c10::cuda::getCurrentCUDAStream().stream(), table, h, a, &blocks);
              CS_ASSERT_TRUE(code == 0, "fused reduce-scatter/AdamW/all-gather launch failed: ", cuda_error_string(code));
-             ctx->barrier();  // every rank's bf16 arena received all shards
+             communication::end_collective(*ctx, kernels::kChanZero, blocks);
            } else {
              // Single rank (or CPU): plain sharded update on the whole arena.
              CS_ASSERT_TRUE(world == 1, "ZeroAdamW across ranks needs symmetric memory on CUDA devices");

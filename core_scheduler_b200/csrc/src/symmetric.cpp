@@ -10,6 +10,8 @@
 #include <thread>
 
 #include "kernels/collectives.h"
+#include "symm_internal.h"
+#include "vmm.h"
 
 namespace cs::communication {
 namespace {
@@ -20,18 +22,6 @@ void *cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
 
 void check(int code, const char *what) {
   CS_ASSERT_TRUE(code == 0, "`", what, "` failed: ", cuda_error_string(code));
-}
-
-kernels::PeerTable table_of(const SymmetricContext &ctx) {
-  kernels::PeerTable t{};
-  for (int p = 0; p < ctx.size; ++p) {
-    t.base[p] = ctx.bases[p];
-    t.flags[p] = ctx.flags[p];
-  }
-  t.rank = ctx.rank;
-  t.size = ctx.size;
-  t.arena_bytes = ctx.arena_bytes;
-  return t;
 }
 
 std::vector<uint8_t> to_bytes(const cudaIpcMemHandle_t &h) {
@@ -50,10 +40,16 @@ int dtype_code(at::ScalarType t) { return t == at::kFloat ? 0 : (t == at::kBFloa
 
 SymmetricContext::~SymmetricContext() {
   if (!owns_) return;
-  // Mappings of peers first, then our own memory. Errors at teardown are ignored on purpose.
-  for (void *p : opened_) cudaIpcCloseMemHandle(p);
-  if (!bases.empty() && bases[rank]) cudaFree(bases[rank]);
-  if (!flags.empty() && flags[rank]) cudaFree(flags[rank]);
+  // Errors at teardown are ignored on purpose.
+  cudaDeviceSynchronize();
+  if (virtual_memory) {
+    vmm_.reset();  // unbinds the multicast object, unmaps every range, releases the handles
+  } else {
+    // Mappings of peers first, then our own memory.
+    for (void *p : opened_) cudaIpcCloseMemHandle(p);
+    if (!bases.empty() && bases[rank]) cudaFree(bases[rank]);
+    if (!flags.empty() && flags[rank]) cudaFree(flags[rank]);
+  }
   if (status) cudaFree(status);
   (void)cudaGetLastError();
 }
@@ -134,6 +130,36 @@ void SymmetricContext::barrier() {
         "symm_barrier");
 }
 
+namespace {
+// vmm::Exchange over the communicator's key/value store
+struct StoreExchange : vmm::Exchange {
+  c10d::Store &store;
+  std::string prefix;
+  int size;
+  StoreExchange(c10d::Store &s, std::string p, int n) : store{s}, prefix{std::move(p)}, size{n} {}
+  void put(const std::string &key, const std::string &value) override {
+    store.set(prefix + key, std::vector<uint8_t>(value.begin(), value.end()));
+  }
+  std::string get(const std::string &key) override {
+    auto raw = store.get(prefix + key);  // blocks until the key exists (store timeout applies)
+    return std::string(raw.begin(), raw.end());
+  }
+  void barrier(const std::string &name) override {
+    store.add(prefix + name, 1);
+    const auto t0 = std::chrono::steady_clock::now();
+    while (store.add(prefix + name, 0) < size) {
+      CS_ASSERT_TRUE(std::chrono::steady_clock::now() - t0 < std::chrono::seconds(120), "timed out in the store barrier `", name, "`");
+      std::this_thread::sleep_for(std::chrono::milliseconds(2));
+    }
+  }
+};
+
+bool env_is(const char *name, const char *value) {
+  const char *e = std::getenv(name);
+  return e != nullptr && std::string(e) == value;
+}
+}  // namespace
+
 std::shared_ptr<SymmetricContext> create_symmetric_context(const Comm &comm, int64_t arena_bytes) {
   auto &impl = *comm.impl();
   CS_ASSERT_TRUE(impl.size <= kernels::kMaxPeers, "symmetric memory supports up to ", kernels::kMaxPeers, " ranks");
@@ -147,19 +173,46 @@ std::shared_ptr<SymmetricContext> create_symmetric_context(const Comm &comm, int
   ctx->bases.assign(ctx->size, nullptr);
   ctx->flags.assign(ctx->size, nullptr);
   ctx->owns_ = true;
+  CS_CHECK_CUDART(cudaMalloc(&ctx->status, sizeof(kernels::DeviceStatus)));
+  CS_CHECK_CUDART(cudaMemset(ctx->status, 0, sizeof(kernels::DeviceStatus)));
+  const int64_t pad_bytes = SymmetricContext::kFlagWords * static_cast<int64_t>(sizeof(uint32_t));
+  static int generation = 0;
+  const std::string prefix = str_cat("cs/symm/", generation++, "/");
+  CS_ASSERT_TRUE(ctx->size == 1 || impl.store != nullptr, "symmetric memory needs the communicator's store to exchange handles");
+
+  // ---- preferred: one cuMemCreate allocation per rank (arena followed by the signal pad), shared as file
+  //      descriptors, with an NVLink multicast object over the same pages --------------------------------
+  if (ctx->size > 1 && !env_is("CS_SYMMETRIC_IPC", "1")) {
+    StoreExchange exchange{*impl.store, prefix, ctx->size};
+    auto arena = std::make_shared<vmm::Arena>();
+    std::string why;
+    const bool want_multicast = !env_is("NCCL_NVLS_ENABLE", "0");
+    if (vmm::create(arena.get(), ctx->rank, ctx->size, device, ctx->arena_bytes + pad_bytes, want_multicast, exchange, &why)) {
+      for (int p = 0; p < ctx->size; ++p) {
+        ctx->bases[p] = arena->peer_va[p];
+        ctx->flags[p] = reinterpret_cast<uint32_t *>(arena->peer_va[p] + ctx->arena_bytes);
+      }
+      ctx->multicast_base = arena->multicast_va;
+      ctx->virtual_memory = true;
+      ctx->vmm_ = std::shared_ptr<void>(arena.get(), [arena](void *) { vmm::destroy(arena.get()); });
+      CS_CHECK_CUDART(cudaMemset(ctx->flags[ctx->rank], 0, static_cast<size_t>(pad_bytes)));
+      CS_CHECK_CUDART(cudaDeviceSynchronize());
+      exchange.barrier("pads_cleared");  // nobody signals into a pad that is still being cleared
+      impl.symmetric = ctx;
+      return ctx;
+    }
+    logger().warn("symmetric arena: virtual-memory path unavailable (", why, "); using cudaMalloc + CUDA IPC without multicast");
+  }
+
+  // ---- fallback: cudaMalloc + CUDA IPC (no multicast) -----------------------------------------------------
   void *base = nullptr, *pad = nullptr;
   CS_CHECK_CUDART(cudaMalloc(&base, ctx->arena_bytes));
-  CS_CHECK_CUDART(cudaMalloc(&pad, SymmetricContext::kFlagWords * sizeof(uint32_t)));
-  CS_CHECK_CUDART(cudaMalloc(&ctx->status, sizeof(kernels::DeviceStatus)));
-  CS_CHECK_CUDART(cudaMemset(pad, 0, SymmetricContext::kFlagWords * sizeof(uint32_t)));
-  CS_CHECK_CUDART(cudaMemset(ctx->status, 0, sizeof(kernels::DeviceStatus)));
+  CS_CHECK_CUDART(cudaMalloc(&pad, static_cast<size_t>(pad_bytes)));
+  CS_CHECK_CUDART(cudaMemset(pad, 0, static_cast<size_t>(pad_bytes)));
   CS_CHECK_CUDART(cudaDeviceSynchronize());
   ctx->bases[ctx->rank] = static_cast<char *>(base);
   ctx->flags[ctx->rank] = static_cast<uint32_t *>(pad);
   if (ctx->size > 1) {
-    CS_ASSERT_TRUE(impl.store != nullptr, "symmetric memory needs the communicator's store to exchange IPC handles");
-    static int generation = 0;
-    const std::string prefix = str_cat("cs/symm/", generation++, "/");
     cudaIpcMemHandle_t h_base, h_pad;
     CS_CHECK_CUDART(cudaIpcGetMemHandle(&h_base, base));
     CS_CHECK_CUDART(cudaIpcGetMemHandle(&h_pad, pad));
@@ -201,6 +254,7 @@ void check_device_status(SymmetricContext &ctx, const char *where) {
 }
 
 // ------------------------------------------------------------------------ collectives ----
+// Every collective below is one kernel launch on the current stream; the barriers are inside the kernels.
 bool symmetric_all_reduce(SymmetricContext &ctx, const std::vector<at::Tensor> &ranges, Operation op) {
   for (auto &r : ranges)
     if (!r.is_cuda() || !r.is_contiguous() || dtype_code(r.scalar_type()) < 0 || r.nbytes() % 16 != 0 ||
@@ -208,22 +262,23 @@ bool symmetric_all_reduce(SymmetricContext &ctx, const std::vector<at::Tensor> &
       return false;
   const float scale = op == kAVG ? 1.0f / static_cast<float>(ctx.size) : 1.0f;
   const auto table = table_of(ctx);
+  auto stream = static_cast<cudaStream_t>(cur_stream());
   for (auto &r : ranges) {
     int64_t offset = 0;
     const int dt = dtype_code(r.scalar_type());
+    int blocks = 0;
     if (ctx.locate(r.data_ptr(), static_cast<int64_t>(r.nbytes()), &offset)) {
-      ctx.barrier();  // every rank's contribution is complete
-      check(kernels::symm_all_reduce_inplace(cur_stream(), table, offset, r.numel(), dt, scale), "symm_all_reduce_inplace");
-      ctx.barrier();  // every slice has been written everywhere
+      const auto h = begin_collective(ctx, kernels::kChanAllReduce);
+      check(kernels::symm_all_reduce(stream, table, h, offset, r.numel(), dt, scale, &blocks), "symm_all_reduce");
+      end_collective(ctx, kernels::kChanAllReduce, blocks);
     } else {
-      // Not in the arena: stage the contribution, reduce straight into the destination.
+      // Not in the arena: stage the contribution, reduce straight into the destination (every rank sums all copies).
       const SymmetricBlock st = ctx.staging(static_cast<int64_t>(r.nbytes()));
-      CS_CHECK_CUDART(cudaMemcpyAsync(ctx.bases[ctx.rank] + st.offset, r.data_ptr(), r.nbytes(), cudaMemcpyDeviceToDevice,
-                                      static_cast<cudaStream_t>(cur_stream())));
-      ctx.barrier();
-      check(kernels::symm_all_reduce_oneshot(cur_stream(), table, st.offset, r.data_ptr(), r.numel(), dt, scale),
-            "symm_all_reduce_oneshot");
-      ctx.barrier();  // staging may be overwritten by the next call only after everyone read it
+      CS_CHECK_CUDART(cudaMemcpyAsync(ctx.bases[ctx.rank] + st.offset, r.data_ptr(), r.nbytes(), cudaMemcpyDeviceToDevice, stream));
+      const auto h = begin_collective(ctx, kernels::kChanReduceScatter);
+      check(kernels::symm_reduce_scatter(stream, table, h, st.offset, r.data_ptr(), r.numel(), dt, scale, &blocks),
+            "symm_reduce_scatter (one-shot all-reduce)");
+      end_collective(ctx, kernels::kChanReduceScatter, blocks);
     }
   }
   return true;
@@ -246,18 +301,29 @@ bool symmetric_all_gather(SymmetricContext &ctx, const std::vector<std::vector<a
       offset = st.offset;
       CS_CHECK_CUDART(cudaMemcpyAsync(ctx.bases[ctx.rank] + offset, send[i].data_ptr(), bytes, cudaMemcpyDeviceToDevice, stream));
     }
-    ctx.barrier();
-    kernels::PullCopyArgs a{};
-    for (int p = 0; p < ctx.size; ++p) {
-      a.src_offset[p] = offset;
-      a.dst[p] = static_cast<char *>(recv[i][p].data_ptr());
+    // Destination slots that form one block of the arena (slot p at dst + p * bytes, the same offset on every
+    // rank) are written by their owners: one multicast store per vector instead of size - 1 pulls.
+    int64_t dst_offset = 0;
+    bool push = ctx.locate(recv[i][0].data_ptr(), bytes * ctx.size, &dst_offset);
+    for (int p = 1; push && p < ctx.size; ++p)
+      push = static_cast<const char *>(recv[i][p].data_ptr()) == static_cast<const char *>(recv[i][0].data_ptr()) + p * bytes;
+    int blocks = 0;
+    const auto h = begin_collective(ctx, kernels::kChanAllGather);
+    if (push) {
+      check(kernels::symm_all_gather_push(stream, table, h, offset, dst_offset, bytes, &blocks), "symm_all_gather_push");
+    } else {
+      kernels::PullCopyArgs a{};
+      for (int p = 0; p < ctx.size; ++p) {
+        a.src_offset[p] = offset;
+        a.dst[p] = static_cast<char *>(recv[i][p].data_ptr());
+      }
+      a.rows = 1;
+      a.row_bytes = bytes;
+      a.src_stride = bytes;
+      a.dst_stride = bytes;
+      check(kernels::symm_pull_copy(stream, table, h, a, &blocks), "symm_pull_copy");
     }
-    a.rows = 1;
-    a.row_bytes = bytes;
-    a.src_stride = bytes;
-    a.dst_stride = bytes;
-    check(kernels::symm_pull_copy(cur_stream(), table, a), "symm_pull_copy");
-    ctx.barrier();
+    end_collective(ctx, kernels::kChanAllGather, blocks);
   }
   return true;
 }
@@ -289,11 +355,12 @@ bool symmetric_reduce_scatter(SymmetricContext &ctx, const std::vector<at::Tenso
         CS_CHECK_CUDART(cudaMemcpyAsync(ctx.bases[ctx.rank] + offset + p * chunk, send[i][p].data_ptr(), chunk,
                                         cudaMemcpyDeviceToDevice, stream));
     }
-    ctx.barrier();
-    check(kernels::symm_pull_reduce(cur_stream(), table, offset + ctx.rank * chunk, recv[i].data_ptr(), recv[i].numel(),
-                                    dtype_code(recv[i].scalar_type()), scale),
-          "symm_pull_reduce");
-    ctx.barrier();
+    int blocks = 0;
+    const auto h = begin_collective(ctx, kernels::kChanReduceScatter);
+    check(kernels::symm_reduce_scatter(stream, table, h, offset + ctx.rank * chunk, recv[i].data_ptr(), recv[i].numel(),
+                                       dtype_code(recv[i].scalar_type()), scale, &blocks),
+          "symm_reduce_scatter");
+    end_collective(ctx, kernels::kChanReduceScatter, blocks);
   }
   return true;
 }
@@ -348,9 +415,10 @@ bool symmetric_all_to_all(SymmetricContext &ctx, const std::vector<at::Tensor> &
     for (int p = 0; p < ctx.size; ++p) a.src_offset[p] = st.offset + ctx.rank * chunk;
   }
   for (int p = 0; p < ctx.size; ++p) a.dst[p] = static_cast<char *>(recv[p].data_ptr());
-  ctx.barrier();
-  check(kernels::symm_pull_copy(cur_stream(), table, a), "symm_pull_copy");
-  ctx.barrier();
+  int blocks = 0;
+  const auto h = begin_collective(ctx, kernels::kChanAllToAll);
+  check(kernels::symm_pull_copy(stream, table, h, a, &blocks), "symm_pull_copy");
+  end_collective(ctx, kernels::kChanAllToAll, blocks);
   return true;
 }
 }  // namespace cs::communication

@@ -10,7 +10,8 @@ the comm stream, max over ranks, median of the iterations after warm-up) and the
   all-gather      (N-1)/N * S / t        (S = gathered bytes)
   reduce-scatter  (N-1)/N * S / t        (S = bytes before the reduction)
   all-to-all      (N-1)/N * S / t
-next to the NVLink reference figures (900 GB/s nominal, 770 GB/s measured peer copy per direction).
+next to the NVLink reference figures (900 GB/s nominal, 770 GB/s measured peer copy per direction). The SM clock
+and the throttle reasons of GPU 0 are sampled during the whole run and printed with the results.
 """
 from __future__ import annotations
 
@@ -24,6 +25,7 @@ import torch.distributed as dist
 
 import core_scheduler_b200 as cs
 from core_scheduler_b200.parallel import init_distributed
+from core_scheduler_b200.utils.clocks import ClockSampler
 
 C = cs._C
 BF = torch.bfloat16
@@ -64,6 +66,10 @@ def main():
     max_bytes = args.max_mb << 20
     ctx = C.create_symmetric_context(comm_p2p, 3 * max_bytes + (64 << 20))
     comms = {"nccl": comm_nccl, "nvp2p": comm_p2p}
+    memory = "multicast" if ctx.has_multicast else ("peer mappings (cuMemCreate)" if ctx.virtual_memory else "peer mappings (CUDA IPC)")
+    if rank == 0:
+        print(f"world {world}; symmetric arena: {memory}", flush=True)
+    sampler = ClockSampler(local_rank).start() if rank == 0 else None
     results = []
     size = 1024
     while size <= max_bytes:
@@ -102,7 +108,9 @@ def main():
             ctx.check_status()
         size *= 4 if size < (1 << 20) else 2
     if rank == 0:
-        print(json.dumps({"world": world, "results": results}))
+        clocks = sampler.stop()
+        print("clocks during the run:", json.dumps(clocks))
+        print(json.dumps({"world": world, "memory": memory, "clocks": clocks, "results": results}))
     dist.barrier()
     dist.destroy_process_group()
 

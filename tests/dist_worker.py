@@ -80,6 +80,62 @@ def case_all_reduce_arena(device, nvp2p):
     ctx.check_status()
 
 
+def case_collectives_arena(device, nvp2p):
+    """All-gather, reduce-scatter and all-reduce on buffers that live in the symmetric arena (the paths that
+    write through the multicast mapping when there is one), each run twice: the kernels reduce in a fixed
+    order, so the second run must reproduce the first bit for bit."""
+    comm, rank, world, s = make_comm(device, True)
+    ctx = C.create_symmetric_context(comm, 96 << 20)
+    expect_mc = os.environ.get("CS_EXPECT_MULTICAST")
+    if expect_mc is not None:
+        assert ctx.has_multicast == (expect_mc == "1"), (ctx.has_multicast, ctx.virtual_memory)
+    for dtype, n in ((torch.float32, 4 * 3001), (torch.bfloat16, 8 * 4099), (torch.float32, 1 << 20)):
+        tol = dict(rtol=2e-2, atol=1e-1) if dtype == torch.bfloat16 else dict(rtol=1e-6, atol=1e-5)
+        # all-gather: every rank's shard lands in slot `rank` of one arena block on every rank
+        src, so, sb = ctx.empty([n], dtype)
+        dst, do, db = ctx.empty([world, n], dtype)
+        src.copy_(seeded(7 * rank + 3, n, dtype=dtype, device=device))
+        torch.cuda.synchronize()
+        results = []
+        for _ in range(2):
+            dst.zero_()
+            torch.cuda.synchronize()
+            C.all_gather(s, comm, [[T(dst[p]) for p in range(world)]], [T(src)])
+            s.synchronize()
+            results.append(dst.clone())
+        for p in range(world):
+            assert torch.equal(results[0][p], seeded(7 * p + 3, n, dtype=dtype, device=device)), (rank, p, dtype, n)
+        assert torch.equal(results[0], results[1])
+        # reduce-scatter: chunk p of every rank's arena block is summed into rank p's output
+        send, so2, sb2 = ctx.empty([world, n], dtype)
+        send.copy_(seeded(11 * rank + 5, world, n, dtype=dtype, device=device))
+        torch.cuda.synchronize()
+        outs = []
+        for _ in range(2):
+            out = torch.zeros(n, dtype=dtype, device=device)
+            C.reduce_scatter(s, comm, [T(out)], [[T(send[p]) for p in range(world)]], "sum")
+            s.synchronize()
+            outs.append(out)
+        e = sum(seeded(11 * r + 5, world, n, dtype=dtype, device=device)[rank].double() for r in range(world))
+        assert torch.allclose(outs[0].double(), e, **tol), (rank, dtype, n)
+        assert torch.equal(outs[0], outs[1])
+        # all-reduce in place, twice from the same inputs
+        buf, bo, bb = ctx.empty([n], dtype)
+        sums = []
+        for _ in range(2):
+            buf.copy_(seeded(13 * rank + 1, n, dtype=dtype, device=device))
+            torch.cuda.synchronize()
+            C.all_reduce(s, comm, [T(buf)], "sum")
+            s.synchronize()
+            sums.append(buf.clone())
+        e = sum(seeded(13 * r + 1, n, dtype=dtype, device=device).double() for r in range(world))
+        assert torch.allclose(sums[0].double(), e, **tol), (rank, dtype, n)
+        assert torch.equal(sums[0], sums[1])
+        for off, nb in ((so, sb), (do, db), (so2, sb2), (bo, bb)):
+            ctx.release(off, nb)
+    ctx.check_status()
+
+
 def case_bucket(device, nvp2p):
     comm, rank, world, s = make_comm(device, nvp2p)
     bucket = cs.AllReduceBucket(1024 * 4, "sum")  # 1024 fp32 elements

@@ -49,6 +49,25 @@ def test_in_place_arena_all_reduce():
 
 
 @needs2
+@pytest.mark.parametrize("memory", ["multicast", "peer", "ipc"])
+def test_collectives_on_arena_buffers_every_memory_path(memory):
+    """The same collectives over the three ways the arena can exist: virtual-memory allocation with an NVLink
+    multicast object (multimem kernels), the same without multicast (peer loads/stores), and cudaMalloc + CUDA
+    IPC. Every rank runs to completion and all ranks leave together."""
+    env = {"multicast": {"NCCL_NVLS_ENABLE": "1", "CS_EXPECT_MULTICAST": "1"},
+           "peer": {"NCCL_NVLS_ENABLE": "0", "CS_EXPECT_MULTICAST": "0"},
+           "ipc": {"CS_SYMMETRIC_IPC": "1", "CS_EXPECT_MULTICAST": "0"}}[memory]
+    run_case("collectives_arena", device="cuda", extra=("nvp2p",), timeout=600, env_extra=env)
+
+
+@needs2
+@pytest.mark.parametrize("case", ["all_reduce_arena", "dp_training", "zero_training"])
+def test_multicast_paths_of_training(case):
+    """Data-parallel and sharded-optimizer steps with the multicast mapping on (all ranks run to completion)."""
+    run_case(case, device="cuda", extra=("nvp2p",), timeout=600, env_extra={"NCCL_NVLS_ENABLE": "1"})
+
+
+@needs2
 def test_zero_fused_step_matches_replicated_adamw():
     run_case("zero_training", device="cuda", extra=("nvp2p",), timeout=600)
 

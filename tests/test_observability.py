@@ -99,3 +99,20 @@ def test_training_state_resume_continues_bit_identically(tmp_path):
     assert got.step == 2 and got.data_cursor == 2 and got.model == "tiny"
     resumed = [step(model2, opt2, b) for b in batches[got.data_cursor:]]
     assert resumed == full[2:]
+
+
+def test_descriptor_of_another_process_can_be_duplicated(tmp_path):
+    """Arena handles travel between ranks as (pid, fd) pairs through the store; the importer duplicates the
+    descriptor with pidfd_getfd. Here the 'handle' is a memfd of this process read by a child process."""
+    import subprocess
+    import sys
+
+    fd = os.memfd_create("cs_handle")
+    os.write(fd, b"symmetric")
+    code = ("import os, sys; sys.path.insert(0, %r); import core_scheduler_b200 as cs; "
+            "n = cs._C.duplicate_descriptor(%d, %d); assert n >= 0, n; print(os.pread(n, 9, 0).decode())"
+            % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))), os.getpid(), fd))
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120, env=dict(os.environ, CS_NO_AUTOBUILD="1"))
+    assert out.returncode == 0 and out.stdout.strip() == "symmetric", out.stdout + out.stderr
+    assert cs._C.duplicate_descriptor(os.getpid(), fd) >= 0  # own descriptors are dup()ed
+    assert cs._C.duplicate_descriptor(os.getpid(), 10 ** 6) == -1
