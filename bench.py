@@ -161,7 +161,8 @@ def make_trainer(args, cs, comm, world, local_rank):
     cs._C.set_backend(args.backend)
     trainer = GPT2Trainer(gpt2_config(args.model, dtype=torch.float32), comm, world, local_rank, mode=args.mode, collectives=args.comm,
                           device="cuda", lr=3e-4, beta1=0.9, beta2=0.95, weight_decay=0.1, bucket_mb=args.bucket_mb, seed=1234,
-                          scheduler=scheduler, overlap_optimizer=not args.no_overlap_optimizer)
+                          scheduler=scheduler, overlap_optimizer=not args.no_overlap_optimizer,
+                          max_tokens=args.micro_batch * args.seq_len)
     trainer.s, trainer.cfg = scheduler, trainer.config
     trainer.tp = args.mode == "tp" and world > 1
     return trainer
@@ -331,6 +332,9 @@ def main():
     if world > 1:
         import torch.distributed as dist
 
+        del batches, loss
+        trainer.close()
+        dist.barrier()
         dist.destroy_process_group()
     return 0
 

@@ -59,6 +59,16 @@ CS_MODULE(ZeroAdamW);
 // the sharded Linears are rank-local; LayerNorm, embedding and classifier parameters are
 // replicated and their gradients are summed over the ranks through the all-reduce bucket.
 // n_head must be divisible by the number of ranks, and so must B*T.
+// Symmetric buffers shared by all blocks of one tensor-parallel model (created on first use): the bf16 partial
+// product awaiting its reduce-scatter and two gathered-gradient buffers used in turn.
+struct TPWorkspace {
+  Tensor partial;
+  Tensor grad_full[2];
+  int next_grad{0};
+  Tensor slots[2];  // [tp, rows, n] bf16: per-source slots of the GEMM -> reduce-scatter epilogue, used in turn
+  int next_slot{0};
+};
+
 struct CS_API TPBlockImpl : module::Module {
   TPBlockImpl(const Scheduler &scheduler, const models::GPT2Config &config, const communication::Comm &comm);
   Tensor forward(const Scheduler &scheduler, const ReadOnlyTensor &x_shard, int64_t batch, int64_t seq);
@@ -72,15 +82,22 @@ struct CS_API TPBlockImpl : module::Module {
   // tensor-parallel size the first (n_head % tp) ranks own one head more (GPT-2 774M: 20 heads over 8 ranks = 3,3,3,3,2,2,2,2).
   int64_t local_heads{0};
   int64_t head_begin{0};
-  Tensor saved_ln1_out, saved_ln2_out;  // row shards kept for the backward re-gather (fused path)
+  // Symmetric-memory path: gathered LayerNorm outputs [M, d], kept from forward to backward (the weight gradients of
+  // c_attn / fc1 read them again), and the model-wide workspace.
+  Tensor a_full, b_full;
+  std::shared_ptr<TPWorkspace> workspace;
+
+ private:
+  bool fused_forward_{false};
+  bool tiled_forward_{false};
 };
 CS_MODULE(TPBlock);
 
 struct CS_API TPGPT2Impl : module::Module {
   TPGPT2Impl(const Scheduler &scheduler, const models::GPT2Config &config, const communication::Comm &comm);
-  // input_ids, labels: the FULL [B, T] batch on every rank (each rank embeds and scores only its
-  // own row shard). Returns this rank's mean loss over its rows; average over ranks for the
-  // global loss.
+  // input_ids, labels: the FULL [B, T] batch on every rank (each rank embeds only its own row shard). With the
+  // vocabulary-parallel classifier (padded vocabulary divisible by 8 * tp) the result is the mean loss over all
+  // rows, identical on every rank; otherwise it is this rank's mean over its own rows.
   Tensor forward_loss(const Scheduler &scheduler, const ReadOnlyTensor &input_ids, const ReadOnlyTensor &labels);
   void backward_loss(const Scheduler &scheduler, const models::GradientSync &sync);
   [[nodiscard]] const models::GPT2Config &config() const { return config_; }
@@ -88,6 +105,8 @@ struct CS_API TPGPT2Impl : module::Module {
   [[nodiscard]] std::vector<std::string> replicated_parameters() const;
   // (first head, number of heads) owned by this rank.
   [[nodiscard]] std::pair<int64_t, int64_t> head_range() const { return {h.front()->head_begin, h.front()->local_heads}; }
+  // True when lm_head is split over the vocabulary (this rank holds rows [rank * V/tp, (rank + 1) * V/tp)).
+  [[nodiscard]] bool vocab_parallel() const { return vocab_parallel_; }
 
   module::Embedding wte{nullptr}, wpe{nullptr};
   std::vector<TPBlock> h;
@@ -99,21 +118,18 @@ struct CS_API TPGPT2Impl : module::Module {
   communication::Comm comm_;
   std::shared_ptr<compute::LinearCrossEntropy::State> lce_state_;
   int64_t batch_{0}, seq_{0};
+  // vocabulary-parallel classifier: lm_head holds rows [rank * V/tp, (rank + 1) * V/tp)
+  bool vocab_parallel_{false};
+  bool ce_fused_{false};
+  std::shared_ptr<TPWorkspace> workspace_;
+  Tensor lnf_full_, stats_full_;                         // persistent gathered buffers (symmetric path)
+  Tensor ce_logits_, ce_lse_, ce_input_;                 // kept from forward_loss to backward_loss
+  ReadOnlyTensor ce_labels_;
 };
 CS_MODULE(TPGPT2);
 
-// Fused tensor-parallel paths (one tcgen05 GEMM kernel each, over peer memory):
-//   all-gather -> GEMM: y[M, out_local] = gather(x_shard)[M, in] * W^T. The kernel's TMA producer
-//     reads every row block of x directly from its owner's symmetric buffer, own block first.
-//   GEMM -> reduce-scatter: the partial product's tiles are reduce-added (fp32) by the epilogue
-//     into the accumulator of the rank that owns the rows; the owner then adds the residual and
-//     rounds to bf16.
-// They apply when the communicator has symmetric memory, tensors are bf16 on the GPU and
-// M / tp is a multiple of 256; otherwise the unfused composition is used.
-CS_API Tensor column_parallel_forward(const Scheduler &scheduler, const communication::Comm &comm,
-                                      const std::shared_ptr<compute::Linear::State> &state, const ReadOnlyTensor &x_shard);
-CS_API Tensor row_parallel_forward(const Scheduler &scheduler, const communication::Comm &comm, const ReadOnlyTensor &weight,
-                                   const ReadOnlyTensor &x, const ReadOnlyTensor *residual_shard, bool weight_is_rhs);
+// Launches of this library's tensor-parallel collective kernels so far (row gathers and switch reduce-scatters on
+// symmetric memory); 0 means the generic collectives were used.
 CS_API int64_t fused_tp_launches();
 
 // Row-shard collectives used by the TP model (comm-stream tasks):

@@ -106,13 +106,21 @@ struct GemmArgs {
   // Fused collectives over peer memory (tensor parallelism); peer_count > 1 enables one of:
   //   a_peers: all-gather -> GEMM. Row block j of A ([m / peer_count, k], leading dim lda) is read
   //            by TMA straight from a_peers[j] (a peer's symmetric memory); no gathered copy exists.
-  //   d_peers: GEMM -> reduce-scatter. Row block j of D is reduce-added (fp32) into d_peers[j]
-  //            ([m / peer_count, n], leading dim ldd) on its owner; epilogue must be kEpiAccumF32.
-  // m / peer_count must be a multiple of 256. Tiles are visited starting with this rank's block.
+  //   d_peers: GEMM -> reduce-scatter. Row block j of D goes to d_peers[j] ([m / peer_count, n], leading dim
+  //            ldd) on its owner: reduce-added in fp32 (epilogue kEpiAccumF32), or stored as bf16 into the slot
+  //            the owner keeps for this rank (epilogue kEpiStoreBf16; the owner sums its slots afterwards).
+  //            Tiles are visited starting with the next rank's block, this rank's own block last.
+  //   ready_flags: GEMM beside an all-gather that is still in flight. A is local memory that the ranks fill in
+  //            row chunks; word [owner * 8 + chunk] of ready_flags reaches ready_epoch (acquire load) once the
+  //            chunk has landed. Tiles are visited in arrival order.
+  // m / peer_count must be a multiple of 256 (and of 256 * ready_chunks).
   int peer_count;
   int peer_rank;
   const void *a_peers[8];
   void *d_peers[8];
+  const uint32_t *ready_flags;
+  uint32_t ready_epoch;
+  int ready_chunks;
 };
 // Returns 0 on success, -1 when the shape/alignment is not supported (caller falls back).
 int gemm_bf16(stream_t stream, const GemmArgs &args);
@@ -144,9 +152,16 @@ int cross_entropy_finalize(stream_t stream, const float *stats, int64_t n_tiles,
                            int64_t ignore_index);
 // logits <- (softmax(logits) - onehot(target)) * grad_scale / count, in place (bf16); padded
 // columns (>= n_valid) and ignored rows become 0.
+// With a vocabulary slice (tensor parallel) `col_offset` is the class of column 0: targets and n_valid are then
+// global class numbers, lse the log-sum-exp over the whole vocabulary.
 int cross_entropy_backward_inplace(stream_t stream, void *logits, int64_t ld, const float *lse,
                                    const int64_t *target, const float *count, float grad_scale, int64_t rows,
-                                   int64_t n, int64_t n_valid, int64_t ignore_index);
+                                   int64_t n, int64_t n_valid, int64_t ignore_index, int64_t col_offset = 0);
+// Per-row statistics of one vocabulary slice (classes [col_offset, col_offset + ld)): out[row] = (log-sum-exp over
+// the slice's valid columns from the GEMM's per-tile partials, or -inf when it has none; the target's logit when the
+// target class falls into the slice's first n_valid_local columns, else 0).
+int cross_entropy_slice_stats(stream_t stream, const float *stats, int64_t n_tiles, const void *logits, int64_t ld,
+                              const int64_t *target, int64_t col_offset, int64_t n_valid_local, float *out, int64_t rows);
 
 // ---- gradient norm ---------------------------------------------------------------------------
 // sumsq[0] += sum(x^2) over n elements (fp32 or bf16 input); caller zeroes sumsq first.

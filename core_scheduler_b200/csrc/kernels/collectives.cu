@@ -288,8 +288,17 @@ __global__ void CS_COMM_BOUNDS all_reduce_kernel(PeerTable t, Handshake h, int64
   close_collective(t, h, 11);
 }
 
+// out = v + residual, elementwise on eight bf16 values (fp32 math)
+__device__ __forceinline__ V4 add_bf16x8(const V4 &v, const V4 &r) {
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  accumulate<1>(acc, v);
+  accumulate<1>(acc, r);
+  return finish<1>(acc, 1.0f);
+}
+
 template <int DTYPE>
-__global__ void CS_COMM_BOUNDS reduce_scatter_kernel(PeerTable t, Handshake h, int64_t src_offset, char *dst, int64_t vecs, float scale) {
+__global__ void CS_COMM_BOUNDS reduce_scatter_kernel(PeerTable t, Handshake h, int64_t src_offset, char *dst, const char *residual,
+                                                     int64_t vecs, float scale) {
   open_collective(t, h, 12);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < vecs; i0 += stride * kUnroll) {
@@ -304,22 +313,29 @@ __global__ void CS_COMM_BOUNDS reduce_scatter_kernel(PeerTable t, Handshake h, i
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
         const int64_t i = i0 + u * stride;
-        if (i < vecs && CS_PEER_OK(t, src_offset + i * 16)) st_v4(dst + i * 16, scaled<DTYPE>(v[u], scale));
+        if (i < vecs && CS_PEER_OK(t, src_offset + i * 16)) {
+          V4 o = scaled<DTYPE>(v[u], scale);
+          if (DTYPE == 1 && residual) o = add_bf16x8(o, ld_v4(residual + i * 16));
+          st_v4(dst + i * 16, o);
+        }
       }
     } else {
 #pragma unroll 1
       for (int u = 0; u < kUnroll; ++u) {
         const int64_t i = i0 + u * stride;
-        if (i < vecs && CS_PEER_OK(t, src_offset + i * 16)) st_v4(dst + i * 16, reduce_vector<DTYPE>(t, src_offset + i * 16, scale));
+        if (i < vecs && CS_PEER_OK(t, src_offset + i * 16)) {
+          V4 o = reduce_vector<DTYPE>(t, src_offset + i * 16, scale);
+          if (DTYPE == 1 && residual) o = add_bf16x8(o, ld_v4(residual + i * 16));
+          st_v4(dst + i * 16, o);
+        }
       }
     }
   }
   close_collective(t, h, 12);
 }
 
-__global__ void CS_COMM_BOUNDS all_gather_push_kernel(PeerTable t, Handshake h, int64_t src_offset, int64_t dst_offset, int64_t vecs) {
+__global__ void CS_COMM_BOUNDS all_gather_push_kernel(PeerTable t, Handshake h, const char *src, int64_t dst_offset, int64_t vecs) {
   open_collective(t, h, 13);
-  const char *src = t.base[t.rank] + src_offset;
   const int64_t mine = dst_offset + static_cast<int64_t>(t.rank) * vecs * 16;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < vecs; i0 += stride * kUnroll) {
@@ -336,6 +352,66 @@ __global__ void CS_COMM_BOUNDS all_gather_push_kernel(PeerTable t, Handshake h, 
     }
   }
   close_collective(t, h, 13);
+}
+
+__global__ void CS_COMM_BOUNDS all_gather_chunked_kernel(PeerTable t, Handshake h, const char *src, int64_t dst_offset, int64_t vecs_per_chunk,
+                                                         int chunks) {
+  open_collective(t, h, 16);
+  __shared__ int last_of_chunk;
+  uint32_t *local = channel_words(t, t.rank, h.channel);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int c = 0; c < chunks; ++c) {
+    const char *from = src + static_cast<int64_t>(c) * vecs_per_chunk * 16;
+    const int64_t to = dst_offset + (static_cast<int64_t>(t.rank) * chunks + c) * vecs_per_chunk * 16;
+    for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < vecs_per_chunk; i0 += stride * kUnroll) {
+      V4 v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t i = i0 + u * stride;
+        if (i < vecs_per_chunk) v[u] = ld_v4(from + i * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t i = i0 + u * stride;
+        if (i < vecs_per_chunk && CS_PEER_OK(t, to + i * 16)) broadcast_vector(t, to + i * 16, v[u]);
+      }
+    }
+    // the block that completes the chunk on this rank announces it to every rank (its own included)
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      last_of_chunk = atomicAdd(local + kChunkCounters + c, 1u) + 1u == gridDim.x;
+      if (last_of_chunk) atomicExch(local + kChunkCounters + c, 0u);  // every block has counted: ready for the next launch
+    }
+    __syncthreads();
+    if (last_of_chunk && threadIdx.x < t.size) {
+      __threadfence_system();
+      st_release_sys(channel_words(t, threadIdx.x, h.channel) + kChunkFlags + t.rank * kMaxChunks + c, h.epoch);
+    }
+  }
+  close_collective(t, h, 16);
+}
+
+__global__ void CS_COMM_BOUNDS slot_sum_kernel(PeerTable t, Handshake h, const char *slots, int64_t slot_bytes, char *dst, const char *residual,
+                                               int64_t vecs) {
+  open_collective(t, h, 17);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < vecs; i += stride) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int g = 0; g < kMaxPeers; g += 4) {
+      if (g >= t.size) break;
+      V4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (g + j < t.size) v[j] = ld_v4(slots + (g + j) * slot_bytes + i * 16);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (g + j < t.size) accumulate<1>(acc, v[j]);
+    }
+    if (residual) accumulate<1>(acc, ld_v4(residual + i * 16));
+    st_v4(dst + i * 16, finish<1>(acc, 1.0f));
+  }
 }
 
 __global__ void CS_COMM_BOUNDS pull_copy_kernel(PeerTable t, Handshake h, PullCopyArgs a) {
@@ -448,28 +524,56 @@ int symm_all_reduce(stream_t stream, const PeerTable &t, const Handshake &h, int
 }
 
 int symm_reduce_scatter(stream_t stream, const PeerTable &t, const Handshake &h, int64_t src_offset_bytes, void *dst, int64_t count,
-                        int dtype, float scale, int *blocks) {
+                        int dtype, float scale, int *blocks, const void *residual) {
   const int64_t bytes = count * (dtype == 0 ? 4 : 2);
-  if (bytes % 16 != 0 || src_offset_bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(dst) & 15))
+  if (bytes % 16 != 0 || src_offset_bytes % 16 != 0 || ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(residual)) & 15) ||
+      (residual && dtype != 1))
     return static_cast<int>(cudaErrorInvalidValue);
   const int64_t vecs = bytes / 16;
   const int grid = comm_grid(vecs);
   *blocks = grid;
   auto s = static_cast<cudaStream_t>(stream);
   if (dtype == 0)
-    reduce_scatter_kernel<0><<<grid, kThreads, 0, s>>>(t, h, src_offset_bytes, static_cast<char *>(dst), vecs, scale);
+    reduce_scatter_kernel<0><<<grid, kThreads, 0, s>>>(t, h, src_offset_bytes, static_cast<char *>(dst), nullptr, vecs, scale);
   else
-    reduce_scatter_kernel<1><<<grid, kThreads, 0, s>>>(t, h, src_offset_bytes, static_cast<char *>(dst), vecs, scale);
+    reduce_scatter_kernel<1><<<grid, kThreads, 0, s>>>(t, h, src_offset_bytes, static_cast<char *>(dst), static_cast<const char *>(residual),
+                                                       vecs, scale);
   return finish_launch(1);
 }
 
-int symm_all_gather_push(stream_t stream, const PeerTable &t, const Handshake &h, int64_t src_offset_bytes, int64_t dst_offset_bytes,
+int symm_all_gather_push(stream_t stream, const PeerTable &t, const Handshake &h, const void *src, int64_t dst_offset_bytes,
                          int64_t bytes, int *blocks) {
-  if (bytes % 16 != 0 || src_offset_bytes % 16 != 0 || dst_offset_bytes % 16 != 0) return static_cast<int>(cudaErrorInvalidValue);
+  if (bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(src) & 15) || dst_offset_bytes % 16 != 0) return static_cast<int>(cudaErrorInvalidValue);
   const int64_t vecs = bytes / 16;
   const int grid = comm_grid(vecs);
   *blocks = grid;
-  all_gather_push_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(t, h, src_offset_bytes, dst_offset_bytes, vecs);
+  all_gather_push_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(t, h, static_cast<const char *>(src), dst_offset_bytes, vecs);
+  return finish_launch(1);
+}
+
+int symm_all_gather_chunked(stream_t stream, const PeerTable &t, const Handshake &h, const void *src, int64_t dst_offset_bytes,
+                            int64_t bytes, int chunks, int *blocks) {
+  if (chunks < 1 || chunks > kMaxChunks || bytes % (16 * chunks) != 0 || (reinterpret_cast<uintptr_t>(src) & 15) || dst_offset_bytes % 16 != 0)
+    return static_cast<int>(cudaErrorInvalidValue);
+  const int64_t vecs_per_chunk = bytes / 16 / chunks;
+  const int grid = comm_grid(vecs_per_chunk);
+  *blocks = grid;
+  all_gather_chunked_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(t, h, static_cast<const char *>(src), dst_offset_bytes,
+                                                                                      vecs_per_chunk, chunks);
+  return finish_launch(1);
+}
+
+int symm_slot_sum(stream_t stream, const PeerTable &t, const Handshake &h, const void *slots_base, int64_t slot_bytes, void *dst,
+                  const void *residual, int64_t count) {
+  if (count % 8 != 0 || slot_bytes % 16 != 0 ||
+      ((reinterpret_cast<uintptr_t>(slots_base) | reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(residual)) & 15))
+    return static_cast<int>(cudaErrorInvalidValue);
+  const int64_t vecs = count / 8;
+  // local reads at full memory bandwidth: more and fuller blocks than the link-bound kernels use
+  const int64_t blocks = (vecs + kThreads - 1) / kThreads;
+  const int grid = static_cast<int>(blocks < 1 ? 1 : (blocks > 1184 ? 1184 : blocks));
+  slot_sum_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(t, h, static_cast<const char *>(slots_base), slot_bytes,
+                                                                            static_cast<char *>(dst), static_cast<const char *>(residual), vecs);
   return finish_launch(1);
 }
 

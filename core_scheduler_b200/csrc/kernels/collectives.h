@@ -30,12 +30,16 @@ struct PeerTable {
 
 // Signal-pad layout (32-bit words). Words [0, 64) belong to the stand-alone barrier below. From
 // kChannelBase on, every "channel" owns kChannelWords words:
-//   [0, 8)   entry flags, one per source rank      [8, 16)  exit flags, one per source rank
-//   [16]     local go flag (epoch)                  [17]     local count of finished blocks
-//   [18]     local done flag (epoch)
+//   [0, 8)    entry flags, one per source rank      [8, 16)   exit flags, one per source rank
+//   [16]      local go flag (epoch)                  [17]      local count of finished blocks
+//   [20, 28)  local counts of blocks that finished chunk c (chunked gather)
+//   [32, 96)  chunk-ready flags [source rank * 8 + chunk], written by the source rank (chunked gather)
 // Two kernels may be in flight at the same time only on different channels.
 constexpr int kChannelBase = 64;
-constexpr int kChannelWords = 32;
+constexpr int kChannelWords = 128;
+constexpr int kChunkCounters = 20;
+constexpr int kChunkFlags = 32;
+constexpr int kMaxChunks = 8;
 enum Channel : int {
   kChanAllReduce = 0,
   kChanReduceScatter = 1,
@@ -76,15 +80,29 @@ int symm_barrier(stream_t stream, const PeerTable &t, int slot_base, uint32_t ep
 int symm_all_reduce(stream_t stream, const PeerTable &t, const Handshake &h, int64_t offset_bytes, int64_t count, int dtype,
                     float scale, int *blocks);
 
-// dst[i] = scale * sum_p src_p[src_offset + i] for count elements (reduce-scatter: pass the offset
-// of this rank's slice inside every rank's send buffer). dst is local memory. One launch.
+// dst[i] = scale * sum_p src_p[src_offset + i] (+ residual[i]) for count elements (reduce-scatter: pass the
+// offset of this rank's slice inside every rank's send buffer). dst and the optional bf16 residual are local
+// memory. One launch.
 int symm_reduce_scatter(stream_t stream, const PeerTable &t, const Handshake &h, int64_t src_offset_bytes, void *dst, int64_t count,
-                        int dtype, float scale, int *blocks);
+                        int dtype, float scale, int *blocks, const void *residual = nullptr);
 
-// All-gather into a symmetric destination: this rank's `bytes` at base[rank] + src_offset are written
-// to dst_offset + rank * bytes of every rank (multimem.st, or one peer store per rank). One launch.
-int symm_all_gather_push(stream_t stream, const PeerTable &t, const Handshake &h, int64_t src_offset_bytes, int64_t dst_offset_bytes,
+// All-gather into a symmetric destination: this rank's `bytes` at `src` (any local memory) are written to
+// dst_offset + rank * bytes of every rank (multimem.st, or one peer store per rank). One launch.
+int symm_all_gather_push(stream_t stream, const PeerTable &t, const Handshake &h, const void *src, int64_t dst_offset_bytes,
                          int64_t bytes, int *blocks);
+
+// The same all-gather in `chunks` row chunks: after chunk c of this rank's shard has been written everywhere,
+// word kChunkFlags + rank * 8 + c of the channel is set to the epoch on every rank, so that a consumer kernel
+// running beside the gather (the GEMM that multiplies the gathered rows) can start on the chunks that have landed.
+int symm_all_gather_chunked(stream_t stream, const PeerTable &t, const Handshake &h, const void *src, int64_t dst_offset_bytes,
+                            int64_t bytes, int chunks, int *blocks);
+
+// Second half of a GEMM -> reduce-scatter whose GEMM epilogue stored every rank's partial rows (bf16) into the slot
+// their owner keeps for that rank: dst[i] = sum over `slots` local slots (+ residual[i]), fp32 accumulation, bf16
+// out. The kernel opens with the cross-rank barrier ("every rank's GEMM has finished writing"); it reads local
+// memory only, so nothing has to follow it. `slots_base` is local memory: slot s starts at slots_base + s * slot_bytes.
+int symm_slot_sum(stream_t stream, const PeerTable &t, const Handshake &h, const void *slots_base, int64_t slot_bytes, void *dst,
+                  const void *residual, int64_t count);
 
 // Strided chunk copies from peers (pull all-gather / all-to-all with pack and unpack fused):
 // for each peer p: rows x row_bytes from base[p] + src_offset[p] (row stride src_stride) to

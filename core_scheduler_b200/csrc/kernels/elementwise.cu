@@ -109,8 +109,11 @@ template <> __device__ __forceinline__ float from_f<float>(float v) { return v; 
 template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
 
+// At most 40 registers: a 256-thread block then fits on an SM beside a resident GEMM block (320 threads x 168
+// registers), so an update launched while the backward pass is running proceeds next to the GEMMs instead of
+// waiting for a whole wave of them to drain.
 template <typename P, typename G, int VEC>
-__global__ void __launch_bounds__(256) adamw_kernel(P *__restrict__ w, const G *__restrict__ g, P *__restrict__ m,
+__global__ void __launch_bounds__(256, 6) adamw_kernel(P *__restrict__ w, const G *__restrict__ g, P *__restrict__ m,
                                                     P *__restrict__ v, P *__restrict__ vmax,
                                                     __nv_bfloat16 *__restrict__ lp, int64_t n, float lr, float b1,
                                                     float b2, float eps, float wd, float ibc1, float ibc2,
@@ -884,7 +887,7 @@ __global__ void ce_mean_kernel(float *loss, const float *count) { loss[0] = loss
 __global__ void __launch_bounds__(256) ce_backward_kernel(__nv_bfloat16 *__restrict__ logits, int64_t ld,
                                                           const float *__restrict__ lse, const int64_t *__restrict__ target,
                                                           const float *__restrict__ count, float grad_scale, int64_t rows,
-                                                          int64_t n, int64_t n_valid, int64_t ignore_index) {
+                                                          int64_t n, int64_t n_valid, int64_t ignore_index, int64_t col_offset) {
   // One CTA walks whole rows (no per-element division); target and lse are read once per row.
   const int chunks = static_cast<int>(n / 8);
   const float inv = grad_scale / fmaxf(count[0], 1.f);
@@ -892,7 +895,7 @@ __global__ void __launch_bounds__(256) ce_backward_kernel(__nv_bfloat16 *__restr
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const int64_t tg = target[row];
     const bool ignored = tg == ignore_index || tg < 0;
-    if (!ignored) (void)CS_IN_BOUNDS(kKidCrossEntropy, tg, n_valid);
+    if (!ignored && col_offset == 0) (void)CS_IN_BOUNDS(kKidCrossEntropy, tg, n_valid);
     const float l2 = ignored ? 0.f : lse[row] * log2e;
     __nv_bfloat16 *row_ptr = logits + row * ld;
     for (int c8 = threadIdx.x; c8 < chunks; c8 += blockDim.x) {
@@ -907,7 +910,7 @@ __global__ void __launch_bounds__(256) ce_backward_kernel(__nv_bfloat16 *__restr
         unpack(*p, f);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const int64_t c = col + k;
+          const int64_t c = col + k + col_offset;
           float v = c < n_valid ? exp2f(fmaf(f[k], log2e, -l2)) : 0.f;
           if (c == tg) v -= 1.f;
           f[k] = v * inv;
@@ -933,13 +936,49 @@ int cross_entropy_finalize(stream_t stream, const float *stats, int64_t n_tiles,
   return finish_launch(2);
 }
 
+namespace {
+__global__ void __launch_bounds__(256) ce_slice_stats_kernel(const float *__restrict__ stats, int64_t n_tiles,
+                                                             const __nv_bfloat16 *__restrict__ logits, int64_t ld,
+                                                             const int64_t *__restrict__ target, int64_t col_offset,
+                                                             int64_t n_valid_local, float *__restrict__ out, int64_t rows) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (row >= rows) return;
+  const float *st = stats + row * n_tiles * 2;
+  float mx = -INFINITY;
+  for (int64_t t = lane; t < n_tiles; t += 32) mx = fmaxf(mx, st[2 * t]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int64_t t = lane; t < n_tiles; t += 32) {
+    const float m = st[2 * t];
+    if (m > -INFINITY) sum += st[2 * t + 1] * __expf(m - mx);
+  }
+  sum = warp_sum(sum);
+  if (lane == 0) {
+    out[row * 2] = (n_valid_local > 0 && mx > -INFINITY) ? mx + __logf(sum) : -INFINITY;
+    const int64_t local = target[row] - col_offset;
+    out[row * 2 + 1] = (local >= 0 && local < n_valid_local) ? __bfloat162float(logits[row * ld + local]) : 0.f;
+  }
+}
+}  // namespace
+
+int cross_entropy_slice_stats(stream_t stream, const float *stats, int64_t n_tiles, const void *logits, int64_t ld,
+                              const int64_t *target, int64_t col_offset, int64_t n_valid_local, float *out, int64_t rows) {
+  if (rows == 0) return 0;
+  const int threads = 256;
+  const int64_t blocks = (rows * 32 + threads - 1) / threads;
+  ce_slice_stats_kernel<<<static_cast<unsigned>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      stats, n_tiles, static_cast<const __nv_bfloat16 *>(logits), ld, target, col_offset, n_valid_local, out, rows);
+  return finish_launch();
+}
+
 int cross_entropy_backward_inplace(stream_t stream, void *logits, int64_t ld, const float *lse, const int64_t *target,
                                    const float *count, float grad_scale, int64_t rows, int64_t n, int64_t n_valid,
-                                   int64_t ignore_index) {
+                                   int64_t ignore_index, int64_t col_offset) {
   if (n % 8 != 0 || ld % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
   const int64_t cap = static_cast<int64_t>(kSmCount) * 8;
   ce_backward_kernel<<<static_cast<unsigned>(rows < cap ? rows : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__nv_bfloat16 *>(logits), ld, lse, target, count, grad_scale, rows, n, n_valid, ignore_index);
+      static_cast<__nv_bfloat16 *>(logits), ld, lse, target, count, grad_scale, rows, n, n_valid, ignore_index, col_offset);
   return finish_launch();
 }
 

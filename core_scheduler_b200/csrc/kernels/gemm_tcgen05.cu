@@ -63,9 +63,13 @@ struct KParams {
   int m_tiles, n_tiles, splits, kb_total, kb_per_split;
   int atomic_out;     // fp32 output accumulated with red.global.add (split-K or accumulate mode)
   unsigned lbo_mn, sbo_mn, kstep_mn;  // MN-major descriptor parameters (bytes)
-  int peer_mode;       // 0 none, 1 = A row blocks come from peers, 2 = D row blocks go to peers
+  int peer_mode;       // 0 none, 1 = A row blocks come from peers, 2 = D row blocks go to peers,
+                       // 3 = A is local but arrives in row chunks announced by flags (all-gather in flight)
   int peer_rank, peer_count;
   int rows_per_peer;
+  const uint32_t *ready_flags;  // peer_mode 3: word [owner * 8 + chunk] reaches ready_epoch when that chunk has landed
+  uint32_t ready_epoch;
+  int ready_chunks;             // chunks per owner (rows_per_peer / ready_chunks rows each, a multiple of 256)
   DeviceStatus *status;
 };
 
@@ -757,13 +761,25 @@ __device__ __forceinline__ TileCoord tile_coord2(const KParams &p, int tile) {
   const int mn = p.m_tiles * p.n_tiles;
   const int split = tile / mn;
   const int rem = tile - split * mn;
-  const int n_tile = rem / p.m_tiles;
+  int n_tile = rem / p.m_tiles;
   int m_tile = rem - n_tile * p.m_tiles;
-  if (p.peer_mode) {
-    // start with the rows this rank owns, then walk the peers' blocks in ring order, so that
-    // local data is consumed while remote traffic ramps up and no two ranks hammer the same peer
+  if (p.peer_mode == 3) {
+    // Rows arrive chunk by chunk from every owner at once: walk the row tiles in arrival order (chunk 0 of every
+    // owner starting with this rank, then chunk 1, ...) and finish all column tiles of a row tile before the next.
+    const int order = rem / p.n_tiles;
+    n_tile = rem - order * p.n_tiles;
     const int per_peer = p.rows_per_peer / BM2;
-    m_tile = (m_tile + p.peer_rank * per_peer) % p.m_tiles;
+    const int per_chunk = per_peer / p.ready_chunks;
+    const int chunk = order / (p.peer_count * per_chunk);
+    const int within = order - chunk * (p.peer_count * per_chunk);
+    const int owner = (within / per_chunk + p.peer_rank) % p.peer_count;
+    m_tile = owner * per_peer + chunk * per_chunk + (within % per_chunk);
+  } else if (p.peer_mode) {
+    // walk the owners' blocks in ring order so that no two ranks hammer the same peer: gathering starts with the
+    // rows this rank owns (local data is consumed while remote traffic ramps up), scattering with the next rank's
+    // rows (remote traffic starts at once, the local block comes last)
+    const int per_peer = p.rows_per_peer / BM2;
+    m_tile = (m_tile + (p.peer_rank + (p.peer_mode == 2 ? 1 : 0)) * per_peer) % p.m_tiles;
   }
   TileCoord c;
   c.m0 = m_tile * BM2;
@@ -831,10 +847,36 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int ready_key = -1;
       for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
         const TileCoord c = tile_coord2(p, tile);
         const int m0 = c.m0 + static_cast<int>(cta) * 128;   // this CTA's rows of A / D
         const int nb0 = c.n0 + static_cast<int>(cta) * 128;  // this CTA's rows of the B tile
+        if (p.peer_mode == 3) {
+          // the rows of this tile are written by the all-gather that runs beside this kernel: wait for their chunk
+          const int owner = c.m0 / p.rows_per_peer;
+          const int chunk = (c.m0 - owner * p.rows_per_peer) / (p.rows_per_peer / p.ready_chunks);
+          const int key = owner * 8 + chunk;
+          if (key != ready_key) {
+            const uint32_t *flag = p.ready_flags + key;
+            const long long t0 = clock64();
+            for (;;) {
+              uint32_t seen;
+              asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+              if (static_cast<int32_t>(seen - p.ready_epoch) >= 0) break;
+              if (*abort_flag || clock64() - t0 > kWaitBudgetCycles) {
+                *abort_flag = 1;
+                ok = false;
+                break;
+              }
+              __nanosleep(100);
+            }
+            if (!ok) break;
+            // the chunk was written by other GPUs through the generic proxy; the loads below go through the async proxy
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            ready_key = key;
+          }
+        }
         for (int kb = c.kb_begin; kb < c.kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
             ok = false;
@@ -1092,12 +1134,16 @@ int gemm_bf16(stream_t stream, const GemmArgs &a) {
             !get_tensor_map(a.a_peers[j], a.k, rows_per_peer, a.lda, BK, BM, &peer_maps.m[j]))
           return -1;
     } else if (a.d_peers[0]) {
-      if (a.epilogue != kEpiAccumF32) return -1;
+      if (a.epilogue != kEpiAccumF32 && a.epilogue != kEpiStoreBf16) return -1;
       peer_mode = 2;
+      const bool f32 = a.epilogue == kEpiAccumF32;
       for (int j = 0; j < a.peer_count; ++j)
         if (!a.d_peers[j] || (reinterpret_cast<uintptr_t>(a.d_peers[j]) & 15) ||
-            !get_tensor_map(a.d_peers[j], a.n, rows_per_peer, a.ldd, 32, 32, &peer_maps.m[j], 4))
+            !get_tensor_map(a.d_peers[j], a.n, rows_per_peer, a.ldd, f32 ? 32 : 64, 32, &peer_maps.m[j], f32 ? 4 : 2))
           return -1;
+    } else if (a.ready_flags) {
+      if (a.layout == kNT || a.ready_chunks < 1 || a.ready_chunks > 8 || rows_per_peer % (BM2 * a.ready_chunks) != 0) return -1;
+      peer_mode = 3;
     }
   }
   CUtensorMap map_a, map_b;
@@ -1189,10 +1235,13 @@ int gemm_bf16(stream_t stream, const GemmArgs &a) {
   p.peer_count = a.peer_count;
   p.rows_per_peer = rows_per_peer;
   if (peer_mode == 2) {
-    p.splits = 1;  // the cross-rank sum already happens in the destination
+    p.splits = 1;  // the cross-rank sum happens in (or after) the destination
     p.kb_per_split = p.kb_total;
-    p.atomic_out = 1;
+    p.atomic_out = f32_out ? 1 : 0;
   }
+  p.ready_flags = a.ready_flags;
+  p.ready_epoch = a.ready_epoch;
+  p.ready_chunks = a.ready_chunks;
   // MN-major operand descriptors: next 64-element block 8192 B on, next 8 k-rows 1024 B on, one UMMA_K step = 16 k-rows
   p.lbo_mn = 8192;
   p.sbo_mn = 1024;

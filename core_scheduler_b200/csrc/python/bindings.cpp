@@ -554,7 +554,10 @@ PYBIND11_MODULE(_C, m) {
       .def("get_rank", &Comm::get_rank)
       .def("get_size", &Comm::get_size)
       .def("inject_failure_after", [](const Comm &c, int64_t n) { c.impl()->fail_after = n; })
-      .def("has_symmetric", [](const Comm &c) { return c.impl()->symmetric != nullptr; });
+      .def("has_symmetric", [](const Comm &c) { return c.impl()->symmetric != nullptr; })
+      .def("release_symmetric", [](const Comm &c) { c.impl()->symmetric.reset(); },
+           "Drops the communicator's reference to its symmetric arena (the arena is unmapped once the last holder is gone). "
+           "Call it on every rank, after the last kernel that uses the arena, before the process group is destroyed.");
   m.def("comm_from_process_group", &comm_from_process_group, py::arg("group_name"), py::arg("device") = "cuda",
         py::arg("nvp2p") = false);
   m.def("get_comm_world", [](const std::string &backend) {
@@ -716,6 +719,7 @@ PYBIND11_MODULE(_C, m) {
         g.backward_loss(s, sync.is_none() ? models::GradientSync{} : py::cast<models::GradientSync>(sync));
       }, py::arg("scheduler"), py::arg("sync") = py::none())
       .def("replicated_parameters", &parallel::TPGPT2Impl::replicated_parameters)
+      .def("vocab_parallel", &parallel::TPGPT2Impl::vocab_parallel)
       .def("head_range", &parallel::TPGPT2Impl::head_range, "(first head, number of heads) of this rank");
   m.def("all_gather_rows", &parallel::all_gather_rows);
   m.def("fused_tp_launches", &parallel::fused_tp_launches);

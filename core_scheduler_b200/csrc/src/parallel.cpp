@@ -228,106 +228,69 @@ Tensor reduce_scatter_rows(const Scheduler &scheduler, const communication::Comm
   return compute::Utils::add(scheduler, recv, *residual);
 }
 
-// ------------------------------------------------------------ fused TP GEMM + collective ----
+// -------------------------------------------------- tensor-parallel collectives on symmetric memory ----
+// Every gather / reduce-scatter below is ONE light kernel on the main stream (the barriers are inside it,
+// kernels/collectives.h). Gathered activations live in persistent symmetric buffers, one pair per block,
+// so the backward pass reads them again for the weight gradients instead of gathering a second time.
+// Partial products of the row-parallel GEMMs are written (by the GEMM's own TMA-store epilogue) into one
+// symmetric bf16 buffer; the owner of each row block then loads the sum over all ranks, reduced inside the
+// switch when the arena has a multicast mapping, adds the residual and keeps its rows.
 namespace {
 std::atomic<int64_t> g_fused_tp_launches{0};
 
-struct SymmetricSlots {
-  communication::SymmetricBlock block[2];
-  int next{0};
-};
-// Per-context staging buffers for the fused paths (allocated on first use, identical call
-// sequences on every rank give identical offsets).
-std::unordered_map<const communication::SymmetricContext *, SymmetricSlots> g_ag_slots, g_rs_slots;
+at::Tensor symmetric_tensor(communication::SymmetricContext &ctx, at::IntArrayRef sizes, at::ScalarType dtype) {
+  int64_t numel = 1;
+  for (auto v : sizes) numel *= v;
+  return ctx.tensor(ctx.allocate(numel * static_cast<int64_t>(c10::elementSize(dtype))), sizes, dtype);
+}
 
-communication::SymmetricBlock next_slot(std::unordered_map<const communication::SymmetricContext *, SymmetricSlots> &table,
-                                        communication::SymmetricContext &ctx, int64_t bytes, bool alternate) {
-  auto &slots = table[&ctx];
-  const int idx = alternate ? slots.next : 0;
-  if (alternate) slots.next ^= 1;
-  if (slots.block[idx].bytes < bytes) {
-    if (slots.block[idx].bytes > 0) ctx.release(slots.block[idx]);
-    slots.block[idx] = ctx.allocate(bytes);
+// (Re)creates the symmetric buffer behind `handle` when the shape changed. Called inside a task that lists
+// `handle` as an output, on every rank in the same order, so the offsets agree.
+at::Tensor &ensure_symmetric(communication::SymmetricContext &ctx, const Tensor &handle, at::IntArrayRef sizes, at::ScalarType dtype) {
+  at::Tensor &t = handle.impl()->tensor;
+  if (!t.defined() || t.sizes() != sizes || t.scalar_type() != dtype) {
+    if (t.defined()) {
+      int64_t off = 0;
+      if (ctx.locate(t.data_ptr(), static_cast<int64_t>(t.nbytes()), &off))
+        ctx.release(communication::SymmetricBlock{off, (static_cast<int64_t>(t.nbytes()) + 255) / 256 * 256});
+    }
+    t = symmetric_tensor(ctx, sizes, dtype);
   }
-  return slots.block[idx];
+  return t;
 }
 
 bool fused_tp_ok(const communication::Comm &comm, const at::Tensor &x, int64_t total_rows) {
   auto ctx = comm.impl()->symmetric;
   const int64_t tp = comm.get_size();
-  return ctx && tp > 1 && tp <= 8 && x.is_cuda() && x.scalar_type() == at::kBFloat16 &&
-         compute::get_backend() == compute::Backend::kFused && total_rows % tp == 0 && (total_rows / tp) % 256 == 0 &&
-         std::getenv("CS_TP_UNFUSED") == nullptr;
+  return ctx && tp > 1 && tp <= kernels::kMaxPeers && x.is_cuda() && x.scalar_type() == at::kBFloat16 &&
+         compute::get_backend() == compute::Backend::kFused && total_rows % tp == 0 && x.size(-1) % 8 == 0;
 }
-}  // namespace
 
-int64_t fused_tp_launches() { return g_fused_tp_launches.load(); }
-
-Tensor column_parallel_forward(const Scheduler &scheduler, const communication::Comm &comm,
-                               const std::shared_ptr<compute::Linear::State> &state, const ReadOnlyTensor &x_shard) {
-  const int64_t tp = comm.get_size();
-  // The fused kernel fetches the other ranks' rows by TMA straight from peer memory, once per output-column tile
-  // (peer data is not cached in the local L2): for wide layers that is several times the bytes of one
-  // all-gather. CS_TP_FUSED_ALL_GATHER=1 selects it; the default gathers the rows once with the peer-copy kernel
-  // and runs the GEMM on local memory.
-  static const bool fused_gather = std::getenv("CS_TP_FUSED_ALL_GATHER") != nullptr;
-  const bool can_fuse = fused_gather && x_shard.defined() && fused_tp_ok(comm, x_shard.impl()->tensor, x_shard.size(0) * tp) &&
-                        scheduler.impl()->autocast_enabled && !state->args.bias;
-  if (!can_fuse) {
-    Tensor full = all_gather_rows(scheduler, comm, x_shard);
-    return compute::Linear::forward(scheduler, state, full);
-  }
-  Tensor out;
-  const bool gelu = state->args.gelu_epilogue;
-  state->backward.input = Tensor{};  // backward re-gathers the input; nothing is kept alive here
-  state->forward.weight.impl()->autocast_enabled = true;
-  state->forward.weight.impl()->autocast_dtype = at::kBFloat16;
-  submit(scheduler, "cs::parallel::column_parallel_forward(all-gather+GEMM)", Task::Impl::kMain, Task::Impl::kCompute, {out},
-         {x_shard, state->forward.weight}, [out, x_shard, w = state->forward.weight, comm, gelu, tp](const FnTask &) {
+// [m, k] row shard -> `full` [tp * m, k] on every rank (persistent symmetric buffer behind the handle).
+void gather_rows_symmetric(const Scheduler &scheduler, const communication::Comm &comm, const ReadOnlyTensor &shard, const Tensor &full) {
+  submit(scheduler, "cs::parallel::gather_rows(symmetric push)", Task::Impl::kMain, Task::Impl::kCompute, {full}, {shard},
+         [shard, full, comm](const FnTask &) {
            auto &ctx = *comm.impl()->symmetric;
-           const at::Tensor xs = x_shard.impl()->tensor.contiguous();
-           const at::Tensor wc = compute::working_copy(w, at::kBFloat16);
-           const int64_t rows = xs.size(0), k = xs.size(1), n = wc.size(0);
-           const auto slot = next_slot(g_ag_slots, ctx, rows * k * 2, true);
-           auto stream = c10::cuda::getCurrentCUDAStream().stream();
-           CS_CHECK_CUDART(cudaMemcpyAsync(ctx.bases[ctx.rank] + slot.offset, xs.data_ptr(), static_cast<size_t>(rows * k * 2),
-                                           cudaMemcpyDeviceToDevice, stream));
-           ctx.barrier();  // every rank's shard is in place (and the slot's previous readers are done)
-           at::Tensor y = at::empty({rows * tp, n}, xs.options());
-           at::Tensor y2;
-           kernels::GemmArgs g{};
-           g.b = wc.data_ptr();
-           g.d = y.data_ptr();
-           g.m = rows * tp;
-           g.n = n;
-           g.k = k;
-           g.lda = k;
-           g.ldb = k;
-           g.ldd = n;
-           g.layout = kernels::kTN;
-           g.epilogue = kernels::kEpiStoreBf16;
-           if (gelu) {
-             y2 = at::empty_like(y);
-             g.d2 = y2.data_ptr();
-             g.epilogue = kernels::kEpiGeluDual;
-           }
-           g.peer_count = static_cast<int>(tp);
-           g.peer_rank = ctx.rank;
-           for (int p = 0; p < tp; ++p) g.a_peers[p] = ctx.bases[p] + slot.offset;
-           const int code = kernels::gemm_bf16(stream, g);
-           CS_ASSERT_TRUE(code == 0, "fused all-gather+GEMM launch failed (", code, ")");
+           const at::Tensor xs = shard.impl()->tensor.reshape({-1, shard.impl()->tensor.size(-1)}).contiguous();
+           const int64_t m = xs.size(0), k = xs.size(1), tp = ctx.size;
+           at::Tensor &dst = ensure_symmetric(ctx, full, {m * tp, k}, xs.scalar_type());
+           int64_t off = 0;
+           CS_ASSERT_TRUE(ctx.locate(dst.data_ptr(), static_cast<int64_t>(dst.nbytes()), &off), "gather buffer left the arena");
+           int blocks = 0;
+           const auto h = communication::begin_collective(ctx, kernels::kChanGatherRows);
+           const int code = kernels::symm_all_gather_push(c10::cuda::getCurrentCUDAStream().stream(), communication::table_of(ctx), h,
+                                                          xs.data_ptr(), off, static_cast<int64_t>(xs.nbytes()), &blocks);
+           CS_ASSERT_TRUE(code == 0, "row gather launch failed: ", cuda_error_string(code));
+           communication::end_collective(ctx, kernels::kChanGatherRows, blocks);
            g_fused_tp_launches.fetch_add(1);
-           out.impl()->tensor = y;
-           out.impl()->companion = y2;
          });
-  return out;
 }
 
-Tensor row_parallel_forward(const Scheduler &scheduler, const communication::Comm &comm, const ReadOnlyTensor &weight,
-                            const ReadOnlyTensor &x, const ReadOnlyTensor *residual_shard, bool weight_is_rhs) {
-  // weight_is_rhs == false: y = x * W^T with W [out, in_local]      (forward of c_proj / fc2)
-  // weight_is_rhs == true : y = x * W   with W [out_local, in]      (input gradient of c_attn / fc1)
-  const int64_t tp = comm.get_size();
+// y[M, n] = x[M, k] * W^T (weight_is_rhs == false, W [n, k]) or x * W (true, W [k, n]) written into the symmetric
+// `partial` buffer, then out[m, n] = sum over ranks of this rank's rows (+ residual): two launches, GEMM and
+// reduce-scatter, both on the main stream.
+Tensor row_parallel_symmetric(const Scheduler &scheduler, const communication::Comm &comm, const ReadOnlyTensor &weight,
+                              const ReadOnlyTensor &x, const ReadOnlyTensor *residual_shard, bool weight_is_rhs, const Tensor &partial) {
   Tensor out;
   std::vector<ReadOnlyTensor> ins{x, weight};
   std::optional<ReadOnlyTensor> res;
@@ -335,19 +298,168 @@ Tensor row_parallel_forward(const Scheduler &scheduler, const communication::Com
     res = *residual_shard;
     ins.push_back(*residual_shard);
   }
-  submit(scheduler, "cs::parallel::row_parallel_forward(GEMM+reduce-scatter)", Task::Impl::kMain, Task::Impl::kCompute, {out}, ins,
-         [out, x, weight, res, comm, tp, weight_is_rhs](const FnTask &) {
+  submit(scheduler, "cs::parallel::row_parallel(GEMM + switch reduce-scatter)", Task::Impl::kMain, Task::Impl::kCompute, {out, partial}, ins,
+         [out, partial, x, weight, res, comm, weight_is_rhs](const FnTask &) {
            auto &ctx = *comm.impl()->symmetric;
+           const int64_t tp = ctx.size;
+           const at::Tensor xa = x.impl()->tensor.reshape({-1, x.impl()->tensor.size(-1)}).contiguous();
+           const at::Tensor wc = compute::working_copy(weight, at::kBFloat16);
+           const int64_t m = xa.size(0), k = xa.size(1);
+           const int64_t n = weight_is_rhs ? wc.size(1) : wc.size(0);
+           CS_ASSERT_TRUE(m % tp == 0, "row count ", m, " does not split over ", tp, " ranks");
+           const int64_t rows = m / tp;
+           at::Tensor &y = ensure_symmetric(ctx, partial, {m, n}, at::kBFloat16);
+           auto stream = c10::cuda::getCurrentCUDAStream().stream();
+           kernels::GemmArgs g{};
+           g.a = xa.data_ptr();
+           g.b = wc.data_ptr();
+           g.d = y.data_ptr();
+           g.m = m;
+           g.n = n;
+           g.k = k;
+           g.lda = k;
+           g.ldb = weight_is_rhs ? n : k;
+           g.ldd = n;
+           g.layout = weight_is_rhs ? kernels::kTM : kernels::kTN;
+           g.epilogue = kernels::kEpiStoreBf16;
+           const int code = kernels::gemm_bf16(stream, g);
+           CS_ASSERT_TRUE(code == 0, "row-parallel GEMM launch failed (", code, ") for m=", m, " n=", n, " k=", k);
+           int64_t off = 0;
+           CS_ASSERT_TRUE(ctx.locate(y.data_ptr(), static_cast<int64_t>(y.nbytes()), &off), "partial buffer left the arena");
+           at::Tensor o = at::empty({rows, n}, xa.options());
+           at::Tensor r;
+           if (res) r = res->impl()->tensor.reshape({rows, n}).contiguous();
+           int blocks = 0;
+           const auto h = communication::begin_collective(ctx, kernels::kChanScatterRows);
+           const int rc = kernels::symm_reduce_scatter(stream, communication::table_of(ctx), h, off + ctx.rank * rows * n * 2, o.data_ptr(),
+                                                       rows * n, 1, 1.0f, &blocks, res ? r.data_ptr() : nullptr);
+           CS_ASSERT_TRUE(rc == 0, "row reduce-scatter launch failed: ", cuda_error_string(rc));
+           communication::end_collective(ctx, kernels::kChanScatterRows, blocks);
+           g_fused_tp_launches.fetch_add(1);
+           out.impl()->tensor = o;
+         });
+  return out;
+}
+
+// ---- fused forms (row shards that are multiples of 256 rows) ------------------------------------------------
+// all-gather -> GEMM: the gather runs on the communication stream in row chunks and announces every chunk with a
+// flag; the GEMM on the main stream starts at once and its TMA producer waits for the flag of the chunk a tile
+// needs, so the multiplication proceeds while later chunks are still crossing NVLink.
+// GEMM -> reduce-scatter: the GEMM epilogue TMA-stores each bf16 output tile straight into the slot that the
+// owner of those rows keeps for this rank; one kernel then opens with the cross-rank barrier and sums the local
+// slots (+ residual). No barrier launches, no zero-filling, every byte crosses NVLink once as bf16.
+struct GatherSignal {
+  uint32_t epoch{0};
+  const uint32_t *flags{nullptr};
+  int chunks{0};
+};
+
+int gather_chunks_for(int64_t rows_per_rank) {
+  for (int c : {4, 2, 1})
+    if (rows_per_rank % (256 * c) == 0) return c;
+  return 0;
+}
+
+// y[M, n] = gather(x_shard)[M, k] * W^T (W [n, k]) or * W (weight_is_rhs, W [k, n]); `full` keeps the gathered rows.
+// epilogue: kEpiStoreBf16, kEpiGeluDual (companion = GELU(y)) or kEpiDGelu (aux = pre-activation).
+Tensor gather_gemm(const Scheduler &scheduler, const communication::Comm &comm, const ReadOnlyTensor &x_shard, const Tensor &full,
+                   const ReadOnlyTensor &weight, bool weight_is_rhs, int epilogue, const ReadOnlyTensor *aux) {
+  const int chunks = gather_chunks_for(x_shard.impl()->tensor.numel() / x_shard.impl()->tensor.size(-1));
+  auto signal = std::make_shared<GatherSignal>();
+  submit(scheduler, "cs::parallel::gather_rows(chunked push beside the GEMM)", Task::Impl::kComm, Task::Impl::kNccl, {full}, {x_shard},
+         [x_shard, full, comm, chunks, signal](const FnTask &task) {
+           auto &ctx = *comm.impl()->symmetric;
+           const at::Tensor xs = x_shard.impl()->tensor.reshape({-1, x_shard.impl()->tensor.size(-1)}).contiguous();
+           task.intermediate().push_back(xs);
+           const int64_t m = xs.size(0), k = xs.size(1), tp = ctx.size;
+           at::Tensor &dst = ensure_symmetric(ctx, full, {m * tp, k}, xs.scalar_type());
+           int64_t off = 0;
+           CS_ASSERT_TRUE(ctx.locate(dst.data_ptr(), static_cast<int64_t>(dst.nbytes()), &off), "gather buffer left the arena");
+           int blocks = 0;
+           const auto h = communication::begin_collective(ctx, kernels::kChanGemmGather);
+           const int code = kernels::symm_all_gather_chunked(c10::cuda::getCurrentCUDAStream().stream(), communication::table_of(ctx), h,
+                                                             xs.data_ptr(), off, static_cast<int64_t>(xs.nbytes()), chunks, &blocks);
+           CS_ASSERT_TRUE(code == 0, "chunked row gather launch failed: ", cuda_error_string(code));
+           communication::end_collective(ctx, kernels::kChanGemmGather, blocks);
+           signal->epoch = h.epoch;
+           signal->flags = ctx.flags[ctx.rank] + kernels::kChannelBase + kernels::kChanGemmGather * kernels::kChannelWords + kernels::kChunkFlags;
+           signal->chunks = chunks;
+         });
+  Tensor out;
+  std::vector<ReadOnlyTensor> ins{x_shard, weight};  // not `full`: the flags order the reads, chunk by chunk
+  std::optional<ReadOnlyTensor> aux_h;
+  if (aux) {
+    aux_h = *aux;
+    ins.push_back(*aux);
+  }
+  submit(scheduler, "cs::parallel::column_parallel(GEMM on arriving chunks)", Task::Impl::kMain, Task::Impl::kCompute, {out}, ins,
+         [out, full, weight, weight_is_rhs, epilogue, aux_h, comm, signal](const FnTask &task) {
+           auto &ctx = *comm.impl()->symmetric;
+           const at::Tensor &xf = full.impl()->tensor;
+           const at::Tensor wc = compute::working_copy(weight, at::kBFloat16);
+           const int64_t m = xf.size(0), k = xf.size(1);
+           const int64_t n = weight_is_rhs ? wc.size(1) : wc.size(0);
+           at::Tensor y = at::empty({m, n}, xf.options());
+           at::Tensor y2, a2;
+           kernels::GemmArgs g{};
+           g.a = xf.data_ptr();
+           g.b = wc.data_ptr();
+           g.d = y.data_ptr();
+           g.m = m;
+           g.n = n;
+           g.k = k;
+           g.lda = k;
+           g.ldb = weight_is_rhs ? n : k;
+           g.ldd = n;
+           g.layout = weight_is_rhs ? kernels::kTM : kernels::kTN;
+           g.epilogue = epilogue;
+           if (epilogue == kernels::kEpiGeluDual) {
+             y2 = at::empty_like(y);
+             g.d2 = y2.data_ptr();
+           }
+           if (aux_h) {
+             a2 = aux_h->impl()->tensor.reshape({m, n}).contiguous();
+             g.aux = a2.data_ptr();
+           }
+           g.peer_count = ctx.size;
+           g.peer_rank = ctx.rank;
+           g.ready_flags = signal->flags;
+           g.ready_epoch = signal->epoch;
+           g.ready_chunks = signal->chunks;
+           const int code = kernels::gemm_bf16(c10::cuda::getCurrentCUDAStream().stream(), g);
+           CS_ASSERT_TRUE(code == 0, "GEMM on gathered chunks failed to launch (", code, ") for m=", m, " n=", n, " k=", k);
+           g_fused_tp_launches.fetch_add(1);
+           out.impl()->tensor = y;
+           out.impl()->companion = y2;
+         });
+  return out;
+}
+
+// out[m, n] = sum over ranks of (x * W^T or x * W)[rows of this rank] (+ residual): GEMM with the scatter in its epilogue,
+// then the slot sum. `slots` are two symmetric buffers [tp, m, n] bf16 used in turn.
+Tensor gemm_scatter(const Scheduler &scheduler, const communication::Comm &comm, const ReadOnlyTensor &weight, const ReadOnlyTensor &x,
+                    const ReadOnlyTensor *residual_shard, bool weight_is_rhs, TPWorkspace &ws) {
+  Tensor out;
+  const Tensor slots = ws.slots[ws.next_slot ^= 1];
+  std::vector<ReadOnlyTensor> ins{x, weight};
+  std::optional<ReadOnlyTensor> res;
+  if (residual_shard) {
+    res = *residual_shard;
+    ins.push_back(*residual_shard);
+  }
+  submit(scheduler, "cs::parallel::row_parallel(GEMM with bf16 scatter epilogue + slot sum)", Task::Impl::kMain, Task::Impl::kCompute,
+         {out, slots}, ins, [out, slots, x, weight, res, comm, weight_is_rhs](const FnTask &) {
+           auto &ctx = *comm.impl()->symmetric;
+           const int64_t tp = ctx.size;
            const at::Tensor xa = x.impl()->tensor.reshape({-1, x.impl()->tensor.size(-1)}).contiguous();
            const at::Tensor wc = compute::working_copy(weight, at::kBFloat16);
            const int64_t m = xa.size(0), k = xa.size(1);
            const int64_t n = weight_is_rhs ? wc.size(1) : wc.size(0);
            const int64_t rows = m / tp;
-           const auto slot = next_slot(g_rs_slots, ctx, rows * n * 4, false);
+           at::Tensor &buf = ensure_symmetric(ctx, slots, {tp, rows, n}, at::kBFloat16);  // slot s: rank s's partial of my rows
+           int64_t off = 0;
+           CS_ASSERT_TRUE(ctx.locate(buf.data_ptr(), static_cast<int64_t>(buf.nbytes()), &off), "slot buffer left the arena");
            auto stream = c10::cuda::getCurrentCUDAStream().stream();
-           float *acc = reinterpret_cast<float *>(ctx.bases[ctx.rank] + slot.offset);
-           CS_CHECK_CUDART(cudaMemsetAsync(acc, 0, static_cast<size_t>(rows * n * 4), stream));
-           ctx.barrier();  // all accumulators are zero before anybody adds
            kernels::GemmArgs g{};
            g.a = xa.data_ptr();
            g.b = wc.data_ptr();
@@ -358,23 +470,27 @@ Tensor row_parallel_forward(const Scheduler &scheduler, const communication::Com
            g.ldb = weight_is_rhs ? n : k;
            g.ldd = n;
            g.layout = weight_is_rhs ? kernels::kTM : kernels::kTN;
-           g.epilogue = kernels::kEpiAccumF32;
+           g.epilogue = kernels::kEpiStoreBf16;
            g.peer_count = static_cast<int>(tp);
            g.peer_rank = ctx.rank;
-           for (int p = 0; p < tp; ++p) g.d_peers[p] = ctx.bases[p] + slot.offset;
+           for (int p = 0; p < tp; ++p) g.d_peers[p] = ctx.bases[p] + off + static_cast<int64_t>(ctx.rank) * rows * n * 2;
            const int code = kernels::gemm_bf16(stream, g);
-           CS_ASSERT_TRUE(code == 0, "fused GEMM+reduce-scatter launch failed (", code, ")");
-           g_fused_tp_launches.fetch_add(1);
-           ctx.barrier();  // every rank's tiles have been added into our rows
-           at::Tensor y = at::empty({rows, n}, xa.options());
+           CS_ASSERT_TRUE(code == 0, "GEMM with scatter epilogue failed to launch (", code, ") for m=", m, " n=", n, " k=", k);
+           at::Tensor o = at::empty({rows, n}, xa.options());
            at::Tensor r;
-           if (res) r = res->impl()->tensor.contiguous();
-           const int rc = kernels::add_f32_residual_to_bf16(stream, acc, res ? r.data_ptr() : nullptr, y.data_ptr(), rows * n);
-           CS_ASSERT_TRUE(rc == 0, "accumulator finalisation failed");
-           out.impl()->tensor = y;
+           if (res) r = res->impl()->tensor.reshape({rows, n}).contiguous();
+           const auto h = communication::begin_collective(ctx, kernels::kChanGemmScatter);
+           const int rc = kernels::symm_slot_sum(stream, communication::table_of(ctx), h, buf.data_ptr(), rows * n * 2, o.data_ptr(),
+                                                 res ? r.data_ptr() : nullptr, rows * n);
+           CS_ASSERT_TRUE(rc == 0, "slot sum launch failed: ", cuda_error_string(rc));
+           g_fused_tp_launches.fetch_add(1);
+           out.impl()->tensor = o;
          });
   return out;
 }
+}  // namespace
+
+int64_t fused_tp_launches() { return g_fused_tp_launches.load(); }
 
 namespace {
 compute::Linear::Options tp_linear(const Scheduler &scheduler, const models::GPT2Config &c, int64_t in, int64_t out) {
@@ -409,15 +525,25 @@ TPBlockImpl::TPBlockImpl(const Scheduler &scheduler, const models::GPT2Config &c
 Tensor TPBlockImpl::forward(const Scheduler &scheduler, const ReadOnlyTensor &x_shard, int64_t batch, int64_t seq) {
   namespace Utils = compute::Utils;
   const int64_t d_local = c_proj->state()->forward.weight.size(1);
-  const bool fuse = x_shard.defined() && fused_tp_ok(comm, x_shard.impl()->tensor, batch * seq) &&
+  const bool fuse = workspace && x_shard.defined() && fused_tp_ok(comm, x_shard.impl()->tensor, batch * seq) &&
                     scheduler.impl()->autocast_enabled;
-  saved_ln1_out = Tensor{};
-  saved_ln2_out = Tensor{};
+  fused_forward_ = fuse;
+  // row shards of whole 256-row tiles take the fused kernels (gather beside the GEMM, scatter in the GEMM epilogue)
+  const bool tiles = fuse && (batch * seq / comm.get_size()) % 256 == 0;
+  tiled_forward_ = tiles;
+  auto mark_bf16 = [](const Tensor &w) {
+    w.impl()->autocast_enabled = true;
+    w.impl()->autocast_dtype = at::kBFloat16;
+  };
   Tensor a = ln1->forward(scheduler, x_shard);                 // [M/tp, d]
   Tensor qkv;                                                   // [M, 3 d/tp]
-  if (fuse) {
-    saved_ln1_out = a;  // backward re-gathers it for the weight gradient
-    qkv = column_parallel_forward(scheduler, comm, c_attn->state(), a);
+  if (tiles) {
+    mark_bf16(c_attn->state()->forward.weight);
+    qkv = gather_gemm(scheduler, comm, a, a_full, c_attn->state()->forward.weight, false, kernels::kEpiStoreBf16, nullptr);
+    c_attn->state()->backward.input = a_full;                  // kept: the weight gradient of c_attn reads it again
+  } else if (fuse) {
+    gather_rows_symmetric(scheduler, comm, a, a_full);
+    qkv = c_attn->forward(scheduler, a_full);
   } else {
     qkv = c_attn->forward(scheduler, all_gather_rows(scheduler, comm, a));
   }
@@ -429,20 +555,25 @@ Tensor TPBlockImpl::forward(const Scheduler &scheduler, const ReadOnlyTensor &x_
     c_proj->state()->backward.input = ctx2;
     c_proj->state()->forward.weight.impl()->autocast_enabled = true;
     c_proj->state()->forward.weight.impl()->autocast_dtype = at::kBFloat16;
-    x1 = row_parallel_forward(scheduler, comm, c_proj->state()->forward.weight, ctx2, &x_shard, false);
+    x1 = tiles ? gemm_scatter(scheduler, comm, c_proj->state()->forward.weight, ctx2, &x_shard, false, *workspace)
+               : row_parallel_symmetric(scheduler, comm, c_proj->state()->forward.weight, ctx2, &x_shard, false, workspace->partial);
   } else {
     x1 = reduce_scatter_rows(scheduler, comm, c_proj->forward(scheduler, ctx2), &x_shard);
   }
   Tensor b = ln2->forward(scheduler, x1);
   Tensor pre;                                                    // [M, 4d/tp], carries GELU
-  if (fuse) {
-    saved_ln2_out = b;
-    pre = column_parallel_forward(scheduler, comm, fc1->state(), b);
+  if (tiles) {
+    mark_bf16(fc1->state()->forward.weight);
+    pre = gather_gemm(scheduler, comm, b, b_full, fc1->state()->forward.weight, false, kernels::kEpiGeluDual, nullptr);
+    fc1->state()->backward.input = b_full;
+  } else if (fuse) {
+    gather_rows_symmetric(scheduler, comm, b, b_full);
+    pre = fc1->forward(scheduler, b_full);
   } else {
     pre = fc1->forward(scheduler, all_gather_rows(scheduler, comm, b));
   }
   if (!fuse) return reduce_scatter_rows(scheduler, comm, fc2->forward(scheduler, pre), &x1);
-  // fused fc2: GELU(pre) is the companion emitted by the fc1 epilogue
+  // fc2 consumes GELU(pre), the companion emitted by the fc1 epilogue
   Tensor act;
   submit(scheduler, "cs::parallel::TPBlock::activation_view", Task::Impl::kMain, Task::Impl::kCompute, {act}, {pre},
          [act, pre](const FnTask &) { act.impl()->tensor = pre.impl()->companion; });
@@ -452,44 +583,70 @@ Tensor TPBlockImpl::forward(const Scheduler &scheduler, const ReadOnlyTensor &x_
   fs->backward.input_count = 2;
   fs->forward.weight.impl()->autocast_enabled = true;
   fs->forward.weight.impl()->autocast_dtype = at::kBFloat16;
-  return row_parallel_forward(scheduler, comm, fs->forward.weight, act, &x1, false);
+  return tiles ? gemm_scatter(scheduler, comm, fs->forward.weight, act, &x1, false, *workspace)
+               : row_parallel_symmetric(scheduler, comm, fs->forward.weight, act, &x1, false, workspace->partial);
 }
 
 Tensor TPBlockImpl::backward(const Scheduler &scheduler, const ReadOnlyTensor &grad_shard, const models::GradientSync &sync) {
   namespace Utils = compute::Utils;
+  const bool fuse = fused_forward_, tiles = tiled_forward_;
   // MLP: reduce-scatter backward = all-gather of the incoming row shard
-  Tensor dz = all_gather_rows(scheduler, comm, grad_shard);      // [M, d]
-  Tensor d_pre = fc2->backward_input(scheduler, dz);
+  Tensor dz, d_pre;                                              // [M, d], [M, 4d/tp]
+  if (tiles) {
+    dz = workspace->grad_full[workspace->next_grad ^= 1];
+    auto fs = fc2->state();
+    const ReadOnlyTensor pre = fs->backward.input;
+    d_pre = gather_gemm(scheduler, comm, grad_shard, dz, fs->forward.weight, true, kernels::kEpiDGelu, &pre);  // includes GELU'
+    fs->backward.input_count = 1;                                // the input-gradient half ran here
+  } else {
+    if (fuse) {
+      dz = workspace->grad_full[workspace->next_grad ^= 1];
+      gather_rows_symmetric(scheduler, comm, grad_shard, dz);
+    } else {
+      dz = all_gather_rows(scheduler, comm, grad_shard);
+    }
+    d_pre = fc2->backward_input(scheduler, dz);
+  }
   fc2->backward_parameter(scheduler, dz);
-  const bool fused_bwd = saved_ln2_out.defined();
   Tensor d_b;                                                    // all-gather backward = reduce-scatter
-  if (fused_bwd) {
-    d_b = row_parallel_forward(scheduler, comm, fc1->state()->forward.weight, d_pre, nullptr, true);
-    fc1->state()->backward.input = all_gather_rows(scheduler, comm, saved_ln2_out);  // re-gather for the weight gradient
+  if (tiles) {
+    d_b = gemm_scatter(scheduler, comm, fc1->state()->forward.weight, d_pre, nullptr, true, *workspace);
+  } else if (fuse) {
+    d_b = row_parallel_symmetric(scheduler, comm, fc1->state()->forward.weight, d_pre, nullptr, true, workspace->partial);
   } else {
     d_b = reduce_scatter_rows(scheduler, comm, fc1->backward_input(scheduler, d_pre));
   }
-  fc1->backward_parameter(scheduler, d_pre);
+  fc1->backward_parameter(scheduler, d_pre);                     // input: the gathered rows kept by forward
   Tensor d_x1 = ln2->backward(scheduler, d_b, grad_shard);       // + residual branch
   sync.push(scheduler, ln2->state()->forward.grad_weight);
   sync.push(scheduler, ln2->state()->forward.grad_bias);
   // attention
-  Tensor dy = all_gather_rows(scheduler, comm, d_x1);
-  Tensor d_ctx = c_proj->backward_input(scheduler, dy);          // [M, d/tp]
+  Tensor dy, d_ctx;                                              // [M, d], [M, d/tp]
+  if (tiles) {
+    dy = workspace->grad_full[workspace->next_grad ^= 1];
+    d_ctx = gather_gemm(scheduler, comm, d_x1, dy, c_proj->state()->forward.weight, true, kernels::kEpiStoreBf16, nullptr);
+  } else {
+    if (fuse) {
+      dy = workspace->grad_full[workspace->next_grad ^= 1];
+      gather_rows_symmetric(scheduler, comm, d_x1, dy);
+    } else {
+      dy = all_gather_rows(scheduler, comm, d_x1);
+    }
+    d_ctx = c_proj->backward_input(scheduler, dy);
+  }
   c_proj->backward_parameter(scheduler, dy);
   Tensor d_qkv = compute::ScaledDotProductAttention::backward_packed(scheduler, attn_state, d_ctx);
   const int64_t three_d_local = c_attn->state()->forward.weight.size(0);
   Tensor d_qkv2 = Utils::view(scheduler, d_qkv, {-1, three_d_local});
   Tensor d_a;
-  if (fused_bwd) {
-    d_a = row_parallel_forward(scheduler, comm, c_attn->state()->forward.weight, d_qkv2, nullptr, true);
-    c_attn->state()->backward.input = all_gather_rows(scheduler, comm, saved_ln1_out);
+  if (tiles) {
+    d_a = gemm_scatter(scheduler, comm, c_attn->state()->forward.weight, d_qkv2, nullptr, true, *workspace);
+  } else if (fuse) {
+    d_a = row_parallel_symmetric(scheduler, comm, c_attn->state()->forward.weight, d_qkv2, nullptr, true, workspace->partial);
   } else {
     d_a = reduce_scatter_rows(scheduler, comm, c_attn->backward_input(scheduler, d_qkv2));
   }
   c_attn->backward_parameter(scheduler, d_qkv2);
-  saved_ln1_out = Tensor{};
-  saved_ln2_out = Tensor{};
   Tensor d_x = ln1->backward(scheduler, d_a, d_x1);
   sync.push(scheduler, ln1->state()->forward.grad_weight);
   sync.push(scheduler, ln1->state()->forward.grad_bias);
@@ -500,19 +657,30 @@ TPGPT2Impl::TPGPT2Impl(const Scheduler &scheduler, const models::GPT2Config &con
     : config_{config}, comm_{comm} {
   const auto dev = config.device().value_or(scheduler.device());
   const int64_t d = config.n_embd();
+  const int64_t tp = comm.get_size();
   wte = register_module("wte", module::Embedding{scheduler, compute::Embedding::Options{config.padded_vocab_size(), d}.device(dev).dtype(config.dtype())});
   wpe = register_module("wpe", module::Embedding{scheduler, compute::Embedding::Options{config.block_size(), d}.device(dev).dtype(config.dtype())});
   compute::Utils::normal_(scheduler, wte->state()->forward.weight, 0, config.init_std());
   compute::Utils::normal_(scheduler, wpe->state()->forward.weight, 0, config.init_std());
-  for (int64_t l = 0; l < config.n_layer(); ++l) h.push_back(register_module(std::to_string(l), TPBlock{scheduler, config, comm}));
+  auto workspace = std::make_shared<TPWorkspace>();
+  for (int64_t l = 0; l < config.n_layer(); ++l) {
+    h.push_back(register_module(std::to_string(l), TPBlock{scheduler, config, comm}));
+    h.back()->workspace = workspace;
+  }
+  workspace_ = workspace;
   lnf = register_module("lnf", module::LayerNorm{scheduler, compute::LayerNorm::Options{d}.device(dev).dtype(config.dtype())});
-  lm_head = register_module("lm_head", module::Linear{scheduler, compute::Linear::Options{d, config.padded_vocab_size()}.bias(false).device(dev).dtype(config.dtype())});
+  // The classifier is split over the vocabulary when it divides evenly (rows [rank * V/tp, (rank+1) * V/tp) of
+  // lm_head live here); otherwise every rank keeps the whole matrix and scores its own token rows.
+  vocab_parallel_ = tp > 1 && config.padded_vocab_size() % (tp * 8) == 0;
+  const int64_t classes = vocab_parallel_ ? config.padded_vocab_size() / tp : config.padded_vocab_size();
+  lm_head = register_module("lm_head", module::Linear{scheduler, compute::Linear::Options{d, classes}.bias(false).device(dev).dtype(config.dtype())});
   compute::Utils::normal_(scheduler, lm_head->state()->forward.weight, 0, config.init_std());
   lce_state_ = compute::LinearCrossEntropy::init(scheduler, lm_head->state(), config.vocab_size(), -100);
 }
 
 std::vector<std::string> TPGPT2Impl::replicated_parameters() const {
-  std::vector<std::string> out{"wte.weight", "wpe.weight", "lnf.weight", "lnf.bias", "lm_head.weight"};
+  std::vector<std::string> out{"wte.weight", "wpe.weight", "lnf.weight", "lnf.bias"};
+  if (!vocab_parallel_) out.push_back("lm_head.weight");
   for (size_t l = 0; l < h.size(); ++l)
     for (const char *k : {".ln1.weight", ".ln1.bias", ".ln2.weight", ".ln2.bias"}) out.push_back(std::to_string(l) + k);
   return out;
@@ -543,13 +711,156 @@ Tensor TPGPT2Impl::forward_loss(const Scheduler &scheduler, const ReadOnlyTensor
   x = Utils::view(scheduler, x, {shard, config_.n_embd()});
   for (auto &block : h) x = block->forward(scheduler, x, batch_, seq_);
   x = lnf->forward(scheduler, x);
-  return compute::LinearCrossEntropy::forward(scheduler, lce_state_, x, lab_shard);
+  if (!vocab_parallel_) return compute::LinearCrossEntropy::forward(scheduler, lce_state_, x, lab_shard);
+
+  // ---- vocabulary-parallel classifier + cross-entropy ------------------------------------------------------
+  // Every rank scores ALL token rows against its slice of the vocabulary; the ranks then exchange, per row, the
+  // log-sum-exp over their slice and the target's logit (non-zero on the one rank that owns the target class):
+  // 8 bytes per row and rank instead of a replicated classifier whose 4 * V * d byte gradient is all-reduced.
+  const bool fuse = workspace_ && x.defined() && fused_tp_ok(comm_, x.impl()->tensor, rows) && scheduler.impl()->autocast_enabled;
+  ce_fused_ = fuse;
+  Tensor x_full;
+  if (fuse) {
+    x_full = lnf_full_;
+    gather_rows_symmetric(scheduler, comm_, x, x_full);
+  } else {
+    x_full = all_gather_rows(scheduler, comm_, x);
+  }
+  const auto &w = lm_head->state()->forward.weight;
+  const int64_t classes = w.size(0), col0 = rank * classes;
+  const int64_t valid_here = std::max<int64_t>(0, std::min<int64_t>(classes, config_.vocab_size() - col0));
+  Tensor logits, stats;  // [M, V/tp] local logits; [M, 2] = (lse over the local slice, target logit or 0)
+  const bool amp = scheduler.impl()->autocast_enabled;
+  submit(scheduler, "cs::parallel::TPGPT2::classifier_slice", Task::Impl::kMain, Task::Impl::kCompute, {logits, stats},
+         {x_full, w, labels}, [=](const FnTask &task) {
+           const at::Tensor &xf = x_full.impl()->tensor;
+           const at::Tensor tgt = labels.impl()->tensor.reshape({-1}).contiguous();
+           const int64_t M = xf.size(0);
+           if (fuse) {
+             const at::Tensor wc = compute::working_copy(w, at::kBFloat16);
+             const int64_t n_tiles = kernels::gemm_ce_stat_tiles(classes);
+             at::Tensor lg = at::empty({M, classes}, xf.options());
+             at::Tensor partials = at::empty({M, n_tiles, 2}, xf.options().dtype(at::kFloat));
+             at::Tensor st = at::empty({M, 2}, xf.options().dtype(at::kFloat));
+             auto stream = c10::cuda::getCurrentCUDAStream().stream();
+             kernels::GemmArgs g{};
+             g.a = xf.data_ptr();
+             g.b = wc.data_ptr();
+             g.d = lg.data_ptr();
+             g.stats = partials.data_ptr<float>();
+             g.m = M;
+             g.n = classes;
+             g.k = xf.size(1);
+             g.lda = g.k;
+             g.ldb = g.k;
+             g.ldd = classes;
+             g.layout = kernels::kTN;
+             g.epilogue = kernels::kEpiCrossEntropy;
+             g.n_valid = std::max<int64_t>(valid_here, 1);
+             const int code = kernels::gemm_bf16(stream, g);
+             CS_ASSERT_TRUE(code == 0, "classifier slice GEMM launch failed (", code, ")");
+             task.intermediate().push_back(partials);
+             const int rc = kernels::cross_entropy_slice_stats(stream, partials.data_ptr<float>(), n_tiles, lg.data_ptr(), classes,
+                                                               tgt.data_ptr<int64_t>(), col0, valid_here, st.data_ptr<float>(), M);
+             CS_ASSERT_TRUE(rc == 0, "cross_entropy_slice_stats failed: ", cuda_error_string(rc));
+             logits.impl()->tensor = lg;
+             stats.impl()->tensor = st;
+             return;
+           }
+           const at::ScalarType ct = xf.scalar_type() == at::kDouble ? at::kDouble : at::kFloat;
+           const at::ScalarType dt = amp && xf.is_cuda() ? at::kBFloat16 : xf.scalar_type();
+           at::Tensor lg = at::linear(xf.to(dt), compute::working_copy(w, dt));
+           at::Tensor lf = lg.to(ct);
+           if (valid_here < classes) lf = lf.clone(), lf.narrow(1, valid_here, classes - valid_here).fill_(-INFINITY);
+           at::Tensor lse = valid_here > 0 ? at::logsumexp(lf, {1}) : at::full({M}, -INFINITY, lf.options());
+           at::Tensor local = tgt - col0;
+           at::Tensor mine = local.ge(0).logical_and(local.lt(valid_here));
+           at::Tensor picked = lg.to(ct).gather(1, at::where(mine, local, at::zeros_like(local)).unsqueeze(1)).squeeze(1);
+           logits.impl()->tensor = lg;
+           stats.impl()->tensor = at::stack({lse, at::where(mine, picked, at::zeros_like(picked))}, 1).contiguous();
+         });
+  Tensor all_stats;  // [tp * M, 2]
+  if (fuse) {
+    all_stats = stats_full_;
+    gather_rows_symmetric(scheduler, comm_, stats, all_stats);
+  } else {
+    all_stats = all_gather_rows(scheduler, comm_, stats);
+  }
+  Tensor loss, lse;  // lse: [M + 1] = global log-sum-exp per row, then the number of rows that count
+  submit(scheduler, "cs::parallel::TPGPT2::combine_loss", Task::Impl::kMain, Task::Impl::kCompute, {loss, lse}, {all_stats, labels},
+         [=](const FnTask &) {
+           const at::Tensor tgt = labels.impl()->tensor.reshape({-1});
+           const int64_t M = tgt.numel();
+           const at::Tensor st = all_stats.impl()->tensor.view({tp, M, 2});
+           at::Tensor global = at::logsumexp(st.select(2, 0), {0});
+           at::Tensor target_logit = st.select(2, 1).sum(0);
+           at::Tensor keep = tgt.ne(-100).to(st.scalar_type());
+           at::Tensor count = keep.sum().clamp_min(1.0);
+           loss.impl()->tensor = ((global - target_logit) * keep).sum() / count;
+           lse.impl()->tensor = at::cat({global, count.reshape({1})}).contiguous();
+         });
+  ce_logits_ = logits;
+  ce_lse_ = lse;
+  ce_labels_ = labels;
+  ce_input_ = x_full;
+  return loss;
 }
 
 void TPGPT2Impl::backward_loss(const Scheduler &scheduler, const models::GradientSync &sync) {
   namespace Utils = compute::Utils;
-  Tensor grad = compute::LinearCrossEntropy::backward(scheduler, lce_state_);
-  sync.push(scheduler, lm_head->state()->forward.grad_weight);
+  Tensor grad;
+  if (!vocab_parallel_) {
+    grad = compute::LinearCrossEntropy::backward(scheduler, lce_state_);
+    sync.push(scheduler, lm_head->state()->forward.grad_weight);
+  } else {
+    const int64_t tp = comm_.get_size(), rank = comm_.get_rank();
+    const auto &w = lm_head->state()->forward.weight;
+    const int64_t classes = w.size(0), col0 = rank * classes;
+    const int64_t valid_here = std::max<int64_t>(0, std::min<int64_t>(classes, config_.vocab_size() - col0));
+    Tensor dlogits;
+    // logits -> (softmax - onehot) * tp / count, in place on the GPU path. The factor tp keeps the convention of the
+    // data-parallel trainer: the optimizer multiplies every gradient by 1 / world.
+    submit(scheduler, "cs::parallel::TPGPT2::classifier_slice_backward", Task::Impl::kMain, Task::Impl::kCompute, {dlogits},
+           {ce_logits_, ce_lse_, ce_labels_}, [=, lg_h = ce_logits_, lse_h = ce_lse_, lab = ce_labels_, fuse = ce_fused_](const FnTask &) {
+             at::Tensor lg = lg_h.impl()->tensor;
+             const at::Tensor &ls = lse_h.impl()->tensor;
+             const at::Tensor tgt = lab.impl()->tensor.reshape({-1}).contiguous();
+             const int64_t M = lg.size(0);
+             if (fuse) {
+               const int rc = kernels::cross_entropy_backward_inplace(c10::cuda::getCurrentCUDAStream().stream(), lg.data_ptr(), classes,
+                                                                      ls.data_ptr<float>(), tgt.data_ptr<int64_t>(), ls.data_ptr<float>() + M,
+                                                                      static_cast<float>(tp), M, classes, col0 + valid_here, -100, col0);
+               CS_ASSERT_TRUE(rc == 0, "cross_entropy_backward_inplace failed: ", cuda_error_string(rc));
+               dlogits.impl()->tensor = lg;
+               return;
+             }
+             const at::ScalarType ct = lg.scalar_type() == at::kDouble ? at::kDouble : at::kFloat;
+             at::Tensor p = at::exp(lg.to(ct) - ls.narrow(0, 0, M).to(ct).unsqueeze(1));
+             if (valid_here < classes) p.narrow(1, valid_here, classes - valid_here).zero_();
+             at::Tensor keep = tgt.ne(-100);
+             at::Tensor local = tgt - col0;
+             at::Tensor mine = local.ge(0).logical_and(local.lt(valid_here)).logical_and(keep);
+             p.scatter_add_(1, at::where(mine, local, at::zeros_like(local)).unsqueeze(1), -mine.to(ct).unsqueeze(1));
+             p.mul_(keep.to(ct).unsqueeze(1));
+             p.mul_(static_cast<double>(tp)).div_(ls.narrow(0, M, 1).to(ct));
+             dlogits.impl()->tensor = p.to(lg.scalar_type());
+           });
+    auto st = lm_head->state();
+    st->backward.input = ce_input_;
+    if (ce_fused_) {
+      st->forward.weight.impl()->autocast_enabled = true;
+      st->forward.weight.impl()->autocast_dtype = at::kBFloat16;
+      grad = (batch_ * seq_ / tp) % 256 == 0 ? gemm_scatter(scheduler, comm_, w, dlogits, nullptr, true, *workspace_)
+                                             : row_parallel_symmetric(scheduler, comm_, w, dlogits, nullptr, true, workspace_->partial);
+    } else {
+      grad = reduce_scatter_rows(scheduler, comm_, lm_head->backward_input(scheduler, dlogits));
+    }
+    lm_head->backward_parameter(scheduler, dlogits);
+    ce_logits_ = Tensor{};
+    ce_lse_ = Tensor{};
+    ce_labels_ = ReadOnlyTensor{};
+    ce_input_ = Tensor{};
+  }
   grad = lnf->backward(scheduler, grad);
   sync.push(scheduler, lnf->state()->forward.grad_weight);
   sync.push(scheduler, lnf->state()->forward.grad_bias);

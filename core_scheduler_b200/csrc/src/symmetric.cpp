@@ -295,12 +295,6 @@ bool symmetric_all_gather(SymmetricContext &ctx, const std::vector<std::vector<a
   auto stream = static_cast<cudaStream_t>(cur_stream());
   for (size_t i = 0; i < send.size(); ++i) {
     const int64_t bytes = static_cast<int64_t>(send[i].nbytes());
-    int64_t offset = 0;
-    if (!ctx.locate(send[i].data_ptr(), bytes, &offset)) {
-      const SymmetricBlock st = ctx.staging(bytes);
-      offset = st.offset;
-      CS_CHECK_CUDART(cudaMemcpyAsync(ctx.bases[ctx.rank] + offset, send[i].data_ptr(), bytes, cudaMemcpyDeviceToDevice, stream));
-    }
     // Destination slots that form one block of the arena (slot p at dst + p * bytes, the same offset on every
     // rank) are written by their owners: one multicast store per vector instead of size - 1 pulls.
     int64_t dst_offset = 0;
@@ -308,10 +302,21 @@ bool symmetric_all_gather(SymmetricContext &ctx, const std::vector<std::vector<a
     for (int p = 1; push && p < ctx.size; ++p)
       push = static_cast<const char *>(recv[i][p].data_ptr()) == static_cast<const char *>(recv[i][0].data_ptr()) + p * bytes;
     int blocks = 0;
-    const auto h = begin_collective(ctx, kernels::kChanAllGather);
     if (push) {
-      check(kernels::symm_all_gather_push(stream, table, h, offset, dst_offset, bytes, &blocks), "symm_all_gather_push");
-    } else {
+      // the source may be any local memory: every rank writes its own shard
+      const auto h = begin_collective(ctx, kernels::kChanAllGather);
+      check(kernels::symm_all_gather_push(stream, table, h, send[i].data_ptr(), dst_offset, bytes, &blocks), "symm_all_gather_push");
+      end_collective(ctx, kernels::kChanAllGather, blocks);
+      continue;
+    }
+    int64_t offset = 0;
+    if (!ctx.locate(send[i].data_ptr(), bytes, &offset)) {
+      const SymmetricBlock st = ctx.staging(bytes);
+      offset = st.offset;
+      CS_CHECK_CUDART(cudaMemcpyAsync(ctx.bases[ctx.rank] + offset, send[i].data_ptr(), bytes, cudaMemcpyDeviceToDevice, stream));
+    }
+    const auto h = begin_collective(ctx, kernels::kChanAllGather);
+    {
       kernels::PullCopyArgs a{};
       for (int p = 0; p < ctx.size; ++p) {
         a.src_offset[p] = offset;

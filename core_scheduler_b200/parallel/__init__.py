@@ -43,6 +43,7 @@ class GPT2Trainer:
          "zero" data parallel with the sharded optimizer: reduce-scatter + AdamW + all-gather in one kernel (GPUs).
          "tp"   tensor + sequence parallel over all ranks; every rank sees the whole batch (GPUs, or Gloo ranks).
     collectives "nvp2p" runs this library's peer-memory kernels (GPUs with peer access), "nccl" the library's.
+    `max_tokens` (tensor parallel with "nvp2p" only) is the largest B*T of a step; it sizes the symmetric arena.
     On GPUs the parameters are fp32 masters with bf16 working copies and the step runs under bf16 autocast; on the
     CPU everything is fp32.
 
@@ -53,7 +54,8 @@ class GPT2Trainer:
 
     def __init__(self, config, comm=None, world: int = 1, local_rank: int = 0, mode: str = "dp", collectives: str = "nvp2p",
                  device: str = "cuda", lr: float = 3e-4, beta1: float = 0.9, beta2: float = 0.95, weight_decay: float = 0.1,
-                 bucket_mb: float = 25.0, seed: int = 1234, scheduler=None, overlap_optimizer: bool = True):
+                 bucket_mb: float = 25.0, seed: int = 1234, scheduler=None, overlap_optimizer: bool = True,
+                 max_tokens: int = 32 * 1024):
         import core_scheduler_b200 as cs
 
         assert mode in ("dp", "zero", "tp") and collectives in ("nvp2p", "nccl")
@@ -71,7 +73,11 @@ class GPT2Trainer:
         lp = dict(lp_dtype=torch.bfloat16) if self.amp else {}
         if mode == "tp" and world > 1:
             if peer:
-                self.symmetric = _C.create_symmetric_context(self.comm, 2 << 30)
+                # gathered activations of every block are kept from forward to backward in symmetric buffers:
+                # two [tokens, d] bf16 per block, plus the partial-product, gradient and classifier buffers
+                rows_bytes = max_tokens * config.n_embd * 2
+                arena = (2 * config.n_layer + 8) * rows_bytes + (256 << 20)
+                self.symmetric = _C.create_symmetric_context(self.comm, int(arena))
             self.model = _C.TPGPT2(s, config, self.comm)
             self.flat = _C.flatten_parameters(s, self.model, **lp)
         else:
@@ -98,6 +104,18 @@ class GPT2Trainer:
                 if overlap_optimizer:
                     self.bucket.attach_optimizer(self.optimizer)
         s.synchronize()
+
+    def close(self):
+        """Releases the symmetric arena in an orderly way: every rank drains its streams, all ranks meet, then the
+        mappings (and the multicast binding) go. Call it on every rank before the process group is destroyed."""
+        self.scheduler.synchronize()
+        if self.symmetric is not None:
+            torch.cuda.synchronize()
+            if dist.is_initialized():
+                dist.barrier()
+            self.model = self.optimizer = self.flat = self.bucket = self.sync = None  # views into the arena
+            self.symmetric = None
+            self.comm.release_symmetric()
 
     def step(self, input_ids, labels):
         """Forward, backward (gradient communication overlapped), optimizer update; returns the loss handle."""

@@ -59,8 +59,9 @@ def merge_tensor_parallel(shards: "list[OrderedDict[str, np.ndarray]]", n_head: 
     """Unites the parameter tables of all tensor-parallel ranks (in rank order) into the unsharded model's table.
 
     Column-parallel Linears (c_attn: the q, k and v rows of the rank's heads; fc1: a contiguous block of rows) are
-    concatenated along the output dimension, row-parallel ones (c_proj, fc2) along the input dimension; everything else
-    is replicated and taken from rank 0."""
+    concatenated along the output dimension, row-parallel ones (c_proj, fc2) along the input dimension; the classifier
+    is concatenated along the vocabulary when the ranks hold slices of it; everything else is replicated and taken
+    from rank 0."""
     world = len(shards)
     d, head_dim = n_embd, n_embd // n_head
     merged: "OrderedDict[str, np.ndarray]" = OrderedDict()
@@ -80,6 +81,9 @@ def merge_tensor_parallel(shards: "list[OrderedDict[str, np.ndarray]]", n_head: 
             value = np.concatenate(parts)
         elif key.endswith("fc2.weight"):
             value = np.concatenate([p.reshape(d, -1) for p in parts], axis=1)
+        elif key == "lm_head.weight" and "wte.weight" in shards[0] and first.size * world == shards[0]["wte.weight"].size:
+            # vocabulary-parallel classifier: rank r holds rows [r * V/world, (r + 1) * V/world)
+            value = np.concatenate([p.reshape(-1, d) for p in parts], axis=0)
         else:
             value = first
         merged[canonical_key(key)] = np.ascontiguousarray(value, dtype=np.float32).reshape(-1)

@@ -51,7 +51,11 @@ int main(int argc, char **argv) {
                                   : model_name == "tiny" ? cs::models::GPT2Config::tiny()
                                                          : cs::models::GPT2Config::gpt2_124m();
   const bool tp = mode == "tp";
-  cs::communication::create_symmetric_context(comm, tp ? (2ll << 30) : config.parameter_count() * 6 + (256ll << 20));
+  // tensor parallel: two gathered [tokens, d] bf16 activations per block stay in symmetric buffers from forward to
+  // backward, plus partial-product, gradient and classifier buffers; ZeRO: fp32 gradients + bf16 copies + staging
+  const int64_t tp_rows_bytes = batch * config.block_size() * config.n_embd() * 2;
+  cs::communication::create_symmetric_context(
+      comm, tp ? (2 * config.n_layer() + 8) * tp_rows_bytes + (256ll << 20) : config.parameter_count() * 6 + (256ll << 20));
 
   cs::models::GPT2 dp_model{nullptr};
   cs::parallel::TPGPT2 tp_model{nullptr};
