@@ -220,6 +220,9 @@ def main():
 
     for i in range(args.warmup):
         loss = trainer.step(*batches[i % len(batches)])
+        if i == 0:
+            trainer.s.synchronize()
+            trainer.check_device_status()  # a broken configuration shows in the first step: stop before timing anything
     trainer.s.synchronize()
     barrier(world)
     if args.profile:
@@ -254,6 +257,7 @@ def main():
     torch.cuda.synchronize()
     launches = C.kernel_launch_count() - launches_before
     device_ms = start.elapsed_time(stop)
+    trainer.check_device_status()  # a kernel that gave up on a bounded wait makes the measurement void: fail loudly
     barrier(world)
     clocks = sampler.stop() if sampler else None
     device_ms = max_over_ranks(device_ms, world)

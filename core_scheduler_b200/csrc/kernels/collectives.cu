@@ -41,7 +41,8 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
 #define CS_PEER_OK(t, byte_offset) ((t).arena_bytes == 0 || CS_IN_BOUNDS(kKidCollective, (byte_offset) + 15, (t).arena_bytes))
 
 constexpr int kThreads = 256;
-// 256 threads x 40 registers fit beside a GEMM CTA (320 threads x 168 registers) on one SM.
+// Light blocks (256 threads, at most 40 registers, no shared memory to speak of): many of them fit on an SM, and a
+// collective never needs more than a fraction of the machine to fill NVLink.
 #define CS_COMM_BOUNDS __launch_bounds__(kThreads, 6)
 
 __device__ __forceinline__ uint32_t *channel_words(const PeerTable &t, int peer, int channel) {
@@ -354,7 +355,8 @@ __global__ void CS_COMM_BOUNDS all_gather_push_kernel(PeerTable t, Handshake h, 
   close_collective(t, h, 13);
 }
 
-__global__ void CS_COMM_BOUNDS all_gather_chunked_kernel(PeerTable t, Handshake h, const char *src, int64_t dst_offset, int64_t vecs_per_chunk,
+// Runs beside the GEMM that consumes the chunks, on the SMs that GEMM leaves free: few blocks, many threads.
+__global__ void __launch_bounds__(1024, 1) all_gather_chunked_kernel(PeerTable t, Handshake h, const char *src, int64_t dst_offset, int64_t vecs_per_chunk,
                                                          int chunks) {
   open_collective(t, h, 16);
   __shared__ int last_of_chunk;
@@ -556,9 +558,10 @@ int symm_all_gather_chunked(stream_t stream, const PeerTable &t, const Handshake
   if (chunks < 1 || chunks > kMaxChunks || bytes % (16 * chunks) != 0 || (reinterpret_cast<uintptr_t>(src) & 15) || dst_offset_bytes % 16 != 0)
     return static_cast<int>(cudaErrorInvalidValue);
   const int64_t vecs_per_chunk = bytes / 16 / chunks;
-  const int grid = comm_grid(vecs_per_chunk);
+  const int64_t wanted = (vecs_per_chunk + 1024 * kUnroll - 1) / (1024 * kUnroll);
+  const int grid = static_cast<int>(wanted < 1 ? 1 : (wanted > kGatherBesideGemmBlocks ? kGatherBesideGemmBlocks : wanted));
   *blocks = grid;
-  all_gather_chunked_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(t, h, static_cast<const char *>(src), dst_offset_bytes,
+  all_gather_chunked_kernel<<<grid, 1024, 0, static_cast<cudaStream_t>(stream)>>>(t, h, static_cast<const char *>(src), dst_offset_bytes,
                                                                                       vecs_per_chunk, chunks);
   return finish_launch(1);
 }

@@ -8,9 +8,14 @@
 // Every collective is ONE launch: the cross-rank barrier that must precede it (all contributions
 // complete) and the one that must follow it (all results written, all sources read) are part of
 // the kernel. Block 0 exchanges flags with the peers, the other blocks wait on a local flag; at
-// the end the last block to finish does the closing exchange. The kernels are built to stay
-// resident next to a GEMM CTA (256 threads, at most 40 registers, no shared memory), so a
-// collective on the communication stream never has to wait for a whole GEMM wave to drain.
+// the end the last block to finish does the closing exchange.
+//
+// Residency. A block of these kernels does NOT fit on an SM beside a block of the GEMM kernel (320 threads x 168
+// registers fill the register files of two of the SM's four partitions), so next to a running GEMM a collective
+// starts when GEMM blocks retire. That is harmless as long as the GEMM does not itself wait for the collective.
+// The one GEMM that does (it consumes rows while symm_all_gather_chunked is still delivering them) therefore
+// launches on all but kGatherBesideGemmBlocks SMs, and that gather uses at most kGatherBesideGemmBlocks blocks:
+// both kernels are always resident together and neither can starve the other.
 #pragma once
 #include <cstdint>
 
@@ -40,6 +45,7 @@ constexpr int kChannelWords = 128;
 constexpr int kChunkCounters = 20;
 constexpr int kChunkFlags = 32;
 constexpr int kMaxChunks = 8;
+constexpr int kGatherBesideGemmBlocks = 16;
 enum Channel : int {
   kChanAllReduce = 0,
   kChanReduceScatter = 1,

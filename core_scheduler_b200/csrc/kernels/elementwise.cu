@@ -109,11 +109,8 @@ template <> __device__ __forceinline__ float from_f<float>(float v) { return v; 
 template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
 
-// At most 40 registers: a 256-thread block then fits on an SM beside a resident GEMM block (320 threads x 168
-// registers), so an update launched while the backward pass is running proceeds next to the GEMMs instead of
-// waiting for a whole wave of them to drain.
 template <typename P, typename G, int VEC>
-__global__ void __launch_bounds__(256, 6) adamw_kernel(P *__restrict__ w, const G *__restrict__ g, P *__restrict__ m,
+__global__ void __launch_bounds__(256) adamw_kernel(P *__restrict__ w, const G *__restrict__ g, P *__restrict__ m,
                                                     P *__restrict__ v, P *__restrict__ vmax,
                                                     __nv_bfloat16 *__restrict__ lp, int64_t n, float lr, float b1,
                                                     float b2, float eps, float wd, float ibc1, float ibc2,

@@ -35,6 +35,7 @@
 #include "api.h"
 #include "bounds_check.h"
 #include "gelu_math.h"
+#include "collectives.h"
 
 namespace cs::kernels {
 namespace {
@@ -1260,7 +1261,8 @@ int gemm_bf16(stream_t stream, const GemmArgs &a) {
   if (!attr_set) return -1;
   const int total_tiles = p.m_tiles * p.n_tiles * p.splits;
   if (pair_kernel) {
-    const int pairs = sm_count / 2;
+    // a GEMM that waits for chunks of an all-gather in flight leaves SMs free for that gather's blocks
+    const int pairs = (sm_count - (peer_mode == 3 ? kGatherBesideGemmBlocks : 0)) / 2;
     const int grid = 2 * (total_tiles < pairs ? total_tiles : pairs);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(grid));

@@ -105,6 +105,17 @@ class GPT2Trainer:
                     self.bucket.attach_optimizer(self.optimizer)
         s.synchronize()
 
+    def check_device_status(self):
+        """Raises when a kernel gave up on a bounded wait (a tensor-core pipeline barrier, a peer's flag): the numbers
+        of such a step are meaningless. Synchronises the device; call it between steps, not inside a timed region."""
+        torch.cuda.synchronize()
+        for name, status in (("gemm", _C.gemm_status()), ("attention", _C.attention_status())):
+            if status[0] != 0:
+                raise RuntimeError(f"{name} kernel reported a timed-out wait: code={status[0]} kernel={status[1]} "
+                                   f"block={status[2]} detail={status[3]}")
+        if self.symmetric is not None:
+            self.symmetric.check_status()
+
     def close(self):
         """Releases the symmetric arena in an orderly way: every rank drains its streams, all ranks meet, then the
         mappings (and the multicast binding) go. Call it on every rank before the process group is destroyed."""
