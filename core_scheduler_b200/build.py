@@ -241,6 +241,53 @@ def _build_programs(root: Path, extra_inc: list, names: dict | None = None) -> l
     return built
 
 
+def build_sanitized() -> list[str]:
+    """Host-side race and memory checks: compiles the C++ sources (not the kernels) with AddressSanitizer and
+    UndefinedBehaviorSanitizer into lib_asan/libcs_b200.so and links the two C++ test programs against it
+    (tests/cpp/bin/*_asan). Run them on the CPU, e.g.
+        ASAN_OPTIONS=detect_leaks=0:protect_shadow_gap=0 tests/cpp/bin/cs_b200_communication_tests_asan --threads 4
+    (scheduler queues, rank-thread communicator, bucket logic, data-loader threads, module tree)."""
+    p = _paths()
+    generate_ninja()
+    subprocess.run([sys.executable, "-m", "ninja", "-f", str(BUILD / "build.ninja"), str(LIBDIR / "libcs_b200.so")], check=True, cwd=str(BUILD))
+    out = HERE / "lib_asan"
+    out.mkdir(exist_ok=True)
+    extra_cpp, extra_cu = _optional_sources()
+    inc = [CSRC / "include", CSRC, CSRC / "src"] + p["torch_inc"] + [p["cuda_home"] / "include"]
+    san = ["-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-g", "-O1"]
+    base = [os.environ.get("CS_CXX", "g++"), "-std=c++20", "-fPIC", "-Wno-interference-size", "-Wno-deprecated-declarations",
+            f"-D_GLIBCXX_USE_CXX11_ABI={p['cxx11_abi']}", "-DUSE_C10D_NCCL", "-DUSE_DISTRIBUTED", "-DUSE_RPC", "-DUSE_CUDA"] + [f"-I{i}" for i in inc]
+    objs = []
+    jobs = []
+    for src in CPP_SOURCES + extra_cpp:
+        obj = BUILD / (src.replace("/", "_") + ".asan.o")
+        extra = [f"-I{p['arrow_inc']}"] if src.endswith("parquet_io.cpp") else ([f"-I{p['nccl_inc']}"] if src.endswith("comm_nccl.cpp") else [])
+        if not obj.exists() or obj.stat().st_mtime < (CSRC / src).stat().st_mtime:
+            jobs.append(subprocess.Popen(base + san + extra + ["-c", str(CSRC / src), "-o", str(obj)]))
+        objs.append(str(obj))
+    for j in jobs:
+        if j.wait() != 0:
+            raise RuntimeError("sanitized compile failed")
+    objs += [str(BUILD / (src.replace("/", "_") + ".o")) for src in CUDA_SOURCES + extra_cu]  # kernels as they are
+    cuda_lib = p["cuda_home"] / "lib64"
+    lib = out / "libcs_b200.so"
+    subprocess.run([base[0], "-shared", *san, *objs, "-o", str(lib), f"-L{p['torch_lib']}", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10",
+                    "-lc10_cuda", f"-L{p['arrow_lib']}", "-l:libarrow.so.2400", "-l:libparquet.so.2400", f"-L{cuda_lib}", "-lcudart", "-ldl",
+                    "-lpthread", f"-Wl,-rpath,{p['torch_lib']}", f"-Wl,-rpath,{p['arrow_lib']}", f"-Wl,-rpath,{cuda_lib}", "-Wl,--no-as-needed",
+                    "-Wl,-soname,libcs_b200.so"], check=True)
+    root = HERE.parent / "tests" / "cpp"
+    (root / "bin").mkdir(exist_ok=True)
+    built = []
+    for stem, name in (("test_ops", "cs_b200_tests_asan"), ("test_communication", "cs_b200_communication_tests_asan")):
+        exe = root / "bin" / name
+        subprocess.run(base + san + [f"-I{root}", str(root / f"{stem}.cpp"), "-o", str(exe), f"-L{out}", "-lcs_b200", f"-L{p['torch_lib']}",
+                                     "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda", f"-L{cuda_lib}", "-lcudart",
+                                     f"-Wl,-rpath,{out}", f"-Wl,-rpath,{p['torch_lib']}", f"-Wl,-rpath,{p['arrow_lib']}", "-Wl,--no-as-needed"],
+                       check=True)
+        built.append(str(exe))
+    return built
+
+
 def is_checked_built() -> bool:
     return (CHECKED_LIBDIR / "libcs_b200.so").exists()
 
@@ -254,5 +301,7 @@ if __name__ == "__main__":
         print("\n".join(build_examples()))
     elif "tests" in sys.argv:
         print("\n".join(build_cpp_tests()))
+    elif "sanitize" in sys.argv:
+        print("\n".join(build_sanitized()))
     else:
         build(verbose="-v" in sys.argv, checked="checked" in sys.argv)

@@ -12,6 +12,9 @@
 // bucket receives the reduced value; kNVP2P is implemented: collectives run as this
 // library's own kernels over peer-mapped symmetric memory (see cs/symmetric.h).
 #pragma once
+#ifdef CS_WITH_MPI
+#include <mpi.h>
+#endif
 #include <functional>
 #include <torch/csrc/distributed/c10d/Backend.hpp>
 #include <torch/csrc/distributed/c10d/Store.hpp>
@@ -54,6 +57,12 @@ struct CS_API Bucket {
   virtual void apply(const Scheduler &scheduler, const Comm &comm) const;
 };
 
+#ifdef CS_WITH_MPI
+// Communicator over the ranks of an MPI group (the reference's entry point, include/communication/communication.h:55).
+// Available when the library is built with -DCS_WITH_MPI against an MPI installation: rank and size come from the
+// group, the store address is broadcast from the group's rank 0, and the collectives run on `backend_type`.
+CS_API Comm get_comm(MPI_Comm group, BackendType backend_type);
+#endif
 // World communicator from the launcher environment. With WORLD_SIZE unset or 1 the result is
 // a single-rank communicator whose collectives are local no-ops/copies.
 CS_API Comm get_comm_world(BackendType backend_type = kNCCL);

@@ -127,6 +127,28 @@ inline std::string str_cat(const Args &...a) {
     }                                                                   \
   } while (0)
 
+// Status checks for the other libraries a program built on this one may call (same names as in the reference's
+// logger.h:51-89). They are plain macros over the status value and need the respective library header only where
+// they are used; this library itself calls none of cuBLAS, cuDNN or NCCL directly.
+#define CS_CHECK_STATUS_(expr, ok_value, what)                                                          \
+  do {                                                                                                   \
+    const auto cs_status_ = (expr);                                                                      \
+    if (!(cs_status_ == (ok_value))) [[unlikely]] {                                                      \
+      ::cs::fail(__FILE__, __LINE__, ::cs::str_cat(what " call `" #expr "` returned code ", static_cast<long long>(cs_status_))); \
+    }                                                                                                    \
+  } while (0)
+#define CS_CHECK_CUBLAS(expr) CS_CHECK_STATUS_(expr, CUBLAS_STATUS_SUCCESS, "cuBLAS")
+#define CS_CHECK_MPI(expr) CS_CHECK_STATUS_(expr, MPI_SUCCESS, "MPI")
+#define CS_CHECK_NCCL(expr) CS_CHECK_STATUS_(expr, ncclSuccess, "NCCL")
+#define CS_CHECK_CUDNN(expr) CS_CHECK_STATUS_(expr, CUDNN_STATUS_SUCCESS, "cuDNN")
+#define CS_CHECK_CUDNN_FE(expr)                                                                          \
+  do {                                                                                                   \
+    const auto cs_status_ = (expr);                                                                      \
+    if (!cs_status_.is_good()) [[unlikely]] {                                                            \
+      ::cs::fail(__FILE__, __LINE__, ::cs::str_cat("cuDNN frontend call `" #expr "` failed: ", cs_status_.get_message())); \
+    }                                                                                                    \
+  } while (0)
+
 namespace cs {
 // ----------------------------------------------------------------------------------------
 // NVTX

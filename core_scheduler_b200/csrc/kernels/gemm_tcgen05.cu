@@ -791,7 +791,10 @@ __device__ __forceinline__ TileCoord tile_coord2(const KParams &p, int tile) {
   return c;
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
+// 128 registers per thread (no spills): the SM's four register files are filled by warps, and a partition that
+// holds three of this block's ten warps then still has room for two warps of a light kernel (collectives, AdamW),
+// so those really run beside a resident GEMM block instead of waiting for it to retire.
+__global__ void __maxnreg__(128)
 gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
              const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_d2,
              const __grid_constant__ PeerMaps peer_maps, const KParams p) {

@@ -172,6 +172,38 @@ std::vector<at::Tensor> merge_adjacent(const std::vector<at::Tensor> &tensors) {
 }
 }  // namespace
 
+#ifdef CS_WITH_MPI
+Comm get_comm(MPI_Comm group, BackendType backend_type) {
+  CS_ASSERT_TRUE(backend_type == kNCCL || backend_type == kNVP2P, "collectives over an MPI group run on kNCCL or kNVP2P");
+  int rank = 0, size = 1;
+  CS_CHECK_MPI(MPI_Comm_rank(group, &rank));
+  CS_CHECK_MPI(MPI_Comm_size(group, &size));
+  auto impl = std::make_shared<Comm::Impl>();
+  impl->type = backend_type;
+  impl->rank = rank;
+  impl->size = size;
+  if (size <= 1) return Comm{impl};
+  // rank 0 of the group opens the store on a port of its own and tells the others where it is
+  char host[256] = "127.0.0.1";
+  int port = 0;
+  if (rank == 0) {
+    if (const char *addr = std::getenv("MASTER_ADDR")) std::snprintf(host, sizeof(host), "%s", addr);
+    port = static_cast<int>(env_int("CS_STORE_PORT", 29517));
+  }
+  CS_CHECK_MPI(MPI_Bcast(host, sizeof(host), MPI_CHAR, 0, group));
+  CS_CHECK_MPI(MPI_Bcast(&port, sizeof(port), MPI_CHAR, 0, group));
+  c10d::TCPStoreOptions opts;
+  opts.port = static_cast<uint16_t>(port);
+  opts.isServer = rank == 0;
+  opts.numWorkers = size;
+  opts.waitWorkers = true;
+  impl->store = c10::make_intrusive<c10d::TCPStore>(std::string(host), opts);
+  impl->backend = create_nccl_backend(impl->store, rank, size);
+  warm_up(*impl);
+  return Comm{impl};
+}
+#endif
+
 Comm get_comm_world(BackendType backend_type) { return lookup_or_create(backend_type, 0); }
 Comm get_comm_node(BackendType backend_type) { return lookup_or_create(backend_type, 1); }
 Comm get_comm_self() {
