@@ -68,3 +68,19 @@ def test_cpp_communication_tests_on_two_gpus():
                           program("cs_b200_communication_tests")], capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert out.stdout.count("9 tests ran, 0 failed") == 2, out.stdout[-3000:]
+
+
+@pytest.mark.skipif(os.environ.get("CS_RUN_SANITIZERS") != "1", reason="set CS_RUN_SANITIZERS=1 (builds the host code with ASan + UBSan, several minutes)")
+def test_host_code_is_clean_under_address_and_undefined_behaviour_sanitizers():
+    """The scheduler, the rank-thread communicator, bucketing, the module tree and the optimizer run the two C++ test
+    programs on the CPU under AddressSanitizer and UndefinedBehaviorSanitizer without a report."""
+    from core_scheduler_b200.build import build_sanitized
+
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", ASAN_OPTIONS="detect_leaks=0:protect_shadow_gap=0:detect_odr_violation=0",
+               UBSAN_OPTIONS="print_stacktrace=1:halt_on_error=1")
+    for exe in build_sanitized():
+        args = [exe, "--threads", "2"] if "communication" in exe else [exe]
+        run = subprocess.run(args, env=env, capture_output=True, text=True, timeout=1800)
+        text = run.stdout + run.stderr
+        assert run.returncode == 0 and "0 failed" in text, text[-3000:]
+        assert "ERROR: AddressSanitizer" not in text and "runtime error:" not in text, text[-3000:]
