@@ -105,6 +105,9 @@ struct CS_API AllReduceBucket : Bucket {
   // the backward pass of the earlier layers is still running (module::AdamWImpl::step_partial).
   using ReducedCallback = std::function<void(const Scheduler &, const std::vector<Tensor> &, Task::Impl::Priority)>;
   void on_reduced(ReducedCallback callback) const;
+  // With `skip` the bucket only groups the tensors and hands them to the hook: for a consumer that reduces the
+  // gradients itself (the sharded optimizer's reduce-scatter + AdamW + all-gather kernel).
+  void skip_reduction(bool skip) const;
 
  private:
   struct Impl;

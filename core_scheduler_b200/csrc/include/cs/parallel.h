@@ -5,8 +5,9 @@
 // parallelism as future work (README.md:43-47). Here:
 //   * data parallel: GradientSync + AllReduceBucket (cs/models.h, cs/communication.h), with the
 //     gradient arena in symmetric memory the bucket all-reduce is this library's peer-memory kernel;
-//   * ZeRO: ZeroAdamW shards the AdamW moments across ranks and performs gradient
-//     reduce-scatter + AdamW + bf16 parameter all-gather as ONE kernel over peer memory;
+//   * ZeRO: ZeroAdamW shards the fp32 master weights and the AdamW moments across ranks (block-interleaved) and
+//     performs gradient reduce-scatter + AdamW + bf16 parameter all-gather as ONE kernel per bucket over peer memory,
+//     overlapped with the backward pass;
 //   * tensor parallel: column/row-parallel Linear with sequence-parallel activations.
 #pragma once
 #include "cs/communication.h"
@@ -24,26 +25,37 @@ CS_API std::shared_ptr<module::FlatParameters> flatten_symmetric(const Scheduler
 
 struct CS_API ZeroAdamWImpl : module::OptimizerModule {
   using Options = optimizer::AdamW::Options;
+  // Ownership granularity: block j of the arenas (kBlock elements) belongs to rank j % world.
+  static constexpr int64_t kBlock = 16384;
   // `flat` must come from flatten_symmetric (fp32 parameters, bf16 working copies).
   ZeroAdamWImpl(const Scheduler &scheduler, const module::Module &module, const std::shared_ptr<module::FlatParameters> &flat,
                 const communication::Comm &comm, const Options &options);
-  // Comm-stream task: barrier, fused reduce-scatter + AdamW + all-gather kernel, barrier; then
-  // refreshes the transposed working copies. Gradients are averaged over the ranks.
+  // Updates the parameters whose gradient handles are given: one kernel per contiguous arena range that reduce-scatters
+  // the range's gradients, runs AdamW on the blocks this rank owns and writes the new bf16 values into every rank's
+  // working copy. Driven per bucket from communication::AllReduceBucket::on_reduced (with an operation-free bucket) the
+  // optimizer runs beside the backward pass; step() then handles what is left.
+  void step_partial(const Scheduler &scheduler, const std::vector<Tensor> &gradients, Task::Impl::Priority priority);
+  // Whatever step_partial has not covered since the last step() (everything, without buckets). Gradients are averaged over the ranks.
   void step(const Scheduler &scheduler) override;
-  // All-gathers the fp32 master shards so that every rank holds the full fp32 parameters
-  // (needed before saving a checkpoint; training itself only reads the bf16 copies).
+  // All-gathers the fp32 master shards into the full fp32 parameter arena of every rank (needed before saving a model
+  // checkpoint; training itself only reads the bf16 copies, and the fp32 arena is not kept current in between).
   void gather_master(const Scheduler &scheduler);
+  // This rank's shards: `shard<rank>.m`, `.v` and `.master` (each shard_count() values: the rank's blocks back to back).
   [[nodiscard]] OrderedDict<std::string, Tensor> named_state_tensors() const override;
   [[nodiscard]] int64_t step_count() const override { return state_->options.t; }
   void set_step_count(int64_t t) override { state_->options.t = t; }
-  [[nodiscard]] int64_t shard_begin() const { return shard_begin_; }
   [[nodiscard]] int64_t shard_count() const { return shard_count_; }
 
  private:
   std::shared_ptr<module::FlatParameters> flat_;
   communication::Comm comm_;
   std::shared_ptr<optimizer::AdamW::State> state_;  // moments of this rank's shard only
-  int64_t shard_begin_{0}, shard_count_{0};
+  Tensor master_;                                   // fp32 master weights of this rank's shard only
+  int64_t shard_count_{0};
+  std::unordered_map<const void *, size_t> slot_of_grad_;
+  std::vector<Tensor> slot_params_;
+  std::vector<char> slot_done_;
+  bool step_open_{false};
 };
 CS_MODULE(ZeroAdamW);
 
@@ -127,6 +139,27 @@ struct CS_API TPGPT2Impl : module::Module {
   ReadOnlyTensor ce_labels_;
 };
 CS_MODULE(TPGPT2);
+
+// ---- the fused tensor-parallel kernels on plain tensors (one rank, current stream) ------------------------------
+// What TPBlock runs inside its tasks, usable on their own (and with the single-GPU loopback contexts of
+// cs/symmetric.h, where one rank at a time is emulated).
+struct GatherSignal {
+  uint32_t epoch{0};               // value the chunk flags reach
+  const uint32_t *flags{nullptr};  // word [owner * 8 + chunk] in this rank's signal pad
+  int chunks{0};
+};
+// all-gather of [rows, k] shards into `full` ([size * rows, k], in the arena) in `chunks` row chunks, each announced by a flag.
+CS_API GatherSignal gather_rows_chunked(communication::SymmetricContext &ctx, const at::Tensor &shard, const at::Tensor &full, int chunks);
+// y = full * W^T (or full * W when weight_is_rhs) by the GEMM whose loads wait for the chunk flags of `signal`;
+// second tensor: GELU(y) for kEpiGeluDual. `epilogue` is a kernels::kEpi* value; `aux` the pre-activation for kEpiDGelu.
+CS_API std::pair<at::Tensor, at::Tensor> gemm_on_gathered_chunks(communication::SymmetricContext &ctx, const at::Tensor &full, const at::Tensor &weight,
+                                                                 bool weight_is_rhs, int epilogue, const at::Tensor &aux, const GatherSignal &signal);
+// GEMM -> reduce-scatter, first half: the epilogue stores this rank's partial rows (bf16) into slot `rank` of every owner's
+// `slots` ([size, rows / size, n], in the arena).
+CS_API void gemm_scatter_to_slots(communication::SymmetricContext &ctx, const at::Tensor &x, const at::Tensor &weight, bool weight_is_rhs,
+                                  const at::Tensor &slots);
+// Second half: cross-rank barrier, then out = sum of the local slots (+ residual).
+CS_API at::Tensor sum_slots(communication::SymmetricContext &ctx, const at::Tensor &slots, const at::Tensor &residual);
 
 // Launches of this library's tensor-parallel collective kernels so far (row gathers and switch reduce-scatters on
 // symmetric memory); 0 means the generic collectives were used.

@@ -53,6 +53,8 @@ struct CS_API SymmetricContext {
   bool locate(const void *ptr, int64_t bytes, int64_t *offset) const;
   // Device-side barrier of all ranks on the current stream (bounded wait).
   void barrier();
+  // Loopback emulation only (see create_loopback_contexts): marks every peer flag of this rank's pad as set.
+  void prime_loopback();
   // Reusable staging block of at least `bytes` (same offset on every rank when every rank asks
   // for the same sizes in the same order).
   SymmetricBlock staging(int64_t bytes);
@@ -67,11 +69,21 @@ struct CS_API SymmetricContext {
   bool owns_{false};
   std::vector<void *> opened_;  // IPC mappings to close
   std::shared_ptr<void> vmm_;   // virtual-memory arena state (vmm::Arena), released with the context
+  std::shared_ptr<void> loopback_;  // shared owner of the emulated ranks' arenas and pads
+  friend std::vector<std::shared_ptr<SymmetricContext>> create_loopback_contexts(int, int64_t);
 };
 
 // Collective: every rank of `comm` must call it with the same size. Attaches the context to
 // the communicator (comm.impl()->symmetric).
 CS_API std::shared_ptr<SymmetricContext> create_symmetric_context(const Comm &comm, int64_t arena_bytes);
+
+// Single-GPU emulation of `ranks` ranks for kernel tests and profiling: one context per emulated rank, all in this
+// process and on the current device, over arenas and signal pads that are plain device allocations ("every peer's
+// memory" is local memory, so there is no multicast mapping). Only one emulated rank's kernel runs at a time, so the
+// peers' flags cannot arrive; prime_loopback() therefore marks every flag a kernel of this context may wait for as
+// already set. Call it before each launch, then run the same collective for rank 0, 1, ... in turn: after the last
+// one the arenas hold what a real run would have produced.
+CS_API std::vector<std::shared_ptr<SymmetricContext>> create_loopback_contexts(int ranks, int64_t arena_bytes);
 
 // The collectives below run on the current stream; they return false when the tensors are
 // not eligible (the caller then uses the library path).

@@ -453,33 +453,42 @@ __global__ void CS_COMM_BOUNDS pull_copy_kernel(PeerTable t, Handshake h, PullCo
 __global__ void CS_COMM_BOUNDS rs_adamw_ag_kernel(PeerTable t, Handshake h, ShardedAdamWArgs a) {
   open_collective(t, h, 15);
   const float gscale = a.clip_coef ? a.grad_scale * a.clip_coef[0] : a.grad_scale;
-  const int64_t vecs = a.shard_count / 4;  // four fp32 per vector
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < vecs;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t elem = a.shard_begin + i * 4;
+  // this rank's blocks that intersect the range: j0, j0 + size, ...
+  const int64_t first = a.range_begin / a.block, last = (a.range_end - 1) / a.block;
+  const int64_t j0 = first + ((t.rank - first % t.size) + t.size) % t.size;
+  const int64_t mine = j0 > last ? 0 : (last - j0) / t.size + 1;
+  const int64_t vecs_per_block = a.block / 4;  // four fp32 per vector
+  const int64_t items = mine * vecs_per_block;
+  for (int64_t w = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; w < items;
+       w += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t k = w / vecs_per_block, q = w - k * vecs_per_block;
+    const int64_t j = j0 + k * t.size;
+    const int64_t elem = j * a.block + q * 4;              // position in the arenas
+    if (elem < a.range_begin || elem >= a.range_end) continue;  // the range may start or end inside a block
+    const int64_t local = (j / t.size) * a.block + q * 4;  // position in this rank's shards
     const V4 gsum = reduce_vector<0>(t, a.grad_offset_bytes + elem * 4, 1.0f);
     const float g[4] = {__uint_as_float(gsum.x), __uint_as_float(gsum.y), __uint_as_float(gsum.z), __uint_as_float(gsum.w)};
-    float4 w = *reinterpret_cast<float4 *>(a.master + i * 4);
-    float4 m = *reinterpret_cast<float4 *>(a.exp_avg + i * 4);
-    float4 v = *reinterpret_cast<float4 *>(a.exp_avg_sq + i * 4);
-    float *wp = &w.x, *mp = &m.x, *vp = &v.x;
+    float4 wv = *reinterpret_cast<float4 *>(a.master + local);
+    float4 m = *reinterpret_cast<float4 *>(a.exp_avg + local);
+    float4 v = *reinterpret_cast<float4 *>(a.exp_avg_sq + local);
+    float *wp = &wv.x, *mp = &m.x, *vp = &v.x;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const float grad = g[k] * gscale;
-      float wt = wp[k];
+    for (int i = 0; i < 4; ++i) {
+      const float grad = g[i] * gscale;
+      float wt = wp[i];
       wt -= a.lr * a.weight_decay * wt;
-      const float mt = a.beta1 * mp[k] + (1.f - a.beta1) * grad;
-      const float vt = a.beta2 * vp[k] + (1.f - a.beta2) * grad * grad;
+      const float mt = a.beta1 * mp[i] + (1.f - a.beta1) * grad;
+      const float vt = a.beta2 * vp[i] + (1.f - a.beta2) * grad * grad;
       wt -= a.lr * (mt * a.inv_bias_correction1) / (sqrtf(vt * a.inv_bias_correction2) + a.eps);
-      wp[k] = wt;
-      mp[k] = mt;
-      vp[k] = vt;
+      wp[i] = wt;
+      mp[i] = mt;
+      vp[i] = vt;
     }
-    *reinterpret_cast<float4 *>(a.master + i * 4) = w;
-    *reinterpret_cast<float4 *>(a.exp_avg + i * 4) = m;
-    *reinterpret_cast<float4 *>(a.exp_avg_sq + i * 4) = v;
+    *reinterpret_cast<float4 *>(a.master + local) = wv;
+    *reinterpret_cast<float4 *>(a.exp_avg + local) = m;
+    *reinterpret_cast<float4 *>(a.exp_avg_sq + local) = v;
     if (a.lp_offset_bytes >= 0) {
-      __nv_bfloat162 lo = __floats2bfloat162_rn(w.x, w.y), hi = __floats2bfloat162_rn(w.z, w.w);
+      __nv_bfloat162 lo = __floats2bfloat162_rn(wv.x, wv.y), hi = __floats2bfloat162_rn(wv.z, wv.w);
       const uint32_t p0 = *reinterpret_cast<uint32_t *>(&lo), p1 = *reinterpret_cast<uint32_t *>(&hi);
       const int64_t off = a.lp_offset_bytes + elem * 2;
       if (t.mc) {
@@ -593,10 +602,11 @@ int symm_pull_copy(stream_t stream, const PeerTable &t, const Handshake &h, cons
 
 int symm_reduce_scatter_adamw_all_gather(stream_t stream, const PeerTable &t, const Handshake &h, const ShardedAdamWArgs &a,
                                          int *blocks) {
-  if (a.shard_count % 4 != 0 || a.shard_begin % 4 != 0 || a.grad_offset_bytes % 16 != 0 ||
-      (a.lp_offset_bytes >= 0 && a.lp_offset_bytes % 16 != 0) || a.shard_count <= 0)
+  if (a.block < 8 || (a.block & (a.block - 1)) != 0 || a.range_begin % 4 != 0 || a.range_end % 4 != 0 || a.range_end <= a.range_begin ||
+      a.grad_offset_bytes % 16 != 0 || (a.lp_offset_bytes >= 0 && a.lp_offset_bytes % 16 != 0))
     return static_cast<int>(cudaErrorInvalidValue);
-  const int grid = comm_grid(a.shard_count / 4 * kUnroll);  // one vector per thread and trip: more blocks per byte
+  const int64_t per_rank = (a.range_end - a.range_begin + t.size - 1) / t.size;
+  const int grid = comm_grid(per_rank / 4 * kUnroll);  // one vector per thread and trip: more blocks per byte
   *blocks = grid;
   rs_adamw_ag_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(t, h, a);
   return finish_launch(1);

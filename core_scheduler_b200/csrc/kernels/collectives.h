@@ -120,16 +120,20 @@ struct PullCopyArgs {
 };
 int symm_pull_copy(stream_t stream, const PeerTable &t, const Handshake &h, const PullCopyArgs &args, int *blocks);
 
-// ZeRO step in one kernel: reduce-scatter of a gradient range (switch reduction or pull, fp32
-// accumulate), AdamW on this rank's shard of (master weights, moments), and all-gather of the
+// ZeRO step in one kernel for the arena range [range_begin, range_end) (elements): reduce-scatter of the gradients
+// (switch reduction or pull, fp32 accumulate), AdamW on the part of the range this rank owns, and all-gather of the
 // updated bf16 working copy by writing it into every rank's bf16 arena.
+// Ownership is interleaved in blocks of `block` elements (a power of two): block j of the arena belongs to rank
+// j % size and is element range [(j / size) * block, ...) of that rank's local master / moment shards. Any range
+// therefore splits evenly over the ranks, whatever its position, and the shard layout does not depend on how the
+// gradients are bucketed.
 struct ShardedAdamWArgs {
   int64_t grad_offset_bytes;   // gradient arena inside the symmetric arena (fp32)
   int64_t lp_offset_bytes;     // bf16 working-copy arena inside the symmetric arena (may be < 0: none)
-  float *master;               // this rank's shard: fp32 master weights, length shard_count
-  float *exp_avg, *exp_avg_sq;
-  int64_t shard_begin;         // first element of this rank's shard inside the arenas
-  int64_t shard_count;
+  float *master;               // this rank's shard: fp32 master weights
+  float *exp_avg, *exp_avg_sq; // this rank's shard of the moments
+  int64_t range_begin, range_end;
+  int64_t block;
   float lr, beta1, beta2, eps, weight_decay, inv_bias_correction1, inv_bias_correction2, grad_scale;
   const float *clip_coef;
 };

@@ -18,6 +18,7 @@
 #include "cs/parallel.h"
 #include "cs/symmetric.h"
 #include "src/vmm.h"
+#include "src/symm_internal.h"
 #include "kernels/collectives.h"
 #include "kernels/api.h"
 
@@ -582,7 +583,15 @@ PYBIND11_MODULE(_C, m) {
         b.on_reduced([weak](const Scheduler &s, const std::vector<Tensor> &grads, Task::Impl::Priority prio) {
           if (auto o = weak.lock()) o->step_partial(s, grads, prio);
         });
-      }, "AdamW over flat arenas: update every bucket's parameters as soon as the bucket has been reduced");
+      }, "AdamW over flat arenas: update every bucket's parameters as soon as the bucket has been reduced")
+      .def("attach_sharded_optimizer", [](const communication::AllReduceBucket &b, const std::shared_ptr<parallel::ZeroAdamWImpl> &opt) {
+        // the bucket only groups the gradients; the optimizer's kernel reduce-scatters them itself
+        std::weak_ptr<parallel::ZeroAdamWImpl> weak = opt;
+        b.skip_reduction(true);
+        b.on_reduced([weak](const Scheduler &s, const std::vector<Tensor> &grads, Task::Impl::Priority prio) {
+          if (auto o = weak.lock()) o->step_partial(s, grads, prio);
+        });
+      }, "ZeroAdamW: reduce-scatter + AdamW + all-gather of every bucket as soon as the backward pass has produced it");
   m.def("all_gather", &communication::AllGather::run);
   m.def("reduce_scatter", [](const Scheduler &s, const Comm &c, const std::vector<Tensor> &recv,
                              const std::vector<std::vector<ReadOnlyTensor>> &send, const std::string &op) {
@@ -685,7 +694,75 @@ PYBIND11_MODULE(_C, m) {
       .def("release", [](SymmetricContext &c, int64_t offset, int64_t bytes) {
         c.release(communication::SymmetricBlock{offset, bytes});
       })
-      .def("check_status", [](SymmetricContext &c) { communication::check_device_status(c, "python"); });
+      .def("check_status", [](SymmetricContext &c) { communication::check_device_status(c, "python"); })
+      // ---- direct calls on torch's current stream: for the single-GPU loopback contexts and kernel tests ----
+      .def("prime_loopback", &SymmetricContext::prime_loopback)
+      .def("all_reduce_", [](SymmetricContext &c, std::vector<at::Tensor> ranges, const std::string &op) {
+        return communication::symmetric_all_reduce(c, ranges, op == "avg" ? communication::kAVG : communication::kSUM);
+      }, py::arg("ranges"), py::arg("op") = "sum")
+      .def("all_gather_", [](SymmetricContext &c, std::vector<at::Tensor> recv, at::Tensor send) {
+        return communication::symmetric_all_gather(c, {recv}, {send});
+      })
+      .def("reduce_scatter_", [](SymmetricContext &c, at::Tensor recv, std::vector<at::Tensor> send, const std::string &op) {
+        return communication::symmetric_reduce_scatter(c, {recv}, {send}, op == "avg" ? communication::kAVG : communication::kSUM);
+      }, py::arg("recv"), py::arg("send"), py::arg("op") = "sum")
+      .def("all_to_all_", [](SymmetricContext &c, std::vector<at::Tensor> recv, std::vector<at::Tensor> send) {
+        return communication::symmetric_all_to_all(c, recv, send);
+      })
+      .def("gather_rows_chunked", [](SymmetricContext &c, at::Tensor shard, at::Tensor full, int chunks) {
+        const auto sig = parallel::gather_rows_chunked(c, shard, full, chunks);
+        return py::make_tuple(sig.epoch, reinterpret_cast<uintptr_t>(sig.flags), sig.chunks);
+      })
+      .def("gemm_on_gathered_chunks", [](SymmetricContext &c, at::Tensor full, at::Tensor weight, bool weight_is_rhs, int epilogue,
+                                          py::object aux, py::tuple signal) {
+        parallel::GatherSignal sig;
+        sig.epoch = signal[0].cast<uint32_t>();
+        sig.flags = reinterpret_cast<const uint32_t *>(signal[1].cast<uintptr_t>());
+        sig.chunks = signal[2].cast<int>();
+        auto r = parallel::gemm_on_gathered_chunks(c, full, weight, weight_is_rhs, epilogue, aux.is_none() ? at::Tensor{} : aux.cast<at::Tensor>(), sig);
+        return py::make_tuple(r.first, r.second.defined() ? py::cast(r.second) : py::none());
+      }, py::arg("full"), py::arg("weight"), py::arg("weight_is_rhs") = false, py::arg("epilogue") = 0, py::arg("aux") = py::none(),
+           py::arg("signal"))
+      .def("gemm_scatter_to_slots", &parallel::gemm_scatter_to_slots)
+      .def("sum_slots", [](SymmetricContext &c, at::Tensor slots, py::object residual) {
+        return parallel::sum_slots(c, slots, residual.is_none() ? at::Tensor{} : residual.cast<at::Tensor>());
+      }, py::arg("slots"), py::arg("residual") = py::none())
+      .def("sharded_adamw_", [](SymmetricContext &c, at::Tensor grads, py::object lp, at::Tensor master_shard, at::Tensor m, at::Tensor v,
+                                int64_t range_begin, int64_t range_end, int64_t block, double lr, double beta1, double beta2, double eps,
+                                double wd, int64_t step, double grad_scale) {
+        // reduce-scatter + AdamW + all-gather in one kernel for the arena range [range_begin, range_end): this rank updates
+        // the blocks it owns (block j belongs to rank j % size; grads fp32 and lp bf16 are arena tensors, the shards local)
+        kernels::ShardedAdamWArgs a{};
+        int64_t g_off = 0, l_off = -1;
+        CS_ASSERT_TRUE(c.locate(grads.data_ptr(), static_cast<int64_t>(grads.nbytes()), &g_off), "grads must live in the arena");
+        if (!lp.is_none()) {
+          at::Tensor l = lp.cast<at::Tensor>();
+          CS_ASSERT_TRUE(c.locate(l.data_ptr(), static_cast<int64_t>(l.nbytes()), &l_off), "the bf16 copy must live in the arena");
+        }
+        a.grad_offset_bytes = g_off;
+        a.lp_offset_bytes = l_off;
+        a.master = master_shard.data_ptr<float>();
+        a.exp_avg = m.data_ptr<float>();
+        a.exp_avg_sq = v.data_ptr<float>();
+        a.range_begin = range_begin;
+        a.range_end = range_end;
+        a.block = block;
+        a.lr = static_cast<float>(lr);
+        a.beta1 = static_cast<float>(beta1);
+        a.beta2 = static_cast<float>(beta2);
+        a.eps = static_cast<float>(eps);
+        a.weight_decay = static_cast<float>(wd);
+        a.inv_bias_correction1 = static_cast<float>(1.0 / (1.0 - std::pow(beta1, static_cast<double>(step))));
+        a.inv_bias_correction2 = static_cast<float>(1.0 / (1.0 - std::pow(beta2, static_cast<double>(step))));
+        a.grad_scale = static_cast<float>(grad_scale);
+        int blocks = 0;
+        const auto h = communication::begin_collective(c, kernels::kChanZero);
+        const int code = kernels::symm_reduce_scatter_adamw_all_gather(c10::cuda::getCurrentCUDAStream().stream(), communication::table_of(c), h, a, &blocks);
+        CS_ASSERT_TRUE(code == 0, "fused reduce-scatter/AdamW/all-gather launch failed: ", cuda_error_string(code));
+        communication::end_collective(c, kernels::kChanZero, blocks);
+      });
+  m.def("create_loopback_contexts", &communication::create_loopback_contexts, py::arg("ranks"), py::arg("arena_bytes"),
+        "One symmetric context per emulated rank, all on the current GPU (kernel tests and profiling on a single device)");
   m.def("duplicate_descriptor", &communication::vmm::duplicate_descriptor, py::arg("pid"), py::arg("fd"),
         "Duplicates descriptor `fd` of process `pid` into this process (how arena handles cross process boundaries); -1 on failure");
   m.def("create_symmetric_context", &communication::create_symmetric_context, py::arg("comm"), py::arg("arena_bytes"));
@@ -709,8 +786,8 @@ PYBIND11_MODULE(_C, m) {
            py::arg("lr") = 1e-3, py::arg("beta1") = 0.9, py::arg("beta2") = 0.999, py::arg("eps") = 1e-8,
            py::arg("weight_decay") = 1e-2)
       .def("gather_master", &parallel::ZeroAdamWImpl::gather_master)
-      .def("shard_begin", &parallel::ZeroAdamWImpl::shard_begin)
-      .def("shard_count", &parallel::ZeroAdamWImpl::shard_count);
+      .def("shard_count", &parallel::ZeroAdamWImpl::shard_count)
+      .def_property_readonly_static("block", [](py::object) { return parallel::ZeroAdamWImpl::kBlock; });
 
   py::class_<parallel::TPGPT2Impl, module::Module, std::shared_ptr<parallel::TPGPT2Impl>>(m, "TPGPT2")
       .def(py::init<const Scheduler &, const models::GPT2Config &, const Comm &>())

@@ -263,10 +263,13 @@ struct AllReduceBucket::Impl {
   int64_t pending_bytes{0};
   int64_t launches{0};
   ReducedCallback callback{};
+  bool skip_reduction{false};
 };
 
 AllReduceBucket::AllReduceBucket(int64_t byteThreshold, Operation operation)
-    : impl_{std::make_shared<Impl>(Impl{byteThreshold, operation, {}, 0, 0, {}})} {}
+    : impl_{std::make_shared<Impl>(Impl{byteThreshold, operation, {}, 0, 0, {}, false})} {}
+
+void AllReduceBucket::skip_reduction(bool skip) const { impl_->skip_reduction = skip; }
 
 void AllReduceBucket::on_reduced(ReducedCallback callback) const { impl_->callback = std::move(callback); }
 
@@ -281,7 +284,7 @@ void AllReduceBucket::push_back(const Scheduler &scheduler, const Comm &comm, Te
 
 void AllReduceBucket::sync(const Scheduler &scheduler, const Comm &comm) const {
   if (impl_->pending.empty()) return;
-  const bool alone = comm.get_size() <= 1;
+  const bool alone = comm.get_size() <= 1 || impl_->skip_reduction;
   if (!alone) AllReduce::run_inplace(scheduler, comm, impl_->pending, impl_->op);
   ++impl_->launches;
   // The communication stream has the highest priority and the longest re-join gap, so work hooked in here runs

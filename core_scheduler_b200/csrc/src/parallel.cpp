@@ -3,6 +3,7 @@
 
 #include <c10/cuda/CUDAStream.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <unordered_map>
@@ -34,55 +35,92 @@ ZeroAdamWImpl::ZeroAdamWImpl(const Scheduler &scheduler, const module::Module &m
   bind(&module);
   flat->params.wait();
   CS_ASSERT_TRUE(flat->params.impl()->tensor.scalar_type() == at::kFloat, "ZeroAdamW needs fp32 master parameters");
-  const int64_t world = comm.get_size();
-  CS_ASSERT_TRUE(flat->total % (world * 4) == 0, "arena length must split into 4-element aligned shards");
-  shard_count_ = flat->total / world;
-  shard_begin_ = shard_count_ * comm.get_rank();
-  // moments only for this rank's shard
+  const int64_t world = comm.get_size(), rank = comm.get_rank();
+  // Ownership of the arena is interleaved in blocks: block j belongs to rank j % world. This rank's shard holds its
+  // blocks back to back (whole blocks; the last one may reach past the arena's end and is then partly unused).
+  const int64_t blocks = (flat->total + kBlock - 1) / kBlock;
+  const int64_t mine = blocks > rank ? (blocks - rank + world - 1) / world : 0;
+  shard_count_ = std::max<int64_t>((blocks + world - 1) / world, 1) * kBlock;  // the same length on every rank
   Tensor shard;
-  submit(scheduler, "cs::parallel::ZeroAdamW::shard_view", Task::Impl::kMain, Task::Impl::kCompute, {shard}, {flat->params},
-         [shard, flat, b = shard_begin_, n = shard_count_](const FnTask &) {
-           shard.impl()->tensor = flat->params.impl()->tensor.narrow(0, b, n);
+  submit(scheduler, "cs::parallel::ZeroAdamW::shard_master", Task::Impl::kMain, Task::Impl::kCompute, {shard}, {flat->params},
+         [shard, flat, rank, world, mine, n = shard_count_](const FnTask &) {
+           const at::Tensor &P = flat->params.impl()->tensor;
+           at::Tensor w = at::zeros({n}, P.options());
+           for (int64_t k = 0; k < mine; ++k) {  // copy block rank + k * world
+             const int64_t begin = (rank + k * world) * kBlock;
+             const int64_t len = std::min<int64_t>(kBlock, flat->total - begin);
+             if (len > 0) w.narrow(0, k * kBlock, len).copy_(P.narrow(0, begin, len));
+           }
+           shard.impl()->tensor = w;
          });
+  master_ = shard;
   state_ = optimizer::AdamW::init(scheduler, shard, options);
   states_.insert("__shard__", state_);
+  auto named = module.named_parameters();
+  for (size_t i = 0; i < flat->slots.size(); ++i) {
+    slot_params_.push_back(named[flat->slots[i].key]);
+    slot_of_grad_.emplace(flat->grad_handles[i].impl().get(), i);
+  }
 }
 
 OrderedDict<std::string, Tensor> ZeroAdamWImpl::named_state_tensors() const {
   OrderedDict<std::string, Tensor> out;
   out.insert(str_cat("shard", comm_.get_rank(), ".m"), state_->tensors.m);
   out.insert(str_cat("shard", comm_.get_rank(), ".v"), state_->tensors.v);
+  out.insert(str_cat("shard", comm_.get_rank(), ".master"), master_);
   return out;
 }
 
-void ZeroAdamWImpl::step(const Scheduler &scheduler) {
+void ZeroAdamWImpl::step_partial(const Scheduler &scheduler, const std::vector<Tensor> &gradients, Task::Impl::Priority priority) {
   const module::Module *m = model();
   CS_ASSERT_TRUE(m != nullptr, "the optimised module is gone");
-  auto ctx = comm_.impl()->symmetric;
-  const int64_t t = ++state_->options.t;
-  auto named = m->named_parameters();
-  std::vector<Tensor> touched;
-  for (auto &slot : flat_->slots) touched.push_back(named[slot.key]);
-  {
-    std::vector<ReadOnlyTensor> writers(flat_->grad_handles.begin(), flat_->grad_handles.end());
-    submit(scheduler, "cs::parallel::ZeroAdamW::join_gradients", Task::Impl::kComm, Task::Impl::kCompute, {flat_->grads}, writers,
-           [handles = flat_->grad_handles](const FnTask &) {
-             for (auto &h : handles)
-               if (h.impl()->fresh && h.impl()->tensor.defined()) h.impl()->tensor.zero_();
-           });
+  if (!step_open_) {
+    step_open_ = true;
+    ++state_->options.t;
+    slot_done_.assign(flat_->slots.size(), 0);
   }
-  std::vector<Tensor> outs{flat_->params, flat_->lp, state_->tensors.m, state_->tensors.v};
-  outs.insert(outs.end(), touched.begin(), touched.end());
-  submit(scheduler, "cs::parallel::ZeroAdamW::step", Task::Impl::kComm, Task::Impl::kNccl, outs, {flat_->grads},
-         [flat = flat_, state = state_, ctx, t, b = shard_begin_, n = shard_count_, world = comm_.get_size(),
-          touched](const FnTask &) {
+  std::vector<size_t> picked;
+  for (auto &g : gradients) {
+    auto it = slot_of_grad_.find(g.impl().get());
+    if (it == slot_of_grad_.end() || slot_done_[it->second]) continue;
+    slot_done_[it->second] = 1;
+    picked.push_back(it->second);
+  }
+  if (picked.empty()) return;
+  std::sort(picked.begin(), picked.end());
+  struct Range {
+    int64_t begin, end;
+  };
+  std::vector<Range> ranges;  // runs of neighbouring slots are contiguous in the arenas (padding included)
+  std::vector<Tensor> outs;
+  std::vector<ReadOnlyTensor> ins;
+  auto slot_end = [&](size_t i) { return i + 1 < flat_->slots.size() ? flat_->slots[i + 1].offset : flat_->total; };
+  for (size_t k = 0; k < picked.size(); ++k) {
+    const size_t i = picked[k];
+    if (k > 0 && picked[k - 1] + 1 == i)
+      ranges.back().end = slot_end(i);
+    else
+      ranges.push_back({flat_->slots[i].offset, slot_end(i)});
+    outs.push_back(slot_params_[i]);
+    ins.push_back(flat_->grad_handles[i]);
+  }
+  outs.push_back(master_);
+  outs.push_back(state_->tensors.m);
+  outs.push_back(state_->tensors.v);
+  auto ctx = comm_.impl()->symmetric;
+  const int64_t t = state_->options.t;
+  submit(scheduler, "cs::parallel::ZeroAdamW::step(reduce-scatter + AdamW + all-gather)", priority, Task::Impl::kNccl, outs, ins,
+         [flat = flat_, state = state_, master = master_, ctx, t, ranges, handles = ins, world = comm_.get_size(),
+          touched = std::vector<Tensor>(outs.begin(), outs.end() - 3)](const FnTask &) {
            const auto &o = state->options;
            const double bc1 = 1.0 - std::pow(o.beta1, static_cast<double>(t));
            const double bc2 = 1.0 - std::pow(o.beta2, static_cast<double>(t));
-           at::Tensor &P = flat->params.impl()->tensor;
            at::Tensor &G = flat->grads.impl()->tensor;
            at::Tensor &L = flat->lp.impl()->tensor;
-           if (ctx && P.is_cuda()) {
+           at::Tensor &W = master.impl()->tensor;
+           for (auto &h : handles)  // a slot nobody wrote this step must not contribute stale values
+             if (h.impl()->fresh && h.impl()->tensor.defined()) const_cast<at::Tensor &>(h.impl()->tensor).zero_();
+           if (ctx && W.is_cuda() && world > 1) {
              int64_t g_off = 0, l_off = -1;
              CS_ASSERT_TRUE(ctx->locate(G.data_ptr(), static_cast<int64_t>(G.nbytes()), &g_off),
                             "ZeroAdamW needs the gradient arena in symmetric memory (use flatten_symmetric)");
@@ -90,48 +128,56 @@ void ZeroAdamWImpl::step(const Scheduler &scheduler) {
                CS_ASSERT_TRUE(ctx->locate(L.data_ptr(), static_cast<int64_t>(L.nbytes()), &l_off),
                               "ZeroAdamW needs the bf16 arena in symmetric memory (use flatten_symmetric)");
              const kernels::PeerTable table = communication::table_of(*ctx);
-             kernels::ShardedAdamWArgs a{};
-             a.grad_offset_bytes = g_off;
-             a.lp_offset_bytes = l_off;
-             a.master = P.data_ptr<float>() + b;
-             a.exp_avg = state->tensors.m.impl()->tensor.data_ptr<float>();
-             a.exp_avg_sq = state->tensors.v.impl()->tensor.data_ptr<float>();
-             a.shard_begin = b;
-             a.shard_count = n;
-             a.lr = static_cast<float>(o.lr);
-             a.beta1 = static_cast<float>(o.beta1);
-             a.beta2 = static_cast<float>(o.beta2);
-             a.eps = static_cast<float>(o.eps);
-             a.weight_decay = static_cast<float>(o.weight_decay);
-             a.inv_bias_correction1 = static_cast<float>(1.0 / bc1);
-             a.inv_bias_correction2 = static_cast<float>(1.0 / bc2);
-             a.grad_scale = static_cast<float>(o.grad_scale / static_cast<double>(world));
-             a.clip_coef = state->clip_coef.impl()->tensor.defined() ? state->clip_coef.impl()->tensor.data_ptr<float>() : nullptr;
-             // one launch: "every rank's gradients are complete" and "every rank's bf16 arena received all
-             // shards" are the barriers at the two ends of the kernel
-             int blocks = 0;
-             const auto h = communication::begin_collective(*ctx, kernels::kChanZero);
-             const int code = kernels::symm_reduce_scatter_adamw_all_gather(c10::cuda::getCurrentCUDAStream().stream(), table, h, a, &blocks);
-             CS_ASSERT_TRUE(code == 0, "fused reduce-scatter/AdamW/all-gather launch failed: ", cuda_error_string(code));
-             communication::end_collective(*ctx, kernels::kChanZero, blocks);
+             for (auto &r : ranges) {
+               kernels::ShardedAdamWArgs a{};
+               a.grad_offset_bytes = g_off;
+               a.lp_offset_bytes = l_off;
+               a.master = W.data_ptr<float>();
+               a.exp_avg = state->tensors.m.impl()->tensor.data_ptr<float>();
+               a.exp_avg_sq = state->tensors.v.impl()->tensor.data_ptr<float>();
+               a.range_begin = r.begin;
+               a.range_end = r.end;
+               a.block = kBlock;
+               a.lr = static_cast<float>(o.lr);
+               a.beta1 = static_cast<float>(o.beta1);
+               a.beta2 = static_cast<float>(o.beta2);
+               a.eps = static_cast<float>(o.eps);
+               a.weight_decay = static_cast<float>(o.weight_decay);
+               a.inv_bias_correction1 = static_cast<float>(1.0 / bc1);
+               a.inv_bias_correction2 = static_cast<float>(1.0 / bc2);
+               a.grad_scale = static_cast<float>(o.grad_scale / static_cast<double>(world));
+               a.clip_coef = state->clip_coef.impl()->tensor.defined() ? state->clip_coef.impl()->tensor.data_ptr<float>() : nullptr;
+               // one launch: "every rank's gradients of this range are complete" and "every rank's bf16 arena received
+               // the updated range" are the barriers at the two ends of the kernel
+               int blocks = 0;
+               const auto h = communication::begin_collective(*ctx, kernels::kChanZero);
+               const int code = kernels::symm_reduce_scatter_adamw_all_gather(c10::cuda::getCurrentCUDAStream().stream(), table, h, a, &blocks);
+               CS_ASSERT_TRUE(code == 0, "fused reduce-scatter/AdamW/all-gather launch failed: ", cuda_error_string(code));
+               communication::end_collective(*ctx, kernels::kChanZero, blocks);
+             }
            } else {
-             // Single rank (or CPU): plain sharded update on the whole arena.
+             // Single rank (or CPU): the same update on the whole range (the shard is the arena, block by block).
              CS_ASSERT_TRUE(world == 1, "ZeroAdamW across ranks needs symmetric memory on CUDA devices");
-             at::Tensor g = G.to(at::kFloat) * o.grad_scale;
-             at::Tensor w = P, mm = state->tensors.m.impl()->tensor, vv = state->tensors.v.impl()->tensor;
-             w.mul_(1 - o.lr * o.weight_decay);
-             mm.mul_(o.beta1).add_(g, 1 - o.beta1);
-             vv.mul_(o.beta2).addcmul_(g, g, 1 - o.beta2);
-             w.sub_((mm / bc1) / ((vv / bc2).sqrt() + o.eps) * o.lr);
-             if (L.defined()) L.copy_(w);
+             at::Tensor mm = state->tensors.m.impl()->tensor, vv = state->tensors.v.impl()->tensor;
+             for (auto &r : ranges) {
+               const int64_t n = r.end - r.begin;
+               at::Tensor g = G.narrow(0, r.begin, n).to(at::kFloat) * o.grad_scale;
+               at::Tensor w = W.narrow(0, r.begin, n), m1 = mm.narrow(0, r.begin, n), v1 = vv.narrow(0, r.begin, n);
+               w.mul_(1 - o.lr * o.weight_decay);
+               m1.mul_(o.beta1).add_(g, 1 - o.beta1);
+               v1.mul_(o.beta2).addcmul_(g, g, 1 - o.beta2);
+               w.sub_((m1 / bc1) / ((v1 / bc2).sqrt() + o.eps) * o.lr);
+               if (L.defined()) L.narrow(0, r.begin, n).copy_(w);
+               flat->params.impl()->tensor.narrow(0, r.begin, n).copy_(w);
+             }
            }
            for (auto &p : touched) {
              auto &impl = *p.impl();
              ++impl.version;
              if (impl.lp.defined()) impl.lp_version = impl.version;
              if (impl.lp_t.defined()) {
-               // the transpose is rebuilt from the fresh bf16 copy (the fp32 arena is only
-               // authoritative inside this rank's shard)
+               // the transpose is rebuilt from the fresh bf16 copy (the fp32 arena is not kept current between
+               // gather_master calls)
                impl.lp_t.copy_(impl.lp.t());
                impl.lp_t_version = impl.version;
              }
@@ -139,20 +185,44 @@ void ZeroAdamWImpl::step(const Scheduler &scheduler) {
          });
 }
 
+void ZeroAdamWImpl::step(const Scheduler &scheduler) {
+  // update whatever the buckets have not handed over yet (everything, when no bucket drives this optimizer)
+  std::vector<Tensor> rest;
+  if (!step_open_) {
+    rest.assign(flat_->grad_handles.begin(), flat_->grad_handles.end());
+  } else {
+    for (size_t i = 0; i < flat_->slots.size(); ++i)
+      if (!slot_done_[i]) rest.push_back(flat_->grad_handles[i]);
+  }
+  step_partial(scheduler, rest, Task::Impl::kComm);
+  step_open_ = false;
+}
+
 void ZeroAdamWImpl::gather_master(const Scheduler &scheduler) {
   const int64_t world = comm_.get_size();
   if (world <= 1) return;
   std::vector<Tensor> recv(static_cast<size_t>(world));
-  Tensor send;
+  Tensor gathered;
   std::vector<Tensor> outs = recv;
-  outs.push_back(send);
-  submit(scheduler, "cs::parallel::ZeroAdamW::shard_views", Task::Impl::kMain, Task::Impl::kCompute, outs, {flat_->params},
-         [flat = flat_, recv, send, n = shard_count_, b = shard_begin_](const FnTask &) {
-           const at::Tensor &P = flat->params.impl()->tensor;
-           for (size_t r = 0; r < recv.size(); ++r) recv[r].impl()->tensor = P.narrow(0, static_cast<int64_t>(r) * n, n);
-           send.impl()->tensor = P.narrow(0, b, n).clone();
+  outs.push_back(gathered);
+  submit(scheduler, "cs::parallel::ZeroAdamW::gather_buffers", Task::Impl::kMain, Task::Impl::kCompute, outs, {master_},
+         [recv, gathered, master = master_, world](const FnTask &) {
+           const at::Tensor &w = master.impl()->tensor;
+           gathered.impl()->tensor = at::empty({world, w.numel()}, w.options());
+           for (size_t r = 0; r < recv.size(); ++r) recv[r].impl()->tensor = gathered.impl()->tensor.select(0, static_cast<int64_t>(r));
          });
-  communication::AllGather::run(scheduler, comm_, {recv}, {send});
+  communication::AllGather::run(scheduler, comm_, {recv}, {master_});
+  std::vector<ReadOnlyTensor> ins(recv.begin(), recv.end());
+  ins.push_back(gathered);
+  submit(scheduler, "cs::parallel::ZeroAdamW::unshard_master", Task::Impl::kComm, Task::Impl::kCompute, {flat_->params}, ins,
+         [flat = flat_, gathered, world](const FnTask &) {
+           // [world, blocks_per_rank, block] -> arena order [blocks_per_rank, world, block]
+           const at::Tensor &g = gathered.impl()->tensor;
+           const int64_t per = g.size(1) / kBlock;
+           at::Tensor ordered = g.view({world, per, kBlock}).permute({1, 0, 2}).reshape({-1});
+           at::Tensor &P = flat->params.impl()->tensor;
+           P.copy_(ordered.narrow(0, 0, P.numel()));
+         });
 }
 
 // ======================================================================================
@@ -341,6 +411,106 @@ Tensor row_parallel_symmetric(const Scheduler &scheduler, const communication::C
   return out;
 }
 
+}  // namespace
+
+// ---- the fused kernels on plain tensors, for one rank, on the current stream ---------------------------------
+GatherSignal gather_rows_chunked(communication::SymmetricContext &ctx, const at::Tensor &shard, const at::Tensor &full, int chunks) {
+  CS_ASSERT_TRUE(shard.is_contiguous() && shard.dim() == 2 && full.dim() == 2 && full.size(0) == shard.size(0) * ctx.size &&
+                     full.size(1) == shard.size(1) && full.scalar_type() == shard.scalar_type(),
+                 "gather_rows_chunked: full must be [size * rows, k] of the shard's dtype");
+  int64_t off = 0;
+  CS_ASSERT_TRUE(ctx.locate(full.data_ptr(), static_cast<int64_t>(full.nbytes()), &off), "the gather buffer must live in the symmetric arena");
+  int blocks = 0;
+  const auto h = communication::begin_collective(ctx, kernels::kChanGemmGather);
+  const int code = kernels::symm_all_gather_chunked(c10::cuda::getCurrentCUDAStream().stream(), communication::table_of(ctx), h, shard.data_ptr(),
+                                                    off, static_cast<int64_t>(shard.nbytes()), chunks, &blocks);
+  CS_ASSERT_TRUE(code == 0, "chunked row gather launch failed: ", cuda_error_string(code));
+  communication::end_collective(ctx, kernels::kChanGemmGather, blocks);
+  GatherSignal signal;
+  signal.epoch = h.epoch;
+  signal.flags = ctx.flags[ctx.rank] + kernels::kChannelBase + kernels::kChanGemmGather * kernels::kChannelWords + kernels::kChunkFlags;
+  signal.chunks = chunks;
+  return signal;
+}
+
+std::pair<at::Tensor, at::Tensor> gemm_on_gathered_chunks(communication::SymmetricContext &ctx, const at::Tensor &full, const at::Tensor &weight,
+                                                          bool weight_is_rhs, int epilogue, const at::Tensor &aux, const GatherSignal &signal) {
+  const int64_t m = full.size(0), k = full.size(1);
+  const int64_t n = weight_is_rhs ? weight.size(1) : weight.size(0);
+  at::Tensor y = at::empty({m, n}, full.options());
+  at::Tensor y2, a2;
+  kernels::GemmArgs g{};
+  g.a = full.data_ptr();
+  g.b = weight.data_ptr();
+  g.d = y.data_ptr();
+  g.m = m;
+  g.n = n;
+  g.k = k;
+  g.lda = k;
+  g.ldb = weight_is_rhs ? n : k;
+  g.ldd = n;
+  g.layout = weight_is_rhs ? kernels::kTM : kernels::kTN;
+  g.epilogue = epilogue;
+  if (epilogue == kernels::kEpiGeluDual) {
+    y2 = at::empty_like(y);
+    g.d2 = y2.data_ptr();
+  }
+  if (aux.defined()) {
+    a2 = aux.reshape({m, n}).contiguous();
+    g.aux = a2.data_ptr();
+  }
+  g.peer_count = ctx.size;
+  g.peer_rank = ctx.rank;
+  g.ready_flags = signal.flags;
+  g.ready_epoch = signal.epoch;
+  g.ready_chunks = signal.chunks;
+  const int code = kernels::gemm_bf16(c10::cuda::getCurrentCUDAStream().stream(), g);
+  CS_ASSERT_TRUE(code == 0, "GEMM on gathered chunks failed to launch (", code, ") for m=", m, " n=", n, " k=", k);
+  return {y, y2};
+}
+
+void gemm_scatter_to_slots(communication::SymmetricContext &ctx, const at::Tensor &x, const at::Tensor &weight, bool weight_is_rhs,
+                           const at::Tensor &slots) {
+  const int64_t tp = ctx.size;
+  const int64_t m = x.size(0), k = x.size(1);
+  const int64_t n = weight_is_rhs ? weight.size(1) : weight.size(0);
+  const int64_t rows = m / tp;
+  CS_ASSERT_TRUE(x.is_contiguous() && m % tp == 0 && slots.dim() == 3 && slots.size(0) == tp && slots.size(1) == rows && slots.size(2) == n &&
+                     slots.scalar_type() == at::kBFloat16,
+                 "gemm_scatter_to_slots: slots must be bf16 [size, rows / size, n]");
+  int64_t off = 0;
+  CS_ASSERT_TRUE(ctx.locate(slots.data_ptr(), static_cast<int64_t>(slots.nbytes()), &off), "the slot buffer must live in the symmetric arena");
+  kernels::GemmArgs g{};
+  g.a = x.data_ptr();
+  g.b = weight.data_ptr();
+  g.m = m;
+  g.n = n;
+  g.k = k;
+  g.lda = k;
+  g.ldb = weight_is_rhs ? n : k;
+  g.ldd = n;
+  g.layout = weight_is_rhs ? kernels::kTM : kernels::kTN;
+  g.epilogue = kernels::kEpiStoreBf16;
+  g.peer_count = static_cast<int>(tp);
+  g.peer_rank = ctx.rank;
+  for (int p = 0; p < tp; ++p) g.d_peers[p] = ctx.bases[p] + off + static_cast<int64_t>(ctx.rank) * rows * n * 2;
+  const int code = kernels::gemm_bf16(c10::cuda::getCurrentCUDAStream().stream(), g);
+  CS_ASSERT_TRUE(code == 0, "GEMM with scatter epilogue failed to launch (", code, ") for m=", m, " n=", n, " k=", k);
+}
+
+at::Tensor sum_slots(communication::SymmetricContext &ctx, const at::Tensor &slots, const at::Tensor &residual) {
+  const int64_t rows = slots.size(1), n = slots.size(2);
+  at::Tensor o = at::empty({rows, n}, slots.options());
+  at::Tensor r;
+  if (residual.defined()) r = residual.reshape({rows, n}).contiguous();
+  const auto h = communication::begin_collective(ctx, kernels::kChanGemmScatter);
+  const int rc = kernels::symm_slot_sum(c10::cuda::getCurrentCUDAStream().stream(), communication::table_of(ctx), h, slots.data_ptr(), rows * n * 2,
+                                        o.data_ptr(), residual.defined() ? r.data_ptr() : nullptr, rows * n);
+  CS_ASSERT_TRUE(rc == 0, "slot sum launch failed: ", cuda_error_string(rc));
+  return o;
+}
+
+namespace {
 // ---- fused forms (row shards that are multiples of 256 rows) ------------------------------------------------
 // all-gather -> GEMM: the gather runs on the communication stream in row chunks and announces every chunk with a
 // flag; the GEMM on the main stream starts at once and its TMA producer waits for the flag of the chunk a tile
@@ -348,12 +518,6 @@ Tensor row_parallel_symmetric(const Scheduler &scheduler, const communication::C
 // GEMM -> reduce-scatter: the GEMM epilogue TMA-stores each bf16 output tile straight into the slot that the
 // owner of those rows keeps for this rank; one kernel then opens with the cross-rank barrier and sums the local
 // slots (+ residual). No barrier launches, no zero-filling, every byte crosses NVLink once as bf16.
-struct GatherSignal {
-  uint32_t epoch{0};
-  const uint32_t *flags{nullptr};
-  int chunks{0};
-};
-
 int gather_chunks_for(int64_t rows_per_rank) {
   for (int c : {4, 2, 1})
     if (rows_per_rank % (256 * c) == 0) return c;
@@ -371,19 +535,8 @@ Tensor gather_gemm(const Scheduler &scheduler, const communication::Comm &comm, 
            auto &ctx = *comm.impl()->symmetric;
            const at::Tensor xs = x_shard.impl()->tensor.reshape({-1, x_shard.impl()->tensor.size(-1)}).contiguous();
            task.intermediate().push_back(xs);
-           const int64_t m = xs.size(0), k = xs.size(1), tp = ctx.size;
-           at::Tensor &dst = ensure_symmetric(ctx, full, {m * tp, k}, xs.scalar_type());
-           int64_t off = 0;
-           CS_ASSERT_TRUE(ctx.locate(dst.data_ptr(), static_cast<int64_t>(dst.nbytes()), &off), "gather buffer left the arena");
-           int blocks = 0;
-           const auto h = communication::begin_collective(ctx, kernels::kChanGemmGather);
-           const int code = kernels::symm_all_gather_chunked(c10::cuda::getCurrentCUDAStream().stream(), communication::table_of(ctx), h,
-                                                             xs.data_ptr(), off, static_cast<int64_t>(xs.nbytes()), chunks, &blocks);
-           CS_ASSERT_TRUE(code == 0, "chunked row gather launch failed: ", cuda_error_string(code));
-           communication::end_collective(ctx, kernels::kChanGemmGather, blocks);
-           signal->epoch = h.epoch;
-           signal->flags = ctx.flags[ctx.rank] + kernels::kChannelBase + kernels::kChanGemmGather * kernels::kChannelWords + kernels::kChunkFlags;
-           signal->chunks = chunks;
+           at::Tensor &dst = ensure_symmetric(ctx, full, {xs.size(0) * ctx.size, xs.size(1)}, xs.scalar_type());
+           *signal = gather_rows_chunked(ctx, xs, dst, chunks);
          });
   Tensor out;
   std::vector<ReadOnlyTensor> ins{x_shard, weight};  // not `full`: the flags order the reads, chunk by chunk
@@ -395,39 +548,10 @@ Tensor gather_gemm(const Scheduler &scheduler, const communication::Comm &comm, 
   submit(scheduler, "cs::parallel::column_parallel(GEMM on arriving chunks)", Task::Impl::kMain, Task::Impl::kCompute, {out}, ins,
          [out, full, weight, weight_is_rhs, epilogue, aux_h, comm, signal](const FnTask &task) {
            auto &ctx = *comm.impl()->symmetric;
-           const at::Tensor &xf = full.impl()->tensor;
            const at::Tensor wc = compute::working_copy(weight, at::kBFloat16);
-           const int64_t m = xf.size(0), k = xf.size(1);
-           const int64_t n = weight_is_rhs ? wc.size(1) : wc.size(0);
-           at::Tensor y = at::empty({m, n}, xf.options());
-           at::Tensor y2, a2;
-           kernels::GemmArgs g{};
-           g.a = xf.data_ptr();
-           g.b = wc.data_ptr();
-           g.d = y.data_ptr();
-           g.m = m;
-           g.n = n;
-           g.k = k;
-           g.lda = k;
-           g.ldb = weight_is_rhs ? n : k;
-           g.ldd = n;
-           g.layout = weight_is_rhs ? kernels::kTM : kernels::kTN;
-           g.epilogue = epilogue;
-           if (epilogue == kernels::kEpiGeluDual) {
-             y2 = at::empty_like(y);
-             g.d2 = y2.data_ptr();
-           }
-           if (aux_h) {
-             a2 = aux_h->impl()->tensor.reshape({m, n}).contiguous();
-             g.aux = a2.data_ptr();
-           }
-           g.peer_count = ctx.size;
-           g.peer_rank = ctx.rank;
-           g.ready_flags = signal->flags;
-           g.ready_epoch = signal->epoch;
-           g.ready_chunks = signal->chunks;
-           const int code = kernels::gemm_bf16(c10::cuda::getCurrentCUDAStream().stream(), g);
-           CS_ASSERT_TRUE(code == 0, "GEMM on gathered chunks failed to launch (", code, ") for m=", m, " n=", n, " k=", k);
+           at::Tensor a2;
+           if (aux_h) a2 = aux_h->impl()->tensor;
+           auto [y, y2] = gemm_on_gathered_chunks(ctx, full.impl()->tensor, wc, weight_is_rhs, epilogue, a2, *signal);
            g_fused_tp_launches.fetch_add(1);
            out.impl()->tensor = y;
            out.impl()->companion = y2;
@@ -453,36 +577,14 @@ Tensor gemm_scatter(const Scheduler &scheduler, const communication::Comm &comm,
            const int64_t tp = ctx.size;
            const at::Tensor xa = x.impl()->tensor.reshape({-1, x.impl()->tensor.size(-1)}).contiguous();
            const at::Tensor wc = compute::working_copy(weight, at::kBFloat16);
-           const int64_t m = xa.size(0), k = xa.size(1);
+           const int64_t m = xa.size(0);
            const int64_t n = weight_is_rhs ? wc.size(1) : wc.size(0);
            const int64_t rows = m / tp;
            at::Tensor &buf = ensure_symmetric(ctx, slots, {tp, rows, n}, at::kBFloat16);  // slot s: rank s's partial of my rows
-           int64_t off = 0;
-           CS_ASSERT_TRUE(ctx.locate(buf.data_ptr(), static_cast<int64_t>(buf.nbytes()), &off), "slot buffer left the arena");
-           auto stream = c10::cuda::getCurrentCUDAStream().stream();
-           kernels::GemmArgs g{};
-           g.a = xa.data_ptr();
-           g.b = wc.data_ptr();
-           g.m = m;
-           g.n = n;
-           g.k = k;
-           g.lda = k;
-           g.ldb = weight_is_rhs ? n : k;
-           g.ldd = n;
-           g.layout = weight_is_rhs ? kernels::kTM : kernels::kTN;
-           g.epilogue = kernels::kEpiStoreBf16;
-           g.peer_count = static_cast<int>(tp);
-           g.peer_rank = ctx.rank;
-           for (int p = 0; p < tp; ++p) g.d_peers[p] = ctx.bases[p] + off + static_cast<int64_t>(ctx.rank) * rows * n * 2;
-           const int code = kernels::gemm_bf16(stream, g);
-           CS_ASSERT_TRUE(code == 0, "GEMM with scatter epilogue failed to launch (", code, ") for m=", m, " n=", n, " k=", k);
-           at::Tensor o = at::empty({rows, n}, xa.options());
+           gemm_scatter_to_slots(ctx, xa, wc, weight_is_rhs, buf);
            at::Tensor r;
-           if (res) r = res->impl()->tensor.reshape({rows, n}).contiguous();
-           const auto h = communication::begin_collective(ctx, kernels::kChanGemmScatter);
-           const int rc = kernels::symm_slot_sum(stream, communication::table_of(ctx), h, buf.data_ptr(), rows * n * 2, o.data_ptr(),
-                                                 res ? r.data_ptr() : nullptr, rows * n);
-           CS_ASSERT_TRUE(rc == 0, "slot sum launch failed: ", cuda_error_string(rc));
+           if (res) r = res->impl()->tensor;
+           at::Tensor o = sum_slots(ctx, buf, r);
            g_fused_tp_launches.fetch_add(1);
            out.impl()->tensor = o;
          });

@@ -243,6 +243,70 @@ std::shared_ptr<SymmetricContext> create_symmetric_context(const Comm &comm, int
   return ctx;
 }
 
+std::vector<std::shared_ptr<SymmetricContext>> create_loopback_contexts(int ranks, int64_t arena_bytes) {
+  CS_ASSERT_TRUE(ranks >= 1 && ranks <= kernels::kMaxPeers, "loopback emulation supports 1 to ", kernels::kMaxPeers, " ranks");
+  int device = 0;
+  CS_CHECK_CUDART(cudaGetDevice(&device));
+  struct Holder {
+    std::vector<void *> blocks;
+    ~Holder() {
+      for (void *p : blocks) cudaFree(p);
+      (void)cudaGetLastError();
+    }
+  };
+  auto holder = std::make_shared<Holder>();
+  const int64_t bytes = round_up(arena_bytes, kAlign);
+  const size_t pad_bytes = SymmetricContext::kFlagWords * sizeof(uint32_t);
+  std::vector<char *> bases(ranks);
+  std::vector<uint32_t *> pads(ranks);
+  for (int r = 0; r < ranks; ++r) {
+    void *base = nullptr, *pad = nullptr;
+    CS_CHECK_CUDART(cudaMalloc(&base, static_cast<size_t>(bytes)));
+    holder->blocks.push_back(base);
+    CS_CHECK_CUDART(cudaMalloc(&pad, pad_bytes));
+    holder->blocks.push_back(pad);
+    CS_CHECK_CUDART(cudaMemset(pad, 0, pad_bytes));
+    bases[r] = static_cast<char *>(base);
+    pads[r] = static_cast<uint32_t *>(pad);
+  }
+  std::vector<std::shared_ptr<SymmetricContext>> out;
+  for (int r = 0; r < ranks; ++r) {
+    auto ctx = std::make_shared<SymmetricContext>();
+    ctx->rank = r;
+    ctx->size = ranks;
+    ctx->device = device;
+    ctx->arena_bytes = bytes;
+    ctx->bases = bases;
+    ctx->flags = pads;
+    ctx->loopback_ = holder;
+    void *status = nullptr;
+    CS_CHECK_CUDART(cudaMalloc(&status, sizeof(kernels::DeviceStatus)));
+    holder->blocks.push_back(status);
+    CS_CHECK_CUDART(cudaMemset(status, 0, sizeof(kernels::DeviceStatus)));
+    ctx->status = status;
+    out.push_back(ctx);
+  }
+  CS_CHECK_CUDART(cudaDeviceSynchronize());
+  return out;
+}
+
+void SymmetricContext::prime_loopback() {
+  CS_ASSERT_TRUE(loopback_ != nullptr, "prime_loopback is for contexts made by create_loopback_contexts");
+  // "already set" for every epoch this context will use: flags are compared as signed distances
+  std::vector<uint32_t> words(kFlagWords, 0);
+  constexpr uint32_t kSet = 0x3fffffffu;
+  for (int i = 0; i < kernels::kChannelBase; ++i) words[i] = kSet;  // stand-alone barrier slots
+  for (int c = 0; c < kernels::kNumChannels; ++c) {
+    uint32_t *w = words.data() + kernels::kChannelBase + c * kernels::kChannelWords;
+    for (int i = 0; i <= 16; ++i) w[i] = kSet;                                            // entry, exit, local go flag
+    for (int i = kernels::kChunkFlags; i < kernels::kChunkFlags + 64; ++i) w[i] = kSet;   // chunk-ready flags
+    w[17] = channel_blocks[c];  // blocks counted so far: the closing barrier's count stays consistent
+  }
+  auto stream = static_cast<cudaStream_t>(cur_stream());
+  CS_CHECK_CUDART(cudaMemcpyAsync(flags[rank], words.data(), words.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, stream));
+  CS_CHECK_CUDART(cudaStreamSynchronize(stream));  // `words` is a local
+}
+
 void check_device_status(SymmetricContext &ctx, const char *where) {
   kernels::DeviceStatus st{};
   CS_CHECK_CUDART(cudaMemcpy(&st, ctx.status, sizeof(st), cudaMemcpyDeviceToHost));

@@ -40,7 +40,8 @@ class GPT2Trainer:
     mode "dp"   data parallel: every rank owns the model; gradient ranges are all-reduced in buckets while the
                 backward pass continues, and the average is folded into the optimizer kernel (the reference's
                 example/gpt2/gpt2_ddp.cpp does the same with NCCL buckets).
-         "zero" data parallel with the sharded optimizer: reduce-scatter + AdamW + all-gather in one kernel (GPUs).
+         "zero" data parallel with the sharded optimizer (fp32 master weights and AdamW moments split over the ranks):
+                reduce-scatter + AdamW + all-gather in one kernel per bucket, overlapped with backward (GPUs).
          "tp"   tensor + sequence parallel over all ranks; every rank sees the whole batch (GPUs, or Gloo ranks).
     collectives "nvp2p" runs this library's peer-memory kernels (GPUs with peer access), "nccl" the library's.
     `max_tokens` (tensor parallel with "nvp2p" only) is the largest B*T of a step; it sizes the symmetric arena.
@@ -92,6 +93,12 @@ class GPT2Trainer:
             assert peer, "the sharded optimizer runs on GPUs with peer access"
             self.optimizer = _C.ZeroAdamW(s, self.model, self.flat, self.comm, lr=lr, beta1=beta1, beta2=beta2,
                                           weight_decay=weight_decay)
+            if overlap_optimizer:
+                # every bucket of gradients is reduce-scattered, turned into an AdamW update of the blocks this rank owns
+                # and all-gathered as bf16 working weights by one kernel, while the backward pass of the earlier layers runs
+                self.bucket = cs.AllReduceBucket(int(bucket_mb * (1 << 20)), "sum")
+                self.bucket.attach_sharded_optimizer(self.optimizer)
+                self.sync = cs.GradientSync(self.comm, self.bucket, True)
         else:
             self.optimizer = cs.AdamW(s, self.model, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay, flat=self.flat)
             if world > 1:

@@ -7,6 +7,8 @@ parameter, no shapes. `cs::load` of either project reads what `write_parameters`
 
     python -m core_scheduler_b200.utils.checkpoint merge --n-head 20 --n-embd 1280 --out model.parquet \
         ckpt/tp_rank0/model.parquet ckpt/tp_rank1/model.parquet ...
+    python -m core_scheduler_b200.utils.checkpoint merge-zero --model ckpt/model.parquet --out ckpt/optimizer.parquet \
+        ckpt/zero_rank0/optimizer.parquet ckpt/zero_rank1/optimizer.parquet ...
 """
 from __future__ import annotations
 
@@ -90,6 +92,41 @@ def merge_tensor_parallel(shards: "list[OrderedDict[str, np.ndarray]]", n_head: 
     return merged
 
 
+ZERO_BLOCK = 16384   # parallel::ZeroAdamWImpl::kBlock: block j of the arenas belongs to rank j % world
+SLOT_ALIGNMENT = 128  # module::FlatParameters::alignment: every parameter starts at a multiple of this many elements
+
+
+def merge_zero(shards: "list[OrderedDict[str, np.ndarray]]", model: "OrderedDict[str, np.ndarray]") -> "OrderedDict[str, np.ndarray]":
+    """Unites the optimizer shard files of a sharded-optimizer (ZeRO) run into the per-parameter table that the
+    replicated AdamW writes and reads (`<parameter>.m`, `<parameter>.v`, `__step__`, `__lr__`), plus `<parameter>.master`
+    (the fp32 master weights, identical to the model file's values after `gather_master`).
+
+    `shards` are the ranks' `zero_rank<r>/optimizer.parquet` tables in rank order; `model` is the model file of the same
+    step. Its key order and sizes give the arena layout: parameters in order, each starting at the next multiple of
+    128 elements. Rank r holds the arena's blocks r, r + world, ... (16384 elements each) back to back."""
+    world = len(shards)
+    offsets, cursor = OrderedDict(), 0
+    for key, value in model.items():
+        offsets[key] = (cursor, value.size)
+        cursor += (value.size + SLOT_ALIGNMENT - 1) // SLOT_ALIGNMENT * SLOT_ALIGNMENT
+    merged: "OrderedDict[str, np.ndarray]" = OrderedDict()
+    arenas = {}
+    for what in ("m", "v", "master"):
+        parts = [s[f"shard{r}.{what}"] for r, s in enumerate(shards)]
+        per = parts[0].size // ZERO_BLOCK
+        # [world, per, block] -> arena order [per, world, block]
+        arenas[what] = np.stack([p.reshape(per, ZERO_BLOCK) for p in parts]).transpose(1, 0, 2).reshape(-1)
+        if arenas[what].size < cursor:
+            raise ValueError(f"the shards hold {arenas[what].size} values, the model needs {cursor}")
+    for key, (begin, size) in offsets.items():
+        for what in ("m", "v", "master"):
+            merged[f"{key}.{what}"] = arenas[what][begin:begin + size]
+    for extra in ("__step__", "__lr__"):
+        if extra in shards[0]:
+            merged[extra] = shards[0][extra]
+    return merged
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = parser.add_subparsers(dest="command", required=True)
@@ -98,6 +135,11 @@ def main(argv=None) -> int:
     merge.add_argument("--n-embd", type=int, required=True)
     merge.add_argument("--out", required=True)
     merge.add_argument("shards", nargs="+")
+    zero = sub.add_parser("merge-zero", help="unite the optimizer shard files of a sharded-optimizer run (given in rank order)")
+    zero.add_argument("--model", required=True, help="model file of the same step (gives the parameter order and sizes)")
+    zero.add_argument("--out", required=True)
+    zero.add_argument("--with-master", action="store_true", help="also keep the `<parameter>.master` rows")
+    zero.add_argument("shards", nargs="+")
     show = sub.add_parser("list", help="print the keys and sizes of a parameter file")
     show.add_argument("file")
     args = parser.parse_args(argv)
@@ -110,6 +152,17 @@ def main(argv=None) -> int:
         merged = merge_tensor_parallel([read_parameters(p) for p in args.shards], args.n_head, args.n_embd)
         write_parameters(merged, args.out)
         print(f"wrote {len(merged)} parameters, {sum(v.size for v in merged.values())} values to {args.out}")
+    elif args.command == "merge-zero":
+        import re
+
+        ranks = [re.search(r"zero_rank(\d+)", p) for p in args.shards]
+        if all(ranks):
+            args.shards = [p for _, p in sorted(zip((int(m.group(1)) for m in ranks), args.shards))]
+        merged = merge_zero([read_parameters(p) for p in args.shards], read_parameters(args.model))
+        if not args.with_master:
+            merged = OrderedDict((k, v) for k, v in merged.items() if not k.endswith(".master"))
+        write_parameters(merged, args.out)
+        print(f"wrote {len(merged)} rows, {sum(v.size for v in merged.values())} values to {args.out}")
     else:
         for key, value in read_parameters(args.file).items():
             print(f"{value.size:12d}  {key}")

@@ -4,6 +4,9 @@
   python -m core_scheduler_b200.utils.microbench elementwise # LayerNorm / GELU / AdamW bandwidth
   python -m core_scheduler_b200.utils.microbench attention    # tcgen05 attention forward vs cuDNN
   python -m core_scheduler_b200.utils.microbench kernels_once # every non-GEMM kernel twice (profiler workload)
+  python -m core_scheduler_b200.utils.microbench collectives_loopback [ranks] [MiB]
+                                                              # collective and fused GEMM+collective kernels of ONE emulated
+                                                              # rank on one GPU (peer memory = local memory): profiler workload
 
 Prints one line per case: achieved TFLOP/s or GB/s and the fraction of the measured peak
 (MEASURED_PEAKS.json at the repository root when present, else the fallback 1.59 PFLOP/s, 6.65 TB/s).
@@ -164,6 +167,77 @@ def bench_attention():
           f"{fb / t_lib_b / 1e9:.0f} TFLOP/s   status {C.attention_status()}")
 
 
+def collectives_loopback():
+    """One launch of every peer-memory kernel as rank 0 of `ranks` emulated ranks on this GPU (all arenas local, peer
+    flags primed): what a profiler can capture of these kernels without a second process. Times are those of the
+    kernel's own memory traffic on local HBM (no NVLink): every peer load and store is a local one."""
+    ranks = int(sys.argv[2]) if len(sys.argv) > 2 else 2
+    mib = int(sys.argv[3]) if len(sys.argv) > 3 else 256
+    _, gbs_peak, tag = peaks()
+    n = (mib << 20) // 4
+    ctxs = C.create_loopback_contexts(ranks, 3 * (mib << 20) + (256 << 20) * 2)
+    ctx = ctxs[0]
+    stream = torch.cuda.current_stream()
+
+    def run(name, fn, nbytes):
+        for _ in range(2):
+            ctx.prime_loopback()
+            fn()
+        torch.cuda.synchronize()
+        ctx.prime_loopback()
+        flush_l2()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        fn()
+        b.record(stream)
+        torch.cuda.synchronize()
+        t = a.elapsed_time(b)
+        ctx.check_status()
+        print(f"{name:58s} {t * 1e3:9.1f} us  {nbytes / t / 1e6:7.0f} GB/s of local traffic ({nbytes / t / 1e6 / gbs_peak:.2f} of {tag} copy bandwidth)", flush=True)
+
+    grads = [c.empty([n], torch.float32)[0] for c in ctxs]
+    for g in grads:
+        g.normal_()
+    # rank 0 reduces its 1/ranks slice: reads it from every rank, writes it to every rank
+    run(f"all_reduce fp32 {mib} MiB, {ranks} ranks (rank 0's slice)", lambda: ctx.all_reduce_([grads[0]], "sum"), 2 * (mib << 20))
+    half = [c.empty([ranks, n // ranks // 2], BF)[0] for c in ctxs]
+    out = torch.empty(n // ranks // 2, device="cuda", dtype=BF)
+    run("reduce_scatter bf16 (rank 0's chunk from every rank)", lambda: ctx.reduce_scatter_(out, [half[0][p] for p in range(ranks)], "sum"),
+        (ranks + 1) * out.numel() * 2)
+    shard = torch.randn(n // ranks // 2, device="cuda").to(BF)
+    run("all_gather bf16 push (rank 0's shard to every rank)", lambda: ctx.all_gather_([half[0][p] for p in range(ranks)], shard),
+        (ranks + 1) * shard.numel() * 2)
+    lps = [c.empty([n], BF)[0] for c in ctxs]
+    block = C.ZeroAdamW.block
+    per = ((n + block - 1) // block + ranks - 1) // ranks * block
+    w, m, v = (torch.zeros(per, device="cuda") for _ in range(3))
+    run("reduce-scatter + AdamW + all-gather (rank 0's blocks)", lambda: ctx.sharded_adamw_(grads[0], lps[0], w, m, v, 0, n, block, 1e-3, 0.9, 0.95,
+                                                                                            1e-8, 0.1, 1, 1.0 / ranks),
+        n // ranks * (4 * ranks + 6 * 4 + 2 * ranks))
+    # tensor-parallel pair: rows gathered in chunks beside the GEMM that consumes them; GEMM with the scatter in its epilogue
+    rows, k, nn = 4096, 1280, 640
+    fulls = [c.empty([ranks * rows, k], BF)[0] for c in ctxs]
+    xs = torch.randn(rows, k, device="cuda").mul_(0.5).to(BF)
+    wt = torch.randn(nn, k, device="cuda").mul_(0.05).to(BF)
+    sig = [None]
+
+    def gather():
+        sig[0] = ctx.gather_rows_chunked(xs, fulls[0], 4)
+
+    run(f"gather rows in 4 chunks [{rows},{k}] x {ranks} ranks", gather, (ranks + 1) * xs.numel() * 2)
+    run(f"GEMM on gathered chunks [{ranks * rows},{k}] x [{nn},{k}]^T", lambda: ctx.gemm_on_gathered_chunks(fulls[0], wt, False, 0, None, sig[0]),
+        fulls[0].numel() * 2 + ranks * rows * nn * 2)
+    slots = [c.empty([ranks, rows, k], BF)[0] for c in ctxs]
+    xa = torch.randn(ranks * rows, nn, device="cuda").mul_(0.5).to(BF)
+    w2 = torch.randn(k, nn, device="cuda").mul_(0.05).to(BF)
+    run(f"GEMM with scatter epilogue [{ranks * rows},{nn}] x [{k},{nn}]^T", lambda: ctx.gemm_scatter_to_slots(xa, w2, False, slots[0]),
+        xa.numel() * 2 + ranks * rows * k * 2)
+    res = torch.randn(rows, k, device="cuda").to(BF)
+    run(f"slot sum + residual [{ranks},{rows},{k}]", lambda: ctx.sum_slots(slots[0], res), (ranks + 2) * rows * k * 2)
+    print("gemm status", C.gemm_status())
+
+
 def gemm_one():
     """One GPT-2 shape (fc1), a handful of launches: the workload for an ncu capture.
 
@@ -280,4 +354,4 @@ def kernels_once():
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     {"gemm": bench_gemm, "elementwise": bench_elementwise, "gemm_one": gemm_one, "attention": bench_attention,
-     "kernels_once": kernels_once}[what]()
+     "kernels_once": kernels_once, "collectives_loopback": collectives_loopback}[what]()

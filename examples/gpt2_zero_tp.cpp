@@ -15,6 +15,7 @@
 #include <cuda_runtime.h>
 
 #include <chrono>
+#include <filesystem>
 #include <iostream>
 
 #include "cs/data.h"
@@ -74,7 +75,16 @@ int main(int argc, char **argv) {
   } else {
     dp_model = cs::models::GPT2{scheduler, config};
     flat = cs::parallel::flatten_symmetric(scheduler, *dp_model, comm);
-    optimizer = std::make_shared<cs::parallel::ZeroAdamWImpl>(scheduler, *dp_model, flat, comm, adamw);
+    auto zero = std::make_shared<cs::parallel::ZeroAdamWImpl>(scheduler, *dp_model, flat, comm, adamw);
+    optimizer = zero;
+    // the bucket only groups the gradients; each bucket is reduce-scattered, updated and all-gathered by one kernel while
+    // the backward pass of the earlier layers is still running
+    bucket.skip_reduction(true);
+    bucket.on_reduced([weak = std::weak_ptr<cs::parallel::ZeroAdamWImpl>(zero)](const cs::Scheduler &s, const std::vector<cs::Tensor> &grads,
+                                                                              cs::Task::Impl::Priority priority) {
+      if (auto z = weak.lock()) z->step_partial(s, grads, priority);
+    });
+    sync = cs::models::GradientSync{comm, &bucket, true};
   }
   const int64_t seq = config.block_size();
   // tensor-parallel ranks consume the same batch; data-parallel (zero) ranks different ones
@@ -97,7 +107,8 @@ int main(int argc, char **argv) {
       tp_model->backward_loss(scheduler, sync);
       bucket.sync(scheduler, comm);
     } else {
-      dp_model->backward_loss(scheduler);
+      dp_model->backward_loss(scheduler, sync);
+      bucket.sync(scheduler, comm);
     }
     optimizer->step(scheduler);
     optimizer->zero_grad(scheduler);
@@ -129,6 +140,13 @@ int main(int argc, char **argv) {
     const std::string dir = tp ? save_dir + "/tp_rank" + std::to_string(rank) : save_dir;
     const cs::module::Module &m = tp ? static_cast<const cs::module::Module &>(*tp_model) : static_cast<const cs::module::Module &>(*dp_model);
     cs::checkpoint::save_training_state(scheduler, dir, m, tp ? optimizer.get() : nullptr, meta, rank, tp ? rank : 0);
+    if (!tp) {
+      // the sharded optimizer state: every rank writes its own blocks (master weights and both moments);
+      // `python -m core_scheduler_b200.utils.checkpoint merge-zero` turns the files into per-parameter tables
+      const std::string shard_dir = save_dir + "/zero_rank" + std::to_string(rank);
+      std::filesystem::create_directories(shard_dir);
+      cs::save(*optimizer, shard_dir + "/optimizer.parquet");
+    }
   }
   watchdog.stop();
   scheduler.impl()->synchronize();

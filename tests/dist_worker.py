@@ -497,6 +497,69 @@ def case_zero_training(device, nvp2p):
         assert torch.allclose(pa[k].lp().float(), pa[k].raw().float(), atol=1e-2, rtol=1e-2), (rank, k)
 
 
+def case_zero_bucketed(device, nvp2p):
+    """The sharded optimizer driven per bucket from the backward pass (reduce-scatter + AdamW + all-gather of every bucket
+    beside the remaining backward work) equals replicated data-parallel AdamW; its per-rank shard files merge into the
+    per-parameter optimizer table of the replicated optimizer."""
+    import shutil
+
+    from core_scheduler_b200.utils.checkpoint import merge_zero, read_parameters
+
+    comm, rank, world, s = make_comm(device, True)
+    _, model = tiny_model(s)
+    _, ref = tiny_model(s)
+    flat = C.flatten_symmetric(s, model, comm)
+    rflat = C.flatten_parameters(s, ref, lp_dtype=torch.bfloat16)
+    opt = C.ZeroAdamW(s, model, flat, comm, lr=1e-2, weight_decay=0.1)
+    bucket = cs.AllReduceBucket(48 * 1024, "sum")
+    bucket.attach_sharded_optimizer(opt)
+    sync = cs.GradientSync(comm, bucket, True)
+    ropt = cs.AdamW(s, ref, lr=1e-2, weight_decay=0.1, flat=rflat)
+    ropt.set_grad_scale(1.0 / world)
+    s.synchronize()
+    init = {k: v.raw().float().clone() for k, v in ref.named_parameters().items()}
+    g = torch.Generator().manual_seed(11)
+    for step in range(3):
+        ids = torch.randint(0, 128, (world, 2, 33), generator=g).to(device)
+        with cs.autocast(s, torch.bfloat16):
+            model.forward_loss(s, T(ids[rank][:, :-1].contiguous()), T(ids[rank][:, 1:].contiguous()))
+        model.backward_loss(s, sync)
+        bucket.sync(s, comm)
+        opt.step(s)
+        opt.zero_grad(s)
+        for r in range(world):
+            with cs.autocast(s, torch.bfloat16):
+                ref.forward_loss(s, T(ids[r][:, :-1].contiguous()), T(ids[r][:, 1:].contiguous()))
+            ref.backward_loss(s)
+        ropt.step(s)
+        ropt.zero_grad(s)
+    assert bucket.launches() >= 6  # several buckets per step
+    opt.gather_master(s)
+    s.synchronize()
+    assert_same_training(model, ref, init, rank, True)
+    # shard files -> per-parameter table
+    directory = f"/tmp/cs_zero_merge_{os.environ.get('MASTER_PORT', '0')}"
+    os.makedirs(f"{directory}/zero_rank{rank}", exist_ok=True)
+    opt.save(f"{directory}/zero_rank{rank}/optimizer.parquet")
+    if rank == 0:
+        model.save(f"{directory}/model.parquet")
+    dist.barrier()
+    merged = merge_zero([read_parameters(f"{directory}/zero_rank{r}/optimizer.parquet") for r in range(world)],
+                        read_parameters(f"{directory}/model.parquet"))
+    assert merged["__step__"][0] == 3
+    rstate = ropt.named_state_tensors()
+    for k, p in model.named_parameters().items():
+        assert torch.allclose(torch.from_numpy(merged[f"{k}.master"].copy()).to(device), p.raw().float().reshape(-1), atol=1e-6), (rank, k)
+        for what in ("m", "v"):
+            got = torch.from_numpy(merged[f"{k}.{what}"].copy()).to(device)
+            want = rstate[f"{k}.{what}"].raw().float().reshape(-1)
+            err = (got - want).norm().item() / (want.norm().item() + 1e-12)
+            assert err < 0.2, (rank, k, what, err)
+    dist.barrier()
+    if rank == 0:
+        shutil.rmtree(directory, ignore_errors=True)
+
+
 def head_range(H, rank, world):
     """Heads of `rank`: the first H % world ranks own one more (same rule as the library)."""
     base, extra = divmod(H, world)

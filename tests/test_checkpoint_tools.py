@@ -2,6 +2,8 @@
 import subprocess
 import sys
 
+from collections import OrderedDict
+
 import numpy as np
 import torch
 
@@ -55,3 +57,36 @@ def test_merge_inverts_the_tensor_parallel_slicing():
     assert sorted(merged) == sorted(full)
     for k, v in full.items():
         assert np.allclose(merged[k], v.reshape(-1).astype(np.float32)), k
+
+
+def test_merge_zero_rebuilds_per_parameter_moments_from_block_interleaved_shards():
+    """Rank r of a sharded-optimizer run holds arena blocks r, r + world, ...; the merge puts every parameter's
+    moments and master weights back together from the ranks' files and the model file's parameter order."""
+    from core_scheduler_b200.utils.checkpoint import SLOT_ALIGNMENT, ZERO_BLOCK, merge_zero
+
+    rng = np.random.default_rng(3)
+    sizes = OrderedDict([("a.weight", 40000), ("a.bias", 100), ("b.weight", 3 * ZERO_BLOCK + 17), ("c", 128)])
+    model = OrderedDict((k, rng.standard_normal(n).astype(np.float32)) for k, n in sizes.items())
+    total = sum((n + SLOT_ALIGNMENT - 1) // SLOT_ALIGNMENT * SLOT_ALIGNMENT for n in sizes.values())
+    world = 4
+    blocks = (total + ZERO_BLOCK - 1) // ZERO_BLOCK
+    per = (blocks + world - 1) // world
+    arena = {w: np.zeros(per * world * ZERO_BLOCK, np.float32) for w in ("m", "v", "master")}
+    cursor, expect = 0, {}
+    for k, n in sizes.items():
+        for w in arena:
+            values = model[k] if w == "master" else rng.standard_normal(n).astype(np.float32)
+            arena[w][cursor:cursor + n] = values
+            expect[f"{k}.{w}"] = values
+        cursor += (n + SLOT_ALIGNMENT - 1) // SLOT_ALIGNMENT * SLOT_ALIGNMENT
+    shards = []
+    for r in range(world):
+        shard = OrderedDict()
+        for w in ("m", "v", "master"):
+            shard[f"shard{r}.{w}"] = arena[w].reshape(per, world, ZERO_BLOCK)[:, r].reshape(-1).copy()
+        shard["__step__"] = np.asarray([7], np.float32)
+        shards.append(shard)
+    merged = merge_zero(shards, model)
+    for k, v in expect.items():
+        assert np.array_equal(merged[k], v), k
+    assert merged["__step__"][0] == 7

@@ -1,4 +1,6 @@
 """Parquet dataset listing, loader sharding arithmetic, pinned staging and the synthetic loader."""
+import os
+
 import numpy as np
 import pyarrow as pa
 import pyarrow.parquet as pq
@@ -6,6 +8,8 @@ import pytest
 import torch
 
 import core_scheduler_b200 as cs
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 C = cs._C
 
@@ -82,3 +86,45 @@ def test_loader_uploads_through_pinned_buffers(tmp_path, gpu_scheduler):
         ids = cs.to_torch(gpu_scheduler, b["input_ids"])
         assert ids.is_cuda and ids.shape == (8, 128)
         assert torch.equal(cs.to_torch(gpu_scheduler, b["labels"]), ids + 1)
+
+
+def test_prepare_text_gen_splits_windows_and_shards(tmp_path):
+    """examples/prepare_text_gen.py: two sources (text file with a carved-out validation set, jsonl), windows of
+    block_size tokens with labels shifted by one, the test split falling back to validation, shard count from the
+    byte budget, and files that LlmDataset / LlmDataLoader read back."""
+    import importlib.util
+    import json
+    import sys
+
+    import pyarrow.parquet as pq
+
+    spec = importlib.util.spec_from_file_location("prepare_text_gen", os.path.join(ROOT, "examples", "prepare_text_gen.py"))
+    prep = importlib.util.module_from_spec(spec)
+    sys.modules["prepare_text_gen"] = prep  # the shard writers of its process pool are looked up by module name
+    spec.loader.exec_module(prep)
+    docs = ["".join(chr(97 + (i + j) % 26) for j in range(40 + i % 7)) for i in range(200)]
+    (tmp_path / "a.txt").write_text("\n\n".join(docs[:120]))
+    with open(tmp_path / "b.jsonl", "w") as f:
+        for d in docs[120:]:
+            f.write(json.dumps({"body": d}) + "\n")
+    config = {"out": str(tmp_path / "out"), "block_size": 16, "tokenizer": None, "seed": 1, "num_proc": 2,
+              "max_shard_size": 2 * 16 * 4 * 60,  # 60 rows per shard
+              "sources": [{"path": str(tmp_path / "a.txt"), "split_ratio": 0.25},
+                          {"path": str(tmp_path / "b.jsonl"), "text_column": "body", "split_ratio": 0.25, "sampling_rate": 0.5}]}
+    report = prep.prepare(config)
+    assert set(report) == {"train", "validation", "test"}
+    rows, shards = report["train"]
+    assert shards == (rows * 2 * 16 * 4 + config["max_shard_size"] - 1) // config["max_shard_size"] and shards >= 2
+    files = sorted(os.listdir(tmp_path / "out" / "train"))
+    assert files[0] == f"data-00000-of-{shards:05d}.parquet" and len(files) == shards
+    table = pq.read_table(tmp_path / "out" / "train" / files[0])
+    ids, labels = table.column("input_ids").to_pylist(), table.column("labels").to_pylist()
+    assert all(len(r) == 16 for r in ids) and all(len(r) == 16 for r in labels)
+    assert all(a[1:] == b[:-1] for a, b in zip(ids, labels))  # labels are the window shifted by one token
+    assert report["test"] == report["validation"]  # no test split given: the validation set serves
+    ds = cs._C.LlmDataset(str(tmp_path / "out" / "train"))
+    assert ds.size() == rows
+    loader = cs._C.LlmDataLoader(ds, 4, 1, False)
+    s = cs.DynamicScheduler(0, device="cpu")
+    batch = loader.load(s)
+    assert cs.to_torch(s, batch["input_ids"]).shape == (4, 16)

@@ -73,6 +73,11 @@ def test_zero_fused_step_matches_replicated_adamw():
 
 
 @needs2
+def test_zero_per_bucket_steps_and_shard_files():
+    run_case("zero_bucketed", device="cuda", extra=("nvp2p",), timeout=600)
+
+
+@needs2
 def test_peer_wait_times_out_with_status_instead_of_hanging():
     run_case("timeout_status", device="cuda", extra=("nvp2p",), timeout=600)
 

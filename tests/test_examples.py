@@ -33,8 +33,8 @@ def test_prepare_text_gen_feeds_the_loader(tmp_path, cpu_scheduler):
     corpus = tmp_path / "corpus.txt"
     corpus.write_text("\n\n".join("document %d " % i + "lorem ipsum dolor sit amet " * 40 for i in range(30)))
     out = tmp_path / "data"
-    r = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "prepare_text_gen.py"), "--input", str(corpus), "--out",
-                        str(out), "--block-size", "64", "--tokenizer", "", "--rows-per-shard", "200"],
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "prepare_text_gen.py"), "--source", str(corpus), "--out",
+                        str(out), "--block-size", "64", "--tokenizer", "", "--split-ratio", "0.1"],
                        capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stdout + r.stderr
     ds = C.LlmDataset(str(out / "train"))
