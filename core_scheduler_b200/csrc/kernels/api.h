@@ -133,15 +133,16 @@ int gemm_status_reset();
 
 // ---- tcgen05 causal attention (forward) -----------------------------------------------------------
 // qkv: packed bf16 [B, T, 3, H, D] (D == 64, T % 128 == 0); out: bf16 [B, T, H*D]; lse: fp32
-// [B, H, T] = log-sum-exp of the scaled scores. Returns -1 when the shape is not covered.
+// [B, H, T] = log-sum-exp of the scaled scores. causal != 0 masks the keys after each query.
+// Returns -1 when the shape is not covered.
 int attention_forward_packed(stream_t stream, const void *qkv, void *out, float *lse, int64_t B, int64_t T, int64_t H, int64_t D,
-                             float scale);
+                             float scale, int causal = 1);
 struct DeviceStatus;
 // Backward of the same attention: dqkv [B, T, 3, H, 64] from qkv, the forward output `out`, its
 // gradient `dout` [B, T, H*64] and `lse`; `delta` is a [3, B, H, T] fp32 workspace (plane 0 receives
 // rowsum(dout * out)). Same shape limits.
 int attention_backward_packed(stream_t stream, const void *qkv, const void *out, const void *dout, const float *lse, float *delta,
-                              void *dqkv, int64_t B, int64_t T, int64_t H, int64_t D, float scale);
+                              void *dqkv, int64_t B, int64_t T, int64_t H, int64_t D, float scale, int causal = 1);
 int attention_status(DeviceStatus *out);
 
 // ---- fused cross-entropy helpers -----------------------------------------------------------

@@ -159,6 +159,7 @@ struct AttnParams {
   float scale_log2e;    // softmax scale * log2(e)
   float scale;
   DeviceStatus *status;
+  int causal;           // 1: keys after the query are masked; 0: every query sees every key
 };
 
 __global__ void __launch_bounds__(THREADS, FWD_CTAS_PER_SM) attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
@@ -182,7 +183,7 @@ __global__ void __launch_bounds__(THREADS, FWD_CTAS_PER_SM) attention_fwd_kernel
   const int qb = gridDim.x - 1 - blockIdx.x;  // longest rows first
   const int h = blockIdx.y, b = blockIdx.z;
   const int q0 = qb * BQ;
-  const int num_kv = 2 * (qb + 1);  // causal: 64-key blocks 0 .. 2 qb + 1
+  const int num_kv = p.causal ? 2 * (qb + 1) : p.T / BKV;  // causal: 64-key blocks 0 .. 2 qb + 1
   const int row_base = b * p.T;
 
   if (threadIdx.x == 0) {
@@ -285,7 +286,7 @@ __global__ void __launch_bounds__(THREADS, FWD_CTAS_PER_SM) attention_fwd_kernel
       if (!mbar_wait(bar(S_FULL), ph, abort_flag)) break;
       fence_after();
       const int k0 = j * BKV;
-      const bool diagonal = k0 + BKV - 1 > q0;  // some key of this block lies beyond some query of the tile
+      const bool diagonal = p.causal && k0 + BKV - 1 > q0;  // some key of this block lies beyond some query of the tile
       // pass 1: row maximum of the (masked) scores. Four independent partial maxima / sums keep the
       // dependent chains short; the TMEM load of the next 16 columns is in flight meanwhile.
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -460,6 +461,7 @@ struct AttnBwdParams {
   int B, T, H;
   float scale, scale_log2e;
   DeviceStatus *status;
+  int causal;
 };
 
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
@@ -534,8 +536,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
   const int r0 = rb * 128;
   const int row_base = b * p.T;
   // streamed 64-row tiles: queries r0 .. T (kDKV) or keys 0 .. r0+128
-  const int c_first = kDKV ? 2 * rb : 0;
-  const int n_iter = kDKV ? p.T / BC - c_first : 2 * (rb + 1);
+  const int c_first = (kDKV && p.causal) ? 2 * rb : 0;
+  const int n_iter = kDKV ? p.T / BC - c_first : (p.causal ? 2 * (rb + 1) : p.T / BC);
 
   if (threadIdx.x == 0) {
     mbar_init(bar(R_FULL), 1);
@@ -677,7 +679,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap qkv_r, const __grid_con
       if (!mbar_wait(bar(SDP_FULL), t & 1, abort_flag)) break;
       fence_after();
       // rows are keys and columns queries (kDKV), or rows queries and columns keys: keep key <= query
-      const bool near_diag = kDKV ? (c0 < r0 + 128) : (c0 + BC > r0);
+      const bool near_diag = p.causal && (kDKV ? (c0 < r0 + 128) : (c0 + BC > r0));
       const float *lse_c = vec + s * 128, *delta_c = lse_c + 64;
       // 16 columns at a time; the TMEM loads of the next 16 are in flight while these are processed
       // per element: P' = exp2(S' * scale*log2e - lse*log2e), dS' = P' * (dP' * scale - delta*scale); the per-column
@@ -850,7 +852,7 @@ DeviceStatus *attn_status_ptr() {
 }  // namespace
 
 int attention_forward_packed(stream_t stream, const void *qkv, void *out, float *lse, int64_t B, int64_t T, int64_t H, int64_t D,
-                             float scale) {
+                             float scale, int causal) {
   if (D != HD || T % BQ != 0 || B <= 0 || H <= 0 || T <= 0) return -1;
   if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(out)) & 15) return -1;
   static const bool disabled = std::getenv("CS_DISABLE_TCGEN05_ATTENTION") != nullptr;
@@ -869,13 +871,14 @@ int attention_forward_packed(stream_t stream, const void *qkv, void *out, float 
   p.scale = scale;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.status = attn_status_ptr();
+  p.causal = causal ? 1 : 0;
   dim3 grid(static_cast<unsigned>(T / BQ), static_cast<unsigned>(H), static_cast<unsigned>(B));
   attention_fwd_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map_q, map_kv, p);
   return finish_launch(1);
 }
 
 int attention_backward_packed(stream_t stream, const void *qkv, const void *out, const void *dout, const float *lse, float *delta,
-                              void *dqkv, int64_t B, int64_t T, int64_t H, int64_t D, float scale) {
+                              void *dqkv, int64_t B, int64_t T, int64_t H, int64_t D, float scale, int causal) {
   if (D != HD || T % 128 != 0 || B <= 0 || H <= 0 || T <= 0) return -1;
   if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(dout) |
        reinterpret_cast<uintptr_t>(dqkv) | reinterpret_cast<uintptr_t>(lse) | reinterpret_cast<uintptr_t>(delta)) & 15)
@@ -905,6 +908,7 @@ int attention_backward_packed(stream_t stream, const void *qkv, const void *out,
   p.scale = scale;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.status = attn_status_ptr();
+  p.causal = causal ? 1 : 0;
   dim3 grid(static_cast<unsigned>(T / 128), static_cast<unsigned>(H), static_cast<unsigned>(B));
   attention_bwd_kernel<true><<<grid, BWD_THREADS, bwd_smem_bytes(true), s>>>(qkv_r, qkv_c, do_r, do_c, p);
   attention_bwd_kernel<false><<<grid, BWD_THREADS, bwd_smem_bytes(false), s>>>(qkv_r, qkv_c, do_r, do_c, p);

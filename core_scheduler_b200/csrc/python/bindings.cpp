@@ -121,25 +121,25 @@ PYBIND11_MODULE(_C, m) {
         py::arg("bias") = py::none(), py::arg("d2") = py::none(), py::arg("stats") = py::none(), py::arg("n_valid") = -1);
   m.def("gemm_ce_stat_tiles", &cs::kernels::gemm_ce_stat_tiles);
   // Raw access to the tcgen05 attention forward kernel (current torch stream).
-  m.def("attention_forward_tcgen05", [](const at::Tensor &qkv, int64_t heads, double scale) {
+  m.def("attention_forward_tcgen05", [](const at::Tensor &qkv, int64_t heads, double scale, bool causal) {
     const int64_t B = qkv.size(0), T = qkv.size(1), D = qkv.size(2) / (3 * heads);
     at::Tensor out = at::empty({B, T, heads * D}, qkv.options());
     at::Tensor lse = at::empty({B, heads, T}, qkv.options().dtype(at::kFloat));
     const int rc = cs::kernels::attention_forward_packed(c10::cuda::getCurrentCUDAStream().stream(), qkv.data_ptr(), out.data_ptr(),
-                                                        lse.data_ptr<float>(), B, T, heads, D, static_cast<float>(scale));
+                                                        lse.data_ptr<float>(), B, T, heads, D, static_cast<float>(scale), causal ? 1 : 0);
     return py::make_tuple(rc, out, lse);
-  });
+  }, py::arg("qkv"), py::arg("heads"), py::arg("scale"), py::arg("causal") = true);
   m.def("attention_backward_tcgen05", [](const at::Tensor &qkv, const at::Tensor &out, const at::Tensor &dout, const at::Tensor &lse,
-                                         int64_t heads, double scale) {
+                                         int64_t heads, double scale, bool causal) {
     const int64_t B = qkv.size(0), T = qkv.size(1), D = qkv.size(2) / (3 * heads);
     at::Tensor dqkv = at::empty_like(qkv);
     at::Tensor delta = at::empty({3, B, heads, T}, qkv.options().dtype(at::kFloat));
     const int rc = cs::kernels::attention_backward_packed(c10::cuda::getCurrentCUDAStream().stream(), qkv.data_ptr(), out.data_ptr(),
                                                           dout.data_ptr(), lse.data_ptr<float>(), delta.data_ptr<float>(),
-                                                          dqkv.data_ptr(), B, T, heads, D, static_cast<float>(scale));
+                                                          dqkv.data_ptr(), B, T, heads, D, static_cast<float>(scale), causal ? 1 : 0);
     CS_ASSERT_TRUE(rc == 0, "attention_backward_packed returned ", rc);
     return py::make_tuple(dqkv, delta.select(0, 0));
-  });
+  }, py::arg("qkv"), py::arg("out"), py::arg("dout"), py::arg("lse"), py::arg("heads"), py::arg("scale"), py::arg("causal") = true);
   m.def("bounds_check_enabled", &cs::kernels::bounds_check_enabled);
   m.def("bounds_report", [](bool reset) {
     cs::kernels::BoundsReport r{};

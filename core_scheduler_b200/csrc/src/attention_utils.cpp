@@ -243,12 +243,13 @@ Tensor ScaledDotProductAttention::forward_packed(const Scheduler &scheduler, con
            CS_ASSERT_TRUE(x.dim() == 3 && x.size(2) % (3 * num_heads) == 0, "packed qkv must be [B,T,3*H*D]");
            const int64_t B = x.size(0), T = x.size(1), D = x.size(2) / (3 * num_heads);
            if (use_own_forward() && x.is_cuda() && x.scalar_type() == at::kBFloat16 && fused_enabled() && x.is_contiguous() &&
-               state->args.is_causal && state->args.dropout_p == 0.0) {
+               state->args.dropout_p == 0.0) {
              at::Tensor o = at::empty({B, T, num_heads * D}, x.options());
              at::Tensor lse = at::empty({B, num_heads, T}, x.options().dtype(at::kFloat));
              const int code = kernels::attention_forward_packed(current_stream(), x.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), B,
                                                                 T, num_heads, D,
-                                                                static_cast<float>(resolve_scale(state->args.scale, D)));
+                                                                static_cast<float>(resolve_scale(state->args.scale, D)),
+                                                                state->args.is_causal ? 1 : 0);
              if (code == 0) {
                saved.out.impl()->tensor = o.view({B, T, num_heads, D}).transpose(1, 2);  // [B,H,T,D] view
                saved.lse.impl()->tensor = lse;
@@ -299,7 +300,8 @@ Tensor ScaledDotProductAttention::backward_packed(const Scheduler &scheduler, co
                at::Tensor delta = at::empty({3, B, H, T}, x.options().dtype(at::kFloat));
                const int code = kernels::attention_backward_packed(
                    current_stream(), x.data_ptr(), o_bthd.data_ptr(), go.data_ptr(), bw.logsumexp.impl()->tensor.data_ptr<float>(),
-                   delta.data_ptr<float>(), packed.data_ptr(), B, T, H, D, static_cast<float>(resolve_scale(args.scale, D)));
+                   delta.data_ptr<float>(), packed.data_ptr(), B, T, H, D, static_cast<float>(resolve_scale(args.scale, D)),
+                   args.is_causal ? 1 : 0);
                if (code == 0) {
                  dqkv.impl()->tensor = packed;
                  return;

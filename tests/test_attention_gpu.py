@@ -84,3 +84,43 @@ def test_backward_through_the_op_uses_own_kernels(gpu_scheduler, monkeypatch):
     ref.backward(do.float())
     assert torch.allclose(out.raw().float(), ref, atol=2e-2, rtol=2e-2)
     assert (dqkv.raw().float() - qr.grad).abs().max().item() < 5e-2
+
+
+@pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 256, 3), (1, 512, 2)])
+def test_non_causal_forward_and_backward_match_reference(B, T, H):
+    """The same kernels without the mask: every query attends to every key."""
+    D = 64
+    torch.manual_seed(11 * B + T + H)
+    qkv = torch.randn(B, T, 3 * H * D, device="cuda").to(BF)
+    dout = torch.randn(B, T, H * D, device="cuda").to(BF)
+    scale = 1.0 / math.sqrt(D)
+    rc, out, lse = C.attention_forward_tcgen05(qkv, H, scale, causal=False)
+    assert rc == 0
+    dqkv, _ = C.attention_backward_tcgen05(qkv, out, dout, lse, H, scale, causal=False)
+    torch.cuda.synchronize()
+    assert C.attention_status()[0] == 0
+    qr = qkv.float().requires_grad_(True)
+    q, k, v = qr.view(B, T, 3, H, D).unbind(2)
+    ref = attention_reference(q, k, v, causal=False).reshape(B, T, H * D)
+    ref.backward(dout.float())
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2)
+    s = torch.einsum("bthd,bshd->bhts", q, k) * scale
+    assert torch.allclose(lse, torch.logsumexp(s, dim=-1), atol=2e-2, rtol=1e-3)
+    got, want = dqkv.float().view(B, T, 3, H, D), qr.grad.view(B, T, 3, H, D)
+    for i, name in enumerate(("dq", "dk", "dv")):
+        err = (got[:, :, i] - want[:, :, i]).abs().max().item()
+        assert err <= 3e-2 * max(1.0, want[:, :, i].abs().max().item()), (name, err)
+
+
+def test_non_causal_attention_through_the_op_stays_on_own_kernels(gpu_scheduler):
+    s = gpu_scheduler
+    B, T, H, D = 2, 256, 2, 64
+    qkv = torch.randn(B, T, 3 * H * D, device="cuda").to(BF)
+    st = C.attention_init(s, is_causal=False)
+    fallbacks = C.library_fallbacks()
+    before = C.kernel_launch_count()
+    out = C.attention_forward_packed(s, st, cs.from_torch(qkv), H)
+    s.synchronize()
+    assert C.kernel_launch_count() - before == 1 and C.library_fallbacks() == fallbacks
+    q, k, v = qkv.float().view(B, T, 3, H, D).unbind(2)
+    assert torch.allclose(out.raw().float(), attention_reference(q, k, v, causal=False).reshape(B, T, H * D), atol=2e-2, rtol=2e-2)
