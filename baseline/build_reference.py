@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Builds the unmodified reference sources into baseline/_ref/ (git-ignored) and the GPT-2 driver.
 
   python baseline/build_reference.py [--reference <checkout>]      (default: $CS_REFERENCE_DIR or ../reference beside the repo)

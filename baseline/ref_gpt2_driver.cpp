@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Benchmark driver for the reference library (TheCoreTeam/core_scheduler) built unmodified into
 // baseline/_ref/libcore_scheduler_core.so: GPT-2 training steps written against the reference's
 // PUBLIC headers only (module::Linear / LayerNorm / Embedding, compute::GeLU,

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Force-included (-include) when compiling the reference project's src/module/module.cpp and
 // src/data/dataloader.cpp against Arrow 24: the sources are not touched. Arrow dropped the
 // three-argument parquet::arrow::OpenFile(file, pool, &reader) that module.cpp calls, and

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 /* Empty stand-in for hwloc: the reference project's CPU-affinity helpers in
  * src/threading/dynamic_scheduler.cpp are compiled but never called. Enough types and inline
  * no-ops for that file to compile; nothing here does any work. */

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 /* Stand-in for hwloc's NVML helper (see ../hwloc.h): never called. */
 #ifndef CS_BASELINE_HWLOC_NVML_SHIM_H
 #define CS_BASELINE_HWLOC_NVML_SHIM_H

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 /* Single-node stand-in for the handful of MPI calls the reference project makes (rank/size, a
  * broadcast from rank 0, the node-local split). MPI is not installed in this image; the ranks are
  * started with RANK / WORLD_SIZE / MASTER_PORT in the environment (torchrun or examples/launch.py)

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 /* See mpi.h in this directory. File-based collectives for ranks of one node. */
 #include "mpi.h"
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Headline benchmark: GPT-2 training tokens/sec (device-timed, max over ranks) on N GPUs of one node.
 
   python bench.py --gpus 1 --steps 10 --warmup 3

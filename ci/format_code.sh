@@ -1,4 +1,5 @@
 #!/bin/bash
+# SPDX-License-Identifier: Apache-2.0
 # Formats the C++ and CUDA sources with clang-format (style file .clang-format at the repository root) and makes
 # every such file end with exactly one newline. Counterpart of the reference project's script/format-code.sh.
 #   ci/format_code.sh          rewrite the files in place

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """core_scheduler_b200: a B200-native training framework with the capabilities of CoreScheduler.
 
 The runtime (future-tensor handles, the three-stream task scheduler, ops, modules, optimizers,

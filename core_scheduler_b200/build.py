@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """In-tree build of the native runtime.
 
 Produces, next to this file:

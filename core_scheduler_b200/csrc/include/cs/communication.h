@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Communicators and collectives as scheduler tasks on the comm stream.
 //
 // Capability parity (reference project paths): include/communication/communication.h:25-59,

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Functional compute ops. Every op is a struct with a State, an Options builder and static
 // init / forward / backward functions that build a task and submit it to a scheduler.
 //

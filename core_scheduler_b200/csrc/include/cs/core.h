@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Core runtime types of the B200 scheduler framework: logging/check macros, NVTX
 // ranges, pooled events, future-tensor handles, tasks and the multi-stream scheduler.
 //

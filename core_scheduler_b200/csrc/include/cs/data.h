@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Token datasets and loaders.
 //
 // Capability parity (reference project paths): include/data/dataset.h:35-41 +

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // GPT-2 built from this library's modules with a hand-written backward pass (no autograd).
 //
 // Structure, parameter names and backward order follow the reference project's example

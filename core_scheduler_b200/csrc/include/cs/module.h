@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Stateful module layer: parameter-owning op states, the module tree with dotted parameter
 // names, optimizer modules and Parquet checkpoints.
 //

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Stateful wrappers of the parameter-owning ops (what model code is written against).
 // Capability parity (reference project paths): include/module/{linear,gelu_linear,layer_norm,
 // embedding}.h and src/module/*.cpp: forward / backward (parameter gradient task and input

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Metrics, progress watchdog and resumable training state.
 //
 // The reference prints one console line per step from its examples

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Functional optimizers and their module wrappers.
 //
 // Capability parity (reference project paths): include/optimizer/adamw.h:31-74,

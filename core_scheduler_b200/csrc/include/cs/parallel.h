@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Parallel training strategies built on the communication layer.
 //
 // The reference project implements data parallelism only (bucketed all-reduce driven from the

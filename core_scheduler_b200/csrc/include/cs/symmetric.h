@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Peer-mapped ("symmetric") device memory for the ranks of one NVSwitch domain, a caching
 // sub-allocator on top of it, and the collectives / fused paths that run as this library's
 // own kernels over peer pointers.

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Host-side launch interface of the hand-written sm_100a kernels. Plain C++ (no torch
 // headers) so the .cu files compile in seconds and the C++ ops call them with raw pointers.
 // Every launcher enqueues on `stream` and returns a cudaError_t value as int (0 = success).

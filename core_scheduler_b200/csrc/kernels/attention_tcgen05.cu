@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Causal self-attention forward on tcgen05 tensor cores for head dimension 64, reading the packed
 // qkv tensor [B, T, 3, H, 64] (the c_attn output) directly and writing [B, T, H*64] plus the
 // per-row log-sum-exp.

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Checked index accessors for the diagnostic build of the kernels (-DCS_BOUNDS_CHECK).
 //
 // In that build every derived global index (row * stride + column, a token id used as a table

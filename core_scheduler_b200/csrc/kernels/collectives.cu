@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Collectives and fused compute+collective kernels over peer-mapped symmetric memory
 // (NVLink 5 through NVSwitch). See collectives.h for the protocol.
 //
@@ -19,6 +20,8 @@
 namespace cs::kernels {
 namespace {
 std::atomic<long long> g_wait_budget{4000000000LL};
+std::atomic<int> g_grid_cap{128};
+std::atomic<int> g_multicast_min_ranks{3};
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -258,32 +261,64 @@ __global__ void barrier_kernel(PeerTable t, int slot_base, uint32_t epoch, long 
 // outstanding per GPU; the grid supplies them (up to one light block per SM), not the per-thread depth.
 constexpr int kUnroll = 4;
 
-template <int DTYPE>
-__global__ void CS_COMM_BOUNDS all_reduce_kernel(PeerTable t, Handshake h, int64_t offset, int64_t vecs, float scale) {
+// How a reducing kernel reaches the other copies. One instantiation per path, so that each gets its own
+// register allocation: the switch path holds kUnroll reduced vectors, the pair path both copies of
+// kUnroll vectors (and trades two resident blocks per SM for them), the general path one vector per peer.
+enum : int { kPathSwitch = 0, kPathPair = 1, kPathPeers = 2 };
+#define CS_REDUCE_BOUNDS(PATH) __launch_bounds__(kThreads, (PATH) == kPathPair ? 4 : 6)
+
+// Sums of the vectors at base + i * 16 for i = i0, i0 + stride, ... (kUnroll of them, those below `end`).
+template <int DTYPE, int PATH>
+__device__ __forceinline__ void reduce_strip(const PeerTable &t, int64_t base, int64_t i0, int64_t stride, int64_t end, float scale,
+                                             V4 (&out)[kUnroll]) {
+  if (PATH == kPathSwitch) {
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < end && CS_PEER_OK(t, base + i * 16)) out[u] = DTYPE == 0 ? mc_ld_reduce_f32(t.mc + base + i * 16) : mc_ld_reduce_bf16(t.mc + base + i * 16);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) out[u] = scaled<DTYPE>(out[u], scale);
+  } else if (PATH == kPathPair) {
+    const char *mine = t.base[t.rank] + base, *theirs = t.base[t.rank ^ 1] + base;
+    V4 other[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < end && CS_PEER_OK(t, base + i * 16)) {
+        other[u] = ld_v4(theirs + i * 16);
+        out[u] = ld_v4(mine + i * 16);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      accumulate<DTYPE>(acc, out[u]);
+      accumulate<DTYPE>(acc, other[u]);
+      out[u] = finish<DTYPE>(acc, scale);
+    }
+  } else {
+#pragma unroll 1
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < end && CS_PEER_OK(t, base + i * 16)) out[u] = reduce_vector<DTYPE>(t, base + i * 16, scale);
+    }
+  }
+}
+
+template <int DTYPE, int PATH>
+__global__ void CS_REDUCE_BOUNDS(PATH) all_reduce_kernel(PeerTable t, Handshake h, int64_t offset, int64_t vecs, float scale) {
   open_collective(t, h, 11);
   int64_t begin, end;
   slice_of(vecs, t.size, t.rank, begin, end);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i0 = begin + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < end; i0 += stride * kUnroll) {
-    if (t.mc) {
-      V4 v[kUnroll];
+    V4 v[kUnroll];
+    reduce_strip<DTYPE, PATH>(t, offset, i0, stride, end, scale, v);
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const int64_t i = i0 + u * stride;
-        if (i < end && CS_PEER_OK(t, offset + i * 16))
-          v[u] = DTYPE == 0 ? mc_ld_reduce_f32(t.mc + offset + i * 16) : mc_ld_reduce_bf16(t.mc + offset + i * 16);
-      }
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const int64_t i = i0 + u * stride;
-        if (i < end && CS_PEER_OK(t, offset + i * 16)) mc_st(t.mc + offset + i * 16, scaled<DTYPE>(v[u], scale));
-      }
-    } else {
-#pragma unroll 1
-      for (int u = 0; u < kUnroll; ++u) {
-        const int64_t i = i0 + u * stride;
-        if (i < end && CS_PEER_OK(t, offset + i * 16)) broadcast_vector(t, offset + i * 16, reduce_vector<DTYPE>(t, offset + i * 16, scale));
-      }
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < end && CS_PEER_OK(t, offset + i * 16)) broadcast_vector(t, offset + i * 16, v[u]);
     }
   }
   close_collective(t, h, 11);
@@ -297,38 +332,20 @@ __device__ __forceinline__ V4 add_bf16x8(const V4 &v, const V4 &r) {
   return finish<1>(acc, 1.0f);
 }
 
-template <int DTYPE>
-__global__ void CS_COMM_BOUNDS reduce_scatter_kernel(PeerTable t, Handshake h, int64_t src_offset, char *dst, const char *residual,
-                                                     int64_t vecs, float scale) {
+template <int DTYPE, int PATH>
+__global__ void CS_REDUCE_BOUNDS(PATH) reduce_scatter_kernel(PeerTable t, Handshake h, int64_t src_offset, char *dst, const char *residual,
+                                                             int64_t vecs, float scale) {
   open_collective(t, h, 12);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < vecs; i0 += stride * kUnroll) {
-    if (t.mc) {
-      V4 v[kUnroll];
+    V4 v[kUnroll];
+    reduce_strip<DTYPE, PATH>(t, src_offset, i0, stride, vecs, scale, v);
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const int64_t i = i0 + u * stride;
-        if (i < vecs && CS_PEER_OK(t, src_offset + i * 16))
-          v[u] = DTYPE == 0 ? mc_ld_reduce_f32(t.mc + src_offset + i * 16) : mc_ld_reduce_bf16(t.mc + src_offset + i * 16);
-      }
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const int64_t i = i0 + u * stride;
-        if (i < vecs && CS_PEER_OK(t, src_offset + i * 16)) {
-          V4 o = scaled<DTYPE>(v[u], scale);
-          if (DTYPE == 1 && residual) o = add_bf16x8(o, ld_v4(residual + i * 16));
-          st_v4(dst + i * 16, o);
-        }
-      }
-    } else {
-#pragma unroll 1
-      for (int u = 0; u < kUnroll; ++u) {
-        const int64_t i = i0 + u * stride;
-        if (i < vecs && CS_PEER_OK(t, src_offset + i * 16)) {
-          V4 o = reduce_vector<DTYPE>(t, src_offset + i * 16, scale);
-          if (DTYPE == 1 && residual) o = add_bf16x8(o, ld_v4(residual + i * 16));
-          st_v4(dst + i * 16, o);
-        }
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < vecs && CS_PEER_OK(t, src_offset + i * 16)) {
+        if (DTYPE == 1 && residual) v[u] = add_bf16x8(v[u], ld_v4(residual + i * 16));
+        st_v4(dst + i * 16, v[u]);
       }
     }
   }
@@ -416,34 +433,36 @@ __global__ void CS_COMM_BOUNDS slot_sum_kernel(PeerTable t, Handshake h, const c
   }
 }
 
-__global__ void CS_COMM_BOUNDS pull_copy_kernel(PeerTable t, Handshake h, PullCopyArgs a) {
+// Blocks [p * per_peer_blocks, (p + 1) * per_peer_blocks) copy from the p-th peer, counted from this rank (local data
+// first, no two ranks start on the same peer). Eight 16-byte loads per thread are in flight.
+__global__ void __launch_bounds__(512) pull_copy_kernel(PeerTable t, Handshake h, PullCopyArgs a, int per_peer_blocks) {
   open_collective(t, h, 14);
-  // work item = (peer, vector); peers are visited starting with ourselves so that local data moves first
+  const int p = (t.rank + static_cast<int>(blockIdx.x) / per_peer_blocks) % t.size;
+  const int bx = static_cast<int>(blockIdx.x) % per_peer_blocks;
+  const char *src = t.base[p] + a.src_offset[p];
+  char *dst = a.dst[p];
   const int64_t vec_per_row = a.row_bytes / 16;
-  const int64_t per_peer = a.rows * vec_per_row;
-  const int64_t total = per_peer * t.size;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += stride * kUnroll) {
-    V4 v[kUnroll];
+  const int64_t total = a.rows * vec_per_row;
+  const int64_t stride = static_cast<int64_t>(per_peer_blocks) * blockDim.x;
+  constexpr int U = 8;
+  const bool flat = a.rows == 1;
+  for (int64_t i0 = static_cast<int64_t>(bx) * blockDim.x + threadIdx.x; i0 < total; i0 += stride * U) {
+    V4 v[U];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < U; ++u) {
       const int64_t i = i0 + u * stride;
       if (i < total) {
-        const int p = (t.rank + static_cast<int>(i / per_peer)) % t.size;
-        const int64_t j = i % per_peer;
-        const int64_t r = j / vec_per_row, c = j - r * vec_per_row;
+        const int64_t r = flat ? 0 : i / vec_per_row, c = i - r * vec_per_row;
         if (!CS_PEER_OK(t, a.src_offset[p] + r * a.src_stride + c * 16)) continue;
-        v[u] = ld_v4(t.base[p] + a.src_offset[p] + r * a.src_stride + c * 16);
+        v[u] = ld_v4(src + r * a.src_stride + c * 16);
       }
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < U; ++u) {
       const int64_t i = i0 + u * stride;
       if (i < total) {
-        const int p = (t.rank + static_cast<int>(i / per_peer)) % t.size;
-        const int64_t j = i % per_peer;
-        const int64_t r = j / vec_per_row, c = j - r * vec_per_row;
-        st_v4(a.dst[p] + r * a.dst_stride + c * 16, v[u]);
+        const int64_t r = flat ? 0 : i / vec_per_row, c = i - r * vec_per_row;
+        st_v4(dst + r * a.dst_stride + c * 16, v[u]);
       }
     }
   }
@@ -503,8 +522,24 @@ __global__ void CS_COMM_BOUNDS rs_adamw_ag_kernel(PeerTable t, Handshake h, Shar
   close_collective(t, h, 15);
 }
 
-// One light block per SM at most; small messages get proportionally fewer blocks.
-int comm_grid(int64_t vecs_per_rank, int cap = 128) {
+int reduce_path(const PeerTable &t) { return t.mc ? kPathSwitch : (t.size == 2 ? kPathPair : kPathPeers); }
+#define CS_DISPATCH_REDUCE(LAUNCH, dtype, path)                 \
+  do {                                                          \
+    const int path_ = (path);                                   \
+    if ((dtype) == 0) {                                         \
+      if (path_ == kPathSwitch) LAUNCH(0, kPathSwitch);         \
+      else if (path_ == kPathPair) LAUNCH(0, kPathPair);        \
+      else LAUNCH(0, kPathPeers);                               \
+    } else {                                                    \
+      if (path_ == kPathSwitch) LAUNCH(1, kPathSwitch);         \
+      else if (path_ == kPathPair) LAUNCH(1, kPathPair);        \
+      else LAUNCH(1, kPathPeers);                               \
+    }                                                           \
+  } while (0)
+
+// Small messages get proportionally fewer blocks than the cap.
+int comm_grid(int64_t vecs_per_rank) {
+  const int cap = g_grid_cap.load();
   const int64_t per_block = static_cast<int64_t>(kThreads) * kUnroll;
   const int64_t blocks = (vecs_per_rank + per_block - 1) / per_block;
   return static_cast<int>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
@@ -513,6 +548,10 @@ int comm_grid(int64_t vecs_per_rank, int cap = 128) {
 
 void set_peer_wait_budget(long long cycles) { g_wait_budget.store(cycles); }
 long long peer_wait_budget() { return g_wait_budget.load(); }
+void set_collective_grid_cap(int blocks) { g_grid_cap.store(blocks < 1 ? 1 : (blocks > 1024 ? 1024 : blocks)); }
+int collective_grid_cap() { return g_grid_cap.load(); }
+void set_multicast_min_ranks(int ranks) { g_multicast_min_ranks.store(ranks < 2 ? 2 : ranks); }
+int multicast_min_ranks() { return g_multicast_min_ranks.load(); }
 
 int symm_barrier(stream_t stream, const PeerTable &t, int slot_base, uint32_t epoch, DeviceStatus *status) {
   barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(t, slot_base, epoch, g_wait_budget.load(), status);
@@ -527,10 +566,9 @@ int symm_all_reduce(stream_t stream, const PeerTable &t, const Handshake &h, int
   const int grid = comm_grid((vecs + t.size - 1) / t.size);
   *blocks = grid;
   auto s = static_cast<cudaStream_t>(stream);
-  if (dtype == 0)
-    all_reduce_kernel<0><<<grid, kThreads, 0, s>>>(t, h, offset_bytes, vecs, scale);
-  else
-    all_reduce_kernel<1><<<grid, kThreads, 0, s>>>(t, h, offset_bytes, vecs, scale);
+#define CS_LAUNCH_ALL_REDUCE(DTYPE, PATH) all_reduce_kernel<DTYPE, PATH><<<grid, kThreads, 0, s>>>(t, h, offset_bytes, vecs, scale)
+  CS_DISPATCH_REDUCE(CS_LAUNCH_ALL_REDUCE, dtype, reduce_path(t));
+#undef CS_LAUNCH_ALL_REDUCE
   return finish_launch(1);
 }
 
@@ -544,11 +582,11 @@ int symm_reduce_scatter(stream_t stream, const PeerTable &t, const Handshake &h,
   const int grid = comm_grid(vecs);
   *blocks = grid;
   auto s = static_cast<cudaStream_t>(stream);
-  if (dtype == 0)
-    reduce_scatter_kernel<0><<<grid, kThreads, 0, s>>>(t, h, src_offset_bytes, static_cast<char *>(dst), nullptr, vecs, scale);
-  else
-    reduce_scatter_kernel<1><<<grid, kThreads, 0, s>>>(t, h, src_offset_bytes, static_cast<char *>(dst), static_cast<const char *>(residual),
-                                                       vecs, scale);
+#define CS_LAUNCH_REDUCE_SCATTER(DTYPE, PATH)                                                                                    \
+  reduce_scatter_kernel<DTYPE, PATH><<<grid, kThreads, 0, s>>>(t, h, src_offset_bytes, static_cast<char *>(dst),                  \
+                                                               DTYPE == 1 ? static_cast<const char *>(residual) : nullptr, vecs, scale)
+  CS_DISPATCH_REDUCE(CS_LAUNCH_REDUCE_SCATTER, dtype, reduce_path(t));
+#undef CS_LAUNCH_REDUCE_SCATTER
   return finish_launch(1);
 }
 
@@ -593,10 +631,13 @@ int symm_pull_copy(stream_t stream, const PeerTable &t, const Handshake &h, cons
   if (a.row_bytes % 16 != 0 || a.src_stride % 16 != 0 || a.dst_stride % 16 != 0) return static_cast<int>(cudaErrorInvalidValue);
   for (int p = 0; p < t.size; ++p)
     if ((a.src_offset[p] % 16) != 0 || (reinterpret_cast<uintptr_t>(a.dst[p]) & 15)) return static_cast<int>(cudaErrorInvalidValue);
-  const int64_t vecs = a.rows * (a.row_bytes / 16) * t.size;
-  const int grid = comm_grid(vecs);
-  *blocks = grid;
-  pull_copy_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(t, h, a);
+  const int64_t vecs = a.rows * (a.row_bytes / 16);
+  const int64_t wanted = (vecs + 512 * 8 - 1) / (512 * 8);
+  const int total = g_grid_cap.load();
+  const int cap = total / t.size > 8 ? total / t.size : 8;  // blocks per peer
+  const int per_peer = static_cast<int>(wanted < 1 ? 1 : (wanted > cap ? cap : wanted));
+  *blocks = per_peer * t.size;
+  pull_copy_kernel<<<per_peer * t.size, 512, 0, static_cast<cudaStream_t>(stream)>>>(t, h, a, per_peer);
   return finish_launch(1);
 }
 

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Launch interface of the peer-memory collective kernels (kernels/collectives.cu).
 // All ranks of one NVSwitch domain map each other's symmetric arena; a kernel on rank r
 // addresses rank p's copy of a buffer as table.base[p] + offset and, when the arena has an
@@ -73,6 +74,17 @@ struct Handshake {
 // provoke the timeout path: the kernel then records DeviceStatus{code=2} and returns.
 void set_peer_wait_budget(long long cycles);
 long long peer_wait_budget();
+
+// Launch tuning of the link-bound kernels, process-wide (every rank must use the same values).
+// grid cap: most blocks one collective launches (default 128; more blocks keep more bytes in flight on
+// NVLink, fewer leave more of each SM to a GEMM running beside the collective).
+// multicast threshold: smallest group that uses the NVLink multicast mapping when one exists (default 3).
+// In a group of two a multimem access also fetches the local copy through the switch, which doubles the
+// bytes on the wire, so pairs use plain peer loads and stores.
+void set_collective_grid_cap(int blocks);
+int collective_grid_cap();
+void set_multicast_min_ranks(int ranks);
+int multicast_min_ranks();
 
 // All ranks arrive and leave together: rank r stores `epoch` into slot (slot_base + r) of every
 // peer's pad and waits until its own pad shows `epoch` from every peer. One CTA.

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Memory-bound sm_100a kernels: AdamW, GELU, residual add, casts/transposes, LayerNorm,
 // embedding, cross-entropy helpers and gradient-norm reductions. All are vectorised to 128-bit
 // accesses and sized so that a launch covers the 148 SMs with several resident CTAs each.

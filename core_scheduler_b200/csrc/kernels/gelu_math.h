@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // GELU in its exact (erf) form, shared by the GEMM epilogues and the stand-alone GELU kernels.
 #pragma once
 

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // bf16 GEMM on the 5th-generation tensor cores (tcgen05) with fp32 accumulators in tensor
 // memory (TMEM), operands staged in shared memory by TMA, and fused epilogues.
 //

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // C entry point that never allocates. It has no counterpart in the reference project.
 //
 // Who needs it: code that drives this library from a place where device allocation is not

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Python bindings of the C++ framework (module core_scheduler_b200._C). The Python layer adds
 // no behaviour of its own to these calls: tests, the benchmark and the examples drive the same
 // C++ objects a C++ program would.
@@ -771,6 +772,10 @@ PYBIND11_MODULE(_C, m) {
                [c](const FnTask &) { c.impl()->symmetric->barrier(); });
   });
   m.def("set_peer_wait_budget", &cs::kernels::set_peer_wait_budget);
+  m.def("set_collective_grid_cap", &cs::kernels::set_collective_grid_cap);
+  m.def("collective_grid_cap", &cs::kernels::collective_grid_cap);
+  m.def("set_multicast_min_ranks", &cs::kernels::set_multicast_min_ranks);
+  m.def("multicast_min_ranks", &cs::kernels::multicast_min_ranks);
   m.def("flatten_symmetric", [](const Scheduler &s, const module::Module &mod, const Comm &c) {
     return parallel::flatten_symmetric(s, mod, c);
   });

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // ScaledDotProductAttention, Utils and Init. See cs/compute.h.
 // Reference behaviour studied in src/compute/{sdpa_flash_attn,sdpa_cudnn,utils,init}.cpp of the
 // reference project: q/k/v arrive as [B,T,H,D]; backward returns dq,dk,dv in the same layout;

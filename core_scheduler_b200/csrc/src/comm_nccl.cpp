@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // NCCL process-group construction (kept in its own translation unit because it needs the
 // NCCL headers that match the libtorch build).
 #include <torch/csrc/distributed/c10d/ProcessGroupNCCL.hpp>

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // In-process communicator group: `size` ranks that live on threads of one process and exchange tensors through
 // shared memory. It exists for host-side tests of everything that sits above a collective (buckets, gradient
 // sync, sharded training loops, failure handling) without GPUs, sockets or a launcher: a rank can be delayed, or

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Communicators and library-backed collectives. See cs/communication.h for the parity map.
 #include "cs/communication.h"
 

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Parameter-owning and activation ops (Linear, GeluLinear, LayerNorm, GeLU, Embedding,
 // CrossEntropy, LinearCrossEntropy, ScaledDotProductAttention). See cs/compute.h.
 //

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Runtime core: logger, pooled events, tensor handles, tasks, the three-stream scheduler,
 // autocast guard and the blocking to_torch bridge. See cs/core.h for the parity map.
 #include "cs/core.h"

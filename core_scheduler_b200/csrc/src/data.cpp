@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Dataset listing and threaded loaders. See cs/data.h for the parity map.
 #include "cs/data.h"
 

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // GPT-2 model. See cs/models.h for the parity map and the fusion list.
 #include <cmath>
 

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Module tree, flat parameter arenas, optimizer-module base and checkpoints.
 // Reference behaviour studied in src/module/module.cpp:32-220 and
 // src/module/optimizer_module.cpp:22-51 of the reference project: depth-first traversal in

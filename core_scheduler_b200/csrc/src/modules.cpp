@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Module wrappers. See cs/modules.h.
 #include "cs/modules.h"
 

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Helpers shared by the op implementation files (not part of the public surface).
 #pragma once
 #include "cs/compute.h"

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // AdamW / AmpAdamW functional ops and module::AdamW. See cs/optimizer.h for the parity map.
 #include "cs/optimizer.h"
 

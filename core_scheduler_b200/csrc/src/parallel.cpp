@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // ZeRO-style sharded optimizer and symmetric-memory flattening. See cs/parallel.h.
 #include "cs/parallel.h"
 

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Arrow/Parquet glue. Checkpoint layout parity: src/module/module.cpp:129-220 of the reference
 // project (key: utf8, value: list<float32>, one row per parameter); token files parity:
 // src/data/dataloader.cpp:118-205 (list columns input_ids / labels, int32 or int64 items).

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Narrow Parquet interface (the only translation unit that includes Arrow headers is
 // parquet_io.cpp). Used by checkpoints and by the token dataset.
 #pragma once

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Glue between the symmetric-memory context and the kernel launch interface (not part of the public surface).
 #pragma once
 #include "cs/symmetric.h"
@@ -10,7 +11,7 @@ inline kernels::PeerTable table_of(const SymmetricContext &ctx) {
     t.base[p] = ctx.bases[p];
     t.flags[p] = ctx.flags[p];
   }
-  t.mc = ctx.multicast_base;
+  t.mc = ctx.size >= kernels::multicast_min_ranks() ? ctx.multicast_base : nullptr;
   t.rank = ctx.rank;
   t.size = ctx.size;
   t.arena_bytes = ctx.arena_bytes;

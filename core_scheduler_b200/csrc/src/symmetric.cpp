@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Symmetric memory context and peer-memory collectives (host side). See cs/symmetric.h.
 #include "cs/symmetric.h"
 

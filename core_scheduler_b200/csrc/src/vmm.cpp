@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // See vmm.h.
 #include "vmm.h"
 

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Virtual-memory-management allocation of the symmetric arena, shared between the processes of one
 // NVSwitch domain, with an NVLink multicast object bound over the same pages.
 //

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Model presets. The model itself (`GPT2`) is implemented in C++ (csrc/src/models_gpt2.cpp)."""
 from __future__ import annotations
 

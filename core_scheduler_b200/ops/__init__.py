@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Ops with explicit backward, as Python objects over the native library.
 
 Each class owns the native State of one op of the reference project's `cs::compute` layer and exposes the same

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Process-group plumbing: one process per GPU, torch.distributed (NCCL on GPUs, Gloo on CPUs)."""
 from __future__ import annotations
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Checkpoint files outside a training process: reading and writing the parameter table, and uniting the
 per-rank files of a tensor-parallel run into the canonical single-model file.
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Read-only sampling of GPU clocks and throttle reasons while a benchmark runs."""
 from __future__ import annotations
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Collective microbenchmark: all-reduce, all-gather, reduce-scatter, all-to-all on bf16 tensors.
 
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
@@ -56,7 +57,15 @@ def main():
     p.add_argument("--max-mb", type=int, default=1024)
     p.add_argument("--backends", default="nccl,nvp2p")
     p.add_argument("--iters", type=int, default=10)
+    p.add_argument("--min-mb", type=float, default=0.0, help="first message size (default 1 KiB)")
+    p.add_argument("--grid-cap", type=int, default=0, help="most blocks per collective launch (library default when 0)")
+    p.add_argument("--multicast-min-ranks", type=int, default=0,
+                   help="smallest group that uses the multicast mapping (library default when 0)")
     args = p.parse_args()
+    if args.grid_cap:
+        C.set_collective_grid_cap(args.grid_cap)
+    if args.multicast_min_ranks:
+        C.set_multicast_min_ranks(args.multicast_min_ranks)
     comm_nccl, rank, world, local_rank = init_distributed("cuda")
     assert world > 1, "launch with torch.distributed.run on at least 2 GPUs"
     s = cs.DynamicScheduler(local_rank, device="cuda")
@@ -66,12 +75,13 @@ def main():
     max_bytes = args.max_mb << 20
     ctx = C.create_symmetric_context(comm_p2p, 3 * max_bytes + (64 << 20))
     comms = {"nccl": comm_nccl, "nvp2p": comm_p2p}
-    memory = "multicast" if ctx.has_multicast else ("peer mappings (cuMemCreate)" if ctx.virtual_memory else "peer mappings (CUDA IPC)")
+    multicast_used = ctx.has_multicast and world >= C.multicast_min_ranks()
+    memory = "multicast" if multicast_used else ("peer mappings (cuMemCreate)" if ctx.virtual_memory else "peer mappings (CUDA IPC)")
     if rank == 0:
-        print(f"world {world}; symmetric arena: {memory}", flush=True)
+        print(f"world {world}; symmetric arena: {memory}; grid cap {C.collective_grid_cap()}", flush=True)
     sampler = ClockSampler(local_rank).start() if rank == 0 else None
     results = []
-    size = 1024
+    size = max(1024, int(args.min_mb * (1 << 20)))
     while size <= max_bytes:
         n = size // 2  # bf16 elements
         chunk = max(8, (n // world) // 8 * 8)
@@ -110,7 +120,7 @@ def main():
     if rank == 0:
         clocks = sampler.stop()
         print("clocks during the run:", json.dumps(clocks))
-        print(json.dumps({"world": world, "memory": memory, "clocks": clocks, "results": results}))
+        print(json.dumps({"world": world, "memory": memory, "grid_cap": C.collective_grid_cap(), "clocks": clocks, "results": results}))
     dist.barrier()
     dist.destroy_process_group()
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Kernel microbenchmarks with CUDA-event timing (after warm-up, L2 flushed between iterations).
 
   python -m core_scheduler_b200.utils.microbench gemm        # tcgen05 GEMM vs torch.matmul (cuBLAS)

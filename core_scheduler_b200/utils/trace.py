@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Chrome-trace export of the scheduler's per-task device timings.
 
   s.set_profiling(True); ... one step ...; rows = s.drain_timings()

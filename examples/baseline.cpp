@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Pure-libtorch autograd GPT-2 for comparison (counterpart of the reference project's
 // example/gpt2/baseline.cpp): bf16 parameters, torch::optim::AdamW, synthetic random tokens,
 // the same tokens/sec print as the framework examples. Nothing of this library's runtime is

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Data-parallel GPT-2 training, one process per GPU (counterpart of the reference project's
 // example/gpt2/gpt2_ddp.cpp). Launch with torchrun-style environment variables (RANK,
 // WORLD_SIZE, LOCAL_RANK, MASTER_ADDR, MASTER_PORT), e.g. through examples/launch.py.

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // GPT-2 training on one device through the C++ API (counterpart of the reference project's
 // example/gpt2/gpt2_single_device.cpp): fp32 master parameters, bf16 autocast on GPUs, cosine
 // learning rate with warm-up, gradient accumulation, loss log as CSV. Data: a Parquet token

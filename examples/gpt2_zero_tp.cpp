@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // GPT-2 training with the sharded optimizer (--mode zero) or tensor + sequence parallelism
 // (--mode tp), one process per GPU. The reference project has neither mode; its data-parallel
 // example is example/gpt2/gpt2_ddp.cpp. Launch with torchrun-style environment variables (RANK,

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Starts one process per GPU with the rendezvous environment the C++ examples read.
 
   python examples/launch.py --nproc 8 [--master-port 29500] -- examples/bin/gpt2_ddp --model 124M --steps 20

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Tokenise text corpora into the Parquet layout the data loader reads.
 
 Counterpart of the reference project's example/dataset/prepare_text_gen.py (lines 24-66 configuration, 95-110 windowing,

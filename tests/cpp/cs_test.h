@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // A very small test harness for the C++ test programs (the image has no GoogleTest): tests register
 // themselves at static-initialisation time, failures are recorded and reported per test, exceptions
 // count as failures, and the process exit code is the number of failed tests.

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Multi-rank tests of the collectives through the C++ API (the counterpart of the reference project's
 // core_scheduler_communication_tests: test/test_all_reduce.cpp, test_all_gather.cpp, test_reduce_scatter.cpp,
 // test_all_to_all.cpp). One process per GPU, started by examples/launch.py or torchrun (RANK, LOCAL_RANK,

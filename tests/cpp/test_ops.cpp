@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Single-device tests of the C++ API against libtorch autograd on the same device (the counterpart of the
 // reference project's core_scheduler_tests: test/test_linear.cpp, test_layer_norm.cpp, test_gelu.cpp,
 // test_embedding.cpp, test_cross_entropy.cpp, test_flash_attention.cpp, test_utils.cpp, test_autocast.cpp,

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Multi-rank test body. Launched by tests/test_distributed*.py through torch.distributed.run:
 
     python -m torch.distributed.run --standalone ... tests/dist_worker.py <device> <case>

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Plain PyTorch references used as oracles by the tests."""
 import math
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """tcgen05 causal attention forward kernel against fp32 masked-softmax attention."""
 import math
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """bench.py prints one JSON line with the keys its callers read."""
 import json
 import os

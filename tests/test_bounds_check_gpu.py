@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Diagnostic kernel build (-DCS_BOUNDS_CHECK): out-of-range indices are recorded and skipped.
 
 Runs in a child process because the checked library is chosen at import time (CS_BOUNDS_CHECK=1).

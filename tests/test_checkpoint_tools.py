@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """core_scheduler_b200.utils.checkpoint: the parameter table outside a training process."""
 import subprocess
 import sys

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """The peer-memory collective kernels and the fused GEMM + collective kernels on ONE GPU.
 
 `create_loopback_contexts(n, bytes)` emulates n ranks in this process: every rank's symmetric arena is a plain

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """The C++ test programs (tests/cpp/): cs_b200_tests for one device, cs_b200_communication_tests for the collectives.
 They mirror the reference project's two GoogleTest executables (test/CMakeLists.txt:15-48) with a small harness of
 their own, since the image has no GoogleTest."""

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Parquet dataset listing, loader sharding arithmetic, pinned staging and the synthetic loader."""
 import os
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Host-side logic of the communication layer with two Gloo ranks on the CPU (no GPU involved)."""
 import os
 import subprocess

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Collectives and parallel training on 2 GPUs: NCCL path and this library's peer-memory kernels.
 
 Runs as child processes (one per GPU) with NVLS switched off, as multi-rank GPU tests should on

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """C++ entry points and the data preparation script."""
 import os
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """tcgen05 GEMM kernel: every layout/epilogue against fp32 PyTorch math, including ragged tiles."""
 import pytest
 import torch

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """End-to-end tiny GPT-2 on the CPU in fp32: loss/gradient parity with an autograd model, one
 optimizer step and a save/load round trip (the plumbing configuration)."""
 import torch

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """sm_100a kernels against plain PyTorch fp32 references of the same op (GPU only)."""
 import math
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Metrics logger, host watchdog and resumable training state (CPU)."""
 import json
 import os

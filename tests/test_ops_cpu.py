@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Op numerics on the CPU (ATen path) against PyTorch autograd, mirroring the reference's unit tests."""
 import math
 

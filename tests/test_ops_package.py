@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """core_scheduler_b200.ops: the object layer over the native ops, checked against PyTorch autograd on the CPU."""
 import torch
 import torch.nn.functional as F

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """AdamW, module tree naming, flat arenas, checkpoints."""
 import os
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Plumbing of the reference arm that can be checked without a GPU: the MPI stand-in and bench.py's fallback line."""
 import json
 import os

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Scheduler semantics: stream classes, ordering across streams, re-join of side tasks, errors."""
 import pytest
 import torch

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """The allocation-free C entry point, called through its exported symbol.
 
 Some users of the library cannot allocate device memory at the point where they need a kernel:
