@@ -47,6 +47,7 @@ from ._C import (  # noqa: E402,F401
     Tensor,
     autocast,
     from_torch,
+    library_fallbacks,
     manual_seed,
     to_torch,
 )
@@ -63,6 +64,7 @@ __all__ = [
     "Tensor",
     "autocast",
     "from_torch",
+    "library_fallbacks",
     "manual_seed",
     "to_torch",
 ]
