@@ -13,6 +13,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <mutex>
 
 #include "collectives.h"
 #include "bounds_check.h"
@@ -20,7 +21,7 @@
 namespace cs::kernels {
 namespace {
 std::atomic<long long> g_wait_budget{4000000000LL};
-std::atomic<int> g_grid_cap{128};
+std::atomic<int> g_grid_cap{256};
 std::atomic<int> g_multicast_min_ranks{3};
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
@@ -469,6 +470,175 @@ __global__ void __launch_bounds__(512) pull_copy_kernel(PeerTable t, Handshake h
   close_collective(t, h, 14);
 }
 
+// ---- bulk copy engine ----------------------------------------------------------------------------------------
+// Copies whose source and destination are plain byte ranges (all-gather, all-to-all, strided pulls) do not need an
+// SM's load/store units: one thread per block drives cp.async.bulk transfers through a ring of shared-memory stages,
+// global (local or a peer's) -> shared completing on an mbarrier, shared -> global (local and peers') as bulk groups.
+// NVLink then carries full-size packets instead of 16-byte vector accesses, and a few dozen single-warp blocks keep
+// megabytes in flight. No load here carries a cluster-multicast qualifier; the sources may be peer memory.
+constexpr int kBulkStages = 4;
+constexpr int kBulkStageBytes = 32 * 1024;
+constexpr int kBulkSmemBytes = kBulkStages * kBulkStageBytes + 128;  // ring + mbarriers
+constexpr int kBulkThreads = 32;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
+               "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void *dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// The ring as seen by the driving thread. Item i uses stage i % kBulkStages; its load is issued kBulkStages - 1 items
+// ahead of its stores. A stage is loaded again only after every store group committed so far has read its source.
+struct BulkRing {
+  uint32_t data, bars;
+  int64_t loaded{0}, stored{0};
+  bool failed{false};
+
+  __device__ void init(unsigned char *smem) {
+    data = smem_u32(smem);
+    bars = data + kBulkStages * kBulkStageBytes;
+    for (int s = 0; s < kBulkStages; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bars + 8u * s) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __device__ void load(const void *src, uint32_t bytes) {
+    const int s = static_cast<int>(loaded % kBulkStages);
+    if (loaded >= kBulkStages) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    bulk_load(data + s * kBulkStageBytes, src, bytes, bars + 8u * s);
+    ++loaded;
+  }
+  // Waits (bounded) for the oldest loaded item and returns its shared-memory address; 0 after a timeout.
+  __device__ uint32_t arrived(const Handshake &h, int kernel_id) {
+    const int s = static_cast<int>(stored % kBulkStages);
+    const uint32_t parity = static_cast<uint32_t>((stored / kBulkStages) & 1);
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bars + 8u * s, parity)) {
+      if (clock64() - t0 > h.budget) {
+        report_timeout(h, kernel_id, 200 + static_cast<int>(blockIdx.x));
+        failed = true;
+        return 0;
+      }
+    }
+    ++stored;
+    return data + s * kBulkStageBytes;
+  }
+  // After a timeout: loads still in flight target this block's shared memory, so let them land (bounded again).
+  __device__ void settle(const Handshake &h) {
+    while (stored < loaded) {
+      const int s = static_cast<int>(stored % kBulkStages);
+      const uint32_t parity = static_cast<uint32_t>((stored / kBulkStages) & 1);
+      const long long t0 = clock64();
+      while (!mbar_try_wait(bars + 8u * s, parity))
+        if (clock64() - t0 > h.budget) return;
+      ++stored;
+    }
+  }
+  // Every store has been performed (not only read from shared memory) and is ordered before what this thread does next.
+  __device__ void drain() {
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    asm volatile("fence.proxy.async;" ::: "memory");
+  }
+};
+
+// All-gather push: this rank's `bytes` at `src` into every rank's arena at dst_offset + rank * bytes.
+// Pieces of at most one stage are dealt to the blocks round-robin.
+__global__ void __launch_bounds__(kBulkThreads) bulk_gather_push_kernel(PeerTable t, Handshake h, const char *src, int64_t dst_offset,
+                                                                        int64_t bytes) {
+  extern __shared__ __align__(128) unsigned char bulk_smem[];
+  open_collective(t, h, 18);
+  if (threadIdx.x == 0) {
+    BulkRing ring;
+    ring.init(bulk_smem);
+    const int64_t pieces = (bytes + kBulkStageBytes - 1) / kBulkStageBytes;
+    const int64_t mine = pieces > blockIdx.x ? (pieces - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int64_t to = dst_offset + static_cast<int64_t>(t.rank) * bytes;
+    auto offset_of = [&](int64_t k) { return (static_cast<int64_t>(blockIdx.x) + k * gridDim.x) * kBulkStageBytes; };
+    auto size_of = [&](int64_t k) {
+      const int64_t rest = bytes - offset_of(k);
+      return static_cast<uint32_t>(rest < kBulkStageBytes ? rest : kBulkStageBytes);
+    };
+    for (int64_t k = 0; k < mine + kBulkStages - 1 && !ring.failed; ++k) {
+      if (k < mine) ring.load(src + offset_of(k), size_of(k));
+      const int64_t j = k - (kBulkStages - 1);
+      if (j >= 0) {
+        const uint32_t from = ring.arrived(h, 18);
+        if (!from) break;  // failed is set
+        for (int p = 0; p < t.size; ++p) {
+          const int peer = (t.rank + p) % t.size;
+          if (CS_PEER_OK(t, to + offset_of(j) + size_of(j) - 16)) bulk_store(t.base[peer] + to + offset_of(j), from, size_of(j));
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
+    }
+    if (ring.failed) ring.settle(h);
+    ring.drain();
+  }
+  close_collective(t, h, 18);
+}
+
+// Strided pulls (all-to-all, all-gather from memory outside the arena): blocks [p * per_peer, (p + 1) * per_peer)
+// copy from the p-th peer counted from this rank. A row longer than one stage is cut into pieces.
+__global__ void __launch_bounds__(kBulkThreads) bulk_pull_copy_kernel(PeerTable t, Handshake h, PullCopyArgs a, int per_peer_blocks) {
+  extern __shared__ __align__(128) unsigned char bulk_smem[];
+  open_collective(t, h, 19);
+  if (threadIdx.x == 0) {
+    BulkRing ring;
+    ring.init(bulk_smem);
+    const int p = (t.rank + static_cast<int>(blockIdx.x) / per_peer_blocks) % t.size;
+    const int bx = static_cast<int>(blockIdx.x) % per_peer_blocks;
+    const char *src = t.base[p] + a.src_offset[p];
+    char *dst = a.dst[p];
+    const int64_t pieces_per_row = (a.row_bytes + kBulkStageBytes - 1) / kBulkStageBytes;
+    const int64_t pieces = a.rows * pieces_per_row;
+    const int64_t mine = pieces > bx ? (pieces - bx + per_peer_blocks - 1) / per_peer_blocks : 0;
+    auto piece_of = [&](int64_t k, int64_t &row, int64_t &col, uint32_t &size) {
+      const int64_t i = bx + k * per_peer_blocks;
+      row = i / pieces_per_row;
+      col = (i - row * pieces_per_row) * kBulkStageBytes;
+      const int64_t rest = a.row_bytes - col;
+      size = static_cast<uint32_t>(rest < kBulkStageBytes ? rest : kBulkStageBytes);
+    };
+    for (int64_t k = 0; k < mine + kBulkStages - 1 && !ring.failed; ++k) {
+      int64_t row, col;
+      uint32_t size;
+      if (k < mine) {
+        piece_of(k, row, col, size);
+        if (!CS_PEER_OK(t, a.src_offset[p] + row * a.src_stride + col + size - 16)) {
+          ring.failed = true;
+          break;
+        }
+        ring.load(src + row * a.src_stride + col, size);
+      }
+      const int64_t j = k - (kBulkStages - 1);
+      if (j >= 0) {
+        piece_of(j, row, col, size);
+        const uint32_t from = ring.arrived(h, 19);
+        if (!from) break;
+        bulk_store(dst + row * a.dst_stride + col, from, size);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
+    }
+    if (ring.failed) ring.settle(h);
+    ring.drain();
+  }
+  close_collective(t, h, 19);
+}
+
 __global__ void CS_COMM_BOUNDS rs_adamw_ag_kernel(PeerTable t, Handshake h, ShardedAdamWArgs a) {
   open_collective(t, h, 15);
   const float gscale = a.clip_coef ? a.grad_scale * a.clip_coef[0] : a.grad_scale;
@@ -520,6 +690,29 @@ __global__ void CS_COMM_BOUNDS rs_adamw_ag_kernel(PeerTable t, Handshake h, Shar
     }
   }
   close_collective(t, h, 15);
+}
+
+// The bulk engine takes over from the vector kernels where its fixed cost (one 32 KB piece per block and trip) pays.
+constexpr int64_t kBulkMinBytes = 512 * 1024;
+constexpr int64_t kBulkMinRowBytes = 4096;
+int bulk_grid_cap() {
+  const int cap = g_grid_cap.load() / 2;  // one block per SM (shared memory), so half the light kernels' share
+  return cap < 8 ? 8 : cap;
+}
+// Opts the two kernels in to their shared-memory size, once per device.
+bool bulk_engine_ready() {
+  static std::mutex mu;
+  static bool done[64] = {};
+  static bool ok[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!done[device]) {
+    done[device] = true;
+    ok[device] = cudaFuncSetAttribute(bulk_gather_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes) == cudaSuccess &&
+                 cudaFuncSetAttribute(bulk_pull_copy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes) == cudaSuccess;
+  }
+  return ok[device];
 }
 
 int reduce_path(const PeerTable &t) { return t.mc ? kPathSwitch : (t.size == 2 ? kPathPair : kPathPeers); }
@@ -593,6 +786,15 @@ int symm_reduce_scatter(stream_t stream, const PeerTable &t, const Handshake &h,
 int symm_all_gather_push(stream_t stream, const PeerTable &t, const Handshake &h, const void *src, int64_t dst_offset_bytes,
                          int64_t bytes, int *blocks) {
   if (bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(src) & 15) || dst_offset_bytes % 16 != 0) return static_cast<int>(cudaErrorInvalidValue);
+  if (bytes >= kBulkMinBytes && bulk_engine_ready()) {
+    const int64_t pieces = (bytes + kBulkStageBytes - 1) / kBulkStageBytes;
+    const int cap = bulk_grid_cap();
+    const int grid = static_cast<int>(pieces > cap ? cap : pieces);
+    *blocks = grid;
+    bulk_gather_push_kernel<<<grid, kBulkThreads, kBulkSmemBytes, static_cast<cudaStream_t>(stream)>>>(t, h, static_cast<const char *>(src),
+                                                                                                       dst_offset_bytes, bytes);
+    return finish_launch(1);
+  }
   const int64_t vecs = bytes / 16;
   const int grid = comm_grid(vecs);
   *blocks = grid;
@@ -631,6 +833,14 @@ int symm_pull_copy(stream_t stream, const PeerTable &t, const Handshake &h, cons
   if (a.row_bytes % 16 != 0 || a.src_stride % 16 != 0 || a.dst_stride % 16 != 0) return static_cast<int>(cudaErrorInvalidValue);
   for (int p = 0; p < t.size; ++p)
     if ((a.src_offset[p] % 16) != 0 || (reinterpret_cast<uintptr_t>(a.dst[p]) & 15)) return static_cast<int>(cudaErrorInvalidValue);
+  if (a.row_bytes >= kBulkMinRowBytes && a.rows * a.row_bytes >= kBulkMinBytes && bulk_engine_ready()) {
+    const int64_t pieces = a.rows * ((a.row_bytes + kBulkStageBytes - 1) / kBulkStageBytes);
+    const int cap = bulk_grid_cap() / t.size > 4 ? bulk_grid_cap() / t.size : 4;  // blocks per peer
+    const int per_peer = static_cast<int>(pieces > cap ? cap : pieces);
+    *blocks = per_peer * t.size;
+    bulk_pull_copy_kernel<<<per_peer * t.size, kBulkThreads, kBulkSmemBytes, static_cast<cudaStream_t>(stream)>>>(t, h, a, per_peer);
+    return finish_launch(1);
+  }
   const int64_t vecs = a.rows * (a.row_bytes / 16);
   const int64_t wanted = (vecs + 512 * 8 - 1) / (512 * 8);
   const int total = g_grid_cap.load();

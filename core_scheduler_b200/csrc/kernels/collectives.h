@@ -76,7 +76,7 @@ void set_peer_wait_budget(long long cycles);
 long long peer_wait_budget();
 
 // Launch tuning of the link-bound kernels, process-wide (every rank must use the same values).
-// grid cap: most blocks one collective launches (default 128; more blocks keep more bytes in flight on
+// grid cap: most blocks one collective launches (default 256; more blocks keep more bytes in flight on
 // NVLink, fewer leave more of each SM to a GEMM running beside the collective).
 // multicast threshold: smallest group that uses the NVLink multicast mapping when one exists (default 3).
 // In a group of two a multimem access also fetches the local copy through the switch, which doubles the

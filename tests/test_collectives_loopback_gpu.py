@@ -91,6 +91,39 @@ def test_all_gather_reduce_scatter_all_to_all(ranks):
                 assert torch.equal(a2a_dst[r][:, p * cols:(p + 1) * cols], seeded(50 + p, rows, cols * ranks, dtype=dtype)[:, r * cols:(r + 1) * cols])
 
 
+@pytest.mark.parametrize("ranks", [2, 4, 8])
+def test_large_copies_through_the_bulk_engine(ranks):
+    """Messages of half a megabyte and more are moved by the cp.async.bulk ring instead of vector loads and stores:
+    sizes that are not multiples of the 32 KB stage, rows shorter and longer than a stage."""
+    n = 300_008  # 1.2 MB of fp32, 36 full stages and a tail
+    ctxs = C.create_loopback_contexts(ranks, 96 << 20)
+    launches = C.kernel_launch_count()
+    dst = [ctx.empty([ranks, n], torch.float32)[0] for ctx in ctxs]
+    each_rank(ctxs, lambda r, ctx: ctx.all_gather_([dst[r][p] for p in range(ranks)], seeded(200 + r, n)))
+    for d in dst:
+        for p in range(ranks):
+            assert torch.equal(d[p], seeded(200 + p, n))
+    outs = [[torch.zeros(n, device="cuda") for _ in range(ranks)] for _ in range(ranks)]
+    src = [ctx.empty([n], torch.float32)[0] for ctx in ctxs]
+    for r in range(ranks):
+        src[r].copy_(seeded(210 + r, n))
+    each_rank(ctxs, lambda r, ctx: ctx.all_gather_(outs[r], src[r]))
+    for r in range(ranks):
+        for p in range(ranks):
+            assert torch.equal(outs[r][p], seeded(210 + p, n))
+    for rows, cols in ((160, 1056), (20, 10_004)):  # 4224-byte rows; 40016-byte rows (one stage and a tail each)
+        a2a_src = [ctx.empty([rows, cols * ranks], torch.float32)[0] for ctx in ctxs]
+        for r in range(ranks):
+            a2a_src[r].copy_(seeded(220 + r, rows, cols * ranks))
+        a2a_dst = [torch.zeros(rows, cols * ranks, device="cuda") for _ in range(ranks)]
+        each_rank(ctxs, lambda r, ctx: ctx.all_to_all_([a2a_dst[r][:, p * cols:(p + 1) * cols] for p in range(ranks)],
+                                                       [a2a_src[r][:, p * cols:(p + 1) * cols] for p in range(ranks)]))
+        for r in range(ranks):
+            for p in range(ranks):
+                assert torch.equal(a2a_dst[r][:, p * cols:(p + 1) * cols], seeded(220 + p, rows, cols * ranks)[:, r * cols:(r + 1) * cols])
+    assert C.kernel_launch_count() > launches
+
+
 @pytest.mark.parametrize("ranks", [2, 4])
 def test_reduce_scatter_adamw_all_gather_in_one_kernel(ranks):
     """Arena ranges that start and end inside ownership blocks; block j belongs to rank j % ranks."""
