@@ -11,12 +11,13 @@
 // the kernel. Block 0 exchanges flags with the peers, the other blocks wait on a local flag; at
 // the end the last block to finish does the closing exchange.
 //
-// Residency. A block of these kernels does NOT fit on an SM beside a block of the GEMM kernel (320 threads x 168
-// registers fill the register files of two of the SM's four partitions), so next to a running GEMM a collective
-// starts when GEMM blocks retire. That is harmless as long as the GEMM does not itself wait for the collective.
-// The one GEMM that does (it consumes rows while symm_all_gather_chunked is still delivering them) therefore
-// launches on all but kGatherBesideGemmBlocks SMs, and that gather uses at most kGatherBesideGemmBlocks blocks:
-// both kernels are always resident together and neither can starve the other.
+// Residency. The pair GEMM is compiled for 128 registers per thread, which leaves room on every SM for light blocks
+// of these kernels (256 threads, at most 40 registers, no shared memory to speak of): a collective proceeds beside a
+// running GEMM. The one GEMM that itself waits for a collective (it consumes rows while symm_all_gather_chunked is
+// still delivering them) launches on all but kGatherBesideGemmBlocks SMs, and that gather uses at most
+// kGatherBesideGemmBlocks blocks of 1024 threads: both kernels are always resident together and neither can starve
+// the other. The bulk-engine kernels need an SM's shared memory and wait for a free SM; nothing waits for them on
+// the device.
 #pragma once
 #include <cstdint>
 

@@ -163,7 +163,8 @@ def test_reduce_scatter_adamw_all_gather_in_one_kernel(ranks):
         assert torch.allclose(lp.double(), w, rtol=1e-2, atol=1e-2)
 
 
-@pytest.mark.parametrize("ranks,rows,chunks", [(2, 512, 2), (4, 256, 1), (8, 1024, 4)])
+# the last two cases move half a megabyte per chunk: the gather then runs on the bulk engine
+@pytest.mark.parametrize("ranks,rows,chunks", [(2, 512, 2), (4, 256, 1), (8, 1024, 4), (2, 2048, 2), (4, 4096, 4)])
 @pytest.mark.parametrize("weight_is_rhs", [False, True])
 def test_gather_beside_gemm(ranks, rows, chunks, weight_is_rhs):
     """all-gather -> GEMM: rows arrive in chunks announced by flags; the GEMM's loads wait for them."""
