@@ -206,6 +206,9 @@ struct FlattenOptions {
   CS_ARG(optional<at::ScalarType>, lp_dtype) = {};  // e.g. kBFloat16 for mixed precision
   CS_ARG(bool, transposed_copies) = false;          // only needed by consumers that want W^T laid out K-major
   CS_ARG(int64_t, pad_total_to) = 1;                // pad arena length (e.g. world size * 128 for sharding)
+  // Parameter names laid out first, in this order, ahead of the others (which keep the module's order). A group of
+  // parameters that is communicated or updated together then forms ONE contiguous range of each arena.
+  CS_ARG(std::vector<std::string>, first) = {};
 };
 
 // Re-homes all parameters of `module` into one contiguous buffer (values preserved), makes

@@ -19,10 +19,12 @@
 namespace cs::parallel {
 // Flattens `module` with its gradient and bf16 working-copy arenas inside the communicator's
 // symmetric memory, so that collectives read and write them in place. The arena length is
-// padded so that it splits evenly into `world * 128`-element shards.
+// padded so that it splits evenly into `world * 128`-element shards. `first`: parameter names laid out ahead of the
+// others (module::FlattenOptions::first), e.g. the parameters that tensor parallelism replicates.
 CS_API std::shared_ptr<module::FlatParameters> flatten_symmetric(const Scheduler &scheduler, const module::Module &module,
                                                                 const communication::Comm &comm,
-                                                                optional<at::ScalarType> lp_dtype = at::kBFloat16);
+                                                                optional<at::ScalarType> lp_dtype = at::kBFloat16,
+                                                                const std::vector<std::string> &first = {});
 
 struct CS_API ZeroAdamWImpl : module::OptimizerModule {
   using Options = optimizer::AdamW::Options;

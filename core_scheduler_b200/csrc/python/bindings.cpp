@@ -254,14 +254,15 @@ PYBIND11_MODULE(_C, m) {
         return out;
       });
   m.def("flatten_parameters",
-        [](const Scheduler &s, const module::Module &mod, py::object lp_dtype, bool transposed, int64_t pad_to) {
+        [](const Scheduler &s, const module::Module &mod, py::object lp_dtype, bool transposed, int64_t pad_to,
+           const std::vector<std::string> &first) {
           module::FlattenOptions o;
           if (!lp_dtype.is_none()) o.lp_dtype(py::cast<at::ScalarType>(lp_dtype));
-          o.transposed_copies(transposed).pad_total_to(pad_to);
+          o.transposed_copies(transposed).pad_total_to(pad_to).first(first);
           return module::flatten_parameters(s, mod, o);
         },
         py::arg("scheduler"), py::arg("module"), py::arg("lp_dtype") = py::none(), py::arg("transposed_copies") = false,
-        py::arg("pad_total_to") = 1);
+        py::arg("pad_total_to") = 1, py::arg("first") = std::vector<std::string>{});
 
   // ---- compute ops ---------------------------------------------------------------------------
   using compute::Linear;
@@ -776,9 +777,11 @@ PYBIND11_MODULE(_C, m) {
   m.def("collective_grid_cap", &cs::kernels::collective_grid_cap);
   m.def("set_multicast_min_ranks", &cs::kernels::set_multicast_min_ranks);
   m.def("multicast_min_ranks", &cs::kernels::multicast_min_ranks);
-  m.def("flatten_symmetric", [](const Scheduler &s, const module::Module &mod, const Comm &c) {
-    return parallel::flatten_symmetric(s, mod, c);
-  });
+  m.def("flatten_symmetric",
+        [](const Scheduler &s, const module::Module &mod, const Comm &c, const std::vector<std::string> &first) {
+          return parallel::flatten_symmetric(s, mod, c, at::kBFloat16, first);
+        },
+        py::arg("scheduler"), py::arg("module"), py::arg("comm"), py::arg("first") = std::vector<std::string>{});
   py::class_<parallel::ZeroAdamWImpl, module::OptimizerModule, std::shared_ptr<parallel::ZeroAdamWImpl>>(m, "ZeroAdamW")
       .def(py::init([](const Scheduler &s, const std::shared_ptr<module::Module> &mod,
                        std::shared_ptr<module::FlatParameters> flat, const Comm &c, double lr, double beta1, double beta2,

@@ -120,7 +120,29 @@ std::shared_ptr<FlatParameters> flatten_parameters(const Scheduler &scheduler, c
   at::ScalarType dtype = at::kFloat;
   bool first = true;
   std::vector<Tensor> param_handles, grad_handles;
-  for (auto &item : params) {
+  // layout order: the names of options.first(), then everything else in the module's order
+  std::vector<std::pair<std::string, Tensor>> ordered;
+  {
+    std::unordered_map<std::string, size_t> rank_of;
+    for (size_t i = 0; i < options.first().size(); ++i) rank_of.emplace(options.first()[i], i);
+    std::vector<std::pair<std::string, Tensor>> head(options.first().size()), tail;
+    std::vector<bool> found(options.first().size(), false);
+    for (auto &item : params) {
+      auto it = rank_of.find(item.first);
+      if (it == rank_of.end()) {
+        tail.emplace_back(item.first, item.second);
+      } else {
+        head[it->second] = {item.first, item.second};
+        found[it->second] = true;
+      }
+    }
+    for (size_t i = 0; i < head.size(); ++i) {
+      CS_ASSERT_TRUE(found[i], "flatten_parameters: `", options.first()[i], "` is not a parameter of the module");
+      ordered.push_back(head[i]);
+    }
+    for (auto &t : tail) ordered.push_back(t);
+  }
+  for (auto &item : ordered) {
     item.second.wait();
     const at::Tensor &t = item.second.impl()->tensor;
     CS_ASSERT_TRUE(t.defined(), "parameter `", item.first, "` is not initialised yet");

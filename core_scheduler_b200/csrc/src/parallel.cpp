@@ -16,10 +16,11 @@ namespace cs::parallel {
 using communication::SymmetricContext;
 
 std::shared_ptr<module::FlatParameters> flatten_symmetric(const Scheduler &scheduler, const module::Module &module,
-                                                         const communication::Comm &comm, optional<at::ScalarType> lp_dtype) {
+                                                         const communication::Comm &comm, optional<at::ScalarType> lp_dtype,
+                                                         const std::vector<std::string> &first) {
   auto ctx = comm.impl()->symmetric;
   module::FlattenOptions opts;
-  opts.lp_dtype(lp_dtype).transposed_copies(false).pad_total_to(comm.get_size() * 128);
+  opts.lp_dtype(lp_dtype).transposed_copies(false).pad_total_to(comm.get_size() * 128).first(first);
   if (ctx) {
     opts.arena_allocator([ctx](int64_t bytes) {
       const auto block = ctx->allocate(bytes);

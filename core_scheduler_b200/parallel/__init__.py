@@ -79,9 +79,18 @@ class GPT2Trainer:
                 # two [tokens, d] bf16 per block, plus the partial-product, gradient and classifier buffers
                 rows_bytes = max_tokens * config.n_embd * 2
                 arena = (2 * config.n_layer + 8) * rows_bytes + (256 << 20)
+                # and this rank's gradient (fp32) and working-copy (bf16) arenas, so that the gradients of the
+                # replicated parameters are reduced where the backward pass wrote them
+                arena += (config.parameter_count() // world + 2 * config.padded_vocab_size * config.n_embd) * 6 + (64 << 20)
                 self.symmetric = _C.create_symmetric_context(self.comm, int(arena))
             self.model = _C.TPGPT2(s, config, self.comm)
-            self.flat = _C.flatten_parameters(s, self.model, **lp)
+            # replicated parameters first: their gradients form one range (one all-reduce launch, one AdamW launch),
+            # and so do the sharded ones
+            replicated = self.model.replicated_parameters()
+            if peer:
+                self.flat = _C.flatten_symmetric(s, self.model, self.comm, first=replicated)
+            else:
+                self.flat = _C.flatten_parameters(s, self.model, first=replicated, **lp)
         else:
             self.model = cs.GPT2(s, config)
             if peer:

@@ -57,7 +57,9 @@ int main(int argc, char **argv) {
   // backward, plus partial-product, gradient and classifier buffers; ZeRO: fp32 gradients + bf16 copies + staging
   const int64_t tp_rows_bytes = batch * config.block_size() * config.n_embd() * 2;
   cs::communication::create_symmetric_context(
-      comm, tp ? (2 * config.n_layer() + 8) * tp_rows_bytes + (256ll << 20) : config.parameter_count() * 6 + (256ll << 20));
+      comm, tp ? (2 * config.n_layer() + 8) * tp_rows_bytes + (320ll << 20) +
+                     (config.parameter_count() / world + 2 * config.padded_vocab_size() * config.n_embd()) * 6
+               : config.parameter_count() * 6 + (256ll << 20));
 
   cs::models::GPT2 dp_model{nullptr};
   cs::parallel::TPGPT2 tp_model{nullptr};
@@ -68,7 +70,9 @@ int main(int argc, char **argv) {
   const auto adamw = cs::optimizer::AdamW::Options{}.lr(3e-4).beta1(0.9).beta2(0.95).weight_decay(0.1);
   if (tp) {
     tp_model = cs::parallel::TPGPT2{scheduler, config, comm};
-    flat = cs::module::flatten_parameters(scheduler, *tp_model, cs::module::FlattenOptions{}.lp_dtype(at::kBFloat16));
+    // gradient and working-copy arenas in symmetric memory, the replicated parameters first: their gradients are one
+    // range that is all-reduced in place, and the sharded parameters are one range for the optimizer
+    flat = cs::parallel::flatten_symmetric(scheduler, *tp_model, comm, at::kBFloat16, tp_model->replicated_parameters());
     auto opt = std::make_shared<cs::module::AdamWImpl>(scheduler, *tp_model, flat, adamw);
     opt->set_grad_scale(1.0 / static_cast<double>(world));
     optimizer = opt;
