@@ -111,9 +111,11 @@ __device__ __forceinline__ void open_collective(const PeerTable &t, const Handsh
 // kernel ends only when this rank's buffers are complete and free to be overwritten.
 __device__ __forceinline__ void close_collective(const PeerTable &t, const Handshake &h, int kernel_id) {
   __shared__ int last;
-  __threadfence_system();
+  // The block barrier orders every thread's stores before thread 0's system-scope fence, which then covers them
+  // all (cumulativity): one fence per block instead of one per warp.
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     uint32_t *local = channel_words(t, t.rank, h.channel);
     const uint32_t done = atomicAdd(local + 17, 1u) + 1u;
     last = done == h.blocks_before + gridDim.x;
@@ -400,9 +402,9 @@ __global__ void __launch_bounds__(1024, 1) all_gather_chunked_kernel(PeerTable t
       }
     }
     // the block that completes the chunk on this rank announces it to every rank (its own included)
-    __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
+      __threadfence_system();  // covers the whole block's stores, which the barrier ordered before it
       last_of_chunk = atomicAdd(local + kChunkCounters + c, 1u) + 1u == gridDim.x;
       if (last_of_chunk) atomicExch(local + kChunkCounters + c, 0u);  // every block has counted: ready for the next launch
     }
