@@ -193,6 +193,42 @@ def test_flat_adamw_equals_per_tensor_adamw(cpu_scheduler):
         assert torch.allclose(pa[k].raw(), pb[k].raw(), atol=1e-5), k
 
 
+def test_flat_arenas_lay_named_parameters_out_first(cpu_scheduler):
+    """`first=` puts a group of parameters ahead of the others, in the given order and without gaps beyond slot
+    padding; values survive, training is unchanged, an unknown name is refused."""
+    s = cpu_scheduler
+    cfg = cs.GPT2Config(n_layer=2, n_head=2, n_embd=32, block_size=16, vocab_size=64, padded_vocab_size=64)
+    cs.manual_seed(6)
+    a = cs.GPT2(s, cfg)
+    cs.manual_seed(6)
+    b = cs.GPT2(s, cfg)
+    group = ["lnf.bias", "1.ln2.weight", "wpe.weight", "0.ln1.bias"]
+    before = {k: v.raw().clone() for k, v in b.named_parameters().items()}
+    flat = C.flatten_parameters(s, b, first=group)
+    slots = flat.slots()
+    assert [k for k, _, _ in slots[:len(group)]] == group
+    rest = [k for k in a.named_parameters().keys() if k not in group]
+    assert [k for k, _, _ in slots[len(group):]] == rest  # module order otherwise
+    end = 0
+    for key, off, n in slots:
+        assert off == end  # consecutive slots: a group is one range
+        end = off + (n + 127) // 128 * 128
+    for k, v in before.items():
+        assert torch.equal(b.named_parameters()[k].raw(), v)
+    oa = cs.AdamW(s, a, lr=1e-2, weight_decay=0.1, flat=C.flatten_parameters(s, a))
+    ob = cs.AdamW(s, b, lr=1e-2, weight_decay=0.1, flat=flat)
+    for i in range(2):
+        ids = torch.randint(0, 64, (2, 16))
+        lab = torch.roll(ids, -1, 1)
+        la = a.forward_loss(s, T(ids), T(lab)); a.backward_loss(s); oa.step(s); oa.zero_grad(s)
+        lb = b.forward_loss(s, T(ids), T(lab)); b.backward_loss(s); ob.step(s); ob.zero_grad(s)
+        assert torch.equal(la.raw(), lb.raw())
+    for k, v in a.named_parameters().items():
+        assert torch.equal(v.raw(), b.named_parameters()[k].raw()), k
+    with pytest.raises(Exception, match="not a parameter"):
+        C.flatten_parameters(s, cs.GPT2(s, cfg), first=["no.such.weight"])
+
+
 def test_symmetric_arena_offsets_coalesce_and_return_to_the_top():
     """The peer-mapped arena hands out offsets; freed neighbours unite, so growing requests keep fitting."""
     ctx = cs._C.SymmetricContext(arena_bytes=1 << 20)
