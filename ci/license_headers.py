@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Checks (or adds) the licence line at the top of every source file.
 
 Counterpart of the reference project's script/add-copyright.py and .github/workflows/copyright.yml: every C++ / CUDA /
@@ -10,20 +11,35 @@ from __future__ import annotations
 
 import argparse
 import os
+import subprocess
 import sys
 
 TAG = "SPDX-License-Identifier: Apache-2.0"
 STYLES = {".cpp": "//", ".h": "//", ".cu": "//", ".cuh": "//", ".c": "//", ".py": "#", ".cmake": "#", ".sh": "#"}
-SKIP_DIRS = {".git", "build", "_work", "gpurun_out", "__pycache__", "_ref", ".pytest_cache", "lib", "lib_checked", "lib_asan", "bin"}
+SKIP_DIRS = {".git", "build", "__pycache__", "_ref", ".pytest_cache", "lib", "lib_checked", "lib_asan", "bin"}
+
+
+def candidates(root):
+    """Files of the checkout that git tracks or would track (ignored files are nobody's sources); outside a git
+    checkout, every file below `root` except build products."""
+    try:
+        out = subprocess.run(["git", "-C", root, "ls-files", "--cached", "--others", "--exclude-standard"], capture_output=True,
+                             text=True, check=True).stdout
+        return [os.path.join(root, line) for line in out.splitlines() if line and os.path.isfile(os.path.join(root, line))]
+    except (OSError, subprocess.CalledProcessError):
+        found = []
+        for base, dirs, files in os.walk(root):
+            dirs[:] = [d for d in dirs if d not in SKIP_DIRS]
+            found.extend(os.path.join(base, name) for name in files)
+        return found
 
 
 def sources(root):
-    for base, dirs, files in os.walk(root):
-        dirs[:] = [d for d in dirs if d not in SKIP_DIRS]
-        for name in sorted(files):
-            ext = os.path.splitext(name)[1]
-            if ext in STYLES or name == "CMakeLists.txt":
-                yield os.path.join(base, name), STYLES.get(ext, "#")
+    for path in sorted(candidates(root)):
+        name = os.path.basename(path)
+        ext = os.path.splitext(name)[1]
+        if ext in STYLES or name == "CMakeLists.txt":
+            yield path, STYLES.get(ext, "#")
 
 
 def has_tag(path):
