@@ -353,6 +353,14 @@ def kernels_once():
 
 
 if __name__ == "__main__":
+    import json
+
+    from core_scheduler_b200.utils.clocks import ClockSampler
+
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    {"gemm": bench_gemm, "elementwise": bench_elementwise, "gemm_one": gemm_one, "attention": bench_attention,
-     "kernels_once": kernels_once, "collectives_loopback": collectives_loopback}[what]()
+    sampler = ClockSampler(torch.cuda.current_device()).start()  # read-only; every table ends with its clock record
+    try:
+        {"gemm": bench_gemm, "elementwise": bench_elementwise, "gemm_one": gemm_one, "attention": bench_attention,
+         "kernels_once": kernels_once, "collectives_loopback": collectives_loopback}[what]()
+    finally:
+        print("clocks during the run:", json.dumps(sampler.stop()), flush=True)
