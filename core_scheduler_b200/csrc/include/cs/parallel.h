@@ -26,6 +26,10 @@ CS_API std::shared_ptr<module::FlatParameters> flatten_symmetric(const Scheduler
                                                                 optional<at::ScalarType> lp_dtype = at::kBFloat16,
                                                                 const std::vector<std::string> &first = {});
 
+// The largest `value` any of the `size` ranks passes under the same `prefix`, agreed on through the key/value store
+// (every rank publishes its value and reads all of them). Returns `value` when there is one rank or no store.
+CS_API int64_t agree_on_max(c10d::Store *store, const std::string &prefix, int rank, int size, int64_t value);
+
 struct CS_API ZeroAdamWImpl : module::OptimizerModule {
   using Options = optimizer::AdamW::Options;
   // Ownership granularity: block j of the arenas (kBlock elements) belongs to rank j % world.

@@ -22,12 +22,32 @@ std::shared_ptr<module::FlatParameters> flatten_symmetric(const Scheduler &sched
   module::FlattenOptions opts;
   opts.lp_dtype(lp_dtype).transposed_copies(false).pad_total_to(comm.get_size() * 128).first(first);
   if (ctx) {
-    opts.arena_allocator([ctx](int64_t bytes) {
-      const auto block = ctx->allocate(bytes);
+    // Symmetric memory only works while every rank allocates the same sizes in the same order: a buffer's offset is
+    // its address on every peer. The arenas of a module whose shards differ in size between ranks (20 heads over 8
+    // ranks) would shift everything allocated after them, so each allocation takes the largest size any rank asks for.
+    static std::atomic<int64_t> calls{0};
+    const std::string prefix = str_cat("cs/flatten_symmetric/", calls.fetch_add(1), "/");
+    auto serial = std::make_shared<int>(0);
+    auto store = comm.impl()->store;
+    opts.arena_allocator([ctx, store, prefix, serial, rank = comm.get_rank(), size = comm.get_size()](int64_t bytes) {
+      const int64_t agreed = agree_on_max(store.get(), str_cat(prefix, (*serial)++, "/"), rank, size, bytes);
+      const auto block = ctx->allocate(agreed);
       return ctx->tensor(block, {bytes}, at::kByte);
     });
   }
   return module::flatten_parameters(scheduler, module, opts);
+}
+
+int64_t agree_on_max(c10d::Store *store, const std::string &prefix, int rank, int size, int64_t value) {
+  if (size <= 1 || store == nullptr) return value;
+  const std::string mine = std::to_string(value);
+  store->set(str_cat(prefix, rank), std::vector<uint8_t>(mine.begin(), mine.end()));
+  int64_t agreed = value;
+  for (int p = 0; p < size; ++p) {
+    const auto raw = store->get(str_cat(prefix, p));  // blocks until that rank has published (store timeout applies)
+    agreed = std::max<int64_t>(agreed, std::stoll(std::string(raw.begin(), raw.end())));
+  }
+  return agreed;
 }
 
 ZeroAdamWImpl::ZeroAdamWImpl(const Scheduler &scheduler, const module::Module &module,

@@ -6,11 +6,13 @@
 // 16-bit cases run on GPUs only.
 //
 //   cs_b200_tests [--filter SUBSTRING]
+#include <torch/csrc/distributed/c10d/HashStore.hpp>
 #include <torch/torch.h>
 #include <unistd.h>
 
 #include <cmath>
 #include <cstdio>
+#include <thread>
 
 #include "cs/compute.h"
 #include "cs/data.h"
@@ -18,6 +20,7 @@
 #include "cs/module.h"
 #include "cs/modules.h"
 #include "cs/optimizer.h"
+#include "cs/parallel.h"
 #include "cs_test.h"
 
 namespace {
@@ -369,6 +372,20 @@ CS_TEST(Module, ParameterKeysAreDottedPathsInRegistrationOrder) {
   for (auto &item : net->named_parameters()) keys.push_back(item.key());
   const std::vector<std::string> expected{"wte.weight", "0.ln.weight", "0.ln.bias", "0.c_proj.weight", "1.ln.weight", "1.ln.bias", "1.c_proj.weight"};
   EXPECT_TRUE(keys == expected);
+}
+
+CS_TEST(Parallel, RanksAgreeOnTheLargestAllocationSize) {
+  // symmetric arenas stay aligned across ranks only if every rank allocates the same sizes: shards of different
+  // sizes (20 heads over 8 ranks) are allocated with the largest size any rank asked for
+  auto store = c10::make_intrusive<c10d::HashStore>();
+  std::vector<int64_t> got(3, 0);
+  std::vector<std::thread> ranks;
+  for (int r = 0; r < 3; ++r)
+    ranks.emplace_back([&, r] { got[r] = cs::parallel::agree_on_max(store.get(), "arena/0/", r, 3, 1000 + 64 * (r % 2)); });
+  for (auto &t : ranks) t.join();
+  for (int r = 0; r < 3; ++r) EXPECT_TRUE(got[r] == 1064);
+  EXPECT_TRUE(cs::parallel::agree_on_max(nullptr, "arena/1/", 0, 4, 7) == 7);      // no store: nothing to agree with
+  EXPECT_TRUE(cs::parallel::agree_on_max(store.get(), "arena/2/", 0, 1, 9) == 9);  // one rank
 }
 
 CS_TEST(Model, TinyGpt2LossFallsOverAFewSteps) {
