@@ -27,7 +27,7 @@ def test_cpp_single_device_tests_on_the_cpu():
     out = subprocess.run([program("cs_b200_tests")], env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), capture_output=True, text=True,
                          timeout=600)
     assert "device: cpu" in out.stdout
-    check(out, 18)
+    check(out, 19)
 
 
 def test_cpp_communication_tests_as_a_single_rank_on_the_cpu():
@@ -58,7 +58,7 @@ def test_cpp_harness_reports_a_filter_and_counts(tmp_path):
 def test_cpp_single_device_tests_on_the_gpu():
     out = subprocess.run([program("cs_b200_tests")], capture_output=True, text=True, timeout=600)
     assert "device: cuda" in out.stdout
-    check(out, 18)
+    check(out, 19)
 
 
 @pytest.mark.gpu
