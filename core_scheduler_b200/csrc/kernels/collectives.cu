@@ -486,7 +486,6 @@ constexpr int kBulkStageBytes = 32 * 1024;
 constexpr int kBulkSmemBytes = kBulkStages * kBulkStageBytes + 128;  // ring + mbarriers
 constexpr int kBulkThreads = 32;
 
-
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
