@@ -125,6 +125,8 @@ class GPT2Trainer:
     def check_device_status(self):
         """Raises when a kernel gave up on a bounded wait (a tensor-core pipeline barrier, a peer's flag): the numbers
         of such a step are meaningless. Synchronises the device; call it between steps, not inside a timed region."""
+        if self.device != "cuda":
+            return  # the CPU paths have no device-side waits
         torch.cuda.synchronize()
         for name, status in (("gemm", _C.gemm_status()), ("attention", _C.attention_status())):
             if status[0] != 0:

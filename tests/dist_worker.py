@@ -90,6 +90,8 @@ def case_collectives_arena(device, nvp2p):
     expect_mc = os.environ.get("CS_EXPECT_MULTICAST")
     if expect_mc is not None:
         assert ctx.has_multicast == (expect_mc == "1"), (ctx.has_multicast, ctx.virtual_memory)
+        if expect_mc == "1":
+            C.set_multicast_min_ranks(2)  # a pair prefers peer loads by default; this case is about the multimem kernels
     for dtype, n in ((torch.float32, 4 * 3001), (torch.bfloat16, 8 * 4099), (torch.float32, 1 << 20)):
         tol = dict(rtol=2e-2, atol=1e-1) if dtype == torch.bfloat16 else dict(rtol=1e-6, atol=1e-5)
         # all-gather: every rank's shard lands in slot `rank` of one arena block on every rank
@@ -366,6 +368,31 @@ def case_trainer(device, nvp2p):
     losses = [tp.step(T(ids[:, :-1].contiguous()), T(ids[:, 1:].contiguous())).raw().float().item() for _ in range(5)]
     assert losses[-1] < losses[0] - 0.2, losses
     # sequence parallel: each rank's loss is the mean over its own share of the token rows
+
+
+def case_tp_trainer_uneven(device, nvp2p):
+    """The tensor-parallel trainer with shards of unequal size (3 heads over 2 ranks). Its parameter and gradient arenas
+    sit in symmetric memory ahead of the activation buffers; ranks that allocated different sizes there would address
+    each other's buffers at shifted offsets. The loss of a repeated batch starts at ln(vocabulary) and falls."""
+    import math
+
+    from core_scheduler_b200.parallel import GPT2Trainer
+
+    comm, rank, world, s = make_comm(device, True)
+    cfg = cs.GPT2Config(n_layer=2, n_head=3, n_embd=192, block_size=128, vocab_size=512, padded_vocab_size=512)
+    tp = GPT2Trainer(cfg, comm, world, int(os.environ.get("LOCAL_RANK", "0")), mode="tp", collectives="nvp2p", device=device, lr=3e-3,
+                     scheduler=s, max_tokens=16 * 128)
+    sizes = [torch.zeros(1, dtype=torch.int64, device=device) for _ in range(world)]
+    dist.all_gather(sizes, torch.tensor([tp.flat.total], dtype=torch.int64, device=device))
+    assert len({int(t.item()) for t in sizes}) > 1, "the case needs shards of different sizes"
+    ids = torch.randint(0, 512, (16, 129), generator=torch.Generator().manual_seed(19)).to(device)
+    x, y = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+    losses = [tp.step(T(x), T(y)).raw().float().item() for _ in range(8)]
+    tp.check_device_status()
+    assert all(math.isfinite(v) for v in losses), losses
+    assert abs(losses[0] - math.log(512)) < 0.5, losses
+    assert losses[-1] < losses[0] - 0.3, losses
+    tp.close()
 
 
 def case_loader_shards_by_rank(device, nvp2p):

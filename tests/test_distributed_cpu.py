@@ -24,6 +24,6 @@ def run_case(case, nproc=2, device="cpu", extra=(), timeout=240, env_extra=None)
 
 
 @pytest.mark.parametrize("case", ["all_reduce", "bucket", "bucket_arena_order", "bucket_gradients_bias", "all_gather", "reduce_scatter", "all_to_all", "dp_training",
-                                  "failure_injection", "watchdog", "tp_training", "tp_uneven_heads", "resume_smaller_world", "loader_shards_by_rank", "trainer", "tp_checkpoint_merge"])
+                                  "failure_injection", "watchdog", "tp_training", "tp_uneven_heads", "resume_smaller_world", "loader_shards_by_rank", "trainer", "tp_trainer_uneven", "tp_checkpoint_merge"])
 def test_two_gloo_ranks(case):
     run_case(case)

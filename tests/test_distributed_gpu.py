@@ -33,15 +33,18 @@ def test_tensor_parallel_matches_single_device(backend):
 
 
 @needs2
-def test_tensor_parallel_fused_gemm_collectives(monkeypatch):
-    monkeypatch.setenv("CS_TP_FUSED_ALL_GATHER", "1")  # also exercise the all-gather -> GEMM kernel (off by default)
+def test_tensor_parallel_fused_gemm_collectives():
     run_case("tp_training_fused", device="cuda", extra=("nvp2p",), timeout=600)
 
 
 @needs2
-def test_tensor_parallel_uneven_heads_fused(monkeypatch):
-    monkeypatch.setenv("CS_TP_FUSED_ALL_GATHER", "1")
+def test_tensor_parallel_uneven_heads_fused():
     run_case("tp_uneven_heads_fused", device="cuda", extra=("nvp2p",), timeout=600)
+
+
+@needs2
+def test_tensor_parallel_trainer_with_unequal_shards_in_symmetric_memory():
+    run_case("tp_trainer_uneven", device="cuda", extra=("nvp2p",), timeout=600)
 
 
 @needs2
