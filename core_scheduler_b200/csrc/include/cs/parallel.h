@@ -20,11 +20,14 @@ namespace cs::parallel {
 // Flattens `module` with its gradient and bf16 working-copy arenas inside the communicator's
 // symmetric memory, so that collectives read and write them in place. The arena length is
 // padded so that it splits evenly into `world * 128`-element shards. `first`: parameter names laid out ahead of the
-// others (module::FlattenOptions::first), e.g. the parameters that tensor parallelism replicates.
+// others (module::FlattenOptions::first), e.g. the parameters that tensor parallelism replicates. `unequal_shards`:
+// the module's parameters differ in size between ranks (tensor-parallel shards of 20 heads over 8 ranks); every arena
+// is then allocated with the largest size any rank needs, so that later symmetric allocations stay aligned.
 CS_API std::shared_ptr<module::FlatParameters> flatten_symmetric(const Scheduler &scheduler, const module::Module &module,
                                                                 const communication::Comm &comm,
                                                                 optional<at::ScalarType> lp_dtype = at::kBFloat16,
-                                                                const std::vector<std::string> &first = {});
+                                                                const std::vector<std::string> &first = {},
+                                                                bool unequal_shards = false);
 
 // The largest `value` any of the `size` ranks passes under the same `prefix`, agreed on through the key/value store
 // (every rank publishes its value and reads all of them). Returns `value` when there is one rank or no store.

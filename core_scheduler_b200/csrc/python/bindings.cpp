@@ -778,10 +778,11 @@ PYBIND11_MODULE(_C, m) {
   m.def("set_multicast_min_ranks", &cs::kernels::set_multicast_min_ranks);
   m.def("multicast_min_ranks", &cs::kernels::multicast_min_ranks);
   m.def("flatten_symmetric",
-        [](const Scheduler &s, const module::Module &mod, const Comm &c, const std::vector<std::string> &first) {
-          return parallel::flatten_symmetric(s, mod, c, at::kBFloat16, first);
+        [](const Scheduler &s, const module::Module &mod, const Comm &c, const std::vector<std::string> &first, bool unequal_shards) {
+          return parallel::flatten_symmetric(s, mod, c, at::kBFloat16, first, unequal_shards);
         },
-        py::arg("scheduler"), py::arg("module"), py::arg("comm"), py::arg("first") = std::vector<std::string>{});
+        py::arg("scheduler"), py::arg("module"), py::arg("comm"), py::arg("first") = std::vector<std::string>{},
+        py::arg("unequal_shards") = false);
   py::class_<parallel::ZeroAdamWImpl, module::OptimizerModule, std::shared_ptr<parallel::ZeroAdamWImpl>>(m, "ZeroAdamW")
       .def(py::init([](const Scheduler &s, const std::shared_ptr<module::Module> &mod,
                        std::shared_ptr<module::FlatParameters> flat, const Comm &c, double lr, double beta1, double beta2,

@@ -17,18 +17,19 @@ using communication::SymmetricContext;
 
 std::shared_ptr<module::FlatParameters> flatten_symmetric(const Scheduler &scheduler, const module::Module &module,
                                                          const communication::Comm &comm, optional<at::ScalarType> lp_dtype,
-                                                         const std::vector<std::string> &first) {
+                                                         const std::vector<std::string> &first, bool unequal_shards) {
   auto ctx = comm.impl()->symmetric;
   module::FlattenOptions opts;
   opts.lp_dtype(lp_dtype).transposed_copies(false).pad_total_to(comm.get_size() * 128).first(first);
   if (ctx) {
     // Symmetric memory only works while every rank allocates the same sizes in the same order: a buffer's offset is
     // its address on every peer. The arenas of a module whose shards differ in size between ranks (20 heads over 8
-    // ranks) would shift everything allocated after them, so each allocation takes the largest size any rank asks for.
+    // ranks) would shift everything allocated after them, so with `unequal_shards` each allocation takes the largest
+    // size any rank asks for. Replicas (data parallel, sharded optimizer) have equal sizes and skip the round trip.
     static std::atomic<int64_t> calls{0};
     const std::string prefix = str_cat("cs/flatten_symmetric/", calls.fetch_add(1), "/");
     auto serial = std::make_shared<int>(0);
-    auto store = comm.impl()->store;
+    auto store = unequal_shards ? comm.impl()->store : c10::intrusive_ptr<c10d::Store>{};
     opts.arena_allocator([ctx, store, prefix, serial, rank = comm.get_rank(), size = comm.get_size()](int64_t bytes) {
       const int64_t agreed = agree_on_max(store.get(), str_cat(prefix, (*serial)++, "/"), rank, size, bytes);
       const auto block = ctx->allocate(agreed);

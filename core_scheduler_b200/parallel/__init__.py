@@ -88,7 +88,7 @@ class GPT2Trainer:
             # and so do the sharded ones
             replicated = self.model.replicated_parameters()
             if peer:
-                self.flat = _C.flatten_symmetric(s, self.model, self.comm, first=replicated)
+                self.flat = _C.flatten_symmetric(s, self.model, self.comm, first=replicated, unequal_shards=True)
             else:
                 self.flat = _C.flatten_parameters(s, self.model, first=replicated, **lp)
         else:

@@ -72,7 +72,8 @@ int main(int argc, char **argv) {
     tp_model = cs::parallel::TPGPT2{scheduler, config, comm};
     // gradient and working-copy arenas in symmetric memory, the replicated parameters first: their gradients are one
     // range that is all-reduced in place, and the sharded parameters are one range for the optimizer
-    flat = cs::parallel::flatten_symmetric(scheduler, *tp_model, comm, at::kBFloat16, tp_model->replicated_parameters());
+    flat = cs::parallel::flatten_symmetric(scheduler, *tp_model, comm, at::kBFloat16, tp_model->replicated_parameters(),
+                                           /*unequal_shards=*/true);
     auto opt = std::make_shared<cs::module::AdamWImpl>(scheduler, *tp_model, flat, adamw);
     opt->set_grad_scale(1.0 / static_cast<double>(world));
     optimizer = opt;
