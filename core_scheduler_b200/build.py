@@ -242,26 +242,29 @@ def _build_programs(root: Path, extra_inc: list, names: dict | None = None) -> l
     return built
 
 
-def build_sanitized() -> list[str]:
+def build_sanitized(kind: str = "address") -> list[str]:
     """Host-side race and memory checks: compiles the C++ sources (not the kernels) with AddressSanitizer and
-    UndefinedBehaviorSanitizer into lib_asan/libcs_b200.so and links the two C++ test programs against it
-    (tests/cpp/bin/*_asan). Run them on the CPU, e.g.
+    UndefinedBehaviorSanitizer (kind "address") or with ThreadSanitizer (kind "thread") into lib_asan/ or lib_tsan/
+    and links the two C++ test programs against it (tests/cpp/bin/*_asan, *_tsan). Run them on the CPU, e.g.
         ASAN_OPTIONS=detect_leaks=0:protect_shadow_gap=0 tests/cpp/bin/cs_b200_communication_tests_asan --threads 4
+        TSAN_OPTIONS=suppressions=tests/cpp/tsan.supp tests/cpp/bin/cs_b200_communication_tests_tsan --threads 4
     (scheduler queues, rank-thread communicator, bucket logic, data-loader threads, module tree)."""
+    assert kind in ("address", "thread")
+    tag = "asan" if kind == "address" else "tsan"
     p = _paths()
     generate_ninja()
     subprocess.run([sys.executable, "-m", "ninja", "-f", str(BUILD / "build.ninja"), str(LIBDIR / "libcs_b200.so")], check=True, cwd=str(BUILD))
-    out = HERE / "lib_asan"
+    out = HERE / f"lib_{tag}"
     out.mkdir(exist_ok=True)
     extra_cpp, extra_cu = _optional_sources()
     inc = [CSRC / "include", CSRC, CSRC / "src"] + p["torch_inc"] + [p["cuda_home"] / "include"]
-    san = ["-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-g", "-O1"]
+    san = [("-fsanitize=address,undefined" if kind == "address" else "-fsanitize=thread"), "-fno-omit-frame-pointer", "-g", "-O1"]
     base = [os.environ.get("CS_CXX", "g++"), "-std=c++20", "-fPIC", "-Wno-interference-size", "-Wno-deprecated-declarations",
             f"-D_GLIBCXX_USE_CXX11_ABI={p['cxx11_abi']}", "-DUSE_C10D_NCCL", "-DUSE_DISTRIBUTED", "-DUSE_RPC", "-DUSE_CUDA"] + [f"-I{i}" for i in inc]
     objs = []
     jobs = []
     for src in CPP_SOURCES + extra_cpp:
-        obj = BUILD / (src.replace("/", "_") + ".asan.o")
+        obj = BUILD / (src.replace("/", "_") + f".{tag}.o")
         extra = [f"-I{p['arrow_inc']}"] if src.endswith("parquet_io.cpp") else ([f"-I{p['nccl_inc']}"] if src.endswith("comm_nccl.cpp") else [])
         if not obj.exists() or obj.stat().st_mtime < (CSRC / src).stat().st_mtime:
             jobs.append(subprocess.Popen(base + san + extra + ["-c", str(CSRC / src), "-o", str(obj)]))
@@ -279,7 +282,7 @@ def build_sanitized() -> list[str]:
     root = HERE.parent / "tests" / "cpp"
     (root / "bin").mkdir(exist_ok=True)
     built = []
-    for stem, name in (("test_ops", "cs_b200_tests_asan"), ("test_communication", "cs_b200_communication_tests_asan")):
+    for stem, name in (("test_ops", f"cs_b200_tests_{tag}"), ("test_communication", f"cs_b200_communication_tests_{tag}")):
         exe = root / "bin" / name
         subprocess.run(base + san + [f"-I{root}", str(root / f"{stem}.cpp"), "-o", str(exe), f"-L{out}", "-lcs_b200", f"-L{p['torch_lib']}",
                                      "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda", f"-L{cuda_lib}", "-lcudart",
@@ -303,6 +306,6 @@ if __name__ == "__main__":
     elif "tests" in sys.argv:
         print("\n".join(build_cpp_tests()))
     elif "sanitize" in sys.argv:
-        print("\n".join(build_sanitized()))
+        print("\n".join(build_sanitized("thread" if "thread" in sys.argv else "address")))
     else:
         build(verbose="-v" in sys.argv, checked="checked" in sys.argv)

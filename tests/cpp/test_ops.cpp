@@ -374,6 +374,25 @@ CS_TEST(Module, ParameterKeysAreDottedPathsInRegistrationOrder) {
   EXPECT_TRUE(keys == expected);
 }
 
+CS_TEST(DataLoader, ProducerThreadHandsOverBatchesThroughTheTwoSlots) {
+  // the worker thread fills one slot while load() uploads the other; labels are the inputs shifted by one token,
+  // two loaders with one seed deliver the same stream, and a loader that is destroyed mid-stream joins its worker
+  const int64_t batch = 3, seq = 17, vocab = 97;
+  cs::data::SyntheticDataLoader a{batch, seq, vocab, 5}, b{batch, seq, vocab, 5};
+  for (int i = 0; i < 12; ++i) {
+    auto xa = a.load(scheduler()), xb = b.load(scheduler());
+    at::Tensor ids = host(xa.at("input_ids")).cpu(), labels = host(xa.at("labels")).cpu();
+    EXPECT_TRUE(ids.sizes() == at::IntArrayRef({batch, seq}) && labels.sizes() == ids.sizes());
+    EXPECT_TRUE(ids.min().item<int64_t>() >= 0 && ids.max().item<int64_t>() < vocab);
+    EXPECT_TRUE(at::equal(ids.slice(1, 1, seq), labels.slice(1, 0, seq - 1)));
+    EXPECT_TRUE(at::equal(ids, host(xb.at("input_ids")).cpu()));
+  }
+  {
+    cs::data::SyntheticDataLoader c{batch, seq, vocab, 6};
+    (void)c.load(scheduler());
+  }
+}
+
 CS_TEST(Parallel, RanksAgreeOnTheLargestAllocationSize) {
   // symmetric arenas stay aligned across ranks only if every rank allocates the same sizes: shards of different
   // sizes (20 heads over 8 ranks) are allocated with the largest size any rank asked for

@@ -27,7 +27,7 @@ def test_cpp_single_device_tests_on_the_cpu():
     out = subprocess.run([program("cs_b200_tests")], env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), capture_output=True, text=True,
                          timeout=600)
     assert "device: cpu" in out.stdout
-    check(out, 19)
+    check(out, 20)
 
 
 def test_cpp_communication_tests_as_a_single_rank_on_the_cpu():
@@ -58,7 +58,7 @@ def test_cpp_harness_reports_a_filter_and_counts(tmp_path):
 def test_cpp_single_device_tests_on_the_gpu():
     out = subprocess.run([program("cs_b200_tests")], capture_output=True, text=True, timeout=600)
     assert "device: cuda" in out.stdout
-    check(out, 19)
+    check(out, 20)
 
 
 @pytest.mark.gpu
@@ -71,17 +71,22 @@ def test_cpp_communication_tests_on_two_gpus():
     assert out.stdout.count("9 tests ran, 0 failed") == 2, out.stdout[-3000:]
 
 
-@pytest.mark.skipif(os.environ.get("CS_RUN_SANITIZERS") != "1", reason="set CS_RUN_SANITIZERS=1 (builds the host code with ASan + UBSan, several minutes)")
-def test_host_code_is_clean_under_address_and_undefined_behaviour_sanitizers():
-    """The scheduler, the rank-thread communicator, bucketing, the module tree and the optimizer run the two C++ test
-    programs on the CPU under AddressSanitizer and UndefinedBehaviorSanitizer without a report."""
+@pytest.mark.skipif(os.environ.get("CS_RUN_SANITIZERS") != "1", reason="set CS_RUN_SANITIZERS=1 (builds the host code with the sanitizers, several minutes)")
+@pytest.mark.parametrize("kind", ["address", "thread"])
+def test_host_code_is_clean_under_the_sanitizers(kind):
+    """The scheduler, the rank-thread communicator, bucketing, the loader's producer thread, the module tree and the
+    optimizer run the two C++ test programs on the CPU under AddressSanitizer + UndefinedBehaviorSanitizer and under
+    ThreadSanitizer without a report. ThreadSanitizer runs with tests/cpp/tsan.supp (NVTX's and oneDNN's own lazy
+    initialisation) and without mutex-misuse reports, which uninstrumented libtorch triggers by itself."""
     from core_scheduler_b200.build import build_sanitized
 
-    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", ASAN_OPTIONS="detect_leaks=0:protect_shadow_gap=0:detect_odr_violation=0",
-               UBSAN_OPTIONS="print_stacktrace=1:halt_on_error=1")
-    for exe in build_sanitized():
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1",
+               ASAN_OPTIONS="detect_leaks=0:protect_shadow_gap=0:detect_odr_violation=0",
+               UBSAN_OPTIONS="print_stacktrace=1:halt_on_error=1",
+               TSAN_OPTIONS=f"suppressions={os.path.join(ROOT, 'tests', 'cpp', 'tsan.supp')} report_signal_unsafe=0 report_mutex_bugs=0")
+    for exe in build_sanitized(kind):
         args = [exe, "--threads", "2"] if "communication" in exe else [exe]
         run = subprocess.run(args, env=env, capture_output=True, text=True, timeout=1800)
         text = run.stdout + run.stderr
         assert run.returncode == 0 and "0 failed" in text, text[-3000:]
-        assert "ERROR: AddressSanitizer" not in text and "runtime error:" not in text, text[-3000:]
+        assert "ERROR: AddressSanitizer" not in text and "runtime error:" not in text and "WARNING: ThreadSanitizer" not in text, text[-3000:]
