@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import sys
 import time
@@ -265,7 +266,6 @@ def main():
     final_loss = float(cs.to_torch(trainer.s, loss).item())
     # Random tokens keep the loss near ln(vocabulary) (10.8 for GPT-2); a step whose numbers went wrong (a buffer read
     # before it was complete, ranks disagreeing on an offset) shows up here long before it shows in the timing.
-    import math
     if not math.isfinite(final_loss) or final_loss > 1.5 * math.log(vocab):
         raise RuntimeError(f"loss {final_loss} after {args.warmup + args.steps} steps is not that of a working training step "
                            f"(expected about ln({vocab}) = {math.log(vocab):.2f}); the measurement is void")
